@@ -1,0 +1,209 @@
+/* ============================================================================
+ * mxk_b200.h — C ABI of the B200 (sm_100a) FP8xFP8 MoE layer library.
+ *
+ * Plain pointers and sizes only; no C++ or torch types.  This is the boundary a
+ * foreign-function binding (ctypes, cgo, JNI ...) attaches to.  The C++
+ * namespace fp8mega in include/megakernel.h forwards to these entry points and
+ * keeps the reference's host interface (reference: src/megakernel.h:54-137).
+ *
+ * All launch functions are asynchronous on the given CUDA stream, allocate
+ * nothing, keep no per-call host state and are CUDA-graph capturable.  They
+ * return 0 on success or a negative MXK_ERR_* / positive cudaError_t value;
+ * mxk_last_error() gives a message for the calling thread's last failure.
+ * Device-side protocol failures (a bounded wait that expired) never trap: they
+ * set the status word read by mxk_read_status() (reference: lf->dbg[8] slots,
+ * src/flags.cuh:197-360, src/prologue.cuh:348,474, src/combine.cuh:562).
+ * ========================================================================== */
+#ifndef MXK_B200_H_
+#define MXK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MXK_ERR_BAD_ARG (-1)      /* geometry / pointer / size rejected          */
+#define MXK_ERR_NO_DRIVER (-2)    /* cuTensorMapEncodeTiled entry point missing  */
+#define MXK_ERR_TENSOR_MAP (-3)   /* tensor-map encoding failed                  */
+#define MXK_ERR_DEVICE (-4)       /* device is not sm_100                        */
+
+/* Geometry of the expert-parallel world.  The reference freezes these at compile
+ * time (src/common.cuh:18-24: EPR=8, topk=8, H=6144, I=2048); here they are
+ * run-time values.  hidden % 256 == 0, intermediate % 128 == 0. */
+typedef struct MxkGeom {
+    int32_t R;                /* ranks (GPUs) in the EP world                    */
+    int32_t rank;             /* this rank                                       */
+    int32_t experts_per_rank; /* local experts; global expert e lives on e / EPR */
+    int32_t topk;
+    int32_t hidden;           /* H                                               */
+    int32_t intermediate;     /* I                                               */
+    int32_t max_tokens;       /* token rows per rank the buffers are sized for   */
+    int32_t slot_capacity;    /* accepted pairs per (source rank, expert);
+                                 0 means max_tokens (src/prologue.cuh:171-174)  */
+} MxkGeom;
+
+/* Byte offsets of every table inside the three caller-allocated blocks.
+ *   sym : inputs of this rank, peers READ it   (reference ProdLayout x_off /
+ *         topk_idx_off / topk_weights_off, src/host_layout.cuh:79-82)
+ *   unk : workspace peers WRITE into            (reference unk_data,
+ *         src/flags_defs.cuh:121-222)
+ *   rwk : private workspace                     (reference rwk_data, :61-175)
+ * All three must be zero-filled once before the first launch. */
+typedef struct MxkLayout {
+    /* sym */
+    int64_t sym_bytes;
+    int64_t x_off;              /* uint8  [max_tokens][H]      E4M3 activations   */
+    int64_t x_sf_off;           /* uint8  [max_tokens][H/128]  UE8M0 1x128 scales */
+    int64_t topk_idx_off;       /* int64  [max_tokens][topk]                      */
+    int64_t topk_weights_off;   /* float  [max_tokens][topk]                      */
+    /* unk */
+    int64_t unk_bytes;
+    int64_t xbar_off;           /* uint32 [R][xbar_stride] arrival epoch per peer */
+    int64_t src_index_table_off;/* uint32 [2][EPR][R][slot_capacity]              */
+    int64_t expert_recv_counts_off; /* uint32 [2][R][recv_stride]                 */
+    int64_t combine_rows_off;   /* bf16   [topk][max_tokens][H]                   */
+    int64_t combine_cnt_off;    /* uint32 [topk][max_tokens] arrivals per pair    */
+    int32_t xbar_stride;        /* words between two peers' barrier slots         */
+    int32_t recv_stride;        /* words per expert_recv_counts row (>= EPR+1)    */
+    /* rwk */
+    int64_t rwk_bytes;
+    int64_t flags_off;          /* MxkStatus-sized header, see mxk_read_status    */
+    int64_t route_slot_counts_off; /* int32 [E]                                   */
+    int64_t pair_state_off;     /* uint8  [max_tokens*topk] 1 = pair accepted     */
+    int64_t prefix_tbl_off;     /* int32  [EPR][R+1]                              */
+    int64_t expert_row_base_off;/* int32  [EPR+1] first pool row of each expert   */
+    int64_t windows_off;        /* int32  [max_windows][4] expert,row0,rows,-     */
+    int64_t tasks_off;          /* int32  [max_tasks][4]   kind,window,ntile,rows */
+    int64_t l1_done_off;        /* uint32 [max_windows]                           */
+    int64_t row_meta_off;       /* int32  [pool_rows][4] src,token,k,weight bits  */
+    int64_t pool_off;           /* uint8  [pool_rows+128][H]   dispatched rows    */
+    int64_t pool_sf_off;        /* uint8  [pool_rows][sf_stride_h]                */
+    int64_t ffn_off;            /* uint8  [pool_rows+128][I]   L1 output          */
+    int64_t ffn_sf_off;         /* uint8  [pool_rows][sf_stride_i]                */
+    int64_t pool_rows;          /* = R * max_tokens * topk                        */
+    int32_t sf_stride_h;        /* bytes per pool_sf row (H/128 rounded to 16)    */
+    int32_t sf_stride_i;        /* bytes per ffn_sf row  (I/128 rounded to 16)    */
+    int32_t max_windows;
+    int32_t max_tasks;
+} MxkLayout;
+
+/* One launch.  Field names follow fp8mega::MegaLaunchArgs (reference
+ * src/megakernel.h:54-114); the fields after max_spins/skip_prologue are new:
+ * geometry and the UE8M0 scale planes (all-null planes == the reference's
+ * scale-free mode). */
+typedef struct MxkLaunchArgs {
+    int32_t R, rank;
+    int32_t tokens;            /* valid tokens of this rank in this launch        */
+    int32_t slot_capacity;
+    int32_t win_cap;           /* rows per window (M tile), 8..128; 0 => 128      */
+    int32_t grid, threads;     /* grid: CTAs of the GEMM kernel, 0 => SM count;
+                                  threads is accepted and ignored                 */
+    int64_t smem;              /* accepted and ignored                            */
+    void* rwk;
+    void* unk;
+    void* const* unk_peers;    /* DEVICE array [R] of every rank's unk base       */
+    const uint8_t* self;       /* this rank's sym base                            */
+    uint8_t* const* peer_bases;/* DEVICE array [R] of every rank's sym base       */
+    const int64_t* topk_idx;   /* optional; NULL => self + topk_idx_off           */
+    const uint8_t* w1;         /* [EPR][2I][H] E4M3 row-major, gate rows then up  */
+    const uint8_t* w2;         /* [EPR][H][I]  E4M3 row-major                     */
+    int32_t group_weights_ready; /* accepted; cross-rank helper scheduling unused */
+    int64_t topk_idx_off, x_off, weights_off;
+    int32_t in_bf16;           /* must be 0                                       */
+    int32_t skip_combine;      /* >0: L2 results are not pushed (diagnostic)      */
+    float* y;                  /* optional FP32 [tokens][H]                       */
+    int32_t max_spins;         /* bound of every device wait, in units of 250 ns;
+                                  0 => 2 s                                        */
+    int32_t skip_prologue;     /* must be 0                                       */
+    /* ---- additions ---- */
+    int32_t experts_per_rank, topk, hidden, intermediate, max_tokens;
+    int64_t x_sf_off;          /* valid when w1_sf != NULL                        */
+    const uint8_t* w1_sf;      /* [EPR][2I/128][H/128] UE8M0 or NULL              */
+    const uint8_t* w2_sf;      /* [EPR][H/128][I/128]  UE8M0 or NULL              */
+    uint16_t* y_bf16;          /* optional bf16 [tokens][H]                       */
+} MxkLaunchArgs;
+
+/* Host-readable copy of the device status header. */
+typedef struct MxkStatus {
+    int64_t launches;      /* completed prologues (reference current_time)       */
+    int32_t status;        /* 0 = ok, else the first MXK_DEV_* code raised       */
+    int32_t n_tasks, n_l1_tasks, n_windows, total_rows;
+    int32_t dbg[8];        /* expiry counters, slot meaning as the reference:
+                              0 barrier, 2 route, 3 task queue, 4 L1->L2 gate /
+                              reduce wait, 5 pipeline barrier, 6 TMEM barrier    */
+} MxkStatus;
+
+#define MXK_DEV_TIMEOUT_BARRIER 1
+#define MXK_DEV_TIMEOUT_GATE 2
+#define MXK_DEV_TIMEOUT_PIPE 3
+#define MXK_DEV_TIMEOUT_REDUCE 4
+#define MXK_DEV_BAD_TABLE 5
+
+const char* mxk_last_error(void);
+int mxk_version(void);
+
+/* Layout of sym / unk / rwk for a geometry (reference: compute_layout,
+ * src/host_layout.cuh:63-113; sizeof(rwk_data)/sizeof(unk_data) exported as
+ * mxk_rwk_bytes / mxk_unk_bytes, torch/csrc/flags_bridge.cu:12-53). */
+int mxk_compute_layout(const MxkGeom* g, MxkLayout* out);
+int64_t mxk_sym_bytes(const MxkGeom* g);
+int64_t mxk_rwk_bytes(const MxkGeom* g);
+int64_t mxk_unk_bytes(const MxkGeom* g);
+
+/* Launchers (reference: fp8mega::launch_prelude / launch_compute / launch_reduce /
+ * launch_full / launch_empty, src/megakernel.cu:203-268).
+ *   prelude : route build + count publish + cross-rank barrier + task set-up
+ *   compute : prelude + dispatch pull + L1 + L2 + combine push
+ *   reduce  : top-k weighted sum of the rows pushed to this rank
+ *   full    : compute + reduce */
+int mxk_launch_prelude(const MxkLaunchArgs* a, void* stream);
+int mxk_launch_compute(const MxkLaunchArgs* a, void* stream);
+int mxk_launch_reduce(const MxkLaunchArgs* a, void* stream);
+int mxk_launch_full(const MxkLaunchArgs* a, void* stream);
+int mxk_launch_empty(int grid, int threads, int64_t smem, void* stream);
+/* Number of kernels one mxk_launch_full enqueues. */
+int mxk_kernels_per_layer(void);
+
+/* Phase-split launcher for diagnostics and single-GPU tests of a multi-rank world
+ * (reference precedent: launch_l1 / launch_l2 under CM_L1L2_SPLIT,
+ * src/megakernel.h:120-126).  Enqueues only the kernels selected by phase_mask, in
+ * layer order.  Kernels of different ranks wait on each other (barrier, arrival
+ * counts), so on ONE device the ranks' phases must be issued phase by phase:
+ * ROUTE for every rank, then SETUP for every rank, and so on. */
+#define MXK_PHASE_ROUTE 1
+#define MXK_PHASE_SETUP 2
+#define MXK_PHASE_DISPATCH 4
+#define MXK_PHASE_GEMM 8
+#define MXK_PHASE_REDUCE 16
+int mxk_launch_phases(const MxkLaunchArgs* a, int phase_mask, void* stream);
+
+/* Deterministic test weights, byte (seed + 131*row + 7*k) & 0x3f at logical
+ * (row, k), row-major (reference: fill_weights_lane writes the same values in
+ * MetaX lane order, src/megakernel.cu:66-105, src/megakernel.h:46-47). */
+int mxk_fill_weights(uint8_t* w, int64_t n_rows, int32_t k_cols, uint32_t seed, void* stream);
+
+/* Registers / shared memory of every kernel, printed to stdout (reference:
+ * dump_kernel_resources, src/megakernel.cu:270-282). */
+int mxk_dump_kernel_resources(void);
+
+/* Synchronous read of the status header of an rwk block. */
+int mxk_read_status(const void* rwk, MxkStatus* out);
+
+/* Window chooser kept for the callers that bind it (reference: mxk_select_win,
+ * torch/csrc/flags_bridge.cu:31-38 -> src/win_select.cuh:95-128). */
+int mxk_select_win(const uint32_t* counts, int E, int cap_hint, int win_min);
+
+/* Symmetric-memory helpers (reference SymmBuffer C++ side,
+ * torch/csrc/apis/mega.hpp:86-195): device allocation that can be exported to
+ * the other ranks' processes, and import of their handles. */
+int mxk_symm_alloc(void** ptr, int64_t bytes);          /* cudaMalloc + zero fill */
+int mxk_symm_free(void* ptr);
+int mxk_ipc_export(void* ptr, uint8_t handle[64]);
+int mxk_ipc_import(const uint8_t handle[64], void** ptr);
+int mxk_ipc_close(void* ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MXK_B200_H_ */

@@ -1,0 +1,1111 @@
+// ============================================================================
+// mxk_kernels.cu — B200 (sm_100a) FP8xFP8 MoE layer: device kernels and the C
+// ABI declared in include/mxk_b200.h.
+//
+// One layer = five launches on the caller's stream:
+//   k_route    per-rank route build: deterministic slot per (token,k) pair,
+//              scatter of pair indices into the owner ranks' tables, count
+//              publish, cross-rank barrier arrival
+//              (reference: route_build_body / publish_counts_body /
+//               xbar_route_ready_body, src/prologue.cuh:126-256, src/flags.cuh:284-377)
+//   k_setup    barrier wait, prefix table, windows, cost-ordered task list
+//              (reference: task_setup_body, src/prologue.cuh:269-498)
+//   k_dispatch EP dispatch: pull routed FP8 rows + 1x128 scales from the peers'
+//              symmetric buffers into the local pool
+//              (reference: r19_pull_flags, src/compute_big.cuh:1691-1946)
+//   k_gemm     persistent grouped GEMM over (window, n-tile) tasks on tcgen05
+//              with TMEM accumulators fed by TMA: L1 gate+up + SwiGLU + FP8
+//              requant, then L2 down + bf16 + combine push to the source rank
+//              (reference: dispatch_pull_body task loop src/compute.cuh:1050-1236,
+//               L1/L2 families src/compute_big.cuh:320-515,1231-1679,
+//               combine push src/combine.cuh:347-477)
+//   k_reduce   top-k weighted sum at the source rank
+//              (reference: reduce_tile_body, src/combine.cuh:488-656)
+// ============================================================================
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/mxk_b200.h"
+#include "mxk_device.cuh"
+
+namespace {
+
+using namespace mxk;
+
+// ------------------------------------------------------------------ constants
+constexpr int kBlockM = 128;          // rows of a window = UMMA M
+constexpr int kBlockK = 128;          // bytes of K per pipeline stage = scale block
+constexpr int kBlockN = 256;          // weight rows per task = UMMA N (two 128-row halves)
+constexpr int kStages = 4;
+constexpr int kABytes = kBlockM * kBlockK;           // 16 KB
+constexpr int kBBytes = kBlockN * kBlockK;           // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;       // 48 KB
+constexpr int kTaskRing = 4;
+constexpr int kGemmThreads = 320;     // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int kEpiWarps = 8;
+constexpr int kTmemCols = 512;        // two accumulator buffers of 256 columns
+constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align*/ + 8192 /*control*/;
+constexpr uint64_t kDefaultLocalWaitNs = 2000000000ull;    // 2 s
+constexpr uint64_t kDefaultRemoteWaitNs = 20000000000ull;  // 20 s
+
+struct DevFlags {  // head of rwk (flags_off)
+    long long current_time;      // completed prologues; the running launch is +1
+    unsigned route_blocks_done;
+    unsigned task_counter;
+    int n_tasks, n_l1_tasks, n_windows, total_rows;
+    int status;
+    int dbg[8];
+    unsigned long long ticks[16];
+};
+
+struct KArgs {
+    int R, rank, EPR, E, topk, H, I, cap, slot_cap, tokens, win_cap;
+    int gemm_grid, skip_combine, scaled;
+    unsigned long long local_wait_ns, remote_wait_ns;
+    uint8_t* rwk;
+    uint8_t* unk;
+    void* const* unk_peers;
+    const uint8_t* self;
+    uint8_t* const* peer_bases;
+    const int64_t* topk_idx;
+    const uint8_t* w1;
+    const uint8_t* w2;
+    const uint8_t* w1_sf;
+    const uint8_t* w2_sf;
+    long long x_off, x_sf_off, weights_off;
+    float* y;
+    uint16_t* y_bf16;
+    MxkLayout L;
+};
+
+__device__ __forceinline__ DevFlags* flags_of(const KArgs& a) {
+    return reinterpret_cast<DevFlags*>(a.rwk + a.L.flags_off);
+}
+__device__ __forceinline__ void raise_status(DevFlags* f, int code, int dbg_slot) {
+    atomicAdd(&f->dbg[dbg_slot], 1);
+    atomicCAS(&f->status, 0, code);
+}
+
+// ============================================================== k_route =======
+// Slots are handed out in ascending pair index idx = token*topk + k, so every
+// table row (and with it the pool row order) is deterministic; the reference
+// uses a shared-memory atomicAdd and accepts any order (src/prologue.cuh:164-180).
+__global__ void __launch_bounds__(1024) k_route(const KArgs a) {
+    DevFlags* f = flags_of(a);
+    __shared__ int s_wtot[32];
+    __shared__ int s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long epoch = f->current_time + 1;  // read before the last block bumps it
+    const int par = (int)(epoch & 1);
+    const int np = a.tokens * a.topk;
+    const int64_t* ti = a.topk_idx;
+    uint8_t* pair_state = a.rwk + a.L.pair_state_off;
+    int* rsc = reinterpret_cast<int*>(a.rwk + a.L.route_slot_counts_off);
+
+    // Arrival counters of the rows peers will push to this rank in this launch.
+    // Safe to clear here: peers push only after this rank has arrived at the
+    // barrier below, and the previous launch's reduce has consumed them.
+    unsigned* cnt = reinterpret_cast<unsigned*>(a.unk + a.L.combine_cnt_off);
+    for (int i = blockIdx.x * blockDim.x + tid; i < a.topk * a.cap; i += gridDim.x * blockDim.x) cnt[i] = 0;
+
+    for (int e = blockIdx.x; e < a.E; e += gridDim.x) {
+        const int dst = e / a.EPR, le = e % a.EPR;
+        uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[dst]);
+        uint32_t* tbl = reinterpret_cast<uint32_t*>(peer_unk + a.L.src_index_table_off) +
+                        (((size_t)par * a.EPR + le) * a.R + a.rank) * (size_t)a.slot_cap;
+        int base = 0;
+        for (int p0 = 0; p0 < np; p0 += 1024) {
+            const int p = p0 + tid;
+            const bool hit = p < np && ti[p] == (int64_t)e;
+            const unsigned bal = __ballot_sync(0xFFFFFFFFu, hit);
+            if (lane == 0) s_wtot[warp] = __popc(bal);
+            __syncthreads();
+            int wpre = 0, tot = 0;
+#pragma unroll
+            for (int w = 0; w < 32; ++w) {
+                const int v = s_wtot[w];
+                wpre += (w < warp) ? v : 0;
+                tot += v;
+            }
+            if (hit) {
+                const int slot = base + wpre + __popc(bal & ((1u << lane) - 1u));
+                const bool ok = slot < a.slot_cap;  // over capacity: dropped (src/prologue.cuh:171-174)
+                if (ok) st_relaxed_sys(tbl + slot, (uint32_t)p);
+                pair_state[p] = ok ? 1 : 0;
+            }
+            base += tot;
+            __syncthreads();
+        }
+        if (tid == 0) {
+            const int c = base < a.slot_cap ? base : a.slot_cap;
+            rsc[e] = c;
+            uint32_t* recv = reinterpret_cast<uint32_t*>(peer_unk + a.L.expert_recv_counts_off) +
+                             ((size_t)par * a.R + a.rank) * a.L.recv_stride;
+            st_relaxed_sys(recv + le, (uint32_t)c);
+        }
+    }
+    if (blockIdx.x == 0)  // invalid expert ids (negative / >= E) take no slot (src/prologue.cuh:166-167)
+        for (int p = tid; p < np; p += 1024)
+            if ((uint64_t)ti[p] >= (uint64_t)a.E) pair_state[p] = 0;
+
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(&f->route_blocks_done, 1u) == gridDim.x - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // Row checksum word ~(sum + 1) at index EPR of each row sent (src/prologue.cuh:248-255).
+    for (int d = tid; d < a.R; d += 1024) {
+        uint32_t csum = 0;
+        for (int le = 0; le < a.EPR; ++le) csum += (uint32_t)__ldcg(rsc + d * a.EPR + le);
+        uint32_t* recv = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) +
+                                                     a.L.expert_recv_counts_off) +
+                         ((size_t)par * a.R + a.rank) * a.L.recv_stride;
+        st_relaxed_sys(recv + a.EPR, ~(csum + 1u));
+    }
+    __threadfence_system();
+    __syncthreads();
+    // Barrier arrival: publish this launch's epoch into every peer's slot for this rank.
+    for (int d = tid; d < a.R; d += 1024) {
+        uint32_t* xb = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) + a.L.xbar_off) +
+                       (size_t)a.rank * a.L.xbar_stride;
+        st_release_sys(xb, (uint32_t)epoch);
+    }
+    if (tid == 0) {
+        f->route_blocks_done = 0;
+        f->current_time = epoch;
+    }
+}
+
+// ============================================================== k_setup =======
+__global__ void __launch_bounds__(1024) k_setup(const KArgs a) {
+    extern __shared__ int s_i[];
+    DevFlags* f = flags_of(a);
+    const int tid = threadIdx.x;
+    const int EPR = a.EPR, R = a.R;
+    int* s_tot = s_i;                  // [EPR]
+    int* s_order = s_tot + EPR;        // [EPR] expert at sorted position p
+    int* s_first = s_order + EPR;      // [EPR+1] first window of position p
+    int* s_base = s_first + EPR + 1;   // [EPR+1] first pool row of expert le
+    const long long epoch = f->current_time;
+    const int par = (int)(epoch & 1);
+
+    // Cross-rank barrier: every rank has published its routes for this epoch.
+    if (tid < R) {
+        const uint32_t* xb = reinterpret_cast<const uint32_t*>(a.unk + a.L.xbar_off) + (size_t)tid * a.L.xbar_stride;
+        const bool ok = spin_until([&] { return (int32_t)(ld_acquire_sys(xb) - (uint32_t)epoch) >= 0; },
+                                   a.remote_wait_ns, nullptr);
+        if (!ok) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 0);
+    }
+    __syncthreads();
+
+    const uint32_t* recv = reinterpret_cast<const uint32_t*>(a.unk + a.L.expert_recv_counts_off) +
+                           (size_t)par * R * a.L.recv_stride;
+    int* prefix = reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off);
+    for (int le = tid; le < EPR; le += 1024) {
+        int c = 0;
+        for (int r = 0; r < R; ++r) {
+            prefix[le * (R + 1) + r] = c;
+            c += (int)__ldcg(recv + (size_t)r * a.L.recv_stride + le);
+        }
+        prefix[le * (R + 1) + R] = c;
+        s_tot[le] = c;
+    }
+    __syncthreads();
+    // Experts by descending row count, ties by index: the hottest experts' windows
+    // are claimed first so the dynamic queue ends on the cheap ones (LPT order).
+    for (int le = tid; le < EPR; le += 1024) {
+        const int c = s_tot[le];
+        int rk = 0;
+        for (int j = 0; j < EPR; ++j) {
+            const int cj = s_tot[j];
+            rk += (cj > c || (cj == c && j < le)) ? 1 : 0;
+        }
+        s_order[rk] = le;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int acc = 0;
+        for (int le = 0; le < EPR; ++le) { s_base[le] = acc; acc += s_tot[le]; }
+        s_base[EPR] = acc;
+        int nw = 0;
+        for (int p = 0; p < EPR; ++p) {
+            s_first[p] = nw;
+            const int c = s_tot[s_order[p]];
+            nw += c > 0 ? (c + a.win_cap - 1) / a.win_cap : 0;
+        }
+        s_first[EPR] = nw;
+    }
+    __syncthreads();
+    int* row_base = reinterpret_cast<int*>(a.rwk + a.L.expert_row_base_off);
+    for (int le = tid; le <= EPR; le += 1024) row_base[le] = s_base[le];
+
+    int n_windows = s_first[EPR];
+    const int total_rows = s_base[EPR];
+    const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
+    bool overflow = false;
+    if (n_windows > a.L.max_windows || (long long)n_windows * (nt1 + nt2) > a.L.max_tasks ||
+        total_rows > a.L.pool_rows) {
+        overflow = true;
+        n_windows = 0;
+    }
+    int4* windows = reinterpret_cast<int4*>(a.rwk + a.L.windows_off);
+    int4* tasks = reinterpret_cast<int4*>(a.rwk + a.L.tasks_off);
+    uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
+    const int n_l1 = n_windows * nt1;
+    if (!overflow)
+        for (int p = 0; p < EPR; ++p) {
+            const int e = s_order[p], c = s_tot[e];
+            const int fw = s_first[p], nw = s_first[p + 1] - fw;
+            if (nw == 0) continue;  // sorted: every later expert is empty too
+            for (int w = tid; w < nw; w += 1024) {
+                const int rows = min(a.win_cap, c - w * a.win_cap);
+                windows[fw + w] = make_int4(e, s_base[e] + w * a.win_cap, rows, 0);
+                l1_done[fw + w] = 0;
+            }
+            for (int i = tid; i < nt1 * nw; i += 1024) {
+                const int nt = i / nw, w = i % nw;
+                tasks[fw * nt1 + i] = make_int4(0, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
+            }
+            for (int i = tid; i < nt2 * nw; i += 1024) {
+                const int nt = i / nw, w = i % nw;
+                tasks[n_l1 + fw * nt2 + i] = make_int4(1, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
+            }
+        }
+    if (tid == 0) {
+        if (overflow) raise_status(f, MXK_DEV_BAD_TABLE, 3);
+        f->n_windows = n_windows;
+        f->n_l1_tasks = n_l1;
+        f->n_tasks = n_windows * (nt1 + nt2);
+        f->total_rows = overflow ? 0 : total_rows;
+        f->task_counter = (unsigned)a.gemm_grid;  // first task of a CTA is its index
+    }
+}
+
+// ============================================================ k_dispatch ======
+// One warp per pool row: locate (expert, source rank, slot), read the pair index
+// the source wrote, then pull the row's H bytes and H/128 scale bytes from the
+// source rank's symmetric buffer with 16-byte loads over NVLink.
+__global__ void __launch_bounds__(256) k_dispatch(const KArgs a) {
+    DevFlags* f = flags_of(a);
+    const int lane = threadIdx.x & 31;
+    const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int nwarps = (gridDim.x * blockDim.x) >> 5;
+    const int total = f->total_rows;
+    const int par = (int)(f->current_time & 1);
+    const int R = a.R, EPR = a.EPR, H = a.H;
+    const int* row_base = reinterpret_cast<const int*>(a.rwk + a.L.expert_row_base_off);
+    const int* prefix = reinterpret_cast<const int*>(a.rwk + a.L.prefix_tbl_off);
+    const uint32_t* tbl = reinterpret_cast<const uint32_t*>(a.unk + a.L.src_index_table_off) +
+                          (size_t)par * EPR * R * a.slot_cap;
+    uint8_t* pool = a.rwk + a.L.pool_off;
+    uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
+    int4* meta = reinterpret_cast<int4*>(a.rwk + a.L.row_meta_off);
+    const int kb = H / 128;
+
+    for (int g = gwarp; g < total; g += nwarps) {
+        int lo = 0, hi = EPR;  // largest le with row_base[le] <= g
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (row_base[mid] <= g) lo = mid; else hi = mid;
+        }
+        const int le = lo;
+        const int gl = g - row_base[le];
+        const int* pf = prefix + le * (R + 1);
+        int slo = 0, shi = R;  // largest src with pf[src] <= gl (src/compute_big.cuh:1760-1769)
+        while (shi - slo > 1) {
+            const int mid = (slo + shi) >> 1;
+            if (pf[mid] <= gl) slo = mid; else shi = mid;
+        }
+        const int src = slo, slot = gl - pf[src];
+        const uint32_t idx = __ldcg(tbl + ((size_t)le * R + src) * a.slot_cap + slot);
+        const int token = (int)(idx / (uint32_t)a.topk), k = (int)(idx % (uint32_t)a.topk);
+        const uint8_t* peer = a.peer_bases[src];
+        const uint4* srow = reinterpret_cast<const uint4*>(peer + a.x_off + (size_t)token * H);
+        uint4* drow = reinterpret_cast<uint4*>(pool + (size_t)g * H);
+        const int n16 = H / 16;
+#pragma unroll 4
+        for (int i = lane; i < n16; i += 32) drow[i] = __ldcg(srow + i);
+        if (a.scaled) {
+            const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
+            for (int i = lane; i < a.L.sf_stride_h; i += 32)
+                pool_sf[(size_t)g * a.L.sf_stride_h + i] = i < kb ? __ldcg(ssf + i) : (uint8_t)127;
+        }
+        if (lane == 0) {
+            const float w = __ldcg(reinterpret_cast<const float*>(peer + a.weights_off) + (size_t)token * a.topk + k);
+            meta[g] = make_int4(src, token, k, __float_as_int(w));
+        }
+    }
+}
+
+// ============================================================== k_gemm ========
+struct GemmSmem {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint64_t task_full[kTaskRing];
+    uint64_t task_empty[kTaskRing];
+    int4 task[kTaskRing];
+    unsigned long long xch[2][2][128];  // amax exchange between the two column halves
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__global__ void __maxnreg__(200)
+k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_constant__ CUtensorMap tm_ffn,
+       const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    GemmSmem* S = reinterpret_cast<GemmSmem*>(tiles + kStages * kStageBytes);
+    DevFlags* f = flags_of(a);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &S->abort_flag;
+    const uint64_t wait_ns = a.local_wait_ns;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&S->full[s], 1); mbar_init(&S->empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&S->tmem_full[b], 1); mbar_init(&S->tmem_empty[b], kEpiWarps); }
+        for (int s = 0; s < kTaskRing; ++s) { mbar_init(&S->task_full[s], 1); mbar_init(&S->task_empty[s], 1 + kEpiWarps); }
+        S->abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    for (int i = threadIdx.x; i < 2 * 2 * 128; i += blockDim.x) (&S->xch[0][0][0])[i] = 0ull;
+    if (warp == 1) {
+        tmem_alloc(&S->tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = S->tmem_base;
+
+    const int n_tasks = f->n_tasks;
+    const int4* tasks = reinterpret_cast<const int4*>(a.rwk + a.L.tasks_off);
+    const int4* windows = reinterpret_cast<const int4*>(a.rwk + a.L.windows_off);
+    uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
+    const int kb1 = a.H / kBlockK, kb2 = a.I / kBlockK;
+    const int nt1 = a.I / 128;
+
+    if (warp == 0) {
+        // ------------------------------------------------ scheduler + TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_pool); tma_prefetch_desc(&tm_ffn);
+            tma_prefetch_desc(&tm_w1); tma_prefetch_desc(&tm_w2);
+            uint32_t stage = 0, phase = 0;
+            for (uint32_t it = 0;; ++it) {
+                const uint32_t slot = it % kTaskRing;
+                if (!mbar_wait(&S->task_empty[slot], ((it / kTaskRing) & 1) ^ 1, wait_ns, abort_flag)) {
+                    raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break;
+                }
+                const int t = it == 0 ? (int)blockIdx.x : (int)atomicAdd(&f->task_counter, 1u);
+                const int4 task = t < n_tasks ? tasks[t] : make_int4(-1, 0, 0, 0);
+                S->task[slot] = task;
+                mbar_arrive(&S->task_full[slot]);
+                if (task.x < 0) break;
+                const int4 win = windows[task.y];
+                const int e = win.x, row0 = win.y;
+                const bool is_l2 = task.x == 1;
+                if (is_l2) {  // every L1 tile of this window must have landed in ffn
+                    const uint32_t need = (uint32_t)nt1 * kEpiWarps;
+                    if (!spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= need; }, wait_ns, abort_flag)) {
+                        raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
+                    }
+                }
+                fence_proxy_async_global();  // pool / ffn rows were written with ordinary stores
+                const CUtensorMap* ma = is_l2 ? &tm_ffn : &tm_pool;
+                const CUtensorMap* mb = is_l2 ? &tm_w2 : &tm_w1;
+                const int nkb = is_l2 ? kb2 : kb1;
+                const int brow0 = is_l2 ? e * a.H + task.z * kBlockN : e * 2 * a.I + task.z * 128;
+                const int brow1 = is_l2 ? brow0 + 128 : brow0 + a.I;
+                bool dead = false;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(&S->empty[stage], phase ^ 1, wait_ns, abort_flag)) { dead = true; break; }
+                    uint8_t* sa = tiles + stage * kStageBytes;
+                    mbar_expect_tx(&S->full[stage], kStageBytes);
+                    tma_load_2d(sa, ma, kb * kBlockK, row0, &S->full[stage]);
+                    tma_load_2d(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[stage]);
+                    tma_load_2d(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[stage]);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; break; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_e4m3(kBlockM, kBlockN);
+            uint32_t stage = 0, phase = 0, acc_it = 0;
+            for (uint32_t it = 0;; ++it) {
+                const uint32_t slot = it % kTaskRing;
+                if (!mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag)) {
+                    raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break;
+                }
+                const int4 task = S->task[slot];
+                mbar_arrive(&S->task_empty[slot]);
+                if (task.x < 0) break;
+                const int nkb = task.x == 1 ? kb2 : kb1;
+                bool dead = false;
+                for (int kb = 0; kb < nkb; ++kb, ++acc_it) {
+                    const uint32_t buf = acc_it & 1;
+                    if (!mbar_wait(&S->tmem_empty[buf], ((acc_it >> 1) & 1) ^ 1, wait_ns, abort_flag) ||
+                        !mbar_wait(&S->full[stage], phase, wait_ns, abort_flag)) { dead = true; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
+                    const uint64_t adesc = umma_smem_desc_sw128(sa);
+                    const uint64_t bdesc = umma_smem_desc_sw128(sa + kABytes);
+                    const uint32_t d = tmem_base + buf * kBlockN;
+#pragma unroll
+                    for (int k4 = 0; k4 < kBlockK / 32; ++k4)
+                        umma_f8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, k4 > 0 ? 1u : 0u);
+                    umma_commit(&S->empty[stage]);      // stage reusable once these MMAs retire
+                    umma_commit(&S->tmem_full[buf]);    // K-block partial sums ready for promotion
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; break; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------- epilogue
+        // Warp w owns TMEM lanes 32*(w%4).. (rows of the window) and column half
+        // h = (w-2)/4: columns [64h,64h+64) of each 128-column accumulator half.
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        const int r = q * 32 + lane;  // row inside the window
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        uint32_t acc_it = 0;
+        const uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
+        uint8_t* ffn = a.rwk + a.L.ffn_off;
+        uint8_t* ffn_sf = a.rwk + a.L.ffn_sf_off;
+        const int4* meta = reinterpret_cast<const int4*>(a.rwk + a.L.row_meta_off);
+        for (uint32_t it = 0;; ++it) {
+            const uint32_t slot = it % kTaskRing;
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag);
+            ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+            if (!ok) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; } break; }
+            const int4 task = S->task[slot];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S->task_empty[slot]);
+            if (task.x < 0) break;
+            const int4 win = windows[task.y];
+            const int e = win.x, row0 = win.y, rows = task.w;
+            const bool is_l2 = task.x == 1;
+            const int nkb = is_l2 ? kb2 : kb1;
+            const bool warp_active = q * 32 < rows;
+            const bool row_valid = r < rows;
+            // scale planes: activation scale per (row, K block); weight scale per
+            // (128-row block, K block) for each of the two accumulator halves
+            const uint8_t* sa_ptr = nullptr;
+            const uint8_t* sb0_ptr = nullptr;
+            const uint8_t* sb1_ptr = nullptr;
+            if (a.scaled) {
+                if (is_l2) {
+                    sa_ptr = ffn_sf + (size_t)(row0 + (row_valid ? r : 0)) * a.L.sf_stride_i;
+                    const uint8_t* wsf = a.w2_sf + ((size_t)e * (a.H / 128) + task.z * 2) * nkb;
+                    sb0_ptr = wsf;
+                    sb1_ptr = wsf + nkb;
+                } else {
+                    sa_ptr = pool_sf + (size_t)(row0 + (row_valid ? r : 0)) * a.L.sf_stride_h;
+                    const uint8_t* wsf = a.w1_sf + (size_t)e * (2 * a.I / 128) * nkb;
+                    sb0_ptr = wsf + (size_t)task.z * nkb;
+                    sb1_ptr = wsf + (size_t)(nt1 + task.z) * nkb;
+                }
+            }
+            float accG[64], accU[64];
+#pragma unroll
+            for (int j = 0; j < 64; ++j) { accG[j] = 0.0f; accU[j] = 0.0f; }
+            bool dead = false;
+            for (int kb = 0; kb < nkb; ++kb, ++acc_it) {
+                const uint32_t buf = acc_it & 1;
+                float sg = 1.0f, su = 1.0f;
+                if (a.scaled) {
+                    const float sa = ue8m0_f32(__ldcg(sa_ptr + kb));  // written earlier in this kernel: no read-only path
+                    sg = sa * ue8m0_f32(__ldg(sb0_ptr + kb));
+                    su = sa * ue8m0_f32(__ldg(sb1_ptr + kb));
+                }
+                bool got = true;
+                if (lane == 0) got = mbar_wait(&S->tmem_full[buf], (acc_it >> 1) & 1, wait_ns, abort_flag);
+                got = __shfl_sync(0xFFFFFFFFu, got ? 1 : 0, 0) != 0;
+                if (!got) { dead = true; break; }
+                tc_fence_after();
+                if (warp_active) {
+                    const uint32_t t0 = lane_addr + buf * kBlockN + half * 64;
+                    uint32_t v[32];
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        tmem_ld32(t0 + c * 32, v);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) accG[c * 32 + j] = fmaf(__uint_as_float(v[j]), sg, accG[c * 32 + j]);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        tmem_ld32(t0 + 128 + c * 32, v);
+                        tmem_wait_ld();
+                        if (c == 1) {  // all reads of this buffer are done: hand it back to the MMA warp
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&S->tmem_empty[buf]);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) accU[c * 32 + j] = fmaf(__uint_as_float(v[j]), su, accU[c * 32 + j]);
+                    }
+                } else {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&S->tmem_empty[buf]);
+                }
+            }
+            if (dead) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; } break; }
+
+            if (!is_l2) {
+                // ---- SwiGLU + per-row 1x128 requantisation to E4M3 -> ffn
+                if (warp_active) {
+                    float amax = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) {
+                        const float g = accG[j];
+                        const float hv = (g / (1.0f + expf(-g))) * accU[j];  // silu(g)*u (src/compute.cuh:242-244)
+                        accG[j] = hv;
+                        amax = fmaxf(amax, fabsf(hv));
+                    }
+                    float inv = 1.0f;
+                    uint32_t ex = 127;
+                    if (a.scaled) {
+                        // the other column half of this row lives in warp +-4: swap partial maxima
+                        const uint32_t tag = it + 1;
+                        volatile unsigned long long* mine = &S->xch[it & 1][half][r];
+                        volatile unsigned long long* theirs = &S->xch[it & 1][half ^ 1][r];
+                        *mine = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(amax);
+                        unsigned long long o = 0;
+                        const bool got = spin_until([&] { o = *theirs; return (uint32_t)(o >> 32) == tag; }, wait_ns, abort_flag);
+                        if (!got) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; }
+                        amax = fmaxf(amax, __uint_as_float((uint32_t)o));
+                        const float s = fmaxf(amax, 1e-4f) / 448.0f;  // per_token_cast_to_fp8, utils/math.py:33-35
+                        const uint32_t bits = __float_as_uint(s);
+                        ex = ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) ? 1u : 0u);
+                        ex = min(254u, max(1u, ex));
+                        inv = __uint_as_float((254u - ex) << 23);
+                    }
+                    if (row_valid) {
+                        uint4* dst = reinterpret_cast<uint4*>(ffn + (size_t)(row0 + r) * a.I + task.z * 128 + half * 64);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint4 o;
+                            o.x = pack_e4m3x4(accG[c * 16 + 0] * inv, accG[c * 16 + 1] * inv, accG[c * 16 + 2] * inv, accG[c * 16 + 3] * inv);
+                            o.y = pack_e4m3x4(accG[c * 16 + 4] * inv, accG[c * 16 + 5] * inv, accG[c * 16 + 6] * inv, accG[c * 16 + 7] * inv);
+                            o.z = pack_e4m3x4(accG[c * 16 + 8] * inv, accG[c * 16 + 9] * inv, accG[c * 16 + 10] * inv, accG[c * 16 + 11] * inv);
+                            o.w = pack_e4m3x4(accG[c * 16 + 12] * inv, accG[c * 16 + 13] * inv, accG[c * 16 + 14] * inv, accG[c * 16 + 15] * inv);
+                            dst[c] = o;
+                        }
+                        if (a.scaled && half == 0) ffn_sf[(size_t)(row0 + r) * a.L.sf_stride_i + task.z] = (uint8_t)ex;
+                    }
+                }
+                // publish: this warp's share of the tile is in global memory
+                fence_proxy_async_global();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) red_release_gpu_add(l1_done + task.y, 1u);
+            } else {
+                // ---- bf16 rows pushed to the source rank + per-pair arrival count
+                if (row_valid && !a.skip_combine) {
+                    const int4 m = meta[row0 + r];  // src, token, k, weight
+                    uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[m.x]);
+                    uint16_t* crow = reinterpret_cast<uint16_t*>(peer_unk + a.L.combine_rows_off) +
+                                     ((size_t)m.z * a.cap + m.y) * a.H + task.z * kBlockN + half * 64;
+                    uint4* d0 = reinterpret_cast<uint4*>(crow);
+                    uint4* d1 = reinterpret_cast<uint4*>(crow + 128);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        uint4 o;
+                        o.x = pack_bf16x2(accG[c * 8 + 0], accG[c * 8 + 1]);
+                        o.y = pack_bf16x2(accG[c * 8 + 2], accG[c * 8 + 3]);
+                        o.z = pack_bf16x2(accG[c * 8 + 4], accG[c * 8 + 5]);
+                        o.w = pack_bf16x2(accG[c * 8 + 6], accG[c * 8 + 7]);
+                        d0[c] = o;
+                        o.x = pack_bf16x2(accU[c * 8 + 0], accU[c * 8 + 1]);
+                        o.y = pack_bf16x2(accU[c * 8 + 2], accU[c * 8 + 3]);
+                        o.z = pack_bf16x2(accU[c * 8 + 4], accU[c * 8 + 5]);
+                        o.w = pack_bf16x2(accU[c * 8 + 6], accU[c * 8 + 7]);
+                        d1[c] = o;
+                    }
+                    __threadfence_system();
+                    uint32_t* cnt = reinterpret_cast<uint32_t*>(peer_unk + a.L.combine_cnt_off) + (size_t)m.z * a.cap + m.y;
+                    red_release_sys_add(cnt, 1u);
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------ teardown
+    if (*abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ============================================================== k_reduce ======
+// y[t] = sum over k (ascending, FP32, product then sum) of w_k * bf16 row_k
+// (reference: src/combine.cuh:601-627, src/bench_check.cuh:484-499).
+__global__ void __launch_bounds__(256) k_reduce(const KArgs a) {
+    DevFlags* f = flags_of(a);
+    __shared__ int s_ok[64];
+    __shared__ float s_w[64];
+    const int tid = threadIdx.x;
+    const int H = a.H, topk = a.topk;
+    const uint8_t* pair_state = a.rwk + a.L.pair_state_off;
+    const uint32_t* cnt = reinterpret_cast<const uint32_t*>(a.unk + a.L.combine_cnt_off);
+    const uint16_t* rows = reinterpret_cast<const uint16_t*>(a.unk + a.L.combine_rows_off);
+    const float* tw = reinterpret_cast<const float*>(a.self + a.weights_off);
+    const uint32_t need = (uint32_t)(H / kBlockN) * 2u;
+    for (int t = blockIdx.x; t < a.tokens; t += gridDim.x) {
+        if (tid < topk) {
+            int ok = pair_state[t * topk + tid];
+            if (ok && !a.skip_combine) {
+                const uint32_t* c = cnt + (size_t)tid * a.cap + t;
+                if (!spin_until([&] { return ld_acquire_sys(c) >= need; }, a.remote_wait_ns, nullptr)) {
+                    raise_status(f, MXK_DEV_TIMEOUT_REDUCE, 4);
+                    ok = 0;
+                }
+            }
+            s_ok[tid] = ok;
+            s_w[tid] = tw[(size_t)t * topk + tid];
+        }
+        __syncthreads();
+        for (int c8 = tid; c8 < H / 8; c8 += 256) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+            for (int k = 0; k < topk; ++k) {
+                if (!s_ok[k]) continue;
+                const float w = s_w[k];
+                const uint4 v = __ldcg(reinterpret_cast<const uint4*>(rows + ((size_t)k * a.cap + t) * H) + c8);
+                const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(u[j] << 16), w));
+                    acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(u[j] & 0xFFFF0000u), w));
+                }
+            }
+            if (a.y) {
+                float4* o = reinterpret_cast<float4*>(a.y + (size_t)t * H + c8 * 8);
+                o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            }
+            if (a.y_bf16) {
+                uint4 o;
+                o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+                o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+                *reinterpret_cast<uint4*>(a.y_bf16 + (size_t)t * H + c8 * 8) = o;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void k_empty() {}
+
+__global__ void k_fill_weights(uint8_t* w, long long n_rows, int k_cols, uint32_t seed) {
+    const long long n = n_rows * k_cols;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const uint32_t row = (uint32_t)(i / k_cols), k = (uint32_t)(i % k_cols);
+        w[i] = (uint8_t)((seed + row * 131u + k * 7u) & 0x3f);
+    }
+}
+
+// =============================================================== host side ====
+thread_local std::string g_err;
+int fail(int code, const std::string& msg) {
+    g_err = msg;
+    return code;
+}
+int cuda_fail(cudaError_t e, const char* what) {
+    g_err = std::string(what) + ": " + cudaGetErrorString(e);
+    return (int)e;
+}
+
+int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+int check_geom(const MxkGeom* g) {
+    if (!g) return fail(MXK_ERR_BAD_ARG, "null geometry");
+    if (g->R < 1 || g->R > 1024 || g->rank < 0 || g->rank >= g->R) return fail(MXK_ERR_BAD_ARG, "bad R/rank");
+    if (g->experts_per_rank < 1 || g->experts_per_rank > 1024) return fail(MXK_ERR_BAD_ARG, "experts_per_rank must be in [1,1024]");
+    if (g->topk < 1 || g->topk > 64) return fail(MXK_ERR_BAD_ARG, "topk must be in [1,64]");
+    if (g->hidden < 256 || g->hidden % 256) return fail(MXK_ERR_BAD_ARG, "hidden must be a positive multiple of 256");
+    if (g->intermediate < 128 || g->intermediate % 128) return fail(MXK_ERR_BAD_ARG, "intermediate must be a positive multiple of 128");
+    if (g->max_tokens < 1) return fail(MXK_ERR_BAD_ARG, "max_tokens must be positive");
+    if (g->slot_capacity < 0) return fail(MXK_ERR_BAD_ARG, "slot_capacity must be >= 0");
+    return 0;
+}
+
+int compute_layout(const MxkGeom* g, MxkLayout* L) {
+    if (int rc = check_geom(g)) return rc;
+    if (!L) return fail(MXK_ERR_BAD_ARG, "null layout");
+    std::memset(L, 0, sizeof(*L));
+    const int64_t R = g->R, EPR = g->experts_per_rank, E = R * EPR, topk = g->topk, H = g->hidden, I = g->intermediate;
+    const int64_t cap = g->max_tokens, slot = g->slot_capacity ? g->slot_capacity : g->max_tokens;
+    int64_t o = 0;
+    auto take = [&](int64_t bytes) { const int64_t at = o; o = align_up(o + bytes, 256); return at; };
+    // sym
+    L->x_off = take(cap * H);
+    L->x_sf_off = take(cap * (H / 128));
+    L->topk_idx_off = take(cap * topk * 8);
+    L->topk_weights_off = take(cap * topk * 4);
+    L->sym_bytes = o;
+    // unk
+    o = 0;
+    L->xbar_stride = 32;  // 128 B apart: one line per writing peer
+    L->xbar_off = take(R * L->xbar_stride * 4);
+    L->recv_stride = (int32_t)align_up(EPR + 1, 64);
+    L->src_index_table_off = take(2 * EPR * R * slot * 4);
+    L->expert_recv_counts_off = take(2 * R * (int64_t)L->recv_stride * 4);
+    L->combine_rows_off = take(topk * cap * H * 2);
+    L->combine_cnt_off = take(topk * cap * 4);
+    L->unk_bytes = o;
+    // rwk
+    o = 0;
+    L->pool_rows = R * cap * topk;
+    L->max_windows = (int32_t)(EPR + L->pool_rows / 8);
+    const int64_t tasks_per_window = I / 128 + H / 256;
+    // windows of fewer than 128 rows exist only for the tail of an expert or when
+    // win_cap < 128; the task table is sized for win_cap >= 32 plus one tail each
+    int64_t max_tasks = (EPR + L->pool_rows / 32) * tasks_per_window;
+    if (max_tasks > 0x7FFFFFF0ll) max_tasks = 0x7FFFFFF0ll;
+    L->max_tasks = (int32_t)max_tasks;
+    L->sf_stride_h = (int32_t)align_up(H / 128, 16);
+    L->sf_stride_i = (int32_t)align_up(I / 128, 16);
+    L->flags_off = take(1024);
+    L->route_slot_counts_off = take(E * 4);
+    L->pair_state_off = take(cap * topk);
+    L->prefix_tbl_off = take(EPR * (R + 1) * 4);
+    L->expert_row_base_off = take((EPR + 1) * 4);
+    L->windows_off = take((int64_t)L->max_windows * 16);
+    L->tasks_off = take((int64_t)L->max_tasks * 16);
+    L->l1_done_off = take((int64_t)L->max_windows * 4);
+    L->row_meta_off = take(L->pool_rows * 16);
+    L->pool_off = take((L->pool_rows + 128) * H);
+    L->pool_sf_off = take(L->pool_rows * L->sf_stride_h);
+    L->ffn_off = take((L->pool_rows + 128) * I);
+    L->ffn_sf_off = take(L->pool_rows * L->sf_stride_i);
+    L->rwk_bytes = o;
+    return 0;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// uint8 [rows][k] row-major, tile 128 rows x 128 bytes, 128-byte swizzle.
+int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t k) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return fail(MXK_ERR_NO_DRIVER, "cuTensorMapEncodeTiled not available from the CUDA driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)k};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MXK_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed, CUresult " + std::to_string((int)r));
+    return 0;
+}
+
+struct DeviceInfo { int sm_count = 0; int cc = 0; bool ok = false; };
+int device_info(DeviceInfo* out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    static thread_local int cached_dev = -1;
+    static thread_local DeviceInfo cached;
+    if (cached_dev != dev) {
+        int major = 0, minor = 0, sms = 0;
+        if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+        cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cached.sm_count = sms;
+        cached.cc = major * 10 + minor;
+        cached.ok = true;
+        cached_dev = dev;
+    }
+    *out = cached;
+    return 0;
+}
+
+int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
+    if (!la) return fail(MXK_ERR_BAD_ARG, "null launch args");
+    MxkGeom g{};
+    g.R = la->R; g.rank = la->rank;
+    // zero geometry fields select the reference's frozen scene (src/common.cuh:18-24)
+    g.experts_per_rank = la->experts_per_rank ? la->experts_per_rank : 8;
+    g.topk = la->topk ? la->topk : 8;
+    g.hidden = la->hidden ? la->hidden : 6144;
+    g.intermediate = la->intermediate ? la->intermediate : 2048;
+    g.max_tokens = la->max_tokens ? la->max_tokens : (la->slot_capacity ? la->slot_capacity : 512);
+    g.slot_capacity = la->slot_capacity;
+    std::memset(k, 0, sizeof(*k));
+    if (int rc = compute_layout(&g, &k->L)) return rc;
+    if (!la->rwk || !la->unk || !la->unk_peers || !la->self || !la->peer_bases)
+        return fail(MXK_ERR_BAD_ARG, "rwk / unk / unk_peers / self / peer_bases must be non-null");
+    if (la->tokens < 0 || la->tokens > g.max_tokens) return fail(MXK_ERR_BAD_ARG, "tokens outside [0, max_tokens]");
+    if (la->in_bf16) return fail(MXK_ERR_BAD_ARG, "in_bf16 input is not supported");
+    if (la->skip_prologue) return fail(MXK_ERR_BAD_ARG, "skip_prologue is not supported");
+    int win = la->win_cap ? la->win_cap : 128;
+    // same rule as the reference binding: window in [8,128], multiple of 8 (torch/csrc/apis/mega.hpp:230-233)
+    if (win < 8 || win > 128 || win % 8) return fail(MXK_ERR_BAD_ARG, "win_cap must be a multiple of 8 in [8,128]");
+    if ((la->w1_sf == nullptr) != (la->w2_sf == nullptr)) return fail(MXK_ERR_BAD_ARG, "w1_sf and w2_sf must both be set or both be null");
+    k->R = g.R; k->rank = g.rank; k->EPR = g.experts_per_rank; k->E = g.R * g.experts_per_rank;
+    k->topk = g.topk; k->H = g.hidden; k->I = g.intermediate; k->cap = g.max_tokens;
+    k->slot_cap = g.slot_capacity ? g.slot_capacity : g.max_tokens;
+    k->tokens = la->tokens; k->win_cap = win;
+    k->skip_combine = la->skip_combine; k->scaled = la->w1_sf != nullptr;
+    k->local_wait_ns = la->max_spins > 0 ? (unsigned long long)la->max_spins * 250ull : kDefaultLocalWaitNs;
+    k->remote_wait_ns = la->max_spins > 0 ? (unsigned long long)la->max_spins * 250ull : kDefaultRemoteWaitNs;
+    k->rwk = static_cast<uint8_t*>(la->rwk); k->unk = static_cast<uint8_t*>(la->unk);
+    k->unk_peers = la->unk_peers; k->self = la->self; k->peer_bases = la->peer_bases;
+    k->topk_idx = la->topk_idx ? la->topk_idx : reinterpret_cast<const int64_t*>(la->self + la->topk_idx_off);
+    k->w1 = la->w1; k->w2 = la->w2; k->w1_sf = la->w1_sf; k->w2_sf = la->w2_sf;
+    k->x_off = la->x_off; k->x_sf_off = la->x_sf_off; k->weights_off = la->weights_off;
+    k->y = la->y; k->y_bf16 = la->y_bf16;
+    DeviceInfo di;
+    if (int rc = device_info(&di)) return rc;
+    if (di.cc / 10 != 10) return fail(MXK_ERR_DEVICE, "this library runs on sm_100 (B200) only, device is sm_" + std::to_string(di.cc));
+    int grid = la->grid > 0 ? la->grid : di.sm_count;
+    if (grid > di.sm_count) grid = di.sm_count;  // CTAs wait on each other: all must be resident
+    k->gemm_grid = grid;
+    return 0;
+}
+
+int launch_route(const KArgs& k, cudaStream_t st) {
+    int rgrid = k.E < 148 ? k.E : 148;
+    k_route<<<rgrid, 1024, 0, st>>>(k);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "launch route");
+}
+int launch_setup(const KArgs& k, cudaStream_t st) {
+    const size_t smem = (size_t)(4 * k.EPR + 2) * sizeof(int);
+    k_setup<<<1, 1024, smem, st>>>(k);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "launch setup");
+}
+int launch_route_setup(const KArgs& k, cudaStream_t st) {
+    if (int rc = launch_route(k, st)) return rc;
+    return launch_setup(k, st);
+}
+int launch_dispatch(const KArgs& k, cudaStream_t st) {
+    DeviceInfo di;
+    if (int rc = device_info(&di)) return rc;
+    k_dispatch<<<di.sm_count * 4, 256, 0, st>>>(k);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "launch dispatch");
+}
+
+int launch_gemm(const KArgs& k, cudaStream_t st) {
+    if (!k.w1 || !k.w2) return fail(MXK_ERR_BAD_ARG, "w1 / w2 must be non-null");
+    CUtensorMap tm_pool, tm_ffn, tm_w1, tm_w2;
+    if (int rc = make_map(&tm_pool, k.rwk + k.L.pool_off, k.L.pool_rows + 128, k.H)) return rc;
+    if (int rc = make_map(&tm_ffn, k.rwk + k.L.ffn_off, k.L.pool_rows + 128, k.I)) return rc;
+    if (int rc = make_map(&tm_w1, k.w1, (int64_t)k.EPR * 2 * k.I, k.H)) return rc;
+    if (int rc = make_map(&tm_w2, k.w2, (int64_t)k.EPR * k.H, k.I)) return rc;
+    static thread_local int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(k_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(k_gemm)");
+        attr_dev = dev;
+    }
+    k_gemm<<<k.gemm_grid, kGemmThreads, kGemmSmem, st>>>(k, tm_pool, tm_ffn, tm_w1, tm_w2);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "launch gemm");
+}
+int launch_dispatch_gemm(const KArgs& k, cudaStream_t st) {
+    if (int rc = launch_dispatch(k, st)) return rc;
+    return launch_gemm(k, st);
+}
+
+int launch_reduce_k(const KArgs& k, cudaStream_t st) {
+    if (!k.y && !k.y_bf16) return fail(MXK_ERR_BAD_ARG, "y or y_bf16 must be non-null");
+    if (k.tokens == 0) return 0;
+    int grid = k.tokens < 1184 ? k.tokens : 1184;
+    k_reduce<<<grid, 256, 0, st>>>(k);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "launch reduce");
+}
+
+}  // namespace
+
+// ================================================================== C ABI =====
+extern "C" {
+
+const char* mxk_last_error(void) { return g_err.c_str(); }
+int mxk_version(void) { return 100; }
+
+int mxk_compute_layout(const MxkGeom* g, MxkLayout* out) { return compute_layout(g, out); }
+int64_t mxk_sym_bytes(const MxkGeom* g) { MxkLayout L; return compute_layout(g, &L) ? -1 : L.sym_bytes; }
+int64_t mxk_rwk_bytes(const MxkGeom* g) { MxkLayout L; return compute_layout(g, &L) ? -1 : L.rwk_bytes; }
+int64_t mxk_unk_bytes(const MxkGeom* g) { MxkLayout L; return compute_layout(g, &L) ? -1 : L.unk_bytes; }
+
+int mxk_launch_prelude(const MxkLaunchArgs* a, void* stream) {
+    KArgs k;
+    if (int rc = build_kargs(a, &k)) return rc;
+    return launch_route_setup(k, static_cast<cudaStream_t>(stream));
+}
+int mxk_launch_compute(const MxkLaunchArgs* a, void* stream) {
+    KArgs k;
+    if (int rc = build_kargs(a, &k)) return rc;
+    if (int rc = launch_route_setup(k, static_cast<cudaStream_t>(stream))) return rc;
+    return launch_dispatch_gemm(k, static_cast<cudaStream_t>(stream));
+}
+int mxk_launch_reduce(const MxkLaunchArgs* a, void* stream) {
+    KArgs k;
+    if (int rc = build_kargs(a, &k)) return rc;
+    return launch_reduce_k(k, static_cast<cudaStream_t>(stream));
+}
+int mxk_launch_full(const MxkLaunchArgs* a, void* stream) {
+    KArgs k;
+    if (int rc = build_kargs(a, &k)) return rc;
+    if (!k.y && !k.y_bf16) return fail(MXK_ERR_BAD_ARG, "y or y_bf16 must be non-null");
+    if (int rc = launch_route_setup(k, static_cast<cudaStream_t>(stream))) return rc;
+    if (int rc = launch_dispatch_gemm(k, static_cast<cudaStream_t>(stream))) return rc;
+    return launch_reduce_k(k, static_cast<cudaStream_t>(stream));
+}
+int mxk_kernels_per_layer(void) { return 5; }
+
+int mxk_launch_phases(const MxkLaunchArgs* a, int phase_mask, void* stream) {
+    KArgs k;
+    if (int rc = build_kargs(a, &k)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (phase_mask & MXK_PHASE_ROUTE) if (int rc = launch_route(k, st)) return rc;
+    if (phase_mask & MXK_PHASE_SETUP) if (int rc = launch_setup(k, st)) return rc;
+    if (phase_mask & MXK_PHASE_DISPATCH) if (int rc = launch_dispatch(k, st)) return rc;
+    if (phase_mask & MXK_PHASE_GEMM) if (int rc = launch_gemm(k, st)) return rc;
+    if (phase_mask & MXK_PHASE_REDUCE) if (int rc = launch_reduce_k(k, st)) return rc;
+    return 0;
+}
+
+int mxk_launch_empty(int grid, int threads, int64_t smem, void* stream) {
+    if (grid < 1 || threads < 1 || threads > 1024 || smem < 0 || smem > 48 * 1024)
+        return fail(MXK_ERR_BAD_ARG, "bad empty-launch geometry");
+    k_empty<<<grid, threads, (size_t)smem, static_cast<cudaStream_t>(stream)>>>();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "launch empty");
+}
+
+int mxk_fill_weights(uint8_t* w, int64_t n_rows, int32_t k_cols, uint32_t seed, void* stream) {
+    if (!w || n_rows < 0 || k_cols < 1) return fail(MXK_ERR_BAD_ARG, "bad fill_weights arguments");
+    if (n_rows == 0) return 0;
+    k_fill_weights<<<1024, 256, 0, static_cast<cudaStream_t>(stream)>>>(w, n_rows, k_cols, seed);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "launch fill_weights");
+}
+
+int mxk_dump_kernel_resources(void) {
+    struct { const char* name; const void* fn; } ks[] = {
+        {"k_route", (const void*)k_route}, {"k_setup", (const void*)k_setup}, {"k_dispatch", (const void*)k_dispatch},
+        {"k_gemm", (const void*)k_gemm}, {"k_reduce", (const void*)k_reduce}};
+    for (auto& k : ks) {
+        cudaFuncAttributes at;
+        cudaError_t e = cudaFuncGetAttributes(&at, k.fn);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncGetAttributes");
+        std::printf("[RES] %-10s regs=%d local=%zu static_smem=%zu max_threads=%d\n", k.name, at.numRegs,
+                    at.localSizeBytes, at.sharedSizeBytes, at.maxThreadsPerBlock);
+    }
+    std::printf("[RES] k_gemm dynamic smem=%d threads=%d\n", kGemmSmem, kGemmThreads);
+    return 0;
+}
+
+int mxk_read_status(const void* rwk, MxkStatus* out) {
+    if (!rwk || !out) return fail(MXK_ERR_BAD_ARG, "null argument");
+    DevFlags f;
+    cudaError_t e = cudaMemcpy(&f, rwk, sizeof(f), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
+    out->launches = f.current_time;
+    out->status = f.status;
+    out->n_tasks = f.n_tasks; out->n_l1_tasks = f.n_l1_tasks; out->n_windows = f.n_windows; out->total_rows = f.total_rows;
+    for (int i = 0; i < 8; ++i) out->dbg[i] = f.dbg[i];
+    return 0;
+}
+
+// Window chooser, restated from the reference's cost model with its own
+// calibration table (src/win_select.cuh:45-128): argmin over {32,48,64,96,128}
+// of waves(win) * t_task(win) with 4 slices per window on a 28-block grid, a
+// skew floor of ceil(max/8) and a 96 cap when max*E > 3*sum.
+int mxk_select_win(const uint32_t* counts, int E, int cap_hint, int win_min) {
+    static const int cand[5] = {32, 48, 64, 96, 128};
+    static const long long tq[5] = {10375, 8251, 8904, 10051, 9792};
+    uint32_t mx = 0;
+    unsigned long long total = 0;
+    for (int e = 0; e < E; ++e) { if (counts[e] > mx) mx = counts[e]; total += counts[e]; }
+    int floor_w = win_min, cap = cap_hint;
+    if (E > 0 && (unsigned long long)mx * E > 3ull * total) {
+        const int need = (int)((mx + 7u) / 8u);
+        if (need > floor_w) floor_w = need;
+        if (floor_w <= 96 && cap > 96) cap = 96;
+    }
+    int best = -1;
+    unsigned long long bc = 0;
+    for (int i = 0; i < 5; ++i) {
+        if (cand[i] < floor_w || cand[i] > cap) continue;
+        unsigned long long W = 0;
+        for (int e = 0; e < E; ++e) W += (counts[e] + (uint32_t)cand[i] - 1u) / (uint32_t)cand[i];
+        const unsigned long long c = ((W * 4ull + 27ull) / 28ull) * (unsigned long long)tq[i];
+        if (best < 0 || c < bc) { best = cand[i]; bc = c; }
+    }
+    return best < 0 ? cap : best;
+}
+
+int mxk_symm_alloc(void** ptr, int64_t bytes) {
+    if (!ptr || bytes <= 0) return fail(MXK_ERR_BAD_ARG, "bad symm_alloc arguments");
+    cudaError_t e = cudaMalloc(ptr, (size_t)bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc");
+    e = cudaMemset(*ptr, 0, (size_t)bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemset");
+    e = cudaDeviceSynchronize();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "cudaDeviceSynchronize");
+}
+int mxk_symm_free(void* ptr) {
+    cudaError_t e = cudaFree(ptr);
+    return e == cudaSuccess ? 0 : cuda_fail(e, "cudaFree");
+}
+int mxk_ipc_export(void* ptr, uint8_t handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaIpcGetMemHandle");
+    std::memcpy(handle, &h, 64);
+    return 0;
+}
+int mxk_ipc_import(const uint8_t handle[64], void** ptr) {
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    return e == cudaSuccess ? 0 : cuda_fail(e, "cudaIpcOpenMemHandle");
+}
+int mxk_ipc_close(void* ptr) {
+    cudaError_t e = cudaIpcCloseMemHandle(ptr);
+    return e == cudaSuccess ? 0 : cuda_fail(e, "cudaIpcCloseMemHandle");
+}
+
+}  // extern "C"

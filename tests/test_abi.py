@@ -1,0 +1,84 @@
+"""CPU-side checks of the C ABI: the library loads without a GPU, exports every symbol
+the header declares, and the layout / argument validation behave (no compute calls)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from mini_mega_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    _lib.build()
+    return _lib.lib()
+
+
+def _declared_functions():
+    src = open(os.path.join(ROOT, "include", "mxk_b200.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(mxk_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _declared_functions()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/mxk_b200.h but not exported"
+    assert sorted(_lib.EXPORTS) == names
+
+
+def test_layout_is_consistent(lib):
+    L = _lib.compute_layout(8, 3, 32, 8, 6144, 2048, 16)
+    assert L.pool_rows == 8 * 16 * 8
+    assert L.recv_stride >= 33 and L.sf_stride_h >= 48 and L.sf_stride_i >= 16
+    offs = [L.x_off, L.x_sf_off, L.topk_idx_off, L.topk_weights_off]
+    assert offs == sorted(offs) and L.sym_bytes > offs[-1]
+    assert all(o % 256 == 0 for o in offs)
+    g = _lib.MxkGeom(8, 3, 32, 8, 6144, 2048, 16, 0)
+    assert lib.mxk_sym_bytes(C.byref(g)) == L.sym_bytes
+    assert lib.mxk_rwk_bytes(C.byref(g)) == L.rwk_bytes
+    assert lib.mxk_unk_bytes(C.byref(g)) == L.unk_bytes
+    # prefill-sized world still fits comfortably in one B200's memory
+    P = _lib.compute_layout(8, 0, 32, 8, 7168, 2048, 4096)
+    assert P.rwk_bytes + P.unk_bytes + P.sym_bytes < 8 << 30
+
+
+@pytest.mark.parametrize("geom", [
+    (0, 0, 8, 8, 6144, 2048, 16, 0),      # no ranks
+    (2, 2, 8, 8, 6144, 2048, 16, 0),      # rank out of range
+    (1, 0, 8, 8, 6100, 2048, 16, 0),      # hidden not a multiple of 256
+    (1, 0, 8, 8, 6144, 2000, 16, 0),      # intermediate not a multiple of 128
+    (1, 0, 8, 0, 6144, 2048, 16, 0),      # topk
+    (1, 0, 8, 8, 6144, 2048, 0, 0),       # max_tokens
+])
+def test_bad_geometry_is_rejected(lib, geom):
+    g = _lib.MxkGeom(*geom)
+    out = _lib.MxkLayout()
+    assert lib.mxk_compute_layout(C.byref(g), C.byref(out)) == -1
+    assert len(lib.mxk_last_error()) > 0
+
+
+def test_launch_argument_validation_needs_no_gpu(lib):
+    a = _lib.MxkLaunchArgs()
+    a.R, a.rank, a.tokens = 1, 0, 4
+    a.experts_per_rank, a.topk, a.hidden, a.intermediate, a.max_tokens = 8, 2, 512, 256, 32
+    assert lib.mxk_launch_full(C.byref(a), None) == -1      # null buffers
+    assert b"non-null" in lib.mxk_last_error()
+    a.hidden = 500
+    assert lib.mxk_launch_full(C.byref(a), None) == -1
+    assert lib.mxk_launch_full(None, None) == -1
+    assert lib.mxk_launch_empty(0, 32, 0, None) == -1
+
+
+def test_select_win_matches_reference_golden(lib):
+    import numpy as np
+    g = np.load(os.path.join(ROOT, "tests", "golden", "sched.npz"))
+    for ci in range(6):
+        counts = np.ascontiguousarray(g[f"win_{ci}_counts"])
+        got = [lib.mxk_select_win(counts.ctypes.data_as(C.POINTER(C.c_uint32)), 256, cap, wmin)
+               for cap in (64, 96, 128) for wmin in (8, 32)]
+        assert got == g[f"win_{ci}_out"].tolist()

@@ -1,0 +1,133 @@
+"""Parity of the CUDA path against the CPU oracle, called through the C ABI.
+
+Tolerances (stated by the reference's own checker and the build target):
+  * routing tables, dispatch layout, counts/offsets, pool bytes: bit-exact
+    (reference: test/check.cu:183-195);
+  * L1 output, decoded from FP8: |d| <= max(2e-3*scale, 7e-2*|want|) (test/check.cu:409);
+  * L2 output (bf16 rows given the device's own FP8 hidden): rel 1e-2 / abs 1e-3
+    (test/check.cu:433);
+  * reduce given the device's own bf16 rows: bit-exact here (reference allows
+    rel 1e-5 / abs 1e-6, test/check.cu:473);
+  * end-to-end y: max relative L2 error per token <= 1e-2 against the oracle.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _stage_checks(world, ref, r, scaled):
+    """Per-phase comparison on rank r, each phase fed with the device's own input."""
+    case = world.case
+    s = ref[r]
+    rows = s.meta.shape[0]
+    H, I, EPR = case.H, case.I, case.EPR
+    # dispatch: pool bytes, scales and staged (src, token, k, weight)
+    meta = world.table(r, "row_meta")[:rows]
+    assert np.array_equal(meta[:, :3], s.meta)
+    wbits = np.array([case.topk_w[m[0], m[1], m[2]] for m in s.meta], np.float32).view(np.int32)
+    assert np.array_equal(meta[:, 3], wbits)
+    pool = world.table(r, "pool")[:rows]
+    assert np.array_equal(pool, s.pool)
+    pool_sf = None
+    if scaled:
+        pool_sf = world.table(r, "pool_sf")[:rows, : H // 128]
+        assert np.array_equal(pool_sf, s.pool_sf)
+    ffn = world.table(r, "ffn")[:rows]
+    ffn_sf = world.table(r, "ffn_sf")[:rows, : I // 128] if scaled else None
+    for le in range(EPR):
+        a, b = int(s.row_base[le]), int(s.row_base[le + 1])
+        if a == b:
+            continue
+        e = r * EPR + le
+        # L1: decoded device FP8 vs the oracle's pre-quantisation expectation
+        want_h = s.h[a:b]
+        got_h = orc.dequant_rows_1x128(np.ascontiguousarray(ffn[a:b]), None if not scaled else np.ascontiguousarray(ffn_sf[a:b]))
+        if scaled:
+            scale = np.repeat(orc.ue8m0_to_f32(np.ascontiguousarray(ffn_sf[a:b])), 128, axis=1)
+            # per-row scale choice may differ by one step at an amax boundary: allow either
+            assert (np.abs(ffn_sf[a:b].astype(int) - s.ffn_sf[a:b].astype(int)) <= 1).all()
+        else:
+            scale = np.ones_like(want_h)
+        d = np.abs(got_h.astype(np.float64) - np.clip(want_h, -448 * scale, 448 * scale))
+        lim = np.maximum(2e-3 * scale, 7e-2 * np.abs(want_h))
+        assert (d <= lim).all(), f"L1 expert {e}: max excess {(d - lim).max()}"
+        # L2 from the device's own hidden bytes
+        want_o = orc.l2(np.ascontiguousarray(ffn[a:b]), None if not scaled else np.ascontiguousarray(ffn_sf[a:b]),
+                        case.w2[e], None if not scaled else case.w2_sf[e])
+        for g in range(a, b):
+            src, tok, k = s.meta[g]
+            got_row = orc.bf16_to_f32(world.table(src, "combine_rows").view(np.uint16)[k, tok])
+            st = orc.check_close(got_row, want_o[g - a], 1e-2, 1e-3)
+            assert st["bad"] == 0, f"L2 expert {e} row {g}: {st}"
+
+
+def _reduce_check(world, r):
+    case = world.case
+    T = case.tokens[r]
+    if T == 0:
+        return
+    comb = world.table(r, "combine_rows").view(np.uint16)
+    want = orc.reduce_all(comb, case.topk_idx[r], case.topk_w[r], T, case.E)
+    got32 = world.y32[r][:T].cpu().numpy()
+    assert np.array_equal(got32, want), "reduce differs from the oracle on the device's own rows"
+    got16 = world.y[r][:T].view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got16, orc.f32_to_bf16(want))
+
+
+def _run_case(case, expert_window=128, full_stage_checks=True, e2e_tol=1e-2):
+    from gpu_world import World, assert_status_ok, check_tables
+    ref = orc.layer_world(case)
+    w = World(case, expert_window=expert_window)
+    try:
+        w.run()
+        assert_status_ok(w)
+        check_tables(w, ref)
+        for r in range(case.R):
+            if full_stage_checks:
+                _stage_checks(w, ref, r, case.scaled)
+            _reduce_check(w, r)
+            T = case.tokens[r]
+            if T:
+                got = w.y32[r][:T].cpu().numpy()
+                err = orc.rel_l2(got, ref[r].y)
+                assert err <= e2e_tol, f"rank {r}: end-to-end relative L2 {err}"
+    finally:
+        w.destroy()
+
+
+def test_toy_scaled():
+    """BASELINE config 0: E=8, topk=2, H=512, I=256, T=32, world=1, UE8M0 block scales,
+    top-k of router logits."""
+    _run_case(orc.gen_case(1, 8, 2, 512, 256, 32, seed=1, routing="logits", scaled=True))
+
+
+def test_toy_reference_mode():
+    """Same shape without scale planes: the reference kernel's own arithmetic (scale == 1)."""
+    _run_case(orc.gen_case(1, 8, 2, 512, 256, 32, seed=2, routing="logits", scaled=False))
+
+
+def test_multi_rank_world_scaled():
+    """4 ranks x 4 experts, ragged token counts including an empty rank."""
+    _run_case(orc.gen_case(4, 4, 4, 1024, 512, [24, 0, 7, 33], seed=3, routing="uniform", scaled=True, cap=40))
+
+
+def test_multi_window_skew():
+    """Zipf routing on few experts: several 128-row windows per expert, and a 64-row window run."""
+    case = orc.gen_case(2, 2, 2, 512, 256, [150, 130], seed=4, routing="zipf", scaled=True)
+    _run_case(case)
+    _run_case(case, expert_window=64)
+
+
+def test_invalid_ids():
+    """Negative expert ids are skipped everywhere (src/prologue.cuh:166-167, src/combine.cuh reduce)."""
+    _run_case(orc.gen_case(2, 4, 4, 512, 256, [20, 12], seed=5, routing="uniform", scaled=True, invalid_frac=0.15))
+
+
+def test_reference_fixture_full_geometry():
+    """The reference harness's own fixture at its frozen geometry (EPR=8, topk=8, H=6144,
+    I=2048, balanced routes, WPROBE weights, byte-pattern x), R=1, 8 tokens."""
+    _run_case(orc.gen_reference_fixture(1, 8, 8, 6144, 2048, 8, "balanced"))
