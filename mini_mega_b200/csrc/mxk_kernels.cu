@@ -357,7 +357,7 @@ struct GemmSmem {
     int abort_flag;
 };
 
-__global__ void __maxnreg__(200)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_constant__ CUtensorMap tm_ffn,
        const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2) {
     extern __shared__ uint8_t smem_raw[];
@@ -521,19 +521,32 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
 #pragma unroll
             for (int j = 0; j < 64; ++j) { accG[j] = 0.0f; accU[j] = 0.0f; }
             bool dead = false;
+            // Activation scale of the next K block, fetched one block ahead.  Pool scales
+            // come from an earlier kernel; ffn scales are produced inside this kernel, so
+            // for an L2 task the first fetch must follow the first accumulator barrier
+            // (the producer has then seen every L1 tile of the window complete).
+            uint32_t e_next = 127;
+            if (a.scaled && !is_l2) e_next = __ldcg(sa_ptr);
             for (int kb = 0; kb < nkb; ++kb, ++acc_it) {
                 const uint32_t buf = acc_it & 1;
-                float sg = 1.0f, su = 1.0f;
+                float sb0 = 1.0f, sb1 = 1.0f;
                 if (a.scaled) {
-                    const float sa = ue8m0_f32(__ldcg(sa_ptr + kb));  // written earlier in this kernel: no read-only path
-                    sg = sa * ue8m0_f32(__ldg(sb0_ptr + kb));
-                    su = sa * ue8m0_f32(__ldg(sb1_ptr + kb));
+                    sb0 = ue8m0_f32(__ldg(sb0_ptr + kb));
+                    sb1 = ue8m0_f32(__ldg(sb1_ptr + kb));
                 }
                 bool got = true;
                 if (lane == 0) got = mbar_wait(&S->tmem_full[buf], (acc_it >> 1) & 1, wait_ns, abort_flag);
                 got = __shfl_sync(0xFFFFFFFFu, got ? 1 : 0, 0) != 0;
                 if (!got) { dead = true; break; }
                 tc_fence_after();
+                float sg = 1.0f, su = 1.0f;
+                if (a.scaled) {
+                    if (is_l2 && kb == 0) e_next = __ldcg(sa_ptr);
+                    const float sa = ue8m0_f32(e_next);
+                    if (kb + 1 < nkb) e_next = __ldcg(sa_ptr + kb + 1);
+                    sg = sa * sb0;
+                    su = sa * sb1;
+                }
                 if (warp_active) {
                     const uint32_t t0 = lane_addr + buf * kBlockN + half * 64;
                     uint32_t v[32];
