@@ -1,0 +1,464 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8xFP8 MoE layer hot path.
+
+    python bench.py --gpus N --steps K --warmup W            # CUDA path, one rank per GPU
+    python bench.py --impl reference --steps K --warmup W    # the CPU path on the host cores
+
+Workload at N GPUs: E=256 experts, topk=8, H=6144, I=2048, FP8 E4M3 with UE8M0 block
+scales (128x128 weights, 1x128 activations), expert parallel over the N GPUs
+(256/N experts per GPU), 16 tokens per rank, every token routed to 8 distinct
+experts uniformly at random — the decode configuration of the baseline, with the
+EP=1/2/4 members of its sweep when fewer than 8 GPUs are used.  A step is one layer.
+`value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the same through
+the public call with host buffers (pinned H2D of x / scales / routing and D2H of y
+inside the timed region).  `points` repeats the device-resident measurement at 16, 64
+and 256 tokens per rank.  Rank 0 prints ONE JSON line.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+E_TOTAL, TOPK, H, I = 256, 8, 6144, 2048
+HBM_FALLBACK_GBS = 6650.0        # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+BF16_FALLBACK_TFLOPS = 1590.0
+NVLINK_GBS = 770.0               # measured peer copy per direction on this pool
+# DRAM bytes per k_gemm launch from the ncu capture summarised under profiles/ (None until captured)
+NCU_TRAFFIC_BYTES = {}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", BF16_FALLBACK_TFLOPS)), "measured"
+    return HBM_FALLBACK_GBS, BF16_FALLBACK_TFLOPS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- workload
+def make_weights(torch, epr, rank, device):
+    """Seeded synthetic expert weights of this rank, directly as E4M3 bytes + UE8M0 exponents
+    (random sign / mantissa, exponent field 3..10, block scale 2^-9): same shapes and value range
+    as N(0, 0.02) weights quantised per 128x128 block, without materialising FP32 tensors."""
+    g = torch.Generator(device=device)
+    g.manual_seed(1000 + rank)
+
+    def fp8_bytes(shape):
+        n = 1
+        for s in shape:
+            n *= s
+        out = torch.empty(n, dtype=torch.uint8, device=device)
+        step = 1 << 28
+        for o in range(0, n, step):
+            m = min(step, n - o)
+            r = torch.randint(0, 256, (m,), generator=g, device=device, dtype=torch.uint8)
+            ex = torch.randint(3, 11, (m,), generator=g, device=device, dtype=torch.uint8)
+            out[o:o + m] = (r & 0x87) | (ex << 3)
+        return out.view(*shape)
+
+    w1 = fp8_bytes((epr, 2 * I, H))
+    w2 = fp8_bytes((epr, H, I))
+    s1 = torch.full((epr, 2 * I // 128, H // 128), 127 - 9, dtype=torch.uint8, device=device)
+    s2 = torch.full((epr, H // 128, I // 128), 127 - 9, dtype=torch.uint8, device=device)
+    s1 += torch.randint(0, 3, s1.shape, generator=g, device=device, dtype=torch.uint8)
+    s2 += torch.randint(0, 3, s2.shape, generator=g, device=device, dtype=torch.uint8)
+    return (w1, s1), (w2, s2)
+
+
+def make_inputs(torch, tokens, rank, seed):
+    """Host-side (pinned) inputs of one step: x E4M3 + 1x128 scales, 8 distinct experts per token
+    uniformly at random, weights = softmax of N(0,1) logits."""
+    g = torch.Generator()
+    g.manual_seed(seed * 7919 + rank)
+    r = torch.randint(0, 256, (tokens, H), generator=g, dtype=torch.uint8)
+    ex = torch.randint(3, 11, (tokens, H), generator=g, dtype=torch.uint8)
+    x = ((r & 0x87) | (ex << 3)).pin_memory()
+    x_sf = (torch.randint(0, 3, (tokens, H // 128), generator=g, dtype=torch.uint8) + (127 - 3)).pin_memory()
+    idx = torch.rand((tokens, E_TOTAL), generator=g).topk(TOPK, dim=1).indices.to(torch.int64).pin_memory()
+    w = torch.softmax(torch.randn((tokens, TOPK), generator=g), dim=1).float().pin_memory()
+    return x, x_sf, idx, w
+
+
+def algorithmic_work(idx_all, n_ranks, rank, tokens):
+    """Per-GPU algorithmic bytes / flops of one layer for the routing actually drawn.
+    idx_all: [n_ranks*tokens, topk] global expert ids of every rank's tokens."""
+    epr = E_TOTAL // n_ranks
+    owner = idx_all // epr
+    mine = owner == rank
+    P = int(mine.sum())                                   # routed pairs landing on this GPU
+    active = int(idx_all[mine].unique().numel())          # local experts with >= 1 row
+    src_rank = (idx_all.new_tensor(range(idx_all.shape[0])) // tokens)[:, None].expand_as(idx_all)
+    P_remote = int((mine & (src_rank != rank)).sum())
+    w_bytes = active * (2 * I * H + H * I + (2 * I // 128) * (H // 128) + (H // 128) * (I // 128))
+    gemm_bytes = w_bytes + P * (H + H // 128) + 2 * P * (I + I // 128) + P * 2 * H
+    layer_bytes = gemm_bytes + P * (H + H // 128) + tokens * TOPK * 2 * H + tokens * 2 * H
+    flops = P * 6 * H * I
+    nvl = max(P_remote * (H + H // 128), P_remote * 2 * H)
+    return {"pairs": P, "active_experts": active, "weight_bytes": w_bytes, "gemm_bytes": gemm_bytes,
+            "layer_bytes": layer_bytes, "flops": flops, "nvlink_bytes": nvl}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+class CpuLayer:
+    """The CPU path on one rank's share of the layer: 8 experts x `rows_per_expert` rows through
+    L1 -> FP8 -> L2 (weights of 8 distinct experts, 302 MB, as the reference's balanced TPR=16
+    scene gives every expert exactly 16 rows) plus the top-k reduce of `tokens` tokens.  Uses the
+    reference's own ref_l1 / ref_quantize_fp8 / ref_l2 / ref_reduce when the compiled shim is
+    present (driven row-parallel like test/check.cu:155-165), else the oracle port."""
+
+    def __init__(self, threads, rows_per_expert=16, tokens=16, experts=8):
+        import numpy as np
+        from oracle import oracle as orc
+        orc.build()
+        self.np, self.orc, self.threads = np, orc, threads
+        self.rows, self.tokens, self.experts = rows_per_expert, tokens, experts
+        self.R = orc.ref_lib()
+        rng = np.random.default_rng(5)
+        self.x = rng.integers(0, 0x40, (experts, rows_per_expert, H)).astype(np.uint8)
+        self.comb = orc.f32_to_bf16(rng.standard_normal((TOPK, tokens, H)).astype(np.float32))
+        self.tidx = rng.integers(0, E_TOTAL, (tokens, TOPK)).astype(np.int64)
+        self.tw = rng.random((tokens, TOPK)).astype(np.float32)
+        R = self.R
+        self.kind = "reference" if (R is not None and R.ref_const(2) == H and R.ref_const(3) == I and
+                                    R.ref_const(1) == TOPK and R.ref_const(0) >= experts) else "port"
+        w1 = orc.fill_weights(experts * 2 * I, H, 17).reshape(experts, 2 * I, H)
+        w2 = orc.fill_weights(experts * H, I, 91).reshape(experts, H, I)
+        if self.kind == "reference":
+            self.w1 = np.zeros((experts, 2 * I * H), np.uint8)
+            self.w2 = np.zeros((experts, H * I), np.uint8)
+            for e in range(experts):
+                R.ref_pack_lane(np.ascontiguousarray(w1[e]), 2 * I, H, self.w1[e])
+                R.ref_pack_lane(np.ascontiguousarray(w2[e]), H, I, self.w2[e])
+        else:
+            self.w1, self.w2 = w1, w2
+
+    def run(self):
+        """One pass; returns seconds."""
+        np, orc, R, th = self.np, self.orc, self.R, self.threads
+        t0 = time.perf_counter()
+        for e in range(self.experts):
+            if self.kind == "reference":
+                ffn = np.zeros((self.rows, I), np.float32)
+                q = np.zeros((self.rows, I), np.uint8)
+                out = np.zeros((self.rows, H), np.float32)
+                R.ref_l1_rows(self.x[e], self.w1.reshape(-1), e, self.rows, ffn.reshape(-1), th)
+                R.ref_quantize(ffn.reshape(-1), self.rows * I, q.reshape(-1))
+                R.ref_l2_rows(q, self.w2.reshape(-1), e, self.rows, out.reshape(-1), th)
+            else:
+                h = orc.l1(self.x[e], None, self.w1[e], None, th)
+                q, _ = orc.requant(h, False)
+                orc.l2(q, None, self.w2[e], None, th)
+        if self.kind == "reference":
+            y = np.zeros((self.tokens, H), np.float32)
+            R.ref_reduce_tokens(self.comb.view(np.uint8).reshape(-1), self.tidx, self.tw, self.tokens, E_TOTAL,
+                                self.tokens, y.reshape(-1), th)
+        else:
+            orc.reduce_all(self.comb, self.tidx, self.tw, self.tokens, E_TOTAL, th)
+        return time.perf_counter() - t0
+
+    def describe(self, tpr):
+        pairs = self.experts * self.rows
+        s = (f"{self.experts} experts x {self.rows} rows = {pairs} routed pairs through L1->FP8->L2 plus the "
+             f"reduce of {self.tokens} tokens per pass")
+        if pairs != tpr * TOPK:
+            s += f", scaled by {tpr * TOPK}/{pairs} to {tpr} tokens per rank"
+        else:
+            s += " (one rank's whole share of the layer, no extrapolation)"
+        return s
+
+
+def cpu_sample_shape(tpr):
+    rows = min(tpr, 16)       # bounded: at most 128 pairs per pass
+    return rows, min(tpr, 16)
+
+
+def cpu_arm(args, n_ranks):
+    """`--impl reference`: every step is one pass of the CPU path over the bounded sample."""
+    threads = os.cpu_count() or 1
+    rows, toks = cpu_sample_shape(args.tpr)
+    layer = CpuLayer(threads, rows, toks)
+    for _ in range(args.warmup):
+        layer.run()
+    secs = [layer.run() for _ in range(args.steps)]
+    scale = (args.tpr * TOPK) / (layer.experts * rows)
+    layer_s = sum(secs) / len(secs) * scale             # one rank's share; ranks run in parallel
+    value = n_ranks * args.tpr / layer_s
+    line = {
+        "impl": "reference", "metric": "tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": n_ranks,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": layer_s * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": workload_config(n_ranks, args.tpr),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": layer.kind,
+                         "sample": layer.describe(args.tpr)},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n, tokens):
+    return {"workload": f"MoE layer decode balanced: E=256 topk=8 H=6144 I=2048 FP8 e4m3 + UE8M0 block scales, "
+                        f"{tokens} tokens/rank, EP={n} ({E_TOTAL // n} experts/GPU), uniform distinct routing",
+            "tokens_per_rank": tokens, "ep": n, "experts_per_gpu": E_TOTAL // n,
+            "l2_policy": "inputs larger than L2 (expert weights streamed per layer >> 126 MB)"}
+
+
+# ----------------------------------------------------------------------------- CUDA arm
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    import mini_mega_b200 as mm
+    from mini_mega_b200 import _lib
+
+    n = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if n > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    assert args.gpus == n, f"--gpus {args.gpus} but WORLD_SIZE={n}"
+    epr = E_TOTAL // n
+    cap = max(256, args.tpr)
+    lib = _lib.lib()
+    buf = mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, H, I)
+    l1, l2 = mm.transform_weights_for_mega_moe(*make_weights(torch, epr, rank, dev))
+    stream = torch.cuda.current_stream()
+    hbm_gbs, bf16_tf, peak_kind = load_peaks()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if n > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if n == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_routing(idx_host, tokens):
+        if n == 1:
+            return idx_host.clone()
+        t = idx_host.to(dev)
+        out = [torch.empty_like(t) for _ in range(n)]
+        dist.all_gather(out, t)
+        return torch.cat(out).cpu()
+
+    def resident_run(tokens, steps, warmup, seed):
+        """Inputs already in the symmetric buffer; K eager layers timed with CUDA events."""
+        x, x_sf, idx, w = make_inputs(torch, tokens, rank, seed)
+        buf.x.view(torch.uint8)[:tokens].copy_(x)
+        buf.x_sf[:tokens].copy_(x_sf)
+        buf.topk_idx[:tokens].copy_(idx)
+        buf.topk_weights[:tokens].copy_(w)
+        y = torch.zeros((tokens, H), dtype=torch.bfloat16, device=dev)
+        for _ in range(warmup):
+            mm.fp8_mega_moe(y, l1, l2, buf)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            mm.fp8_mega_moe(y, l1, l2, buf)
+        e1.record(stream)
+        barrier()
+        ms = max_over_ranks(e0.elapsed_time(e1))
+        st = buf.status()
+        assert st.status == 0, f"device status {st.status} dbg {list(st.dbg)}"
+        return ms / steps, all_routing(idx, tokens), y
+
+    def gemm_kernel_ms(tokens, steps, warmup):
+        """Average k_gemm duration: events bracket the GEMM phase alone on the launching stream."""
+        y = torch.zeros((tokens, H), dtype=torch.bfloat16, device=dev)
+        a = buf.launch_args(tokens, l1, l2, y_bf16=y)
+        evs = []
+        for i in range(warmup + steps):
+            _lib.check(lib.mxk_launch_phases(C.byref(a), 1 | 2 | 4, stream.cuda_stream), "prologue+dispatch")
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            _lib.check(lib.mxk_launch_phases(C.byref(a), 8, stream.cuda_stream), "gemm")
+            e1.record(stream)
+            _lib.check(lib.mxk_launch_phases(C.byref(a), 16, stream.cuda_stream), "reduce")
+            if i >= warmup:
+                evs.append((e0, e1))
+        barrier()
+        return max_over_ranks(sum(a_.elapsed_time(b_) for a_, b_ in evs) / len(evs))
+
+    def e2e_run(tokens, steps, warmup, seed):
+        """Public call with HOST buffers: pinned H2D of the step's inputs and D2H of y each step."""
+        x, x_sf, idx, w = make_inputs(torch, tokens, rank, seed)
+        y = torch.zeros((tokens, H), dtype=torch.bfloat16, device=dev)
+        y_host = torch.empty((tokens, H), dtype=torch.bfloat16).pin_memory()
+
+        def step():
+            buf.x.view(torch.uint8)[:tokens].copy_(x, non_blocking=True)
+            buf.x_sf[:tokens].copy_(x_sf, non_blocking=True)
+            buf.topk_idx[:tokens].copy_(idx, non_blocking=True)
+            buf.topk_weights[:tokens].copy_(w, non_blocking=True)
+            mm.fp8_mega_moe(y, l1, l2, buf)
+            y_host.copy_(y, non_blocking=True)
+
+        for _ in range(warmup):
+            step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            step()
+        e1.record(stream)
+        barrier()
+        ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+        h2d = x.numel() + x_sf.numel() + idx.numel() * 8 + w.numel() * 4
+        return ms, h2d, y_host.numel() * 2
+
+    fp8_peak = 2.0 * bf16_tf * 1e12
+
+    def binding(work):
+        t_h = work["layer_bytes"] / (hbm_gbs * 1e9)
+        t_f = work["flops"] / fp8_peak
+        t_n = work["nvlink_bytes"] / (NVLINK_GBS * 1e9)
+        t = max(t_h, t_f, t_n)
+        return t, ("hbm" if t == t_h else "tensor" if t == t_f else "nvlink")
+
+    # ---- headline: timed region with clock sampling ----
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms_step, routing, _ = resident_run(args.tpr, args.steps, args.warmup, seed=1)
+    clocks = sampler.stop() if sampler else None
+    work = algorithmic_work(routing, n, rank, args.tpr)
+    gemm_ms = gemm_kernel_ms(args.tpr, max(3, min(args.steps, 20)), 3)
+    e2e_ms, h2d, d2h = e2e_run(args.tpr, args.steps, args.warmup, seed=1)
+
+    points = []
+    for tpr in (16, 64, 256):
+        if tpr == args.tpr:
+            ms, wk = ms_step, work
+        else:
+            ms, rt, _ = resident_run(tpr, max(3, min(args.steps, 20)), 3, seed=2)
+            wk = algorithmic_work(rt, n, rank, tpr)
+        t_roof, bound = binding(wk)
+        points.append({"tokens_per_rank": tpr, "us_per_layer": ms * 1e3, "tokens_per_s_per_gpu": tpr / (ms * 1e-3),
+                       "bound": bound, "roofline_us": t_roof * 1e6, "roofline_frac": t_roof / (ms * 1e-3),
+                       "active_experts": wk["active_experts"], "pairs": wk["pairs"]})
+
+    cpu = None
+    if rank == 0 and n == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        rows, toks = cpu_sample_shape(args.tpr)
+        layer = CpuLayer(threads, rows, toks)
+        layer.run()
+        secs = [layer.run() for _ in range(8)]          # ~10 s of CPU work
+        layer_s = sum(secs) / len(secs) * (args.tpr * TOPK) / (layer.experts * rows)
+        cpu = {"value": args.tpr / layer_s, "unit": "tokens/s", "cores": threads, "kind": layer.kind,
+               "sample": layer.describe(args.tpr), "ms_per_layer": layer_s * 1e3}
+
+    if rank == 0:
+        achieved = work["gemm_bytes"] / (gemm_ms * 1e-3) / 1e9
+        line = {
+            "metric": "tokens_per_s", "value": n * args.tpr / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": n,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": workload_config(n, args.tpr),
+            "us_per_layer": ms_step * 1e3,
+            "e2e": {"value": n * args.tpr / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": int(lib.mxk_kernels_per_layer()) * args.steps,
+            "roofline": {"kernel": "k_gemm", "bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
+                         "frac": achieved / hbm_gbs, "peak_kind": f"of {peak_kind}",
+                         "traffic": NCU_TRAFFIC_BYTES.get((n, args.tpr)), "kernel_us": gemm_ms * 1e3,
+                         "algorithmic_bytes": work["gemm_bytes"], "active_experts": work["active_experts"],
+                         "pairs": work["pairs"]},
+            "points": points,
+            "clocks": clocks,
+        }
+        if cpu:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    buf.destroy()
+    if n > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tpr", type=int, default=16, help="tokens per rank of the headline point")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return  # rank 0 alone runs the CPU arm
+        cpu_arm(args, args.gpus)
+        return
+    gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()
