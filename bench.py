@@ -4,11 +4,12 @@
     python bench.py --gpus N --steps K --warmup W            # CUDA path, one rank per GPU
     python bench.py --impl reference --steps K --warmup W    # the CPU path on the host cores
 
-Workload at N GPUs: E=256 experts, topk=8, H=6144, I=2048, FP8 E4M3 with UE8M0 block
-scales (128x128 weights, 1x128 activations), expert parallel over the N GPUs
-(256/N experts per GPU), 16 tokens per rank, every token routed to 8 distinct
-experts uniformly at random — the decode configuration of the baseline, with the
-EP=1/2/4 members of its sweep when fewer than 8 GPUs are used.  A step is one layer.
+Workload: the baseline's balanced decode layer as ONE fixed job — E=256 experts, topk=8,
+H=6144, I=2048, FP8 E4M3 with UE8M0 block scales (128x128 weights, 1x128 activations),
+128 tokens in total, every token routed to 8 distinct experts uniformly at random —
+split expert-parallel over the N GPUs: 256/N experts and 128/N tokens per rank.  At N=8
+this is exactly "16 tokens per rank, EP over 8 GPUs, 32 experts/GPU"; at N=1 the same job
+runs on one GPU (strong scaling).  A step is one layer.
 `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the same through
 the public call with host buffers (pinned H2D of x / scales / routing and D2H of y
 inside the timed region).  `points` repeats the device-resident measurement at 16, 64
@@ -244,7 +245,7 @@ def cpu_arm(args, n_ranks):
     line = {
         "impl": "reference", "metric": "tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": n_ranks,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": layer_s * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
         "config": workload_config(n_ranks, args.tpr),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": layer.kind,
                          "sample": layer.describe(args.tpr)},
@@ -254,9 +255,10 @@ def cpu_arm(args, n_ranks):
 
 
 def workload_config(n, tokens):
-    return {"workload": f"MoE layer decode balanced: E=256 topk=8 H=6144 I=2048 FP8 e4m3 + UE8M0 block scales, "
-                        f"{tokens} tokens/rank, EP={n} ({E_TOTAL // n} experts/GPU), uniform distinct routing",
-            "tokens_per_rank": tokens, "ep": n, "experts_per_gpu": E_TOTAL // n,
+    return {"workload": f"MoE layer decode balanced: E={E_TOTAL} topk=8 H=6144 I=2048 FP8 e4m3 + UE8M0 block "
+                        f"scales, {n * tokens} tokens in total = {tokens} tokens/rank, EP={n} "
+                        f"({E_TOTAL // n} experts/GPU), uniform distinct routing",
+            "tokens_per_rank": tokens, "global_tokens": n * tokens, "ep": n, "experts_per_gpu": E_TOTAL // n,
             "l2_policy": "inputs larger than L2 (expert weights streamed per layer >> 126 MB)"}
 
 
@@ -393,7 +395,7 @@ def gpu_arm(args):
     e2e_ms, h2d, d2h = e2e_run(args.tpr, args.steps, args.warmup, seed=1)
 
     points = []
-    for tpr in (16, 64, 256):
+    for tpr in (() if args.no_points else (16, 64, 256)):
         if tpr == args.tpr:
             ms, wk = ms_step, work
         else:
@@ -420,7 +422,7 @@ def gpu_arm(args):
         line = {
             "metric": "tokens_per_s", "value": n * args.tpr / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": n,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
             "config": workload_config(n, args.tpr),
             "us_per_layer": ms_step * 1e3,
             "e2e": {"value": n * args.tpr / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
@@ -448,9 +450,16 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--tpr", type=int, default=16, help="tokens per rank of the headline point")
+    ap.add_argument("--global-tokens", type=int, default=128, help="tokens of the whole job (split over the ranks)")
+    ap.add_argument("--tpr", type=int, default=0, help="tokens per rank; overrides --global-tokens")
+    ap.add_argument("--experts", type=int, default=256, help="total experts (smaller for profiling captures)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-points", action="store_true", help="skip the 16/64/256 tokens-per-rank sweep")
     args = ap.parse_args()
+    global E_TOTAL
+    E_TOTAL = args.experts
+    if args.tpr <= 0:
+        args.tpr = max(1, args.global_tokens // max(1, args.gpus))
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) != 0:

@@ -151,6 +151,32 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// D[tmem] (+)= (A * 2^(sfa-127)) * (B * 2^(sfb-127))^T: E4M3 operands with one UE8M0 scale
+// per row and per 32-wide K slice, scales read from TMEM (see umma_idesc_mx_e4m3).
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+        : "memory");
+}
+// Shared -> tensor memory copy of one 32-row x 16-byte scale tile, replicated to the four
+// 32-lane groups: afterwards lane l (mod 32), column c+j holds bytes [16*l + 4*j, +4).
+__device__ __forceinline__ void utccp_32x128b_warpx4(uint32_t tmem_dst, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(sdesc) : "memory");
+}
+// Descriptor of a 512-byte scale tile in shared memory: no swizzle, 8-row groups 128 B apart.
+__device__ __forceinline__ uint64_t umma_smem_desc_sf(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)(128 >> 4) << 32;   // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;            // descriptor version
+    return d;
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i receives lane (base+i).
@@ -183,6 +209,13 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr) {
 // Instruction descriptor, kind::f8f6f4: D=F32, A=B=E4M3, both K-major.
 __host__ __device__ constexpr uint32_t umma_idesc_e4m3(int m, int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// Block-scaled instruction descriptor, kind::mxf8f6f4: A=B=E4M3 K-major, UE8M0 scales,
+// K=32 per instruction; sf_id selects which of the four scale bytes of a TMEM column
+// (i.e. which 32-wide K slice of the staged group) applies to A and to B.
+__host__ __device__ constexpr uint32_t umma_idesc_mx_e4m3(int m, int n, uint32_t a_sf_id, uint32_t b_sf_id) {
+    return (b_sf_id << 4) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(m >> 4) << 24) | (a_sf_id << 29);
 }
 
 // E4M3 pack with round-to-nearest-even and saturation to +-448 (NaN -> 0x7F).

@@ -1,0 +1,401 @@
+// ============================================================================
+// mxk_gemm.cuh — persistent grouped GEMM of the MoE layer on tcgen05.
+// Included by mxk_kernels.cu after KArgs / DevFlags are defined.
+//
+// One CTA per SM pulls (window, n-tile) tasks from a global queue:
+//   L1 task: D[128 rows, 256] = X_window . [W1 gate rows | W1 up rows]^T over K = H,
+//            epilogue SwiGLU -> per-row 1x128 UE8M0 requantisation -> ffn (E4M3)
+//   L2 task: D[128 rows, 256] = ffn_window . W2[256 rows]^T over K = I,
+//            epilogue bf16 -> rows pushed to the source rank's combine_rows
+// (reference: task loop src/compute.cuh:1050-1236, L1 family
+//  src/compute_big.cuh:320-515,888-1161, L2 family :1231-1679, fused combine push
+//  src/combine.cuh:347-372; there the MMA is a register-fragment warp MMA and the
+//  four N/K slices of a window synchronise through flags.)
+//
+// The whole K extent accumulates in tensor memory with the block-scaled MMA
+// (kind::mxf8f6f4): the UE8M0 scale of each 128-wide K block — 1x128 per
+// activation row, 128x128 per weight block — is staged as a TMEM scale tile, so
+// the epilogue runs once per task.
+//
+// Warp roles (384 threads):
+//   warp 0      task scheduler + TMA producer (operand tiles, 4-stage ring)
+//   warp 1      MMA issuer (one lane), owns the TMEM allocation
+//   warp 2      scale-tile builder: global scale planes -> shared tiles for UTCCP
+//   warp 3      idle
+//   warps 4-11  epilogue: warp w reads TMEM lanes 32*(w%4).., column half (w-4)/4
+// ============================================================================
+#pragma once
+
+constexpr int kStages = 4;
+constexpr int kABytes = kBlockM * kBlockK;           // 16 KB activation tile
+constexpr int kBBytes = kBlockN * kBlockK;           // 32 KB weight tile (two 128-row halves)
+constexpr int kStageBytes = kABytes + kBBytes;       // 48 KB
+constexpr int kTaskRing = 4;
+constexpr int kGemmThreads = 384;
+constexpr int kEpiWarps = 8;
+constexpr int kFirstEpiWarp = 4;
+constexpr int kTmemCols = 512;
+constexpr int kTmemSfCol = 256;       // scale tiles live behind the 256 accumulator columns
+constexpr int kSfRing = 4;            // shared-memory scale-tile slots (one per 4 K blocks)
+constexpr int kSfSlotBytes = 3 * 512; // A rows, weight half 0, weight half 1
+constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align*/ + kSfRing * kSfSlotBytes + 8192 /*control*/;
+
+struct GemmSmem {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t sf_full[kSfRing];
+    uint64_t sf_empty[kSfRing];
+    uint64_t tmem_full;
+    uint64_t tmem_empty;
+    uint64_t task_full[kTaskRing];
+    uint64_t task_empty[kTaskRing];
+    int4 task[kTaskRing];
+    unsigned long long xch[2][2][128];  // amax exchange between the two column halves
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_constant__ CUtensorMap tm_ffn,
+       const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sf_tiles = tiles + kStages * kStageBytes;                 // 1024-aligned
+    GemmSmem* S = reinterpret_cast<GemmSmem*>(sf_tiles + kSfRing * kSfSlotBytes);
+    DevFlags* f = flags_of(a);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &S->abort_flag;
+    const uint64_t wait_ns = a.local_wait_ns;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&S->full[s], 1); mbar_init(&S->empty[s], 1); }
+        for (int s = 0; s < kSfRing; ++s) { mbar_init(&S->sf_full[s], 1); mbar_init(&S->sf_empty[s], 1); }
+        mbar_init(&S->tmem_full, 1);
+        mbar_init(&S->tmem_empty, kEpiWarps);
+        for (int s = 0; s < kTaskRing; ++s) { mbar_init(&S->task_full[s], 1); mbar_init(&S->task_empty[s], 2 + kEpiWarps); }
+        S->abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    for (int i = threadIdx.x; i < 2 * 2 * 128; i += blockDim.x) (&S->xch[0][0][0])[i] = 0ull;
+    if (warp == 1) {
+        tmem_alloc(&S->tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = S->tmem_base;
+
+    const int n_tasks = f->n_tasks;
+    const int4* tasks = reinterpret_cast<const int4*>(a.rwk + a.L.tasks_off);
+    const int4* windows = reinterpret_cast<const int4*>(a.rwk + a.L.windows_off);
+    uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
+    const int kb1 = a.H / kBlockK, kb2 = a.I / kBlockK;
+    const int nt1 = a.I / 128;
+    const uint32_t l1_need = (uint32_t)nt1 * kEpiWarps;   // arrivals that complete a window's ffn rows
+
+    if (warp == 0) {
+        // ------------------------------------------------ scheduler + TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_pool); tma_prefetch_desc(&tm_ffn);
+            tma_prefetch_desc(&tm_w1); tma_prefetch_desc(&tm_w2);
+            uint32_t stage = 0, phase = 0;
+            for (uint32_t it = 0;; ++it) {
+                const uint32_t slot = it % kTaskRing;
+                if (!mbar_wait(&S->task_empty[slot], ((it / kTaskRing) & 1) ^ 1, wait_ns, abort_flag)) {
+                    raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break;
+                }
+                const int t = it == 0 ? (int)blockIdx.x : (int)atomicAdd(&f->task_counter, 1u);
+                const int4 task = t < n_tasks ? tasks[t] : make_int4(-1, 0, 0, 0);
+                S->task[slot] = task;
+                mbar_arrive(&S->task_full[slot]);
+                if (task.x < 0) break;
+                const int4 win = windows[task.y];
+                const int e = win.x, row0 = win.y;
+                const bool is_l2 = task.x == 1;
+                if (is_l2) {  // every L1 tile of this window must have landed in ffn
+                    if (!spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= l1_need; }, wait_ns, abort_flag)) {
+                        raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
+                    }
+                }
+                fence_proxy_async_global();  // pool / ffn rows were written with ordinary stores
+                const CUtensorMap* ma = is_l2 ? &tm_ffn : &tm_pool;
+                const CUtensorMap* mb = is_l2 ? &tm_w2 : &tm_w1;
+                const int nkb = is_l2 ? kb2 : kb1;
+                const int brow0 = is_l2 ? e * a.H + task.z * kBlockN : e * 2 * a.I + task.z * 128;
+                const int brow1 = is_l2 ? brow0 + 128 : brow0 + a.I;
+                bool dead = false;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(&S->empty[stage], phase ^ 1, wait_ns, abort_flag)) { dead = true; break; }
+                    uint8_t* sa = tiles + stage * kStageBytes;
+                    mbar_expect_tx(&S->full[stage], kStageBytes);
+                    tma_load_2d(sa, ma, kb * kBlockK, row0, &S->full[stage]);
+                    tma_load_2d(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[stage]);
+                    tma_load_2d(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[stage]);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; break; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, sfg = 0;
+            for (uint32_t it = 0;; ++it) {
+                const uint32_t slot = it % kTaskRing;
+                if (!mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag)) {
+                    raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break;
+                }
+                const int4 task = S->task[slot];
+                mbar_arrive(&S->task_empty[slot]);
+                if (task.x < 0) break;
+                const int nkb = task.x == 1 ? kb2 : kb1;
+                // the epilogue must have drained the previous task's accumulators
+                bool dead = !mbar_wait(&S->tmem_empty, (it & 1) ^ 1, wait_ns, abort_flag);
+                uint32_t sf_slot = 0, tsf = 0;
+                for (int kb = 0; kb < nkb && !dead; ++kb) {
+                    if ((kb & 3) == 0) {  // a new group of four K blocks: stage its scale tiles in TMEM
+                        sf_slot = sfg % kSfRing;
+                        if (!mbar_wait(&S->sf_full[sf_slot], (sfg / kSfRing) & 1, wait_ns, abort_flag)) { dead = true; break; }
+                        tc_fence_after();
+                        tsf = tmem_base + kTmemSfCol + (sfg & 1) * 16;
+                        const uint32_t ssf = smem_u32(sf_tiles + sf_slot * kSfSlotBytes);
+                        utccp_32x128b_warpx4(tsf, umma_smem_desc_sf(ssf));             // activation rows
+                        utccp_32x128b_warpx4(tsf + 4, umma_smem_desc_sf(ssf + 512));   // weight rows 0..127
+                        utccp_32x128b_warpx4(tsf + 8, umma_smem_desc_sf(ssf + 1024));  // weight rows 128..255
+                    }
+                    if (!mbar_wait(&S->full[stage], phase, wait_ns, abort_flag)) { dead = true; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
+                    const uint64_t adesc = umma_smem_desc_sw128(sa);
+                    const uint64_t bdesc = umma_smem_desc_sw128(sa + kABytes);
+                    const uint32_t idesc = umma_idesc_mx_e4m3(kBlockM, kBlockN, kb & 3, kb & 3);
+#pragma unroll
+                    for (int k4 = 0; k4 < kBlockK / 32; ++k4)
+                        umma_mxf8(tmem_base, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, tsf, tsf + 4,
+                                  (kb > 0 || k4 > 0) ? 1u : 0u);
+                    umma_commit(&S->empty[stage]);  // stage reusable once these MMAs retire
+                    if ((kb & 3) == 3 || kb == nkb - 1) { umma_commit(&S->sf_empty[sf_slot]); ++sfg; }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; break; }
+                umma_commit(&S->tmem_full);  // accumulators complete
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------ scale-tile builder
+        // Slot layout (what UTCCP 32x128b.warpx4 expects): tile byte 16*l + 4*j + i is the
+        // scale of row l + 32*j for K block i of the group.  The two weight tiles repeat one
+        // 4-byte word (a 128x128 block has one scale per K block).
+        const uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
+        const uint8_t* ffn_sf = a.rwk + a.L.ffn_sf_off;
+        uint32_t sfg = 0;
+        for (uint32_t it = 0;; ++it) {
+            const uint32_t slot = it % kTaskRing;
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag);
+            ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+            if (!ok) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; } break; }
+            const int4 task = S->task[slot];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S->task_empty[slot]);
+            if (task.x < 0) break;
+            const int4 win = windows[task.y];
+            const int e = win.x, row0 = win.y, rows = task.w;
+            const bool is_l2 = task.x == 1;
+            const int nkb = is_l2 ? kb2 : kb1;
+            const uint8_t* asf = nullptr;   // activation scale rows of this window
+            int asf_stride = 0;
+            const uint8_t* wsf0 = nullptr;
+            const uint8_t* wsf1 = nullptr;
+            if (a.scaled) {
+                if (is_l2) {
+                    // ffn scales are written by L1 epilogues of this same kernel
+                    bool ready = true;
+                    if (lane == 0) ready = spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= l1_need; }, wait_ns, abort_flag);
+                    ready = __shfl_sync(0xFFFFFFFFu, ready ? 1 : 0, 0) != 0;
+                    if (!ready) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; } break; }
+                    asf = ffn_sf + (size_t)row0 * a.L.sf_stride_i;
+                    asf_stride = a.L.sf_stride_i;
+                    wsf0 = a.w2_sf + ((size_t)e * (a.H / 128) + task.z * 2) * nkb;
+                    wsf1 = wsf0 + nkb;
+                } else {
+                    asf = pool_sf + (size_t)row0 * a.L.sf_stride_h;
+                    asf_stride = a.L.sf_stride_h;
+                    wsf0 = a.w1_sf + ((size_t)e * (2 * a.I / 128) + task.z) * nkb;
+                    wsf1 = wsf0 + (size_t)nt1 * nkb;
+                }
+            }
+            bool dead = false;
+            for (int g = 0; g * 4 < nkb; ++g, ++sfg) {
+                const uint32_t sslot = sfg % kSfRing;
+                bool free_ = true;
+                if (lane == 0) free_ = mbar_wait(&S->sf_empty[sslot], ((sfg / kSfRing) & 1) ^ 1, wait_ns, abort_flag);
+                free_ = __shfl_sync(0xFFFFFFFFu, free_ ? 1 : 0, 0) != 0;
+                if (!free_) { dead = true; break; }
+                uint4 va = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+                uint32_t w0 = 0x7F7F7F7Fu, w1 = 0x7F7F7F7Fu;
+                if (a.scaled) {
+                    uint32_t wa[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int r = lane + 32 * j;
+                        wa[j] = r < rows ? __ldcg(reinterpret_cast<const uint32_t*>(asf + (size_t)r * asf_stride) + g) : 0x7F7F7F7Fu;
+                    }
+                    va = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+                    w0 = 0; w1 = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int kb = g * 4 + i;
+                        const uint32_t b0 = kb < nkb ? __ldg(wsf0 + kb) : 127u;
+                        const uint32_t b1 = kb < nkb ? __ldg(wsf1 + kb) : 127u;
+                        w0 |= b0 << (8 * i);
+                        w1 |= b1 << (8 * i);
+                    }
+                }
+                uint4* dst = reinterpret_cast<uint4*>(sf_tiles + sslot * kSfSlotBytes);
+                dst[lane] = va;
+                dst[32 + lane] = make_uint4(w0, w0, w0, w0);
+                dst[64 + lane] = make_uint4(w1, w1, w1, w1);
+                fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor-core copy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&S->sf_full[sslot]);
+            }
+            if (dead) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; } break; }
+        }
+    } else if (warp >= kFirstEpiWarp) {
+        // ------------------------------------------------------------- epilogue
+        const int q = warp & 3, half = (warp - kFirstEpiWarp) >> 2;
+        const int r = q * 32 + lane;  // row inside the window
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        uint8_t* ffn = a.rwk + a.L.ffn_off;
+        uint8_t* ffn_sf = a.rwk + a.L.ffn_sf_off;
+        const int4* meta = reinterpret_cast<const int4*>(a.rwk + a.L.row_meta_off);
+        for (uint32_t it = 0;; ++it) {
+            const uint32_t slot = it % kTaskRing;
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag);
+            ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+            if (!ok) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; } break; }
+            const int4 task = S->task[slot];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S->task_empty[slot]);
+            if (task.x < 0) break;
+            const int4 win = windows[task.y];
+            const int row0 = win.y, rows = task.w;
+            const bool is_l2 = task.x == 1;
+            const bool warp_active = q * 32 < rows;
+            const bool row_valid = r < rows;
+
+            bool got = true;
+            if (lane == 0) got = mbar_wait(&S->tmem_full, it & 1, wait_ns, abort_flag);
+            got = __shfl_sync(0xFFFFFFFFu, got ? 1 : 0, 0) != 0;
+            if (!got) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; } break; }
+            tc_fence_after();
+            // drain this warp's share of the accumulators into registers, then release TMEM
+            uint32_t vg[64], vu[64];
+            if (warp_active) {
+                const uint32_t t0 = lane_addr + half * 64;
+                tmem_ld32(t0, *reinterpret_cast<uint32_t(*)[32]>(&vg[0]));
+                tmem_ld32(t0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&vg[32]));
+                tmem_ld32(t0 + 128, *reinterpret_cast<uint32_t(*)[32]>(&vu[0]));
+                tmem_ld32(t0 + 160, *reinterpret_cast<uint32_t(*)[32]>(&vu[32]));
+                tmem_wait_ld();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S->tmem_empty);
+
+            if (!is_l2) {
+                // ---- SwiGLU + per-row 1x128 requantisation to E4M3 -> ffn
+                if (warp_active) {
+                    float amax = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) {
+                        const float g = __uint_as_float(vg[j]);
+                        const float hv = (g / (1.0f + expf(-g))) * __uint_as_float(vu[j]);  // silu(g)*u (src/compute.cuh:242-244)
+                        vg[j] = __float_as_uint(hv);
+                        amax = fmaxf(amax, fabsf(hv));
+                    }
+                    float inv = 1.0f;
+                    uint32_t ex = 127;
+                    if (a.scaled) {
+                        // the other column half of this row lives in warp +-4: swap partial maxima
+                        const uint32_t tag = it + 1;
+                        volatile unsigned long long* mine = &S->xch[it & 1][half][r];
+                        volatile unsigned long long* theirs = &S->xch[it & 1][half ^ 1][r];
+                        *mine = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(amax);
+                        unsigned long long o = 0;
+                        const bool gotx = spin_until([&] { o = *theirs; return (uint32_t)(o >> 32) == tag; }, wait_ns, abort_flag);
+                        if (!gotx) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; }
+                        amax = fmaxf(amax, __uint_as_float((uint32_t)o));
+                        const float s = fmaxf(amax, 1e-4f) / 448.0f;  // per_token_cast_to_fp8, utils/math.py:33-35
+                        const uint32_t bits = __float_as_uint(s);
+                        ex = ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) ? 1u : 0u);
+                        ex = min(254u, max(1u, ex));
+                        inv = __uint_as_float((254u - ex) << 23);
+                    }
+                    if (row_valid) {
+                        uint4* dst = reinterpret_cast<uint4*>(ffn + (size_t)(row0 + r) * a.I + task.z * 128 + half * 64);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint4 o;
+                            o.x = pack_e4m3x4(__uint_as_float(vg[c * 16 + 0]) * inv, __uint_as_float(vg[c * 16 + 1]) * inv,
+                                              __uint_as_float(vg[c * 16 + 2]) * inv, __uint_as_float(vg[c * 16 + 3]) * inv);
+                            o.y = pack_e4m3x4(__uint_as_float(vg[c * 16 + 4]) * inv, __uint_as_float(vg[c * 16 + 5]) * inv,
+                                              __uint_as_float(vg[c * 16 + 6]) * inv, __uint_as_float(vg[c * 16 + 7]) * inv);
+                            o.z = pack_e4m3x4(__uint_as_float(vg[c * 16 + 8]) * inv, __uint_as_float(vg[c * 16 + 9]) * inv,
+                                              __uint_as_float(vg[c * 16 + 10]) * inv, __uint_as_float(vg[c * 16 + 11]) * inv);
+                            o.w = pack_e4m3x4(__uint_as_float(vg[c * 16 + 12]) * inv, __uint_as_float(vg[c * 16 + 13]) * inv,
+                                              __uint_as_float(vg[c * 16 + 14]) * inv, __uint_as_float(vg[c * 16 + 15]) * inv);
+                            dst[c] = o;
+                        }
+                        if (a.scaled && half == 0) ffn_sf[(size_t)(row0 + r) * a.L.sf_stride_i + task.z] = (uint8_t)ex;
+                    }
+                }
+                // publish: this warp's share of the tile is in global memory
+                fence_proxy_async_global();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) red_release_gpu_add(l1_done + task.y, 1u);
+            } else {
+                // ---- bf16 rows pushed to the source rank + per-pair arrival count
+                if (row_valid && !a.skip_combine) {
+                    const int4 m = meta[row0 + r];  // src, token, k, weight
+                    uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[m.x]);
+                    uint16_t* crow = reinterpret_cast<uint16_t*>(peer_unk + a.L.combine_rows_off) +
+                                     ((size_t)m.z * a.cap + m.y) * a.H + task.z * kBlockN + half * 64;
+                    uint4* d0 = reinterpret_cast<uint4*>(crow);
+                    uint4* d1 = reinterpret_cast<uint4*>(crow + 128);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        uint4 o;
+                        o.x = pack_bf16x2(__uint_as_float(vg[c * 8 + 0]), __uint_as_float(vg[c * 8 + 1]));
+                        o.y = pack_bf16x2(__uint_as_float(vg[c * 8 + 2]), __uint_as_float(vg[c * 8 + 3]));
+                        o.z = pack_bf16x2(__uint_as_float(vg[c * 8 + 4]), __uint_as_float(vg[c * 8 + 5]));
+                        o.w = pack_bf16x2(__uint_as_float(vg[c * 8 + 6]), __uint_as_float(vg[c * 8 + 7]));
+                        d0[c] = o;
+                        o.x = pack_bf16x2(__uint_as_float(vu[c * 8 + 0]), __uint_as_float(vu[c * 8 + 1]));
+                        o.y = pack_bf16x2(__uint_as_float(vu[c * 8 + 2]), __uint_as_float(vu[c * 8 + 3]));
+                        o.z = pack_bf16x2(__uint_as_float(vu[c * 8 + 4]), __uint_as_float(vu[c * 8 + 5]));
+                        o.w = pack_bf16x2(__uint_as_float(vu[c * 8 + 6]), __uint_as_float(vu[c * 8 + 7]));
+                        d1[c] = o;
+                    }
+                    __threadfence_system();
+                    uint32_t* cnt = reinterpret_cast<uint32_t*>(peer_unk + a.L.combine_cnt_off) + (size_t)m.z * a.cap + m.y;
+                    red_release_sys_add(cnt, 1u);
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------ teardown
+    if (*abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}

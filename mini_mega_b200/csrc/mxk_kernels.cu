@@ -41,15 +41,6 @@ using namespace mxk;
 constexpr int kBlockM = 128;          // rows of a window = UMMA M
 constexpr int kBlockK = 128;          // bytes of K per pipeline stage = scale block
 constexpr int kBlockN = 256;          // weight rows per task = UMMA N (two 128-row halves)
-constexpr int kStages = 4;
-constexpr int kABytes = kBlockM * kBlockK;           // 16 KB
-constexpr int kBBytes = kBlockN * kBlockK;           // 32 KB
-constexpr int kStageBytes = kABytes + kBBytes;       // 48 KB
-constexpr int kTaskRing = 4;
-constexpr int kGemmThreads = 320;     // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
-constexpr int kEpiWarps = 8;
-constexpr int kTmemCols = 512;        // two accumulator buffers of 256 columns
-constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align*/ + 8192 /*control*/;
 constexpr uint64_t kDefaultLocalWaitNs = 2000000000ull;    // 2 s
 constexpr uint64_t kDefaultRemoteWaitNs = 20000000000ull;  // 20 s
 
@@ -344,327 +335,7 @@ __global__ void __launch_bounds__(256) k_dispatch(const KArgs a) {
 }
 
 // ============================================================== k_gemm ========
-struct GemmSmem {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
-    uint64_t tmem_full[2];
-    uint64_t tmem_empty[2];
-    uint64_t task_full[kTaskRing];
-    uint64_t task_empty[kTaskRing];
-    int4 task[kTaskRing];
-    unsigned long long xch[2][2][128];  // amax exchange between the two column halves
-    uint32_t tmem_base;
-    int abort_flag;
-};
-
-__global__ void __launch_bounds__(kGemmThreads, 1)
-k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_constant__ CUtensorMap tm_ffn,
-       const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    GemmSmem* S = reinterpret_cast<GemmSmem*>(tiles + kStages * kStageBytes);
-    DevFlags* f = flags_of(a);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    volatile int* abort_flag = &S->abort_flag;
-    const uint64_t wait_ns = a.local_wait_ns;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&S->full[s], 1); mbar_init(&S->empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&S->tmem_full[b], 1); mbar_init(&S->tmem_empty[b], kEpiWarps); }
-        for (int s = 0; s < kTaskRing; ++s) { mbar_init(&S->task_full[s], 1); mbar_init(&S->task_empty[s], 1 + kEpiWarps); }
-        S->abort_flag = 0;
-        mbar_fence_init();
-        fence_proxy_async_smem();
-    }
-    for (int i = threadIdx.x; i < 2 * 2 * 128; i += blockDim.x) (&S->xch[0][0][0])[i] = 0ull;
-    if (warp == 1) {
-        tmem_alloc(&S->tmem_base, kTmemCols);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = S->tmem_base;
-
-    const int n_tasks = f->n_tasks;
-    const int4* tasks = reinterpret_cast<const int4*>(a.rwk + a.L.tasks_off);
-    const int4* windows = reinterpret_cast<const int4*>(a.rwk + a.L.windows_off);
-    uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
-    const int kb1 = a.H / kBlockK, kb2 = a.I / kBlockK;
-    const int nt1 = a.I / 128;
-
-    if (warp == 0) {
-        // ------------------------------------------------ scheduler + TMA producer
-        if (lane == 0) {
-            tma_prefetch_desc(&tm_pool); tma_prefetch_desc(&tm_ffn);
-            tma_prefetch_desc(&tm_w1); tma_prefetch_desc(&tm_w2);
-            uint32_t stage = 0, phase = 0;
-            for (uint32_t it = 0;; ++it) {
-                const uint32_t slot = it % kTaskRing;
-                if (!mbar_wait(&S->task_empty[slot], ((it / kTaskRing) & 1) ^ 1, wait_ns, abort_flag)) {
-                    raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break;
-                }
-                const int t = it == 0 ? (int)blockIdx.x : (int)atomicAdd(&f->task_counter, 1u);
-                const int4 task = t < n_tasks ? tasks[t] : make_int4(-1, 0, 0, 0);
-                S->task[slot] = task;
-                mbar_arrive(&S->task_full[slot]);
-                if (task.x < 0) break;
-                const int4 win = windows[task.y];
-                const int e = win.x, row0 = win.y;
-                const bool is_l2 = task.x == 1;
-                if (is_l2) {  // every L1 tile of this window must have landed in ffn
-                    const uint32_t need = (uint32_t)nt1 * kEpiWarps;
-                    if (!spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= need; }, wait_ns, abort_flag)) {
-                        raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
-                    }
-                }
-                fence_proxy_async_global();  // pool / ffn rows were written with ordinary stores
-                const CUtensorMap* ma = is_l2 ? &tm_ffn : &tm_pool;
-                const CUtensorMap* mb = is_l2 ? &tm_w2 : &tm_w1;
-                const int nkb = is_l2 ? kb2 : kb1;
-                const int brow0 = is_l2 ? e * a.H + task.z * kBlockN : e * 2 * a.I + task.z * 128;
-                const int brow1 = is_l2 ? brow0 + 128 : brow0 + a.I;
-                bool dead = false;
-                for (int kb = 0; kb < nkb; ++kb) {
-                    if (!mbar_wait(&S->empty[stage], phase ^ 1, wait_ns, abort_flag)) { dead = true; break; }
-                    uint8_t* sa = tiles + stage * kStageBytes;
-                    mbar_expect_tx(&S->full[stage], kStageBytes);
-                    tma_load_2d(sa, ma, kb * kBlockK, row0, &S->full[stage]);
-                    tma_load_2d(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[stage]);
-                    tma_load_2d(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[stage]);
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
-                }
-                if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; break; }
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc_e4m3(kBlockM, kBlockN);
-            uint32_t stage = 0, phase = 0, acc_it = 0;
-            for (uint32_t it = 0;; ++it) {
-                const uint32_t slot = it % kTaskRing;
-                if (!mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag)) {
-                    raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break;
-                }
-                const int4 task = S->task[slot];
-                mbar_arrive(&S->task_empty[slot]);
-                if (task.x < 0) break;
-                const int nkb = task.x == 1 ? kb2 : kb1;
-                bool dead = false;
-                for (int kb = 0; kb < nkb; ++kb, ++acc_it) {
-                    const uint32_t buf = acc_it & 1;
-                    if (!mbar_wait(&S->tmem_empty[buf], ((acc_it >> 1) & 1) ^ 1, wait_ns, abort_flag) ||
-                        !mbar_wait(&S->full[stage], phase, wait_ns, abort_flag)) { dead = true; break; }
-                    tc_fence_after();
-                    const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
-                    const uint64_t adesc = umma_smem_desc_sw128(sa);
-                    const uint64_t bdesc = umma_smem_desc_sw128(sa + kABytes);
-                    const uint32_t d = tmem_base + buf * kBlockN;
-#pragma unroll
-                    for (int k4 = 0; k4 < kBlockK / 32; ++k4)
-                        umma_f8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, k4 > 0 ? 1u : 0u);
-                    umma_commit(&S->empty[stage]);      // stage reusable once these MMAs retire
-                    umma_commit(&S->tmem_full[buf]);    // K-block partial sums ready for promotion
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
-                }
-                if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; break; }
-            }
-        }
-    } else {
-        // ------------------------------------------------------------- epilogue
-        // Warp w owns TMEM lanes 32*(w%4).. (rows of the window) and column half
-        // h = (w-2)/4: columns [64h,64h+64) of each 128-column accumulator half.
-        const int q = warp & 3, half = (warp - 2) >> 2;
-        const int r = q * 32 + lane;  // row inside the window
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-        uint32_t acc_it = 0;
-        const uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
-        uint8_t* ffn = a.rwk + a.L.ffn_off;
-        uint8_t* ffn_sf = a.rwk + a.L.ffn_sf_off;
-        const int4* meta = reinterpret_cast<const int4*>(a.rwk + a.L.row_meta_off);
-        for (uint32_t it = 0;; ++it) {
-            const uint32_t slot = it % kTaskRing;
-            bool ok = true;
-            if (lane == 0) ok = mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag);
-            ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
-            if (!ok) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; } break; }
-            const int4 task = S->task[slot];
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&S->task_empty[slot]);
-            if (task.x < 0) break;
-            const int4 win = windows[task.y];
-            const int e = win.x, row0 = win.y, rows = task.w;
-            const bool is_l2 = task.x == 1;
-            const int nkb = is_l2 ? kb2 : kb1;
-            const bool warp_active = q * 32 < rows;
-            const bool row_valid = r < rows;
-            // scale planes: activation scale per (row, K block); weight scale per
-            // (128-row block, K block) for each of the two accumulator halves
-            const uint8_t* sa_ptr = nullptr;
-            const uint8_t* sb0_ptr = nullptr;
-            const uint8_t* sb1_ptr = nullptr;
-            if (a.scaled) {
-                if (is_l2) {
-                    sa_ptr = ffn_sf + (size_t)(row0 + (row_valid ? r : 0)) * a.L.sf_stride_i;
-                    const uint8_t* wsf = a.w2_sf + ((size_t)e * (a.H / 128) + task.z * 2) * nkb;
-                    sb0_ptr = wsf;
-                    sb1_ptr = wsf + nkb;
-                } else {
-                    sa_ptr = pool_sf + (size_t)(row0 + (row_valid ? r : 0)) * a.L.sf_stride_h;
-                    const uint8_t* wsf = a.w1_sf + (size_t)e * (2 * a.I / 128) * nkb;
-                    sb0_ptr = wsf + (size_t)task.z * nkb;
-                    sb1_ptr = wsf + (size_t)(nt1 + task.z) * nkb;
-                }
-            }
-            float accG[64], accU[64];
-#pragma unroll
-            for (int j = 0; j < 64; ++j) { accG[j] = 0.0f; accU[j] = 0.0f; }
-            bool dead = false;
-            // Activation scale of the next K block, fetched one block ahead.  Pool scales
-            // come from an earlier kernel; ffn scales are produced inside this kernel, so
-            // for an L2 task the first fetch must follow the first accumulator barrier
-            // (the producer has then seen every L1 tile of the window complete).
-            uint32_t e_next = 127;
-            if (a.scaled && !is_l2) e_next = __ldcg(sa_ptr);
-            for (int kb = 0; kb < nkb; ++kb, ++acc_it) {
-                const uint32_t buf = acc_it & 1;
-                float sb0 = 1.0f, sb1 = 1.0f;
-                if (a.scaled) {
-                    sb0 = ue8m0_f32(__ldg(sb0_ptr + kb));
-                    sb1 = ue8m0_f32(__ldg(sb1_ptr + kb));
-                }
-                bool got = true;
-                if (lane == 0) got = mbar_wait(&S->tmem_full[buf], (acc_it >> 1) & 1, wait_ns, abort_flag);
-                got = __shfl_sync(0xFFFFFFFFu, got ? 1 : 0, 0) != 0;
-                if (!got) { dead = true; break; }
-                tc_fence_after();
-                float sg = 1.0f, su = 1.0f;
-                if (a.scaled) {
-                    if (is_l2 && kb == 0) e_next = __ldcg(sa_ptr);
-                    const float sa = ue8m0_f32(e_next);
-                    if (kb + 1 < nkb) e_next = __ldcg(sa_ptr + kb + 1);
-                    sg = sa * sb0;
-                    su = sa * sb1;
-                }
-                if (warp_active) {
-                    const uint32_t t0 = lane_addr + buf * kBlockN + half * 64;
-                    uint32_t v[32];
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        tmem_ld32(t0 + c * 32, v);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) accG[c * 32 + j] = fmaf(__uint_as_float(v[j]), sg, accG[c * 32 + j]);
-                    }
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        tmem_ld32(t0 + 128 + c * 32, v);
-                        tmem_wait_ld();
-                        if (c == 1) {  // all reads of this buffer are done: hand it back to the MMA warp
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&S->tmem_empty[buf]);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) accU[c * 32 + j] = fmaf(__uint_as_float(v[j]), su, accU[c * 32 + j]);
-                    }
-                } else {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&S->tmem_empty[buf]);
-                }
-            }
-            if (dead) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; } break; }
-
-            if (!is_l2) {
-                // ---- SwiGLU + per-row 1x128 requantisation to E4M3 -> ffn
-                if (warp_active) {
-                    float amax = 0.0f;
-#pragma unroll
-                    for (int j = 0; j < 64; ++j) {
-                        const float g = accG[j];
-                        const float hv = (g / (1.0f + expf(-g))) * accU[j];  // silu(g)*u (src/compute.cuh:242-244)
-                        accG[j] = hv;
-                        amax = fmaxf(amax, fabsf(hv));
-                    }
-                    float inv = 1.0f;
-                    uint32_t ex = 127;
-                    if (a.scaled) {
-                        // the other column half of this row lives in warp +-4: swap partial maxima
-                        const uint32_t tag = it + 1;
-                        volatile unsigned long long* mine = &S->xch[it & 1][half][r];
-                        volatile unsigned long long* theirs = &S->xch[it & 1][half ^ 1][r];
-                        *mine = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(amax);
-                        unsigned long long o = 0;
-                        const bool got = spin_until([&] { o = *theirs; return (uint32_t)(o >> 32) == tag; }, wait_ns, abort_flag);
-                        if (!got) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; }
-                        amax = fmaxf(amax, __uint_as_float((uint32_t)o));
-                        const float s = fmaxf(amax, 1e-4f) / 448.0f;  // per_token_cast_to_fp8, utils/math.py:33-35
-                        const uint32_t bits = __float_as_uint(s);
-                        ex = ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) ? 1u : 0u);
-                        ex = min(254u, max(1u, ex));
-                        inv = __uint_as_float((254u - ex) << 23);
-                    }
-                    if (row_valid) {
-                        uint4* dst = reinterpret_cast<uint4*>(ffn + (size_t)(row0 + r) * a.I + task.z * 128 + half * 64);
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            uint4 o;
-                            o.x = pack_e4m3x4(accG[c * 16 + 0] * inv, accG[c * 16 + 1] * inv, accG[c * 16 + 2] * inv, accG[c * 16 + 3] * inv);
-                            o.y = pack_e4m3x4(accG[c * 16 + 4] * inv, accG[c * 16 + 5] * inv, accG[c * 16 + 6] * inv, accG[c * 16 + 7] * inv);
-                            o.z = pack_e4m3x4(accG[c * 16 + 8] * inv, accG[c * 16 + 9] * inv, accG[c * 16 + 10] * inv, accG[c * 16 + 11] * inv);
-                            o.w = pack_e4m3x4(accG[c * 16 + 12] * inv, accG[c * 16 + 13] * inv, accG[c * 16 + 14] * inv, accG[c * 16 + 15] * inv);
-                            dst[c] = o;
-                        }
-                        if (a.scaled && half == 0) ffn_sf[(size_t)(row0 + r) * a.L.sf_stride_i + task.z] = (uint8_t)ex;
-                    }
-                }
-                // publish: this warp's share of the tile is in global memory
-                fence_proxy_async_global();
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) red_release_gpu_add(l1_done + task.y, 1u);
-            } else {
-                // ---- bf16 rows pushed to the source rank + per-pair arrival count
-                if (row_valid && !a.skip_combine) {
-                    const int4 m = meta[row0 + r];  // src, token, k, weight
-                    uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[m.x]);
-                    uint16_t* crow = reinterpret_cast<uint16_t*>(peer_unk + a.L.combine_rows_off) +
-                                     ((size_t)m.z * a.cap + m.y) * a.H + task.z * kBlockN + half * 64;
-                    uint4* d0 = reinterpret_cast<uint4*>(crow);
-                    uint4* d1 = reinterpret_cast<uint4*>(crow + 128);
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        uint4 o;
-                        o.x = pack_bf16x2(accG[c * 8 + 0], accG[c * 8 + 1]);
-                        o.y = pack_bf16x2(accG[c * 8 + 2], accG[c * 8 + 3]);
-                        o.z = pack_bf16x2(accG[c * 8 + 4], accG[c * 8 + 5]);
-                        o.w = pack_bf16x2(accG[c * 8 + 6], accG[c * 8 + 7]);
-                        d0[c] = o;
-                        o.x = pack_bf16x2(accU[c * 8 + 0], accU[c * 8 + 1]);
-                        o.y = pack_bf16x2(accU[c * 8 + 2], accU[c * 8 + 3]);
-                        o.z = pack_bf16x2(accU[c * 8 + 4], accU[c * 8 + 5]);
-                        o.w = pack_bf16x2(accU[c * 8 + 6], accU[c * 8 + 7]);
-                        d1[c] = o;
-                    }
-                    __threadfence_system();
-                    uint32_t* cnt = reinterpret_cast<uint32_t*>(peer_unk + a.L.combine_cnt_off) + (size_t)m.z * a.cap + m.y;
-                    red_release_sys_add(cnt, 1u);
-                }
-            }
-        }
-    }
-
-    // ------------------------------------------------------------------ teardown
-    if (*abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        __syncwarp();
-        tmem_dealloc(tmem_base, kTmemCols);
-    }
-}
+#include "mxk_gemm.cuh"
 
 // ============================================================== k_reduce ======
 // y[t] = sum over k (ascending, FP32, product then sum) of w_k * bf16 row_k
