@@ -1,0 +1,120 @@
+"""Worker of the multi-process tests (one process per rank).
+
+mode "gpu":  real expert-parallel layer over NCCL-bootstrapped IPC buffers, one GPU per rank;
+             three launches on the same buffers with different inputs (exercises the epoch-parity
+             tables, counter reset and ragged / empty ranks); y checked against the oracle.
+mode "gloo": CPU ranks: each rank derives its own routing share, ranks exchange them like the
+             device scatter does, and the assembled tables must equal the whole-world oracle.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from oracle import oracle as orc  # noqa: E402
+
+
+def cases(R):
+    return [
+        orc.gen_case(R, 4, 4, 1024, 512, [24 + 3 * r for r in range(R)], seed=21, routing="uniform", scaled=True, cap=48),
+        orc.gen_case(R, 4, 4, 1024, 512, [0 if r == R - 1 else 9 + r for r in range(R)], seed=22, routing="zipf",
+                     scaled=True, cap=48),
+        orc.gen_case(R, 4, 4, 1024, 512, [48] * R, seed=23, routing="uniform", scaled=True, cap=48, invalid_frac=0.1),
+    ]
+
+
+def run_gpu():
+    import mini_mega_b200 as mm
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    group = dist.group.WORLD
+    buf = None
+    worst = 0.0
+    for ci, case in enumerate(cases(world)):
+        if buf is None:
+            buf = mm.get_symm_buffer_for_mega_moe(group, case.E, case.cap, case.topk, case.H, case.I)
+        T = case.tokens[rank]
+        buf.x.view(torch.uint8).copy_(torch.from_numpy(case.x[rank]))
+        buf.x_sf.copy_(torch.from_numpy(case.x_sf[rank]))
+        buf.topk_idx.copy_(torch.from_numpy(case.topk_idx[rank]))
+        buf.topk_weights.copy_(torch.from_numpy(case.topk_w[rank]))
+        sl = slice(rank * case.EPR, (rank + 1) * case.EPR)
+        l1, l2 = mm.transform_weights_for_mega_moe(
+            (torch.from_numpy(case.w1[sl]).cuda(), torch.from_numpy(case.w1_sf[sl]).cuda()),
+            (torch.from_numpy(case.w2[sl]).cuda(), torch.from_numpy(case.w2_sf[sl]).cuda()))
+        y = torch.zeros((T, case.H), dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+        dist.barrier()
+        mm.fp8_mega_moe(y, l1, l2, buf)
+        torch.cuda.synchronize()
+        st = buf.status()
+        assert st.status == 0, f"rank {rank} case {ci}: device status {st.status} dbg {list(st.dbg)}"
+        ref = orc.layer_world(case)
+        # integer tables of this rank: bit-exact
+        par = int(st.launches & 1)
+        s = ref[rank]
+        assert np.array_equal(buf.table("route_slot_counts").cpu().numpy(), s.route_slot_counts)
+        assert np.array_equal(buf.table("prefix_tbl").cpu().numpy(), s.prefix_tbl)
+        tbl = buf.table("src_index_table")[par].cpu().numpy().astype(np.uint32)
+        for le in range(case.EPR):     # rows are defined up to their count; later slots keep older launches
+            for src in range(world):
+                n = int(s.prefix_tbl[le, src + 1] - s.prefix_tbl[le, src])
+                assert np.array_equal(tbl[le, src, :n], s.src_index_table[le, src, :n]), (ci, le, src)
+        rows = s.meta.shape[0]
+        assert np.array_equal(buf.table("row_meta")[:rows, :3].cpu().numpy(), s.meta)
+        assert np.array_equal(buf.table("pool")[:rows].cpu().numpy(), s.pool)
+        if T:
+            err = orc.rel_l2(y.float().cpu().numpy(), ref[rank].y)
+            worst = max(worst, err)
+            assert err <= 1e-2, f"rank {rank} case {ci}: relative L2 {err}"
+        dist.barrier()
+    buf.destroy()
+    print(f"MP_OK rank={rank} worst_rel_l2={worst:.3e}", flush=True)
+    dist.destroy_process_group()
+
+
+def run_gloo():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo")
+    case = cases(world)[0]
+    want = orc.route_world(case)
+    # this rank's routing share: counts per global expert and the ordered pair list per expert
+    E, EPR, topk, cap = case.E, case.EPR, case.topk, case.cap
+    idx = case.topk_idx[rank, : case.tokens[rank]].reshape(-1)
+    counts = np.zeros(E, np.int64)
+    rows = [[] for _ in range(E)]
+    for p, e in enumerate(idx):
+        if 0 <= e < E and counts[e] < cap:
+            rows[e].append(p)
+            counts[e] += 1
+    assert np.array_equal(counts.astype(np.int32), want[rank].route_slot_counts)
+    # "scatter": every rank publishes its rows; owners assemble [le][src][slot] and the prefix table
+    gathered = [None] * world
+    dist.all_gather_object(gathered, rows)
+    tbl = np.zeros((EPR, world, cap), np.uint32)
+    prefix = np.zeros((EPR, world + 1), np.int32)
+    for le in range(EPR):
+        c = 0
+        for src in range(world):
+            r_ = gathered[src][rank * EPR + le]
+            tbl[le, src, : len(r_)] = r_
+            prefix[le, src] = c
+            c += len(r_)
+        prefix[le, world] = c
+    assert np.array_equal(tbl, want[rank].src_index_table)
+    assert np.array_equal(prefix, want[rank].prefix_tbl)
+    total = torch.tensor([int(prefix[:, world].sum())])
+    dist.all_reduce(total)
+    assert int(total) == int(sum((case.topk_idx[r, : case.tokens[r]] >= 0).sum() for r in range(world)))
+    print(f"MP_OK rank={rank}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    {"gpu": run_gpu, "gloo": run_gloo}[sys.argv[1]]()
