@@ -178,6 +178,37 @@ int mxk_kernels_per_layer(void);
 #define MXK_PHASE_REDUCE 16
 int mxk_launch_phases(const MxkLaunchArgs* a, int phase_mask, void* stream);
 
+/* Whole layer for callers that must not allocate device memory.  No counterpart in the
+ * reference (its callers always allocate rwk / unk themselves).
+ *
+ * Some hosts cannot call cudaMalloc when a layer has to run: an inference server whose
+ * memory pool already owns the whole GPU (a fresh cudaMalloc simply fails there), a
+ * plugin loaded into somebody else's runtime that forbids allocation after start-up, or
+ * code running where an allocation would synchronise the device at a bad moment.  For
+ * them this entry point keeps the two workspace blocks (unk and rwk) and the two
+ * one-entry pointer tables in a fixed array inside the library image instead of taking
+ * them from the caller.  It calls no cudaMalloc / cudaFree and no allocating library
+ * routine; every GPU that loads the library carries the array (mxk_static_scratch_bytes(),
+ * 32 MiB) from load until exit.
+ *
+ * Arguments are those of mxk_launch_full for a single-rank world (R = 1, rank = 0): the
+ * caller still passes its input block `self` (x, x_sf, topk_idx, topk_weights at the
+ * usual offsets), the weights and y / y_bf16; the fields rwk, unk, unk_peers and
+ * peer_bases are ignored.  A geometry whose workspace (256 + unk_bytes + rwk_bytes of
+ * mxk_compute_layout) exceeds the array is rejected with MXK_ERR_BAD_ARG and a message
+ * that states both sizes.
+ *
+ * The first call on a device asks the CUDA runtime for the array's device address
+ * (once per device, with that device current); make that first call outside any stream
+ * capture.  All calls share the one array and it keeps the previous call's contents: the
+ * status header and the barrier slot are cleared at the start of every call, everything
+ * else is rewritten before it is read.  Two calls that overlap on the GPU (different
+ * streams, or several threads) would race on the array: issue them on one stream or
+ * serialise them yourself.  mxk_read_status cannot be used with it; a device-side expiry
+ * shows up as wrong output only. */
+int mxk_launch_full_static(const MxkLaunchArgs* a, void* stream);
+int64_t mxk_static_scratch_bytes(void);
+
 /* Deterministic test weights, byte (seed + 131*row + 7*k) & 0x3f at logical
  * (row, k), row-major (reference: fill_weights_lane writes the same values in
  * MetaX lane order, src/megakernel.cu:66-105, src/megakernel.h:46-47). */

@@ -75,7 +75,8 @@ class MxkStatus(C.Structure):
 EXPORTS = [
     "mxk_last_error", "mxk_version", "mxk_compute_layout", "mxk_sym_bytes", "mxk_rwk_bytes", "mxk_unk_bytes",
     "mxk_launch_prelude", "mxk_launch_compute", "mxk_launch_reduce", "mxk_launch_full", "mxk_launch_empty",
-    "mxk_kernels_per_layer", "mxk_launch_phases", "mxk_fill_weights", "mxk_dump_kernel_resources", "mxk_read_status", "mxk_select_win",
+    "mxk_kernels_per_layer", "mxk_launch_phases", "mxk_launch_full_static",
+    "mxk_static_scratch_bytes", "mxk_fill_weights", "mxk_dump_kernel_resources", "mxk_read_status", "mxk_select_win",
     "mxk_symm_alloc", "mxk_symm_free", "mxk_ipc_export", "mxk_ipc_import", "mxk_ipc_close",
 ]
 
@@ -102,6 +103,8 @@ def lib():
         getattr(L, n).argtypes = [C.POINTER(MxkGeom)]
     for n in ("mxk_launch_prelude", "mxk_launch_compute", "mxk_launch_reduce", "mxk_launch_full"):
         getattr(L, n).argtypes = [C.POINTER(MxkLaunchArgs), C.c_void_p]
+    L.mxk_launch_full_static.argtypes = [C.POINTER(MxkLaunchArgs), C.c_void_p]
+    L.mxk_static_scratch_bytes.restype = C.c_int64
     L.mxk_launch_phases.argtypes = [C.POINTER(MxkLaunchArgs), C.c_int, C.c_void_p]
     L.mxk_launch_empty.argtypes = [C.c_int, C.c_int, C.c_int64, C.c_void_p]
     L.mxk_fill_weights.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_uint32, C.c_void_p]

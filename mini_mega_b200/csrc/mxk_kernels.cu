@@ -638,6 +638,37 @@ int launch_reduce_k(const KArgs& k, cudaStream_t st) {
     return e == cudaSuccess ? 0 : cuda_fail(e, "launch reduce");
 }
 
+// ------------------------------------------------------------ static scratch
+// Workspace for mxk_launch_full_static: lives in the module image, so it exists on every
+// GPU that loads this library from load until exit and never goes through an allocator.
+constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB
+constexpr size_t kStaticPtrBytes = 256;            // two pointer tables of one entry each
+constexpr int kStaticMaxDevices = 64;
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
+
+__global__ void k_static_ptrs(void** sym_table, void** unk_table, void* sym, void* unk) {
+    sym_table[0] = sym;
+    unk_table[0] = unk;
+}
+
+// Device address of g_static_scratch on the current device.  In host code the array's
+// name is only a stand-in, so the address is asked from the runtime once per device.
+int static_scratch_base(uint8_t** out) {
+    static uint8_t* base[kStaticMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= kStaticMaxDevices) return fail(MXK_ERR_BAD_ARG, "device index beyond the static scratch table");
+    if (!base[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        base[dev] = static_cast<uint8_t*>(p);
+    }
+    *out = base[dev];
+    return 0;
+}
+
 }  // namespace
 
 // ================================================================== C ABI =====
@@ -676,6 +707,54 @@ int mxk_launch_full(const MxkLaunchArgs* a, void* stream) {
     return launch_reduce_k(k, static_cast<cudaStream_t>(stream));
 }
 int mxk_kernels_per_layer(void) { return 5; }
+
+int mxk_launch_full_static(const MxkLaunchArgs* a, void* stream) {
+    if (!a) return fail(MXK_ERR_BAD_ARG, "null launch args");
+    if (a->R != 1 || a->rank != 0) return fail(MXK_ERR_BAD_ARG, "mxk_launch_full_static serves a single-rank world only (R=1)");
+    if (!a->self) return fail(MXK_ERR_BAD_ARG, "self (the input block) must be non-null");
+    MxkGeom g{};
+    g.R = 1; g.rank = 0;
+    g.experts_per_rank = a->experts_per_rank ? a->experts_per_rank : 8;
+    g.topk = a->topk ? a->topk : 8;
+    g.hidden = a->hidden ? a->hidden : 6144;
+    g.intermediate = a->intermediate ? a->intermediate : 2048;
+    g.max_tokens = a->max_tokens ? a->max_tokens : (a->slot_capacity ? a->slot_capacity : 512);
+    g.slot_capacity = a->slot_capacity;
+    MxkLayout L;
+    if (int rc = compute_layout(&g, &L)) return rc;
+    const size_t need = kStaticPtrBytes + (size_t)L.unk_bytes + (size_t)L.rwk_bytes;
+    if (need > kStaticScratchBytes)
+        return fail(MXK_ERR_BAD_ARG, "workspace of this geometry needs " + std::to_string(need) +
+                                         " bytes, the static scratch holds " + std::to_string(kStaticScratchBytes));
+    uint8_t* base = nullptr;
+    if (int rc = static_scratch_base(&base)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* unk = base + kStaticPtrBytes;
+    uint8_t* rwk = unk + L.unk_bytes;
+    // The array keeps whatever the previous call left.  What the protocol needs at zero is
+    // the status header (launch counter, status word, expiry counters) and the barrier slot.
+    cudaError_t e = cudaMemsetAsync(rwk + L.flags_off, 0, 1024, st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status header)");
+    e = cudaMemsetAsync(unk + L.xbar_off, 0, (size_t)L.xbar_stride * 4, st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(barrier slot)");
+    void** sym_table = reinterpret_cast<void**>(base);
+    void** unk_table = reinterpret_cast<void**>(base + 128);
+    k_static_ptrs<<<1, 1, 0, st>>>(sym_table, unk_table, const_cast<uint8_t*>(a->self), unk);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "launch static pointer set-up");
+    MxkLaunchArgs b = *a;
+    b.rwk = rwk;
+    b.unk = unk;
+    b.unk_peers = reinterpret_cast<void* const*>(unk_table);
+    b.peer_bases = reinterpret_cast<uint8_t* const*>(sym_table);
+    KArgs k;
+    if (int rc = build_kargs(&b, &k)) return rc;
+    if (!k.y && !k.y_bf16) return fail(MXK_ERR_BAD_ARG, "y or y_bf16 must be non-null");
+    if (int rc = launch_route_setup(k, st)) return rc;
+    if (int rc = launch_dispatch_gemm(k, st)) return rc;
+    return launch_reduce_k(k, st);
+}
+int64_t mxk_static_scratch_bytes(void) { return (int64_t)kStaticScratchBytes; }
 
 int mxk_launch_phases(const MxkLaunchArgs* a, int phase_mask, void* stream) {
     KArgs k;
