@@ -258,7 +258,7 @@ def cpu_arm(args, n_ranks):
 
 
 def workload_config(n, tokens):
-    return {"workload": f"MoE layer decode balanced: E={E_TOTAL} topk=8 H=6144 I=2048 FP8 e4m3 + UE8M0 block "
+    return {"workload": f"MoE layer balanced: E={E_TOTAL} topk=8 H={H} I=2048 FP8 e4m3 + UE8M0 block "
                         f"scales, {n * tokens} tokens in total = {tokens} tokens/rank, EP={n} "
                         f"({E_TOTAL // n} experts/GPU), uniform distinct routing",
             "tokens_per_rank": tokens, "global_tokens": n * tokens, "ep": n, "experts_per_gpu": E_TOTAL // n,
@@ -284,7 +284,7 @@ def gpu_arm(args):
         group = dist.group.WORLD
     assert args.gpus == n, f"--gpus {args.gpus} but WORLD_SIZE={n}"
     epr = E_TOTAL // n
-    cap = max(256, args.tpr)
+    cap = max(256, args.tpr) if not args.no_points else args.tpr
     lib = _lib.lib()
     buf = mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, H, I)
     l1, l2 = mm.transform_weights_for_mega_moe(*make_weights(torch, epr, rank, dev))
@@ -332,6 +332,13 @@ def gpu_arm(args):
         ms = max_over_ranks(e0.elapsed_time(e1))
         st = buf.status()
         assert st.status == 0, f"device status {st.status} dbg {list(st.dbg)}"
+        if args.ticks and rank == 0:
+            tk = list(st.ticks)
+            life = max(tk[6], 1)
+            names = ["prod_wait_stage", "prod_wait_gate", "mma_wait_tiles", "mma_wait_drain", "mma_wait_sf",
+                     "epi_wait_acc", "cta_life", "prod_wait_ring", "epi_busy"]
+            print("ticks(% of CTA lifetime): " + " ".join(f"{n}={100.0 * tk[i] / life:.1f}" for i, n in enumerate(names)),
+                  file=sys.stderr, flush=True)
         return ms / steps, all_routing(idx, tokens), y
 
     def gemm_kernel_ms(tokens, steps, warmup):
@@ -458,11 +465,15 @@ def main():
     ap.add_argument("--global-tokens", type=int, default=128, help="tokens of the whole job (split over the ranks)")
     ap.add_argument("--tpr", type=int, default=0, help="tokens per rank; overrides --global-tokens")
     ap.add_argument("--experts", type=int, default=256, help="total experts (smaller for profiling captures)")
+    ap.add_argument("--hidden", type=int, default=6144, help="H (7168 for the prefill-sized configuration)")
+    ap.add_argument("--ticks", action="store_true", help="print the GEMM kernel's wait-time breakdown to stderr")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-points", action="store_true", help="skip the 16/64/256 tokens-per-rank sweep")
     args = ap.parse_args()
-    global E_TOTAL
-    E_TOTAL = args.experts
+    if args.ticks:
+        os.environ["MXK_TICKS"] = "1"
+    global E_TOTAL, H
+    E_TOTAL, H = args.experts, args.hidden
     if args.tpr <= 0:
         args.tpr = max(1, args.global_tokens // max(1, args.gpus))
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -132,6 +132,13 @@ typedef struct MxkStatus {
     int32_t dbg[8];        /* expiry counters, slot meaning as the reference:
                               0 barrier, 2 route, 3 task queue, 4 L1->L2 gate /
                               reduce wait, 5 pipeline barrier, 6 TMEM barrier    */
+    uint64_t ticks[16];    /* SM cycles of the last layer summed over the GEMM CTAs
+                              (reference: pre_ticks readers, torch/csrc/flags_bridge.cu:44-51):
+                              0 TMA producer blocked on a free stage, 1 on the L1->L2 gate,
+                              2 MMA issuer blocked on operand tiles, 3 on the accumulator
+                              drain, 4 on scale tiles, 5 epilogue blocked on accumulators,
+                              6 CTA lifetime, 7 producer blocked on the task ring,
+                              8 epilogue busy                                         */
 } MxkStatus;
 
 #define MXK_DEV_TIMEOUT_BARRIER 1

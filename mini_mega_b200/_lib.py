@@ -68,7 +68,8 @@ class MxkLaunchArgs(C.Structure):
 
 class MxkStatus(C.Structure):
     _fields_ = [("launches", C.c_int64), ("status", C.c_int32), ("n_tasks", C.c_int32), ("n_l1_tasks", C.c_int32),
-                ("n_windows", C.c_int32), ("total_rows", C.c_int32), ("dbg", C.c_int32 * 8)]
+                ("n_windows", C.c_int32), ("total_rows", C.c_int32), ("dbg", C.c_int32 * 8),
+                ("ticks", C.c_uint64 * 16)]
 
 
 # every symbol include/mxk_b200.h declares; tests check that the library exports them

@@ -36,9 +36,16 @@ constexpr int kEpiWarps = 8;
 constexpr int kFirstEpiWarp = 4;
 constexpr int kTmemCols = 512;
 constexpr int kTmemSfCol = 256;       // scale tiles live behind the 256 accumulator columns
-constexpr int kSfRing = 4;            // shared-memory scale-tile slots (one per 4 K blocks)
+constexpr int kSfRing = 8;            // shared-memory scale-tile slots (one per 4 K blocks)
 constexpr int kSfSlotBytes = 3 * 512; // A rows, weight half 0, weight half 1
 constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align*/ + kSfRing * kSfSlotBytes + 8192 /*control*/;
+
+// Wait-time accounting (reference: clock64 phase stamps in local_flags.pre_ticks,
+// src/kernel.cuh:52-124): each role sums the cycles it spent blocked and adds them to
+// DevFlags::ticks at exit.  Slots: 0 producer/empty stage, 1 producer/L1->L2 gate, 2 MMA/full
+// stage, 3 MMA/accumulator drain, 4 MMA/scale tile, 5 epilogue/accumulators ready,
+// 6 CTA lifetime, 7 producer/task ring, 8 epilogue busy (drain to stores issued).
+#define MXK_TIMED(slot_var, expr) ([&] { if (!timed) return (expr); const long long t0_ = clock64(); const bool r_ = (expr); slot_var += clock64() - t0_; return r_; }())
 
 struct GemmSmem {
     uint64_t full[kStages];
@@ -66,6 +73,7 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &S->abort_flag;
     const uint64_t wait_ns = a.local_wait_ns;
+    const bool timed = a.ticks != 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&S->full[s], 1); mbar_init(&S->empty[s], 1); }
@@ -86,6 +94,7 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = S->tmem_base;
+    const long long t_start = clock64();
 
     const int n_tasks = f->n_tasks;
     const int4* tasks = reinterpret_cast<const int4*>(a.rwk + a.L.tasks_off);
@@ -101,9 +110,10 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
             tma_prefetch_desc(&tm_pool); tma_prefetch_desc(&tm_ffn);
             tma_prefetch_desc(&tm_w1); tma_prefetch_desc(&tm_w2);
             uint32_t stage = 0, phase = 0;
+            long long w_empty = 0, w_gate = 0, w_ring = 0;
             for (uint32_t it = 0;; ++it) {
                 const uint32_t slot = it % kTaskRing;
-                if (!mbar_wait(&S->task_empty[slot], ((it / kTaskRing) & 1) ^ 1, wait_ns, abort_flag)) {
+                if (!MXK_TIMED(w_ring, mbar_wait(&S->task_empty[slot], ((it / kTaskRing) & 1) ^ 1, wait_ns, abort_flag))) {
                     raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break;
                 }
                 const int t = it == 0 ? (int)blockIdx.x : (int)atomicAdd(&f->task_counter, 1u);
@@ -115,7 +125,7 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 const int e = win.x, row0 = win.y;
                 const bool is_l2 = task.x == 1;
                 if (is_l2) {  // every L1 tile of this window must have landed in ffn
-                    if (!spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= l1_need; }, wait_ns, abort_flag)) {
+                    if (!MXK_TIMED(w_gate, spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= l1_need; }, wait_ns, abort_flag))) {
                         raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
                     }
                 }
@@ -127,7 +137,7 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 const int brow1 = is_l2 ? brow0 + 128 : brow0 + a.I;
                 bool dead = false;
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!mbar_wait(&S->empty[stage], phase ^ 1, wait_ns, abort_flag)) { dead = true; break; }
+                    if (!MXK_TIMED(w_empty, mbar_wait(&S->empty[stage], phase ^ 1, wait_ns, abort_flag))) { dead = true; break; }
                     uint8_t* sa = tiles + stage * kStageBytes;
                     mbar_expect_tx(&S->full[stage], kStageBytes);
                     tma_load_2d(sa, ma, kb * kBlockK, row0, &S->full[stage]);
@@ -137,11 +147,15 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 }
                 if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; break; }
             }
+            atomicAdd(&f->ticks[0], (unsigned long long)w_empty);
+            atomicAdd(&f->ticks[1], (unsigned long long)w_gate);
+            atomicAdd(&f->ticks[7], (unsigned long long)w_ring);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, sfg = 0;
+            long long w_full = 0, w_drain = 0, w_sf = 0;
             for (uint32_t it = 0;; ++it) {
                 const uint32_t slot = it % kTaskRing;
                 if (!mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag)) {
@@ -152,12 +166,12 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 if (task.x < 0) break;
                 const int nkb = task.x == 1 ? kb2 : kb1;
                 // the epilogue must have drained the previous task's accumulators
-                bool dead = !mbar_wait(&S->tmem_empty, (it & 1) ^ 1, wait_ns, abort_flag);
+                bool dead = !MXK_TIMED(w_drain, mbar_wait(&S->tmem_empty, (it & 1) ^ 1, wait_ns, abort_flag));
                 uint32_t sf_slot = 0, tsf = 0;
                 for (int kb = 0; kb < nkb && !dead; ++kb) {
                     if ((kb & 3) == 0) {  // a new group of four K blocks: stage its scale tiles in TMEM
                         sf_slot = sfg % kSfRing;
-                        if (!mbar_wait(&S->sf_full[sf_slot], (sfg / kSfRing) & 1, wait_ns, abort_flag)) { dead = true; break; }
+                        if (!MXK_TIMED(w_sf, mbar_wait(&S->sf_full[sf_slot], (sfg / kSfRing) & 1, wait_ns, abort_flag))) { dead = true; break; }
                         tc_fence_after();
                         tsf = tmem_base + kTmemSfCol + (sfg & 1) * 16;
                         const uint32_t ssf = smem_u32(sf_tiles + sf_slot * kSfSlotBytes);
@@ -165,7 +179,7 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                         utccp_32x128b_warpx4(tsf + 4, umma_smem_desc_sf(ssf + 512));   // weight rows 0..127
                         utccp_32x128b_warpx4(tsf + 8, umma_smem_desc_sf(ssf + 1024));  // weight rows 128..255
                     }
-                    if (!mbar_wait(&S->full[stage], phase, wait_ns, abort_flag)) { dead = true; break; }
+                    if (!MXK_TIMED(w_full, mbar_wait(&S->full[stage], phase, wait_ns, abort_flag))) { dead = true; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
                     const uint64_t adesc = umma_smem_desc_sw128(sa);
@@ -182,6 +196,9 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                 if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; break; }
                 umma_commit(&S->tmem_full);  // accumulators complete
             }
+            atomicAdd(&f->ticks[2], (unsigned long long)w_full);
+            atomicAdd(&f->ticks[3], (unsigned long long)w_drain);
+            atomicAdd(&f->ticks[4], (unsigned long long)w_sf);
         }
     } else if (warp == 2) {
         // ------------------------------------------------------ scale-tile builder
@@ -227,40 +244,50 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                     wsf1 = wsf0 + (size_t)nt1 * nkb;
                 }
             }
+            // Per group of four K blocks: 4 activation words per lane (rows l, l+32, l+64, l+96)
+            // and one word per weight half.  The loads of group g+1 are issued before the wait
+            // for group g's slot, so their latency hides behind the ring.
+            const int ngroups = (nkb + 3) >> 2;
+            auto load_group = [&](int g, uint32_t (&wa)[4], uint32_t& w0, uint32_t& w1) {
+                wa[0] = wa[1] = wa[2] = wa[3] = 0x7F7F7F7Fu;
+                w0 = w1 = 0x7F7F7F7Fu;
+                if (!a.scaled || g >= ngroups) return;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int r = lane + 32 * j;
+                    if (r < rows) wa[j] = __ldcg(reinterpret_cast<const uint32_t*>(asf + (size_t)r * asf_stride) + g);
+                }
+                w0 = 0; w1 = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int kb = g * 4 + i;
+                    const uint32_t b0 = kb < nkb ? __ldg(wsf0 + kb) : 127u;
+                    const uint32_t b1 = kb < nkb ? __ldg(wsf1 + kb) : 127u;
+                    w0 |= b0 << (8 * i);
+                    w1 |= b1 << (8 * i);
+                }
+            };
+            uint32_t wa[4], w0, w1;
+            load_group(0, wa, w0, w1);
             bool dead = false;
-            for (int g = 0; g * 4 < nkb; ++g, ++sfg) {
+            for (int g = 0; g < ngroups; ++g, ++sfg) {
+                uint32_t na[4], n0, n1;
+                load_group(g + 1, na, n0, n1);
                 const uint32_t sslot = sfg % kSfRing;
                 bool free_ = true;
                 if (lane == 0) free_ = mbar_wait(&S->sf_empty[sslot], ((sfg / kSfRing) & 1) ^ 1, wait_ns, abort_flag);
                 free_ = __shfl_sync(0xFFFFFFFFu, free_ ? 1 : 0, 0) != 0;
                 if (!free_) { dead = true; break; }
-                uint4 va = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-                uint32_t w0 = 0x7F7F7F7Fu, w1 = 0x7F7F7F7Fu;
-                if (a.scaled) {
-                    uint32_t wa[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int r = lane + 32 * j;
-                        wa[j] = r < rows ? __ldcg(reinterpret_cast<const uint32_t*>(asf + (size_t)r * asf_stride) + g) : 0x7F7F7F7Fu;
-                    }
-                    va = make_uint4(wa[0], wa[1], wa[2], wa[3]);
-                    w0 = 0; w1 = 0;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int kb = g * 4 + i;
-                        const uint32_t b0 = kb < nkb ? __ldg(wsf0 + kb) : 127u;
-                        const uint32_t b1 = kb < nkb ? __ldg(wsf1 + kb) : 127u;
-                        w0 |= b0 << (8 * i);
-                        w1 |= b1 << (8 * i);
-                    }
-                }
                 uint4* dst = reinterpret_cast<uint4*>(sf_tiles + sslot * kSfSlotBytes);
-                dst[lane] = va;
+                dst[lane] = make_uint4(wa[0], wa[1], wa[2], wa[3]);
                 dst[32 + lane] = make_uint4(w0, w0, w0, w0);
                 dst[64 + lane] = make_uint4(w1, w1, w1, w1);
                 fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor-core copy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&S->sf_full[sslot]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) wa[j] = na[j];
+                w0 = n0; w1 = n1;
             }
             if (dead) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; } break; }
         }
@@ -272,6 +299,7 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
         uint8_t* ffn = a.rwk + a.L.ffn_off;
         uint8_t* ffn_sf = a.rwk + a.L.ffn_sf_off;
         const int4* meta = reinterpret_cast<const int4*>(a.rwk + a.L.row_meta_off);
+        long long w_acc = 0, t_busy = 0;
         for (uint32_t it = 0;; ++it) {
             const uint32_t slot = it % kTaskRing;
             bool ok = true;
@@ -289,7 +317,8 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
             const bool row_valid = r < rows;
 
             bool got = true;
-            if (lane == 0) got = mbar_wait(&S->tmem_full, it & 1, wait_ns, abort_flag);
+            if (lane == 0) got = MXK_TIMED(w_acc, mbar_wait(&S->tmem_full, it & 1, wait_ns, abort_flag));
+            const long long t_busy0 = clock64();
             got = __shfl_sync(0xFFFFFFFFu, got ? 1 : 0, 0) != 0;
             if (!got) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; } break; }
             tc_fence_after();
@@ -354,9 +383,10 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                         if (a.scaled && half == 0) ffn_sf[(size_t)(row0 + r) * a.L.sf_stride_i + task.z] = (uint8_t)ex;
                     }
                 }
-                // publish: this warp's share of the tile is in global memory
+                // publish: this warp's share of the tile is in global memory.  The release of
+                // lane 0 is cumulative over the other lanes' stores ordered before it by the
+                // warp barrier; the proxy fence orders them against the TMA reads of L2 tasks.
                 fence_proxy_async_global();
-                __threadfence();
                 __syncwarp();
                 if (lane == 0) red_release_gpu_add(l1_done + task.y, 1u);
             } else {
@@ -382,13 +412,19 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                         o.w = pack_bf16x2(__uint_as_float(vu[c * 8 + 6]), __uint_as_float(vu[c * 8 + 7]));
                         d1[c] = o;
                     }
-                    __threadfence_system();
+                    // release at system scope: this thread's row segment is visible before the count
                     uint32_t* cnt = reinterpret_cast<uint32_t*>(peer_unk + a.L.combine_cnt_off) + (size_t)m.z * a.cap + m.y;
                     red_release_sys_add(cnt, 1u);
                 }
             }
+            t_busy += clock64() - t_busy0;
+        }
+        if (warp == kFirstEpiWarp && lane == 0) {
+            atomicAdd(&f->ticks[5], (unsigned long long)w_acc);
+            atomicAdd(&f->ticks[8], (unsigned long long)t_busy);
         }
     }
+    if (threadIdx.x == 0) atomicAdd(&f->ticks[6], (unsigned long long)(clock64() - t_start));
 
     // ------------------------------------------------------------------ teardown
     if (*abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain

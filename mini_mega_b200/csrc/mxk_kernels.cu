@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -56,7 +57,7 @@ struct DevFlags {  // head of rwk (flags_off)
 
 struct KArgs {
     int R, rank, EPR, E, topk, H, I, cap, slot_cap, tokens, win_cap;
-    int gemm_grid, skip_combine, scaled;
+    int gemm_grid, skip_combine, scaled, ticks;
     unsigned long long local_wait_ns, remote_wait_ns;
     uint8_t* rwk;
     uint8_t* unk;
@@ -275,6 +276,7 @@ __global__ void __launch_bounds__(1024) k_setup(const KArgs a) {
         f->n_tasks = n_windows * (nt1 + nt2);
         f->total_rows = overflow ? 0 : total_rows;
         f->task_counter = (unsigned)a.gemm_grid;  // first task of a CTA is its index
+        for (int i = 0; i < 16; ++i) f->ticks[i] = 0;
     }
 }
 
@@ -424,8 +426,8 @@ int check_geom(const MxkGeom* g) {
     if (g->R < 1 || g->R > 1024 || g->rank < 0 || g->rank >= g->R) return fail(MXK_ERR_BAD_ARG, "bad R/rank");
     if (g->experts_per_rank < 1 || g->experts_per_rank > 1024) return fail(MXK_ERR_BAD_ARG, "experts_per_rank must be in [1,1024]");
     if (g->topk < 1 || g->topk > 64) return fail(MXK_ERR_BAD_ARG, "topk must be in [1,64]");
-    if (g->hidden < 256 || g->hidden % 256) return fail(MXK_ERR_BAD_ARG, "hidden must be a positive multiple of 256");
-    if (g->intermediate < 128 || g->intermediate % 128) return fail(MXK_ERR_BAD_ARG, "intermediate must be a positive multiple of 128");
+    if (g->hidden < 256 || g->hidden % 256 || g->hidden > 8192) return fail(MXK_ERR_BAD_ARG, "hidden must be a multiple of 256 in [256, 8192]");
+    if (g->intermediate < 128 || g->intermediate % 128 || g->intermediate > 8192) return fail(MXK_ERR_BAD_ARG, "intermediate must be a multiple of 128 in [128, 8192]");
     if (g->max_tokens < 1) return fail(MXK_ERR_BAD_ARG, "max_tokens must be positive");
     if (g->slot_capacity < 0) return fail(MXK_ERR_BAD_ARG, "slot_capacity must be >= 0");
     return 0;
@@ -564,6 +566,10 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     k->slot_cap = g.slot_capacity ? g.slot_capacity : g.max_tokens;
     k->tokens = la->tokens; k->win_cap = win;
     k->skip_combine = la->skip_combine; k->scaled = la->w1_sf != nullptr;
+    {
+        static const int ticks_env = [] { const char* e = std::getenv("MXK_TICKS"); return e && e[0] == '1' ? 1 : 0; }();
+        k->ticks = ticks_env;  // MXK_TICKS=1: the GEMM kernel accounts its wait cycles (MxkStatus.ticks)
+    }
     k->local_wait_ns = la->max_spins > 0 ? (unsigned long long)la->max_spins * 250ull : kDefaultLocalWaitNs;
     k->remote_wait_ns = la->max_spins > 0 ? (unsigned long long)la->max_spins * 250ull : kDefaultRemoteWaitNs;
     k->rwk = static_cast<uint8_t*>(la->rwk); k->unk = static_cast<uint8_t*>(la->unk);
@@ -808,6 +814,7 @@ int mxk_read_status(const void* rwk, MxkStatus* out) {
     out->status = f.status;
     out->n_tasks = f.n_tasks; out->n_l1_tasks = f.n_l1_tasks; out->n_windows = f.n_windows; out->total_rows = f.total_rows;
     for (int i = 0; i < 8; ++i) out->dbg[i] = f.dbg[i];
+    for (int i = 0; i < 16; ++i) out->ticks[i] = f.ticks[i];
     return 0;
 }
 
