@@ -86,6 +86,8 @@ typedef struct MxkLayout {
     int32_t sf_stride_i;        /* bytes per ffn_sf row  (I/128 rounded to 16)    */
     int32_t max_windows;
     int32_t max_tasks;
+    int64_t pool_ready_off;     /* uint32 [max_windows] rows of a window dispatched   */
+    int64_t expert_first_win_off; /* int32 [EPR] first window id of each expert      */
 } MxkLayout;
 
 /* One launch.  Field names follow fp8mega::MegaLaunchArgs (reference
@@ -138,7 +140,8 @@ typedef struct MxkStatus {
                               2 MMA issuer blocked on operand tiles, 3 on the accumulator
                               drain, 4 on scale tiles, 5 epilogue blocked on accumulators,
                               6 CTA lifetime, 7 producer blocked on the task ring,
-                              8 epilogue busy                                         */
+                              8 epilogue busy; 9..13 phase ends in ns since CTA start
+                              (route, set-up, dispatch, GEMM, reduce)                 */
 } MxkStatus;
 
 #define MXK_DEV_TIMEOUT_BARRIER 1
@@ -169,7 +172,7 @@ int mxk_launch_compute(const MxkLaunchArgs* a, void* stream);
 int mxk_launch_reduce(const MxkLaunchArgs* a, void* stream);
 int mxk_launch_full(const MxkLaunchArgs* a, void* stream);
 int mxk_launch_empty(int grid, int threads, int64_t smem, void* stream);
-/* Number of kernels one mxk_launch_full enqueues. */
+/* Number of kernels one mxk_launch_full enqueues (one persistent kernel). */
 int mxk_kernels_per_layer(void);
 
 /* Phase-split launcher for diagnostics and single-GPU tests of a multi-rank world

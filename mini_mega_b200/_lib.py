@@ -47,6 +47,7 @@ class MxkLayout(C.Structure):
         ("row_meta_off", C.c_int64), ("pool_off", C.c_int64), ("pool_sf_off", C.c_int64), ("ffn_off", C.c_int64),
         ("ffn_sf_off", C.c_int64), ("pool_rows", C.c_int64),
         ("sf_stride_h", C.c_int32), ("sf_stride_i", C.c_int32), ("max_windows", C.c_int32), ("max_tasks", C.c_int32),
+        ("pool_ready_off", C.c_int64), ("expert_first_win_off", C.c_int64),
     ]
 
 

@@ -62,44 +62,38 @@ struct GemmSmem {
     int abort_flag;
 };
 
-__global__ void __launch_bounds__(kGemmThreads, 1)
-k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_constant__ CUtensorMap tm_ffn,
-       const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_w2) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* sf_tiles = tiles + kStages * kStageBytes;                 // 1024-aligned
-    GemmSmem* S = reinterpret_cast<GemmSmem*>(sf_tiles + kSfRing * kSfSlotBytes);
-    DevFlags* f = flags_of(a);
+// Barrier initialisation (one thread) — part of the kernel prologue.
+__device__ void gemm_init_barriers(GemmSmem* S) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&S->full[s], 1); mbar_init(&S->empty[s], 1); }
+    for (int s = 0; s < kSfRing; ++s) { mbar_init(&S->sf_full[s], 1); mbar_init(&S->sf_empty[s], 1); }
+    mbar_init(&S->tmem_full, 1);
+    mbar_init(&S->tmem_empty, kEpiWarps);
+    for (int s = 0; s < kTaskRing; ++s) { mbar_init(&S->task_full[s], 1); mbar_init(&S->task_empty[s], 2 + kEpiWarps); }
+    S->abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+}
+
+// The GEMM phase of the persistent kernel; called by all threads of the CTA after the
+// set-up tables of this launch are visible.  Returns when every role has left its loop.
+__device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t* sf_tiles, GemmSmem* S,
+                           const uint32_t tmem_base, const CUtensorMap* tm_pool_p, const CUtensorMap* tm_ffn_p,
+                           const CUtensorMap* tm_w1_p, const CUtensorMap* tm_w2_p) {
+    const CUtensorMap& tm_pool = *tm_pool_p;
+    const CUtensorMap& tm_ffn = *tm_ffn_p;
+    const CUtensorMap& tm_w1 = *tm_w1_p;
+    const CUtensorMap& tm_w2 = *tm_w2_p;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &S->abort_flag;
     const uint64_t wait_ns = a.local_wait_ns;
     const bool timed = a.ticks != 0;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&S->full[s], 1); mbar_init(&S->empty[s], 1); }
-        for (int s = 0; s < kSfRing; ++s) { mbar_init(&S->sf_full[s], 1); mbar_init(&S->sf_empty[s], 1); }
-        mbar_init(&S->tmem_full, 1);
-        mbar_init(&S->tmem_empty, kEpiWarps);
-        for (int s = 0; s < kTaskRing; ++s) { mbar_init(&S->task_full[s], 1); mbar_init(&S->task_empty[s], 2 + kEpiWarps); }
-        S->abort_flag = 0;
-        mbar_fence_init();
-        fence_proxy_async_smem();
-    }
-    for (int i = threadIdx.x; i < 2 * 2 * 128; i += blockDim.x) (&S->xch[0][0][0])[i] = 0ull;
-    if (warp == 1) {
-        tmem_alloc(&S->tmem_base, kTmemCols);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = S->tmem_base;
     const long long t_start = clock64();
 
-    const int n_tasks = f->n_tasks;
+    const int n_tasks = ld_relaxed_gpu(&f->n_tasks);  // written by the set-up phase of this same kernel
     const int4* tasks = reinterpret_cast<const int4*>(a.rwk + a.L.tasks_off);
     const int4* windows = reinterpret_cast<const int4*>(a.rwk + a.L.windows_off);
     uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
+    const uint32_t* pool_ready = reinterpret_cast<const uint32_t*>(a.rwk + a.L.pool_ready_off);
     const int kb1 = a.H / kBlockK, kb2 = a.I / kBlockK;
     const int nt1 = a.I / 128;
     const uint32_t l1_need = (uint32_t)nt1 * kEpiWarps;   // arrivals that complete a window's ffn rows
@@ -117,15 +111,20 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                     raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break;
                 }
                 const int t = it == 0 ? (int)blockIdx.x : (int)atomicAdd(&f->task_counter, 1u);
-                const int4 task = t < n_tasks ? tasks[t] : make_int4(-1, 0, 0, 0);
+                const int4 task = t < n_tasks ? ld_relaxed_gpu_v4(tasks + t) : make_int4(-1, 0, 0, 0);
                 S->task[slot] = task;
                 mbar_arrive(&S->task_full[slot]);
                 if (task.x < 0) break;
-                const int4 win = windows[task.y];
+                const int4 win = ld_relaxed_gpu_v4(windows + task.y);
                 const int e = win.x, row0 = win.y;
                 const bool is_l2 = task.x == 1;
                 if (is_l2) {  // every L1 tile of this window must have landed in ffn
                     if (!MXK_TIMED(w_gate, spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= l1_need; }, wait_ns, abort_flag))) {
+                        raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
+                    }
+                } else {      // every row of this window must have been pulled into the pool
+                    const uint32_t need_rows = (uint32_t)win.z;
+                    if (!MXK_TIMED(w_gate, spin_until([&] { return ld_acquire_gpu(pool_ready + task.y) >= need_rows; }, wait_ns, abort_flag))) {
                         raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
                     }
                 }
@@ -218,7 +217,7 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
             __syncwarp();
             if (lane == 0) mbar_arrive(&S->task_empty[slot]);
             if (task.x < 0) break;
-            const int4 win = windows[task.y];
+            const int4 win = ld_relaxed_gpu_v4(windows + task.y);
             const int e = win.x, row0 = win.y, rows = task.w;
             const bool is_l2 = task.x == 1;
             const int nkb = is_l2 ? kb2 : kb1;
@@ -229,15 +228,22 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
             if (a.scaled) {
                 if (is_l2) {
                     // ffn scales are written by L1 epilogues of this same kernel
-                    bool ready = true;
-                    if (lane == 0) ready = spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= l1_need; }, wait_ns, abort_flag);
-                    ready = __shfl_sync(0xFFFFFFFFu, ready ? 1 : 0, 0) != 0;
+                    // every lane acquires for itself: its own scale loads below must be ordered
+                    // after the counter, and a warp shuffle gives no memory ordering
+                    bool ready = spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= l1_need; }, wait_ns, abort_flag);
+                    ready = __all_sync(0xFFFFFFFFu, ready ? 1 : 0) != 0;
                     if (!ready) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; } break; }
                     asf = ffn_sf + (size_t)row0 * a.L.sf_stride_i;
                     asf_stride = a.L.sf_stride_i;
                     wsf0 = a.w2_sf + ((size_t)e * (a.H / 128) + task.z * 2) * nkb;
                     wsf1 = wsf0 + nkb;
                 } else {
+                    // pool scales are written by the dispatch phase of this same kernel
+                    bool ready = true;
+                    const uint32_t need_rows = (uint32_t)win.z;
+                    ready = spin_until([&] { return ld_acquire_gpu(pool_ready + task.y) >= need_rows; }, wait_ns, abort_flag);
+                    ready = __all_sync(0xFFFFFFFFu, ready ? 1 : 0) != 0;
+                    if (!ready) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; } break; }
                     asf = pool_sf + (size_t)row0 * a.L.sf_stride_h;
                     asf_stride = a.L.sf_stride_h;
                     wsf0 = a.w1_sf + ((size_t)e * (2 * a.I / 128) + task.z) * nkb;
@@ -255,7 +261,7 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int r = lane + 32 * j;
-                    if (r < rows) wa[j] = __ldcg(reinterpret_cast<const uint32_t*>(asf + (size_t)r * asf_stride) + g);
+                    if (r < rows) wa[j] = ld_relaxed_gpu(reinterpret_cast<const uint32_t*>(asf + (size_t)r * asf_stride) + g);
                 }
                 w0 = 0; w1 = 0;
 #pragma unroll
@@ -310,7 +316,7 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
             __syncwarp();
             if (lane == 0) mbar_arrive(&S->task_empty[slot]);
             if (task.x < 0) break;
-            const int4 win = windows[task.y];
+            const int4 win = ld_relaxed_gpu_v4(windows + task.y);
             const int row0 = win.y, rows = task.w;
             const bool is_l2 = task.x == 1;
             const bool warp_active = q * 32 < rows;
@@ -383,16 +389,16 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
                         if (a.scaled && half == 0) ffn_sf[(size_t)(row0 + r) * a.L.sf_stride_i + task.z] = (uint8_t)ex;
                     }
                 }
-                // publish: this warp's share of the tile is in global memory.  The release of
-                // lane 0 is cumulative over the other lanes' stores ordered before it by the
-                // warp barrier; the proxy fence orders them against the TMA reads of L2 tasks.
+                // publish: every lane makes its own stores visible at GPU scope (and to the TMA
+                // reads of the L2 tasks) before lane 0 counts the warp's share as done
+                __threadfence();
                 fence_proxy_async_global();
                 __syncwarp();
                 if (lane == 0) red_release_gpu_add(l1_done + task.y, 1u);
             } else {
                 // ---- bf16 rows pushed to the source rank + per-pair arrival count
                 if (row_valid && !a.skip_combine) {
-                    const int4 m = meta[row0 + r];  // src, token, k, weight
+                    const int4 m = ld_relaxed_gpu_v4(meta + row0 + r);  // src, token, k, weight
                     uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[m.x]);
                     uint16_t* crow = reinterpret_cast<uint16_t*>(peer_unk + a.L.combine_rows_off) +
                                      ((size_t)m.z * a.cap + m.y) * a.H + task.z * kBlockN + half * 64;
@@ -426,12 +432,4 @@ k_gemm(const KArgs a, const __grid_constant__ CUtensorMap tm_pool, const __grid_
     }
     if (threadIdx.x == 0) atomicAdd(&f->ticks[6], (unsigned long long)(clock64() - t_start));
 
-    // ------------------------------------------------------------------ teardown
-    if (*abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        __syncwarp();
-        tmem_dealloc(tmem_base, kTmemCols);
-    }
 }

@@ -2,25 +2,10 @@
 // mxk_kernels.cu — B200 (sm_100a) FP8xFP8 MoE layer: device kernels and the C
 // ABI declared in include/mxk_b200.h.
 //
-// One layer = five launches on the caller's stream:
-//   k_route    per-rank route build: deterministic slot per (token,k) pair,
-//              scatter of pair indices into the owner ranks' tables, count
-//              publish, cross-rank barrier arrival
-//              (reference: route_build_body / publish_counts_body /
-//               xbar_route_ready_body, src/prologue.cuh:126-256, src/flags.cuh:284-377)
-//   k_setup    barrier wait, prefix table, windows, cost-ordered task list
-//              (reference: task_setup_body, src/prologue.cuh:269-498)
-//   k_dispatch EP dispatch: pull routed FP8 rows + 1x128 scales from the peers'
-//              symmetric buffers into the local pool
-//              (reference: r19_pull_flags, src/compute_big.cuh:1691-1946)
-//   k_gemm     persistent grouped GEMM over (window, n-tile) tasks on tcgen05
-//              with TMEM accumulators fed by TMA: L1 gate+up + SwiGLU + FP8
-//              requant, then L2 down + bf16 + combine push to the source rank
-//              (reference: dispatch_pull_body task loop src/compute.cuh:1050-1236,
-//               L1/L2 families src/compute_big.cuh:320-515,1231-1679,
-//               combine push src/combine.cuh:347-477)
-//   k_reduce   top-k weighted sum at the source rank
-//              (reference: reduce_tile_body, src/combine.cuh:488-656)
+// One layer = ONE launch of the persistent kernel k_mega (one CTA per SM), which runs
+// the phases route -> set-up -> dispatch -> grouped GEMMs (+ combine push) -> reduce
+// (mxk_phases.cuh, mxk_gemm.cuh).  mxk_launch_phases can run any subset of phases per
+// launch; the single-GPU tests of a multi-rank world use that to interleave the ranks.
 // ============================================================================
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -49,6 +34,8 @@ struct DevFlags {  // head of rwk (flags_off)
     long long current_time;      // completed prologues; the running launch is +1
     unsigned route_blocks_done;
     unsigned task_counter;
+    unsigned setup_epoch;        // epoch whose tables CTA 0 has published
+    unsigned pad_;
     int n_tasks, n_l1_tasks, n_windows, total_rows;
     int status;
     int dbg[8];
@@ -83,319 +70,81 @@ __device__ __forceinline__ void raise_status(DevFlags* f, int code, int dbg_slot
     atomicCAS(&f->status, 0, code);
 }
 
-// ============================================================== k_route =======
-// Slots are handed out in ascending pair index idx = token*topk + k, so every
-// table row (and with it the pool row order) is deterministic; the reference
-// uses a shared-memory atomicAdd and accepts any order (src/prologue.cuh:164-180).
-__global__ void __launch_bounds__(1024) k_route(const KArgs a) {
-    DevFlags* f = flags_of(a);
-    __shared__ int s_wtot[32];
-    __shared__ int s_last;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const long long epoch = f->current_time + 1;  // read before the last block bumps it
-    const int par = (int)(epoch & 1);
-    const int np = a.tokens * a.topk;
-    const int64_t* ti = a.topk_idx;
-    uint8_t* pair_state = a.rwk + a.L.pair_state_off;
-    int* rsc = reinterpret_cast<int*>(a.rwk + a.L.route_slot_counts_off);
-
-    // Arrival counters of the rows peers will push to this rank in this launch.
-    // Safe to clear here: peers push only after this rank has arrived at the
-    // barrier below, and the previous launch's reduce has consumed them.
-    unsigned* cnt = reinterpret_cast<unsigned*>(a.unk + a.L.combine_cnt_off);
-    for (int i = blockIdx.x * blockDim.x + tid; i < a.topk * a.cap; i += gridDim.x * blockDim.x) cnt[i] = 0;
-
-    for (int e = blockIdx.x; e < a.E; e += gridDim.x) {
-        const int dst = e / a.EPR, le = e % a.EPR;
-        uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[dst]);
-        uint32_t* tbl = reinterpret_cast<uint32_t*>(peer_unk + a.L.src_index_table_off) +
-                        (((size_t)par * a.EPR + le) * a.R + a.rank) * (size_t)a.slot_cap;
-        int base = 0;
-        for (int p0 = 0; p0 < np; p0 += 1024) {
-            const int p = p0 + tid;
-            const bool hit = p < np && ti[p] == (int64_t)e;
-            const unsigned bal = __ballot_sync(0xFFFFFFFFu, hit);
-            if (lane == 0) s_wtot[warp] = __popc(bal);
-            __syncthreads();
-            int wpre = 0, tot = 0;
-#pragma unroll
-            for (int w = 0; w < 32; ++w) {
-                const int v = s_wtot[w];
-                wpre += (w < warp) ? v : 0;
-                tot += v;
-            }
-            if (hit) {
-                const int slot = base + wpre + __popc(bal & ((1u << lane) - 1u));
-                const bool ok = slot < a.slot_cap;  // over capacity: dropped (src/prologue.cuh:171-174)
-                if (ok) st_relaxed_sys(tbl + slot, (uint32_t)p);
-                pair_state[p] = ok ? 1 : 0;
-            }
-            base += tot;
-            __syncthreads();
-        }
-        if (tid == 0) {
-            const int c = base < a.slot_cap ? base : a.slot_cap;
-            rsc[e] = c;
-            uint32_t* recv = reinterpret_cast<uint32_t*>(peer_unk + a.L.expert_recv_counts_off) +
-                             ((size_t)par * a.R + a.rank) * a.L.recv_stride;
-            st_relaxed_sys(recv + le, (uint32_t)c);
-        }
-    }
-    if (blockIdx.x == 0)  // invalid expert ids (negative / >= E) take no slot (src/prologue.cuh:166-167)
-        for (int p = tid; p < np; p += 1024)
-            if ((uint64_t)ti[p] >= (uint64_t)a.E) pair_state[p] = 0;
-
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(&f->route_blocks_done, 1u) == gridDim.x - 1) ? 1 : 0;
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    // Row checksum word ~(sum + 1) at index EPR of each row sent (src/prologue.cuh:248-255).
-    for (int d = tid; d < a.R; d += 1024) {
-        uint32_t csum = 0;
-        for (int le = 0; le < a.EPR; ++le) csum += (uint32_t)__ldcg(rsc + d * a.EPR + le);
-        uint32_t* recv = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) +
-                                                     a.L.expert_recv_counts_off) +
-                         ((size_t)par * a.R + a.rank) * a.L.recv_stride;
-        st_relaxed_sys(recv + a.EPR, ~(csum + 1u));
-    }
-    __threadfence_system();
-    __syncthreads();
-    // Barrier arrival: publish this launch's epoch into every peer's slot for this rank.
-    for (int d = tid; d < a.R; d += 1024) {
-        uint32_t* xb = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) + a.L.xbar_off) +
-                       (size_t)a.rank * a.L.xbar_stride;
-        st_release_sys(xb, (uint32_t)epoch);
-    }
-    if (tid == 0) {
-        f->route_blocks_done = 0;
-        f->current_time = epoch;
-    }
-}
-
-// ============================================================== k_setup =======
-__global__ void __launch_bounds__(1024) k_setup(const KArgs a) {
-    extern __shared__ int s_i[];
-    DevFlags* f = flags_of(a);
-    const int tid = threadIdx.x;
-    const int EPR = a.EPR, R = a.R;
-    int* s_tot = s_i;                  // [EPR]
-    int* s_order = s_tot + EPR;        // [EPR] expert at sorted position p
-    int* s_first = s_order + EPR;      // [EPR+1] first window of position p
-    int* s_base = s_first + EPR + 1;   // [EPR+1] first pool row of expert le
-    const long long epoch = f->current_time;
-    const int par = (int)(epoch & 1);
-
-    // Cross-rank barrier: every rank has published its routes for this epoch.
-    if (tid < R) {
-        const uint32_t* xb = reinterpret_cast<const uint32_t*>(a.unk + a.L.xbar_off) + (size_t)tid * a.L.xbar_stride;
-        const bool ok = spin_until([&] { return (int32_t)(ld_acquire_sys(xb) - (uint32_t)epoch) >= 0; },
-                                   a.remote_wait_ns, nullptr);
-        if (!ok) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 0);
-    }
-    __syncthreads();
-
-    const uint32_t* recv = reinterpret_cast<const uint32_t*>(a.unk + a.L.expert_recv_counts_off) +
-                           (size_t)par * R * a.L.recv_stride;
-    int* prefix = reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off);
-    for (int le = tid; le < EPR; le += 1024) {
-        int c = 0;
-        for (int r = 0; r < R; ++r) {
-            prefix[le * (R + 1) + r] = c;
-            c += (int)__ldcg(recv + (size_t)r * a.L.recv_stride + le);
-        }
-        prefix[le * (R + 1) + R] = c;
-        s_tot[le] = c;
-    }
-    __syncthreads();
-    // Experts by descending row count, ties by index: the hottest experts' windows
-    // are claimed first so the dynamic queue ends on the cheap ones (LPT order).
-    for (int le = tid; le < EPR; le += 1024) {
-        const int c = s_tot[le];
-        int rk = 0;
-        for (int j = 0; j < EPR; ++j) {
-            const int cj = s_tot[j];
-            rk += (cj > c || (cj == c && j < le)) ? 1 : 0;
-        }
-        s_order[rk] = le;
-    }
-    __syncthreads();
-    if (tid == 0) {
-        int acc = 0;
-        for (int le = 0; le < EPR; ++le) { s_base[le] = acc; acc += s_tot[le]; }
-        s_base[EPR] = acc;
-        int nw = 0;
-        for (int p = 0; p < EPR; ++p) {
-            s_first[p] = nw;
-            const int c = s_tot[s_order[p]];
-            nw += c > 0 ? (c + a.win_cap - 1) / a.win_cap : 0;
-        }
-        s_first[EPR] = nw;
-    }
-    __syncthreads();
-    int* row_base = reinterpret_cast<int*>(a.rwk + a.L.expert_row_base_off);
-    for (int le = tid; le <= EPR; le += 1024) row_base[le] = s_base[le];
-
-    int n_windows = s_first[EPR];
-    const int total_rows = s_base[EPR];
-    const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
-    bool overflow = false;
-    if (n_windows > a.L.max_windows || (long long)n_windows * (nt1 + nt2) > a.L.max_tasks ||
-        total_rows > a.L.pool_rows) {
-        overflow = true;
-        n_windows = 0;
-    }
-    int4* windows = reinterpret_cast<int4*>(a.rwk + a.L.windows_off);
-    int4* tasks = reinterpret_cast<int4*>(a.rwk + a.L.tasks_off);
-    uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
-    const int n_l1 = n_windows * nt1;
-    if (!overflow)
-        for (int p = 0; p < EPR; ++p) {
-            const int e = s_order[p], c = s_tot[e];
-            const int fw = s_first[p], nw = s_first[p + 1] - fw;
-            if (nw == 0) continue;  // sorted: every later expert is empty too
-            for (int w = tid; w < nw; w += 1024) {
-                const int rows = min(a.win_cap, c - w * a.win_cap);
-                windows[fw + w] = make_int4(e, s_base[e] + w * a.win_cap, rows, 0);
-                l1_done[fw + w] = 0;
-            }
-            for (int i = tid; i < nt1 * nw; i += 1024) {
-                const int nt = i / nw, w = i % nw;
-                tasks[fw * nt1 + i] = make_int4(0, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
-            }
-            for (int i = tid; i < nt2 * nw; i += 1024) {
-                const int nt = i / nw, w = i % nw;
-                tasks[n_l1 + fw * nt2 + i] = make_int4(1, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
-            }
-        }
-    if (tid == 0) {
-        if (overflow) raise_status(f, MXK_DEV_BAD_TABLE, 3);
-        f->n_windows = n_windows;
-        f->n_l1_tasks = n_l1;
-        f->n_tasks = n_windows * (nt1 + nt2);
-        f->total_rows = overflow ? 0 : total_rows;
-        f->task_counter = (unsigned)a.gemm_grid;  // first task of a CTA is its index
-        for (int i = 0; i < 16; ++i) f->ticks[i] = 0;
-    }
-}
-
-// ============================================================ k_dispatch ======
-// One warp per pool row: locate (expert, source rank, slot), read the pair index
-// the source wrote, then pull the row's H bytes and H/128 scale bytes from the
-// source rank's symmetric buffer with 16-byte loads over NVLink.
-__global__ void __launch_bounds__(256) k_dispatch(const KArgs a) {
-    DevFlags* f = flags_of(a);
-    const int lane = threadIdx.x & 31;
-    const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int nwarps = (gridDim.x * blockDim.x) >> 5;
-    const int total = f->total_rows;
-    const int par = (int)(f->current_time & 1);
-    const int R = a.R, EPR = a.EPR, H = a.H;
-    const int* row_base = reinterpret_cast<const int*>(a.rwk + a.L.expert_row_base_off);
-    const int* prefix = reinterpret_cast<const int*>(a.rwk + a.L.prefix_tbl_off);
-    const uint32_t* tbl = reinterpret_cast<const uint32_t*>(a.unk + a.L.src_index_table_off) +
-                          (size_t)par * EPR * R * a.slot_cap;
-    uint8_t* pool = a.rwk + a.L.pool_off;
-    uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
-    int4* meta = reinterpret_cast<int4*>(a.rwk + a.L.row_meta_off);
-    const int kb = H / 128;
-
-    for (int g = gwarp; g < total; g += nwarps) {
-        int lo = 0, hi = EPR;  // largest le with row_base[le] <= g
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (row_base[mid] <= g) lo = mid; else hi = mid;
-        }
-        const int le = lo;
-        const int gl = g - row_base[le];
-        const int* pf = prefix + le * (R + 1);
-        int slo = 0, shi = R;  // largest src with pf[src] <= gl (src/compute_big.cuh:1760-1769)
-        while (shi - slo > 1) {
-            const int mid = (slo + shi) >> 1;
-            if (pf[mid] <= gl) slo = mid; else shi = mid;
-        }
-        const int src = slo, slot = gl - pf[src];
-        const uint32_t idx = __ldcg(tbl + ((size_t)le * R + src) * a.slot_cap + slot);
-        const int token = (int)(idx / (uint32_t)a.topk), k = (int)(idx % (uint32_t)a.topk);
-        const uint8_t* peer = a.peer_bases[src];
-        const uint4* srow = reinterpret_cast<const uint4*>(peer + a.x_off + (size_t)token * H);
-        uint4* drow = reinterpret_cast<uint4*>(pool + (size_t)g * H);
-        const int n16 = H / 16;
-#pragma unroll 4
-        for (int i = lane; i < n16; i += 32) drow[i] = __ldcg(srow + i);
-        if (a.scaled) {
-            const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
-            for (int i = lane; i < a.L.sf_stride_h; i += 32)
-                pool_sf[(size_t)g * a.L.sf_stride_h + i] = i < kb ? __ldcg(ssf + i) : (uint8_t)127;
-        }
-        if (lane == 0) {
-            const float w = __ldcg(reinterpret_cast<const float*>(peer + a.weights_off) + (size_t)token * a.topk + k);
-            meta[g] = make_int4(src, token, k, __float_as_int(w));
-        }
-    }
-}
-
-// ============================================================== k_gemm ========
+#include "mxk_phases.cuh"
 #include "mxk_gemm.cuh"
 
-// ============================================================== k_reduce ======
-// y[t] = sum over k (ascending, FP32, product then sum) of w_k * bf16 row_k
-// (reference: src/combine.cuh:601-627, src/bench_check.cuh:484-499).
-__global__ void __launch_bounds__(256) k_reduce(const KArgs a) {
-    DevFlags* f = flags_of(a);
-    __shared__ int s_ok[64];
+// ============================================================== k_mega ========
+// The persistent kernel: one CTA per SM runs the phases selected by phase_mask in
+// layer order.  CTAs wait on each other (route arrival, set-up flag, L1->L2 and
+// pool counters), so the grid never exceeds the SM count and every CTA is resident.
+__global__ void __launch_bounds__(kGemmThreads, 1)
+k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap tm_pool,
+       const __grid_constant__ CUtensorMap tm_ffn, const __grid_constant__ CUtensorMap tm_w1,
+       const __grid_constant__ CUtensorMap tm_w2) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sf_tiles = tiles + kStages * kStageBytes;
+    GemmSmem* S = reinterpret_cast<GemmSmem*>(sf_tiles + kSfRing * kSfSlotBytes);
+    __shared__ int s_small[64];
     __shared__ float s_w[64];
-    const int tid = threadIdx.x;
-    const int H = a.H, topk = a.topk;
-    const uint8_t* pair_state = a.rwk + a.L.pair_state_off;
-    const uint32_t* cnt = reinterpret_cast<const uint32_t*>(a.unk + a.L.combine_cnt_off);
-    const uint16_t* rows = reinterpret_cast<const uint16_t*>(a.unk + a.L.combine_rows_off);
-    const float* tw = reinterpret_cast<const float*>(a.self + a.weights_off);
-    const uint32_t need = (uint32_t)(H / kBlockN) * 2u;
-    for (int t = blockIdx.x; t < a.tokens; t += gridDim.x) {
-        if (tid < topk) {
-            int ok = pair_state[t * topk + tid];
-            if (ok && !a.skip_combine) {
-                const uint32_t* c = cnt + (size_t)tid * a.cap + t;
-                if (!spin_until([&] { return ld_acquire_sys(c) >= need; }, a.remote_wait_ns, nullptr)) {
-                    raise_status(f, MXK_DEV_TIMEOUT_REDUCE, 4);
-                    ok = 0;
-                }
-            }
-            s_ok[tid] = ok;
-            s_w[tid] = tw[(size_t)t * topk + tid];
+    DevFlags* f = flags_of(a);
+    const int warp = threadIdx.x >> 5;
+    const bool do_gemm = (phase_mask & MXK_PHASE_GEMM) != 0;
+
+    // the launch counter is advanced by CTA 0 at the end of the route phase, after every
+    // CTA has arrived there — i.e. after this read
+    const long long epoch = ld_relaxed_gpu(&f->current_time) + ((phase_mask & MXK_PHASE_ROUTE) ? 1 : 0);
+
+    if (do_gemm) {
+        if (threadIdx.x == 0) gemm_init_barriers(S);
+        for (int i = threadIdx.x; i < 2 * 2 * 128; i += blockDim.x) (&S->xch[0][0][0])[i] = 0ull;
+        if (warp == 1) {
+            tmem_alloc(&S->tmem_base, kTmemCols);
+            tmem_relinquish();
         }
-        __syncthreads();
-        for (int c8 = tid; c8 < H / 8; c8 += 256) {
-            float acc[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-            for (int k = 0; k < topk; ++k) {
-                if (!s_ok[k]) continue;
-                const float w = s_w[k];
-                const uint4 v = __ldcg(reinterpret_cast<const uint4*>(rows + ((size_t)k * a.cap + t) * H) + c8);
-                const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(u[j] << 16), w));
-                    acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(u[j] & 0xFFFF0000u), w));
-                }
-            }
-            if (a.y) {
-                float4* o = reinterpret_cast<float4*>(a.y + (size_t)t * H + c8 * 8);
-                o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-            }
-            if (a.y_bf16) {
-                uint4 o;
-                o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-                o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-                *reinterpret_cast<uint4*>(a.y_bf16 + (size_t)t * H + c8 * 8) = o;
-            }
-        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    uint32_t tmem_base = 0;
+    if (do_gemm) {
+        tc_fence_after();
+        tmem_base = S->tmem_base;
+    }
+
+    // Phase stamps in ns since this CTA started (MxkStatus.ticks 9..13: end of route, set-up,
+    // dispatch, GEMM, reduce; CTA 0 for the first two, maximum over CTAs for the rest).
+    const bool stamp = a.ticks != 0 && threadIdx.x == 0;
+    const uint64_t t0 = stamp ? gtimer_ns() : 0;
+
+    if (phase_mask & MXK_PHASE_ROUTE) route_phase(a, f, epoch, s_small);
+    if (stamp && blockIdx.x == 0) f->ticks[9] = gtimer_ns() - t0;
+
+    bool tables_ok = true;
+    if (phase_mask & MXK_PHASE_SETUP) {
+        // the tile region is idle until the GEMM phase: CTA 0 borrows it as scratch
+        if (blockIdx.x == 0) setup_phase_leader(a, f, epoch, reinterpret_cast<int*>(tiles));
+        else tables_ok = setup_phase_wait(a, f, epoch, s_small);
         __syncthreads();
     }
+    if (stamp && blockIdx.x == 0) f->ticks[10] = gtimer_ns() - t0;
+
+    if ((phase_mask & MXK_PHASE_DISPATCH) && tables_ok) dispatch_phase(a, f, epoch);
+    if (stamp) atomicMax(&f->ticks[11], (unsigned long long)(gtimer_ns() - t0));
+
+    if (do_gemm) {
+        if (tables_ok) gemm_phase(a, f, tiles, sf_tiles, S, tmem_base, &tm_pool, &tm_ffn, &tm_w1, &tm_w2);
+        if (S->abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain
+        tc_fence_before();
+        __syncthreads();
+        if (warp == 1) {
+            __syncwarp();
+            tmem_dealloc(tmem_base, kTmemCols);
+        }
+    }
+    if (stamp) atomicMax(&f->ticks[12], (unsigned long long)(gtimer_ns() - t0));
+
+    if (phase_mask & MXK_PHASE_REDUCE) reduce_phase(a, f, s_small, s_w);
+    if (stamp) atomicMax(&f->ticks[13], (unsigned long long)(gtimer_ns() - t0));
 }
 
 __global__ void k_empty() {}
@@ -477,6 +226,8 @@ int compute_layout(const MxkGeom* g, MxkLayout* L) {
     L->windows_off = take((int64_t)L->max_windows * 16);
     L->tasks_off = take((int64_t)L->max_tasks * 16);
     L->l1_done_off = take((int64_t)L->max_windows * 4);
+    L->pool_ready_off = take((int64_t)L->max_windows * 4);
+    L->expert_first_win_off = take(EPR * 4);
     L->row_meta_off = take(L->pool_rows * 16);
     L->pool_off = take((L->pool_rows + 128) * H);
     L->pool_sf_off = take(L->pool_rows * L->sf_stride_h);
@@ -587,61 +338,37 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     return 0;
 }
 
-int launch_route(const KArgs& k, cudaStream_t st) {
-    int rgrid = k.E < 148 ? k.E : 148;
-    k_route<<<rgrid, 1024, 0, st>>>(k);
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : cuda_fail(e, "launch route");
-}
-int launch_setup(const KArgs& k, cudaStream_t st) {
-    const size_t smem = (size_t)(4 * k.EPR + 2) * sizeof(int);
-    k_setup<<<1, 1024, smem, st>>>(k);
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : cuda_fail(e, "launch setup");
-}
-int launch_route_setup(const KArgs& k, cudaStream_t st) {
-    if (int rc = launch_route(k, st)) return rc;
-    return launch_setup(k, st);
-}
-int launch_dispatch(const KArgs& k, cudaStream_t st) {
-    DeviceInfo di;
-    if (int rc = device_info(&di)) return rc;
-    k_dispatch<<<di.sm_count * 4, 256, 0, st>>>(k);
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : cuda_fail(e, "launch dispatch");
-}
+constexpr int kPhaseAll = MXK_PHASE_ROUTE | MXK_PHASE_SETUP | MXK_PHASE_DISPATCH | MXK_PHASE_GEMM | MXK_PHASE_REDUCE;
 
-int launch_gemm(const KArgs& k, cudaStream_t st) {
-    if (!k.w1 || !k.w2) return fail(MXK_ERR_BAD_ARG, "w1 / w2 must be non-null");
+// One launch of the persistent kernel running the phases in `mask`.
+int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
+    mask &= kPhaseAll;
+    if ((mask & MXK_PHASE_REDUCE) && !k.y && !k.y_bf16) return fail(MXK_ERR_BAD_ARG, "y or y_bf16 must be non-null");
+    if ((mask & MXK_PHASE_REDUCE) && k.tokens == 0) mask &= ~MXK_PHASE_REDUCE;  // nothing to reduce on this rank
+    if (mask == 0) return 0;
     CUtensorMap tm_pool, tm_ffn, tm_w1, tm_w2;
-    if (int rc = make_map(&tm_pool, k.rwk + k.L.pool_off, k.L.pool_rows + 128, k.H)) return rc;
-    if (int rc = make_map(&tm_ffn, k.rwk + k.L.ffn_off, k.L.pool_rows + 128, k.I)) return rc;
-    if (int rc = make_map(&tm_w1, k.w1, (int64_t)k.EPR * 2 * k.I, k.H)) return rc;
-    if (int rc = make_map(&tm_w2, k.w2, (int64_t)k.EPR * k.H, k.I)) return rc;
+    std::memset(&tm_pool, 0, sizeof(tm_pool));
+    std::memset(&tm_ffn, 0, sizeof(tm_ffn));
+    std::memset(&tm_w1, 0, sizeof(tm_w1));
+    std::memset(&tm_w2, 0, sizeof(tm_w2));
+    if (mask & MXK_PHASE_GEMM) {
+        if (!k.w1 || !k.w2) return fail(MXK_ERR_BAD_ARG, "w1 / w2 must be non-null");
+        if (int rc = make_map(&tm_pool, k.rwk + k.L.pool_off, k.L.pool_rows + 128, k.H)) return rc;
+        if (int rc = make_map(&tm_ffn, k.rwk + k.L.ffn_off, k.L.pool_rows + 128, k.I)) return rc;
+        if (int rc = make_map(&tm_w1, k.w1, (int64_t)k.EPR * 2 * k.I, k.H)) return rc;
+        if (int rc = make_map(&tm_w2, k.w2, (int64_t)k.EPR * k.H, k.I)) return rc;
+    }
     static thread_local int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(k_gemm)");
+        cudaError_t e = cudaFuncSetAttribute(k_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(k_mega)");
         attr_dev = dev;
     }
-    k_gemm<<<k.gemm_grid, kGemmThreads, kGemmSmem, st>>>(k, tm_pool, tm_ffn, tm_w1, tm_w2);
+    k_mega<<<k.gemm_grid, kGemmThreads, kGemmSmem, st>>>(k, mask, tm_pool, tm_ffn, tm_w1, tm_w2);
     cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : cuda_fail(e, "launch gemm");
-}
-int launch_dispatch_gemm(const KArgs& k, cudaStream_t st) {
-    if (int rc = launch_dispatch(k, st)) return rc;
-    return launch_gemm(k, st);
-}
-
-int launch_reduce_k(const KArgs& k, cudaStream_t st) {
-    if (!k.y && !k.y_bf16) return fail(MXK_ERR_BAD_ARG, "y or y_bf16 must be non-null");
-    if (k.tokens == 0) return 0;
-    int grid = k.tokens < 1184 ? k.tokens : 1184;
-    k_reduce<<<grid, 256, 0, st>>>(k);
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : cuda_fail(e, "launch reduce");
+    return e == cudaSuccess ? 0 : cuda_fail(e, "launch k_mega");
 }
 
 // ------------------------------------------------------------ static scratch
@@ -691,28 +418,26 @@ int64_t mxk_unk_bytes(const MxkGeom* g) { MxkLayout L; return compute_layout(g, 
 int mxk_launch_prelude(const MxkLaunchArgs* a, void* stream) {
     KArgs k;
     if (int rc = build_kargs(a, &k)) return rc;
-    return launch_route_setup(k, static_cast<cudaStream_t>(stream));
+    return launch_mega(k, MXK_PHASE_ROUTE | MXK_PHASE_SETUP, static_cast<cudaStream_t>(stream));
 }
 int mxk_launch_compute(const MxkLaunchArgs* a, void* stream) {
     KArgs k;
     if (int rc = build_kargs(a, &k)) return rc;
-    if (int rc = launch_route_setup(k, static_cast<cudaStream_t>(stream))) return rc;
-    return launch_dispatch_gemm(k, static_cast<cudaStream_t>(stream));
+    return launch_mega(k, kPhaseAll & ~MXK_PHASE_REDUCE, static_cast<cudaStream_t>(stream));
 }
 int mxk_launch_reduce(const MxkLaunchArgs* a, void* stream) {
     KArgs k;
     if (int rc = build_kargs(a, &k)) return rc;
-    return launch_reduce_k(k, static_cast<cudaStream_t>(stream));
+    if (!k.y && !k.y_bf16) return fail(MXK_ERR_BAD_ARG, "y or y_bf16 must be non-null");
+    return launch_mega(k, MXK_PHASE_REDUCE, static_cast<cudaStream_t>(stream));
 }
 int mxk_launch_full(const MxkLaunchArgs* a, void* stream) {
     KArgs k;
     if (int rc = build_kargs(a, &k)) return rc;
     if (!k.y && !k.y_bf16) return fail(MXK_ERR_BAD_ARG, "y or y_bf16 must be non-null");
-    if (int rc = launch_route_setup(k, static_cast<cudaStream_t>(stream))) return rc;
-    if (int rc = launch_dispatch_gemm(k, static_cast<cudaStream_t>(stream))) return rc;
-    return launch_reduce_k(k, static_cast<cudaStream_t>(stream));
+    return launch_mega(k, kPhaseAll, static_cast<cudaStream_t>(stream));
 }
-int mxk_kernels_per_layer(void) { return 5; }
+int mxk_kernels_per_layer(void) { return 1; }
 
 int mxk_launch_full_static(const MxkLaunchArgs* a, void* stream) {
     if (!a) return fail(MXK_ERR_BAD_ARG, "null launch args");
@@ -756,22 +481,14 @@ int mxk_launch_full_static(const MxkLaunchArgs* a, void* stream) {
     KArgs k;
     if (int rc = build_kargs(&b, &k)) return rc;
     if (!k.y && !k.y_bf16) return fail(MXK_ERR_BAD_ARG, "y or y_bf16 must be non-null");
-    if (int rc = launch_route_setup(k, st)) return rc;
-    if (int rc = launch_dispatch_gemm(k, st)) return rc;
-    return launch_reduce_k(k, st);
+    return launch_mega(k, kPhaseAll, st);
 }
 int64_t mxk_static_scratch_bytes(void) { return (int64_t)kStaticScratchBytes; }
 
 int mxk_launch_phases(const MxkLaunchArgs* a, int phase_mask, void* stream) {
     KArgs k;
     if (int rc = build_kargs(a, &k)) return rc;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (phase_mask & MXK_PHASE_ROUTE) if (int rc = launch_route(k, st)) return rc;
-    if (phase_mask & MXK_PHASE_SETUP) if (int rc = launch_setup(k, st)) return rc;
-    if (phase_mask & MXK_PHASE_DISPATCH) if (int rc = launch_dispatch(k, st)) return rc;
-    if (phase_mask & MXK_PHASE_GEMM) if (int rc = launch_gemm(k, st)) return rc;
-    if (phase_mask & MXK_PHASE_REDUCE) if (int rc = launch_reduce_k(k, st)) return rc;
-    return 0;
+    return launch_mega(k, phase_mask, static_cast<cudaStream_t>(stream));
 }
 
 int mxk_launch_empty(int grid, int threads, int64_t smem, void* stream) {
@@ -792,8 +509,7 @@ int mxk_fill_weights(uint8_t* w, int64_t n_rows, int32_t k_cols, uint32_t seed, 
 
 int mxk_dump_kernel_resources(void) {
     struct { const char* name; const void* fn; } ks[] = {
-        {"k_route", (const void*)k_route}, {"k_setup", (const void*)k_setup}, {"k_dispatch", (const void*)k_dispatch},
-        {"k_gemm", (const void*)k_gemm}, {"k_reduce", (const void*)k_reduce}};
+        {"k_mega", (const void*)k_mega}, {"k_fill_weights", (const void*)k_fill_weights}};
     for (auto& k : ks) {
         cudaFuncAttributes at;
         cudaError_t e = cudaFuncGetAttributes(&at, k.fn);
@@ -801,7 +517,7 @@ int mxk_dump_kernel_resources(void) {
         std::printf("[RES] %-10s regs=%d local=%zu static_smem=%zu max_threads=%d\n", k.name, at.numRegs,
                     at.localSizeBytes, at.sharedSizeBytes, at.maxThreadsPerBlock);
     }
-    std::printf("[RES] k_gemm dynamic smem=%d threads=%d\n", kGemmSmem, kGemmThreads);
+    std::printf("[RES] k_mega dynamic smem=%d threads=%d\n", kGemmSmem, kGemmThreads);
     return 0;
 }
 

@@ -1,0 +1,356 @@
+// ============================================================================
+// mxk_phases.cuh — the non-GEMM phases of the MoE layer as CTA-cooperative
+// device functions of the persistent kernel (k_mega in mxk_kernels.cu).  Every
+// function is called by ALL threads of a CTA; block size is read at run time.
+//
+//   route_phase     per-rank route build: deterministic slot per (token,k) pair,
+//                   scatter of pair indices into the owner ranks' tables, count
+//                   publish; CTA 0 then writes the row checksums, releases the
+//                   cross-rank barrier flags and advances the launch counter
+//                   (reference: route_build_body / publish_counts_body /
+//                    xbar_route_ready_body, src/prologue.cuh:126-256, src/flags.cuh:284-377)
+//   setup_phase     CTA 0: barrier wait, prefix table, windows, cost-ordered task
+//                   list; the other CTAs wait for its "set-up done" flag
+//                   (reference: task_setup_body, src/prologue.cuh:269-498)
+//   dispatch_phase  EP dispatch: one warp per pool row pulls the routed FP8 row
+//                   and its 1x128 scales from the source rank's symmetric buffer
+//                   (reference: r19_pull_flags, src/compute_big.cuh:1691-1946)
+//   reduce_phase    top-k weighted sum at the source rank
+//                   (reference: reduce_tile_body, src/combine.cuh:488-656)
+// ============================================================================
+#pragma once
+
+// Slots are handed out in ascending pair index idx = token*topk + k, so every
+// table row (and with it the pool row order) is deterministic; the reference
+// uses a shared-memory atomicAdd and accepts any order (src/prologue.cuh:164-180).
+__device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_wtot /*[32]*/) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nthr = blockDim.x, nwarps = nthr >> 5;
+    const int par = (int)(epoch & 1);
+    const int np = a.tokens * a.topk;
+    const int64_t* ti = a.topk_idx;
+    uint8_t* pair_state = a.rwk + a.L.pair_state_off;
+    int* rsc = reinterpret_cast<int*>(a.rwk + a.L.route_slot_counts_off);
+
+    // Arrival counters of the rows peers will push to this rank in this launch.
+    // Safe to clear here: peers push only after this rank has arrived at the
+    // barrier below, and the previous launch's reduce has consumed them.
+    unsigned* cnt = reinterpret_cast<unsigned*>(a.unk + a.L.combine_cnt_off);
+    for (int i = blockIdx.x * nthr + tid; i < a.topk * a.cap; i += gridDim.x * nthr) cnt[i] = 0;
+
+    for (int e = blockIdx.x; e < a.E; e += gridDim.x) {
+        const int dst = e / a.EPR, le = e % a.EPR;
+        uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[dst]);
+        uint32_t* tbl = reinterpret_cast<uint32_t*>(peer_unk + a.L.src_index_table_off) +
+                        (((size_t)par * a.EPR + le) * a.R + a.rank) * (size_t)a.slot_cap;
+        int base = 0;
+        for (int p0 = 0; p0 < np; p0 += nthr) {
+            const int p = p0 + tid;
+            const bool hit = p < np && ti[p] == (int64_t)e;
+            const unsigned bal = __ballot_sync(0xFFFFFFFFu, hit);
+            if (lane == 0) s_wtot[warp] = __popc(bal);
+            __syncthreads();
+            int wpre = 0, tot = 0;
+            for (int w = 0; w < nwarps; ++w) {
+                const int v = s_wtot[w];
+                wpre += (w < warp) ? v : 0;
+                tot += v;
+            }
+            if (hit) {
+                const int slot = base + wpre + __popc(bal & ((1u << lane) - 1u));
+                const bool ok = slot < a.slot_cap;  // over capacity: dropped (src/prologue.cuh:171-174)
+                if (ok) st_relaxed_sys(tbl + slot, (uint32_t)p);
+                pair_state[p] = ok ? 1 : 0;
+            }
+            base += tot;
+            __syncthreads();
+        }
+        if (tid == 0) {
+            const int c = base < a.slot_cap ? base : a.slot_cap;
+            rsc[e] = c;
+            uint32_t* recv = reinterpret_cast<uint32_t*>(peer_unk + a.L.expert_recv_counts_off) +
+                             ((size_t)par * a.R + a.rank) * a.L.recv_stride;
+            st_relaxed_sys(recv + le, (uint32_t)c);
+        }
+    }
+    if (blockIdx.x == 0)  // invalid expert ids (negative / >= E) take no slot (src/prologue.cuh:166-167)
+        for (int p = tid; p < np; p += nthr)
+            if ((uint64_t)ti[p] >= (uint64_t)a.E) pair_state[p] = 0;
+
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) atomicAdd(&f->route_blocks_done, 1u);
+    if (blockIdx.x != 0) return;
+
+    // ---- CTA 0: every CTA's tables are out; close the rows and signal the peers
+    if (tid == 0) {
+        const unsigned want = gridDim.x;
+        if (!spin_until([&] { return ld_acquire_gpu(&f->route_blocks_done) >= want; }, a.local_wait_ns, nullptr))
+            raise_status(f, MXK_DEV_TIMEOUT_PIPE, 2);
+    }
+    __syncthreads();
+    // Row checksum word ~(sum + 1) at index EPR of each row sent (src/prologue.cuh:248-255).
+    for (int d = tid; d < a.R; d += nthr) {
+        uint32_t csum = 0;
+        for (int le = 0; le < a.EPR; ++le) csum += (uint32_t)ld_relaxed_gpu(rsc + d * a.EPR + le);
+        uint32_t* recv = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) +
+                                                     a.L.expert_recv_counts_off) +
+                         ((size_t)par * a.R + a.rank) * a.L.recv_stride;
+        st_relaxed_sys(recv + a.EPR, ~(csum + 1u));
+    }
+    __threadfence_system();
+    __syncthreads();
+    // Barrier arrival: publish this launch's epoch into every peer's slot for this rank.
+    for (int d = tid; d < a.R; d += nthr) {
+        uint32_t* xb = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) + a.L.xbar_off) +
+                       (size_t)a.rank * a.L.xbar_stride;
+        st_release_sys(xb, (uint32_t)epoch);
+    }
+    if (tid == 0) {
+        f->route_blocks_done = 0;
+        f->current_time = epoch;  // every CTA has read the old value before arriving above
+    }
+    __syncthreads();
+}
+
+// CTA 0 builds the tables; `s_i` is scratch shared memory of 4*EPR + 2 ints.
+__device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch, int* s_i) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int EPR = a.EPR, R = a.R;
+    int* s_tot = s_i;                  // [EPR]
+    int* s_order = s_tot + EPR;        // [EPR] expert at sorted position p
+    int* s_first = s_order + EPR;      // [EPR+1] first window of position p
+    int* s_base = s_first + EPR + 1;   // [EPR+1] first pool row of expert le
+    const int par = (int)(epoch & 1);
+
+    // Cross-rank barrier: every rank has published its routes for this epoch.
+    for (int r = tid; r < R; r += nthr) {
+        const uint32_t* xb = reinterpret_cast<const uint32_t*>(a.unk + a.L.xbar_off) + (size_t)r * a.L.xbar_stride;
+        const bool ok = spin_until([&] { return (int32_t)(ld_acquire_sys(xb) - (uint32_t)epoch) >= 0; },
+                                   a.remote_wait_ns, nullptr);
+        if (!ok) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 0);
+    }
+    __syncthreads();
+
+    const uint32_t* recv = reinterpret_cast<const uint32_t*>(a.unk + a.L.expert_recv_counts_off) +
+                           (size_t)par * R * a.L.recv_stride;
+    int* prefix = reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off);
+    for (int le = tid; le < EPR; le += nthr) {
+        int c = 0;
+        for (int r = 0; r < R; ++r) {
+            prefix[le * (R + 1) + r] = c;
+            c += (int)ld_relaxed_sys(recv + (size_t)r * a.L.recv_stride + le);
+        }
+        prefix[le * (R + 1) + R] = c;
+        s_tot[le] = c;
+    }
+    __syncthreads();
+    // Experts by descending row count, ties by index: the hottest experts' windows
+    // are claimed first so the dynamic queue ends on the cheap ones (LPT order).
+    for (int le = tid; le < EPR; le += nthr) {
+        const int c = s_tot[le];
+        int rk = 0;
+        for (int j = 0; j < EPR; ++j) {
+            const int cj = s_tot[j];
+            rk += (cj > c || (cj == c && j < le)) ? 1 : 0;
+        }
+        s_order[rk] = le;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int acc = 0;
+        for (int le = 0; le < EPR; ++le) { s_base[le] = acc; acc += s_tot[le]; }
+        s_base[EPR] = acc;
+        int nw = 0;
+        for (int p = 0; p < EPR; ++p) {
+            s_first[p] = nw;
+            const int c = s_tot[s_order[p]];
+            nw += c > 0 ? (c + a.win_cap - 1) / a.win_cap : 0;
+        }
+        s_first[EPR] = nw;
+    }
+    __syncthreads();
+    int* row_base = reinterpret_cast<int*>(a.rwk + a.L.expert_row_base_off);
+    int* first_win = reinterpret_cast<int*>(a.rwk + a.L.expert_first_win_off);
+    for (int le = tid; le <= EPR; le += nthr) row_base[le] = s_base[le];
+    for (int p = tid; p < EPR; p += nthr) first_win[s_order[p]] = s_first[p];
+
+    int n_windows = s_first[EPR];
+    const int total_rows = s_base[EPR];
+    const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
+    bool overflow = false;
+    if (n_windows > a.L.max_windows || (long long)n_windows * (nt1 + nt2) > a.L.max_tasks ||
+        total_rows > a.L.pool_rows) {
+        overflow = true;
+        n_windows = 0;
+    }
+    int4* windows = reinterpret_cast<int4*>(a.rwk + a.L.windows_off);
+    int4* tasks = reinterpret_cast<int4*>(a.rwk + a.L.tasks_off);
+    uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
+    uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off);
+    const int n_l1 = n_windows * nt1;
+    if (!overflow)
+        for (int p = 0; p < EPR; ++p) {
+            const int e = s_order[p], c = s_tot[e];
+            const int fw = s_first[p], nw = s_first[p + 1] - fw;
+            if (nw == 0) break;  // sorted: every later expert is empty too
+            for (int w = tid; w < nw; w += nthr) {
+                const int rows = min(a.win_cap, c - w * a.win_cap);
+                windows[fw + w] = make_int4(e, s_base[e] + w * a.win_cap, rows, 0);
+                l1_done[fw + w] = 0;
+                pool_ready[fw + w] = 0;
+            }
+            for (int i = tid; i < nt1 * nw; i += nthr) {
+                const int nt = i / nw, w = i % nw;
+                tasks[fw * nt1 + i] = make_int4(0, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
+            }
+            for (int i = tid; i < nt2 * nw; i += nthr) {
+                const int nt = i / nw, w = i % nw;
+                tasks[n_l1 + fw * nt2 + i] = make_int4(1, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
+            }
+        }
+    if (tid == 0) {
+        if (overflow) raise_status(f, MXK_DEV_BAD_TABLE, 3);
+        f->n_windows = n_windows;
+        f->n_l1_tasks = n_l1;
+        f->n_tasks = n_windows * (nt1 + nt2);
+        f->total_rows = overflow ? 0 : total_rows;
+        f->task_counter = gridDim.x;  // first task of a CTA is its index
+        for (int i = 0; i < 16; ++i) f->ticks[i] = 0;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) st_release_gpu(&f->setup_epoch, (uint32_t)epoch);
+}
+
+// Every other CTA waits until CTA 0 has published the tables of this epoch.
+__device__ bool setup_phase_wait(const KArgs& a, DevFlags* f, long long epoch, int* s_flag) {
+    if (threadIdx.x == 0) {
+        const bool ok = spin_until([&] { return ld_acquire_gpu(&f->setup_epoch) == (uint32_t)epoch; },
+                                   a.remote_wait_ns + a.local_wait_ns, nullptr);
+        if (!ok) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 1);
+        *s_flag = ok ? 1 : 0;
+    }
+    __syncthreads();
+    return *s_flag != 0;
+}
+
+// One warp per pool row: locate (expert, source rank, slot), read the pair index
+// the source wrote, then pull the row's H bytes and H/128 scale bytes from the
+// source rank's symmetric buffer with 16-byte loads over NVLink; finally count
+// the row into its window's pool_ready counter (the TMA producer of the GEMM
+// phase waits on it).
+__device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch) {
+    const int lane = threadIdx.x & 31;
+    const int nwarps_cta = blockDim.x >> 5;
+    const int gwarp = blockIdx.x * nwarps_cta + (threadIdx.x >> 5);
+    const int nwarps = gridDim.x * nwarps_cta;
+    const int total = ld_relaxed_gpu(&f->total_rows);
+    const int par = (int)(epoch & 1);
+    const int R = a.R, EPR = a.EPR, H = a.H;
+    const int* row_base = reinterpret_cast<const int*>(a.rwk + a.L.expert_row_base_off);
+    const int* first_win = reinterpret_cast<const int*>(a.rwk + a.L.expert_first_win_off);
+    const int* prefix = reinterpret_cast<const int*>(a.rwk + a.L.prefix_tbl_off);
+    const uint32_t* tbl = reinterpret_cast<const uint32_t*>(a.unk + a.L.src_index_table_off) +
+                          (size_t)par * EPR * R * a.slot_cap;
+    uint8_t* pool = a.rwk + a.L.pool_off;
+    uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
+    int4* meta = reinterpret_cast<int4*>(a.rwk + a.L.row_meta_off);
+    uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off);
+    const int kb = H / 128;
+
+    for (int g = gwarp; g < total; g += nwarps) {
+        int lo = 0, hi = EPR;  // largest le with row_base[le] <= g
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (ld_relaxed_gpu(row_base + mid) <= g) lo = mid; else hi = mid;
+        }
+        const int le = lo;
+        const int gl = g - ld_relaxed_gpu(row_base + le);
+        const int* pf = prefix + le * (R + 1);
+        int slo = 0, shi = R;  // largest src with pf[src] <= gl (src/compute_big.cuh:1760-1769)
+        while (shi - slo > 1) {
+            const int mid = (slo + shi) >> 1;
+            if (ld_relaxed_gpu(pf + mid) <= gl) slo = mid; else shi = mid;
+        }
+        const int src = slo, slot = gl - ld_relaxed_gpu(pf + src);
+        const uint32_t idx = ld_relaxed_sys(tbl + ((size_t)le * R + src) * a.slot_cap + slot);
+        const int token = (int)(idx / (uint32_t)a.topk), k = (int)(idx % (uint32_t)a.topk);
+        const uint8_t* peer = a.peer_bases[src];
+        const uint4* srow = reinterpret_cast<const uint4*>(peer + a.x_off + (size_t)token * H);
+        uint4* drow = reinterpret_cast<uint4*>(pool + (size_t)g * H);
+        const int n16 = H / 16;
+#pragma unroll 4
+        for (int i = lane; i < n16; i += 32) drow[i] = ld_relaxed_sys_v4(srow + i);
+        if (a.scaled) {
+            const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
+            for (int i = lane; i < a.L.sf_stride_h; i += 32)
+                pool_sf[(size_t)g * a.L.sf_stride_h + i] = i < kb ? ld_relaxed_sys_u8(ssf + i) : (uint8_t)127;
+        }
+        if (lane == 0) {
+            const float w = __uint_as_float(ld_relaxed_sys(reinterpret_cast<const uint32_t*>(peer + a.weights_off) + (size_t)token * a.topk + k));
+            meta[g] = make_int4(src, token, k, __float_as_int(w));
+        }
+        // the row is complete: every lane makes its stores visible at GPU scope and to TMA
+        // (a release by lane 0 alone does not cover the other lanes' stores), then count the row
+        __threadfence();
+        fence_proxy_async_global();
+        __syncwarp();
+        if (lane == 0) red_release_gpu_add(pool_ready + ld_relaxed_gpu(first_win + le) + gl / a.win_cap, 1u);
+    }
+}
+
+// y[t] = sum over k (ascending, FP32, product then sum) of w_k * bf16 row_k
+// (reference: src/combine.cuh:601-627, src/bench_check.cuh:484-499).
+__device__ void reduce_phase(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, float* s_w /*[64]*/) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int H = a.H, topk = a.topk;
+    const uint8_t* pair_state = a.rwk + a.L.pair_state_off;
+    const uint32_t* cnt = reinterpret_cast<const uint32_t*>(a.unk + a.L.combine_cnt_off);
+    const uint16_t* rows = reinterpret_cast<const uint16_t*>(a.unk + a.L.combine_rows_off);
+    const float* tw = reinterpret_cast<const float*>(a.self + a.weights_off);
+    const uint32_t need = (uint32_t)(H / kBlockN) * 2u;
+    for (int t = blockIdx.x; t < a.tokens; t += gridDim.x) {
+        if (tid < topk) {
+            int ok = ld_relaxed_gpu_u8(pair_state + t * topk + tid);
+            if (ok && !a.skip_combine) {
+                const uint32_t* c = cnt + (size_t)tid * a.cap + t;
+                if (!spin_until([&] { return ld_acquire_sys(c) >= need; }, a.remote_wait_ns, nullptr)) {
+                    raise_status(f, MXK_DEV_TIMEOUT_REDUCE, 4);
+                    ok = 0;
+                }
+            }
+            s_ok[tid] = ok;
+            s_w[tid] = tw[(size_t)t * topk + tid];
+        }
+        __syncthreads();
+        for (int c8 = tid; c8 < H / 8; c8 += nthr) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+            for (int k = 0; k < topk; ++k) {
+                if (!s_ok[k]) continue;
+                const float w = s_w[k];
+                const uint4 v = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(rows + ((size_t)k * a.cap + t) * H) + c8);
+                const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(u[j] << 16), w));
+                    acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(u[j] & 0xFFFF0000u), w));
+                }
+            }
+            if (a.y) {
+                float4* o = reinterpret_cast<float4*>(a.y + (size_t)t * H + c8 * 8);
+                o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            }
+            if (a.y_bf16) {
+                uint4 o;
+                o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+                o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+                *reinterpret_cast<uint4*>(a.y_bf16 + (size_t)t * H + c8 * 8) = o;
+            }
+        }
+        __syncthreads();
+    }
+}

@@ -97,6 +97,31 @@ def _run_case(case, expert_window=128, full_stage_checks=True, e2e_tol=1e-2):
                 assert err <= e2e_tol, f"rank {r}: end-to-end relative L2 {err}"
     finally:
         w.destroy()
+    if case.R == 1:
+        _run_fused(case, ref[0].y, expert_window, e2e_tol)
+
+
+def _run_fused(case, want_y, expert_window, e2e_tol):
+    """The same case through ONE launch of the whole layer (mxk_launch_full via fp8_mega_moe),
+    twice on the same buffers: phases then overlap inside the persistent kernel."""
+    import mini_mega_b200 as mm
+    from gpu_world import dev_weights, load_inputs
+    buf = mm.get_symm_buffer_for_mega_moe(None, case.E, case.cap, case.topk, case.H, case.I,
+                                          expert_window=expert_window)
+    try:
+        load_inputs(case, [buf])
+        l1, l2 = dev_weights(case, 0)
+        T = case.tokens[0]
+        for _ in range(2):
+            y = torch.zeros((T, case.H), dtype=torch.bfloat16, device="cuda")
+            mm.fp8_mega_moe(y, l1, l2, buf)
+            torch.cuda.synchronize()
+            st = buf.status()
+            assert st.status == 0, f"device status {st.status} dbg {list(st.dbg)}"
+            err = orc.rel_l2(y.float().cpu().numpy(), orc.bf16_to_f32(orc.f32_to_bf16(want_y)))
+            assert err <= e2e_tol, f"fused launch: end-to-end relative L2 {err}"
+    finally:
+        buf.destroy()
 
 
 def test_toy_scaled():
