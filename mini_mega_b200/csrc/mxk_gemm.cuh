@@ -105,6 +105,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             tma_prefetch_desc(&tm_w1); tma_prefetch_desc(&tm_w2);
             uint32_t stage = 0, phase = 0;
             long long w_empty = 0, w_gate = 0, w_ring = 0;
+            const uint64_t stream_policy = l2_policy_evict_first();
             for (uint32_t it = 0;; ++it) {
                 const uint32_t slot = it % kTaskRing;
                 if (!MXK_TIMED(w_ring, mbar_wait(&S->task_empty[slot], ((it / kTaskRing) & 1) ^ 1, wait_ns, abort_flag))) {
@@ -140,8 +141,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                     uint8_t* sa = tiles + stage * kStageBytes;
                     mbar_expect_tx(&S->full[stage], kStageBytes);
                     tma_load_2d(sa, ma, kb * kBlockK, row0, &S->full[stage]);
-                    tma_load_2d(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[stage]);
-                    tma_load_2d(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[stage]);
+                    tma_load_2d_hint(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[stage], stream_policy);
+                    tma_load_2d_hint(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[stage], stream_policy);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
                 if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; break; }
@@ -420,7 +421,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                     }
                     // release at system scope: this thread's row segment is visible before the count
                     uint32_t* cnt = reinterpret_cast<uint32_t*>(peer_unk + a.L.combine_cnt_off) + (size_t)m.z * a.cap + m.y;
-                    red_release_sys_add(cnt, 1u);
+                    if (a.R > 1) red_release_sys_add(cnt, 1u); else red_release_gpu_add(cnt, 1u);
                 }
             }
             t_busy += clock64() - t_busy0;

@@ -34,13 +34,16 @@ struct DevFlags {  // head of rwk (flags_off)
     long long current_time;      // completed prologues; the running launch is +1
     unsigned route_blocks_done;
     unsigned task_counter;
-    unsigned setup_epoch;        // epoch whose tables CTA 0 has published
-    unsigned pad_;
+    unsigned pad0_[2];
     int n_tasks, n_l1_tasks, n_windows, total_rows;
     int status;
     int dbg[8];
     unsigned long long ticks[16];
+    unsigned long long dbg_ts[8];  // set-up leader time stamps (diagnostic, MXK_TICKS=1)
+    unsigned setup_epoch;        // epoch whose tables CTA 0 has published; alone in its 128-byte
+    unsigned pad2_[31];          // line: every CTA polls it while CTA 0 writes the fields above
 };
+static_assert(sizeof(DevFlags) <= 1024, "status header must fit its 1 KB slot");
 
 struct KArgs {
     int R, rank, EPR, E, topk, H, I, cap, slot_cap, tokens, win_cap;
@@ -115,9 +118,11 @@ k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap 
     // dispatch, GEMM, reduce; CTA 0 for the first two, maximum over CTAs for the rest).
     const bool stamp = a.ticks != 0 && threadIdx.x == 0;
     const uint64_t t0 = stamp ? gtimer_ns() : 0;
+    if (stamp && blockIdx.x == 0 && (phase_mask & MXK_PHASE_SETUP))
+        for (int i = 0; i < 16; ++i) f->ticks[i] = 0;  // other CTAs add to them only after the set-up flag
 
     if (phase_mask & MXK_PHASE_ROUTE) route_phase(a, f, epoch, s_small);
-    if (stamp && blockIdx.x == 0) f->ticks[9] = gtimer_ns() - t0;
+    if (stamp && blockIdx.x == 0) { f->ticks[9] = gtimer_ns() - t0; f->ticks[14] -= t0; f->ticks[15] -= t0; }
 
     bool tables_ok = true;
     if (phase_mask & MXK_PHASE_SETUP) {
@@ -128,7 +133,10 @@ k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap 
     }
     if (stamp && blockIdx.x == 0) f->ticks[10] = gtimer_ns() - t0;
 
-    if ((phase_mask & MXK_PHASE_DISPATCH) && tables_ok) dispatch_phase(a, f, epoch);
+    if ((phase_mask & MXK_PHASE_DISPATCH) && tables_ok) {
+        dispatch_phase(a, f, epoch, reinterpret_cast<int*>(tiles));  // tile region still idle: scratch
+        __syncthreads();
+    }
     if (stamp) atomicMax(&f->ticks[11], (unsigned long long)(gtimer_ns() - t0));
 
     if (do_gemm) {

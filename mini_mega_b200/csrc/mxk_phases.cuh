@@ -77,10 +77,12 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
         for (int p = tid; p < np; p += nthr)
             if ((uint64_t)ti[p] >= (uint64_t)a.E) pair_state[p] = 0;
 
-    __threadfence_system();
+    if (a.ticks && blockIdx.x == 0 && tid == 0) f->ticks[14] = gtimer_ns();
+    fence_world(a.R > 1);  // this thread's table / count stores are out before the CTA arrives
     __syncthreads();
     if (tid == 0) atomicAdd(&f->route_blocks_done, 1u);
     if (blockIdx.x != 0) return;
+    if (a.ticks && tid == 0) f->ticks[15] = gtimer_ns();
 
     // ---- CTA 0: every CTA's tables are out; close the rows and signal the peers
     if (tid == 0) {
@@ -98,9 +100,9 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
                          ((size_t)par * a.R + a.rank) * a.L.recv_stride;
         st_relaxed_sys(recv + a.EPR, ~(csum + 1u));
     }
-    __threadfence_system();
-    __syncthreads();
-    // Barrier arrival: publish this launch's epoch into every peer's slot for this rank.
+    // Barrier arrival: publish this launch's epoch into every peer's slot for this rank.  The
+    // release of thread d covers its own checksum store; the other CTAs' stores were fenced
+    // before their arrival, which this CTA acquired above.
     for (int d = tid; d < a.R; d += nthr) {
         uint32_t* xb = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) + a.L.xbar_off) +
                        (size_t)a.rank * a.L.xbar_stride;
@@ -126,11 +128,14 @@ __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch,
     // Cross-rank barrier: every rank has published its routes for this epoch.
     for (int r = tid; r < R; r += nthr) {
         const uint32_t* xb = reinterpret_cast<const uint32_t*>(a.unk + a.L.xbar_off) + (size_t)r * a.L.xbar_stride;
-        const bool ok = spin_until([&] { return (int32_t)(ld_acquire_sys(xb) - (uint32_t)epoch) >= 0; },
+        const bool ok = spin_until([&] { return (int32_t)(ld_relaxed_sys(xb) - (uint32_t)epoch) >= 0; },
                                    a.remote_wait_ns, nullptr);
         if (!ok) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 0);
     }
+    fence_world(a.R > 1);  // acquire side of the barrier, once for all polled flags
     __syncthreads();
+    const bool ts = a.ticks != 0 && tid == 0;
+    if (ts) f->dbg_ts[0] = gtimer_ns();
 
     const uint32_t* recv = reinterpret_cast<const uint32_t*>(a.unk + a.L.expert_recv_counts_off) +
                            (size_t)par * R * a.L.recv_stride;
@@ -145,6 +150,7 @@ __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch,
         s_tot[le] = c;
     }
     __syncthreads();
+    if (ts) f->dbg_ts[1] = gtimer_ns();
     // Experts by descending row count, ties by index: the hottest experts' windows
     // are claimed first so the dynamic queue ends on the cheap ones (LPT order).
     for (int le = tid; le < EPR; le += nthr) {
@@ -157,19 +163,30 @@ __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch,
         s_order[rk] = le;
     }
     __syncthreads();
-    if (tid == 0) {
-        int acc = 0;
-        for (int le = 0; le < EPR; ++le) { s_base[le] = acc; acc += s_tot[le]; }
-        s_base[EPR] = acc;
-        int nw = 0;
-        for (int p = 0; p < EPR; ++p) {
-            s_first[p] = nw;
-            const int c = s_tot[s_order[p]];
-            nw += c > 0 ? (c + a.win_cap - 1) / a.win_cap : 0;
+    if (ts) f->dbg_ts[2] = gtimer_ns();
+    if (tid < 32) {
+        // exclusive scans by warp 0: pool rows in expert-index order, windows in sorted order
+        const int lane = tid;
+        int carry_rows = 0, carry_win = 0;
+        for (int b = 0; b < EPR; b += 32) {
+            const int i = b + lane;
+            const int c = i < EPR ? s_tot[i] : 0;
+            const int cs = i < EPR ? s_tot[s_order[i]] : 0;
+            const int w = cs > 0 ? (cs + a.win_cap - 1) / a.win_cap : 0;
+            int ic = c, iw = w;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int uc = __shfl_up_sync(0xFFFFFFFFu, ic, d), uw = __shfl_up_sync(0xFFFFFFFFu, iw, d);
+                if (lane >= d) { ic += uc; iw += uw; }
+            }
+            if (i < EPR) { s_base[i] = carry_rows + ic - c; s_first[i] = carry_win + iw - w; }
+            carry_rows += __shfl_sync(0xFFFFFFFFu, ic, 31);
+            carry_win += __shfl_sync(0xFFFFFFFFu, iw, 31);
         }
-        s_first[EPR] = nw;
+        if (lane == 0) { s_base[EPR] = carry_rows; s_first[EPR] = carry_win; }
     }
     __syncthreads();
+    if (ts) f->dbg_ts[3] = gtimer_ns();
     int* row_base = reinterpret_cast<int*>(a.rwk + a.L.expert_row_base_off);
     int* first_win = reinterpret_cast<int*>(a.rwk + a.L.expert_first_win_off);
     for (int le = tid; le <= EPR; le += nthr) row_base[le] = s_base[le];
@@ -189,26 +206,30 @@ __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch,
     uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
     uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off);
     const int n_l1 = n_windows * nt1;
-    if (!overflow)
-        for (int p = 0; p < EPR; ++p) {
+    if (!overflow) {
+        // one warp per expert (sorted position p), lanes over its windows and tasks
+        const int lane = tid & 31, wid = tid >> 5, nwarps = nthr >> 5;
+        for (int p = wid; p < EPR; p += nwarps) {
             const int e = s_order[p], c = s_tot[e];
             const int fw = s_first[p], nw = s_first[p + 1] - fw;
             if (nw == 0) break;  // sorted: every later expert is empty too
-            for (int w = tid; w < nw; w += nthr) {
+            for (int w = lane; w < nw; w += 32) {
                 const int rows = min(a.win_cap, c - w * a.win_cap);
                 windows[fw + w] = make_int4(e, s_base[e] + w * a.win_cap, rows, 0);
                 l1_done[fw + w] = 0;
                 pool_ready[fw + w] = 0;
             }
-            for (int i = tid; i < nt1 * nw; i += nthr) {
+            for (int i = lane; i < nt1 * nw; i += 32) {
                 const int nt = i / nw, w = i % nw;
                 tasks[fw * nt1 + i] = make_int4(0, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
             }
-            for (int i = tid; i < nt2 * nw; i += nthr) {
+            for (int i = lane; i < nt2 * nw; i += 32) {
                 const int nt = i / nw, w = i % nw;
                 tasks[n_l1 + fw * nt2 + i] = make_int4(1, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
             }
         }
+    }
+    if (ts) f->dbg_ts[4] = gtimer_ns();
     if (tid == 0) {
         if (overflow) raise_status(f, MXK_DEV_BAD_TABLE, 3);
         f->n_windows = n_windows;
@@ -216,18 +237,22 @@ __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch,
         f->n_tasks = n_windows * (nt1 + nt2);
         f->total_rows = overflow ? 0 : total_rows;
         f->task_counter = gridDim.x;  // first task of a CTA is its index
-        for (int i = 0; i < 16; ++i) f->ticks[i] = 0;
     }
     __threadfence();
     __syncthreads();
+    if (ts) f->dbg_ts[5] = gtimer_ns();
     if (tid == 0) st_release_gpu(&f->setup_epoch, (uint32_t)epoch);
+    if (ts) f->dbg_ts[6] = gtimer_ns();
 }
 
 // Every other CTA waits until CTA 0 has published the tables of this epoch.
 __device__ bool setup_phase_wait(const KArgs& a, DevFlags* f, long long epoch, int* s_flag) {
     if (threadIdx.x == 0) {
-        const bool ok = spin_until([&] { return ld_acquire_gpu(&f->setup_epoch) == (uint32_t)epoch; },
+        // relaxed polls with a short back-off (148 CTAs watch this word while CTA 0 works),
+        // one acquire fence once it flips
+        const bool ok = spin_until([&] { if (ld_relaxed_gpu(&f->setup_epoch) == (uint32_t)epoch) return true; __nanosleep(200); return false; },
                                    a.remote_wait_ns + a.local_wait_ns, nullptr);
+        fence_acq_rel_gpu();
         if (!ok) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 1);
         *s_flag = ok ? 1 : 0;
     }
@@ -240,7 +265,7 @@ __device__ bool setup_phase_wait(const KArgs& a, DevFlags* f, long long epoch, i
 // source rank's symmetric buffer with 16-byte loads over NVLink; finally count
 // the row into its window's pool_ready counter (the TMA producer of the GEMM
 // phase waits on it).
-__device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch) {
+__device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_tab) {
     const int lane = threadIdx.x & 31;
     const int nwarps_cta = blockDim.x >> 5;
     const int gwarp = blockIdx.x * nwarps_cta + (threadIdx.x >> 5);
@@ -248,9 +273,6 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch) {
     const int total = ld_relaxed_gpu(&f->total_rows);
     const int par = (int)(epoch & 1);
     const int R = a.R, EPR = a.EPR, H = a.H;
-    const int* row_base = reinterpret_cast<const int*>(a.rwk + a.L.expert_row_base_off);
-    const int* first_win = reinterpret_cast<const int*>(a.rwk + a.L.expert_first_win_off);
-    const int* prefix = reinterpret_cast<const int*>(a.rwk + a.L.prefix_tbl_off);
     const uint32_t* tbl = reinterpret_cast<const uint32_t*>(a.unk + a.L.src_index_table_off) +
                           (size_t)par * EPR * R * a.slot_cap;
     uint8_t* pool = a.rwk + a.L.pool_off;
@@ -258,30 +280,55 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch) {
     int4* meta = reinterpret_cast<int4*>(a.rwk + a.L.row_meta_off);
     uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off);
     const int kb = H / 128;
+    if (blockIdx.x * nwarps_cta >= total) return;  // no row for this CTA (uniform per CTA)
+
+    // Row-lookup tables of this launch, copied once per CTA into shared memory: the per-row
+    // searches would otherwise be chains of dependent global loads.
+    int* row_base = s_tab;                  // [EPR+1]
+    int* first_win = row_base + EPR + 1;    // [EPR]
+    int* prefix = first_win + EPR;          // [EPR][R+1]
+    {
+        const int* g_base = reinterpret_cast<const int*>(a.rwk + a.L.expert_row_base_off);
+        const int* g_fw = reinterpret_cast<const int*>(a.rwk + a.L.expert_first_win_off);
+        const int* g_pf = reinterpret_cast<const int*>(a.rwk + a.L.prefix_tbl_off);
+        for (int i = threadIdx.x; i <= EPR; i += blockDim.x) row_base[i] = ld_relaxed_gpu(g_base + i);
+        for (int i = threadIdx.x; i < EPR; i += blockDim.x) first_win[i] = ld_relaxed_gpu(g_fw + i);
+        for (int i = threadIdx.x; i < EPR * (R + 1); i += blockDim.x) prefix[i] = ld_relaxed_gpu(g_pf + i);
+        __syncthreads();
+    }
 
     for (int g = gwarp; g < total; g += nwarps) {
         int lo = 0, hi = EPR;  // largest le with row_base[le] <= g
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
-            if (ld_relaxed_gpu(row_base + mid) <= g) lo = mid; else hi = mid;
+            if (row_base[mid] <= g) lo = mid; else hi = mid;
         }
         const int le = lo;
-        const int gl = g - ld_relaxed_gpu(row_base + le);
+        const int gl = g - row_base[le];
         const int* pf = prefix + le * (R + 1);
         int slo = 0, shi = R;  // largest src with pf[src] <= gl (src/compute_big.cuh:1760-1769)
         while (shi - slo > 1) {
             const int mid = (slo + shi) >> 1;
-            if (ld_relaxed_gpu(pf + mid) <= gl) slo = mid; else shi = mid;
+            if (pf[mid] <= gl) slo = mid; else shi = mid;
         }
-        const int src = slo, slot = gl - ld_relaxed_gpu(pf + src);
+        const int src = slo, slot = gl - pf[src];
         const uint32_t idx = ld_relaxed_sys(tbl + ((size_t)le * R + src) * a.slot_cap + slot);
         const int token = (int)(idx / (uint32_t)a.topk), k = (int)(idx % (uint32_t)a.topk);
         const uint8_t* peer = a.peer_bases[src];
         const uint4* srow = reinterpret_cast<const uint4*>(peer + a.x_off + (size_t)token * H);
         uint4* drow = reinterpret_cast<uint4*>(pool + (size_t)g * H);
         const int n16 = H / 16;
-#pragma unroll 4
-        for (int i = lane; i < n16; i += 32) drow[i] = ld_relaxed_sys_v4(srow + i);
+        // batches of 8 loads in flight per lane before the first store (the strong loads are
+        // not reordered by the compiler, so issue order is what hides the NVLink latency)
+        for (int i0 = lane; i0 < n16; i0 += 32 * 8) {
+            uint4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (i0 + 32 * j < n16) v[j] = ld_relaxed_sys_v4(srow + i0 + 32 * j);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (i0 + 32 * j < n16) drow[i0 + 32 * j] = v[j];
+        }
         if (a.scaled) {
             const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
             for (int i = lane; i < a.L.sf_stride_h; i += 32)
@@ -296,7 +343,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch) {
         __threadfence();
         fence_proxy_async_global();
         __syncwarp();
-        if (lane == 0) red_release_gpu_add(pool_ready + ld_relaxed_gpu(first_win + le) + gl / a.win_cap, 1u);
+        if (lane == 0) red_release_gpu_add(pool_ready + first_win[le] + gl / a.win_cap, 1u);
     }
 }
 
@@ -315,10 +362,11 @@ __device__ void reduce_phase(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, fl
             int ok = ld_relaxed_gpu_u8(pair_state + t * topk + tid);
             if (ok && !a.skip_combine) {
                 const uint32_t* c = cnt + (size_t)tid * a.cap + t;
-                if (!spin_until([&] { return ld_acquire_sys(c) >= need; }, a.remote_wait_ns, nullptr)) {
+                if (!spin_until([&] { return ld_relaxed_sys(c) >= need; }, a.remote_wait_ns, nullptr)) {
                     raise_status(f, MXK_DEV_TIMEOUT_REDUCE, 4);
                     ok = 0;
                 }
+                fence_world(a.R > 1);  // acquire: the counted row segments are visible
             }
             s_ok[tid] = ok;
             s_w[tid] = tw[(size_t)t * topk + tid];
@@ -328,15 +376,22 @@ __device__ void reduce_phase(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, fl
             float acc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-            for (int k = 0; k < topk; ++k) {
-                if (!s_ok[k]) continue;
-                const float w = s_w[k];
-                const uint4 v = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(rows + ((size_t)k * a.cap + t) * H) + c8);
-                const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+            for (int k0 = 0; k0 < topk; k0 += 8) {
+                uint4 v[8];  // up to 8 rows in flight, then summed in k order
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(u[j] << 16), w));
-                    acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(u[j] & 0xFFFF0000u), w));
+                for (int kk = 0; kk < 8; ++kk)
+                    if (k0 + kk < topk && s_ok[k0 + kk])
+                        v[kk] = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(rows + ((size_t)(k0 + kk) * a.cap + t) * H) + c8);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    if (k0 + kk >= topk || !s_ok[k0 + kk]) continue;
+                    const float w = s_w[k0 + kk];
+                    const uint32_t u[4] = {v[kk].x, v[kk].y, v[kk].z, v[kk].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(u[j] << 16), w));
+                        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(u[j] & 0xFFFF0000u), w));
+                    }
                 }
             }
             if (a.y) {
