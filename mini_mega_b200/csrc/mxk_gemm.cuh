@@ -38,6 +38,7 @@ constexpr int kTmemCols = 512;
 constexpr int kTmemSfCol = 256;       // scale tiles live behind the 256 accumulator columns
 constexpr int kSfRing = 8;            // shared-memory scale-tile slots (one per 4 K blocks)
 constexpr int kSfSlotBytes = 3 * 512; // A rows, weight half 0, weight half 1
+constexpr int kPrefetchBytesPerCta = 704 * 1024;  // L2 prefetch during the prologue: 148 CTAs x 704 KB = 104 MB
 constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align*/ + kSfRing * kSfSlotBytes + 8192 /*control*/;
 
 // Wait-time accounting (reference: clock64 phase stamps in local_flags.pre_ticks,

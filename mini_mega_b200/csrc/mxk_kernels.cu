@@ -121,6 +121,22 @@ k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap 
     if (stamp && blockIdx.x == 0 && (phase_mask & MXK_PHASE_SETUP))
         for (int i = 0; i < 16; ++i) f->ticks[i] = 0;  // other CTAs add to them only after the set-up flag
 
+    // While routing, barrier and dispatch run, HBM would sit idle: pull a slice of the expert
+    // weights into L2 now (any W1 tile of a non-empty expert is needed later in this layer; the
+    // streaming loads are evict-first, so these lines survive until their task comes up).
+    if (do_gemm && (phase_mask & MXK_PHASE_ROUTE) && threadIdx.x == 32) {
+        const int nt1 = a.I / 128, nkb = a.H / kBlockK;
+        const int per_cta = min(nkb, kPrefetchBytesPerCta / (2 * kABytes));
+        for (int tile = blockIdx.x; tile < a.EPR * nt1 && tile < (int)gridDim.x; tile += gridDim.x) {
+            const int e = tile / nt1, nt = tile % nt1;
+            const int row0 = e * 2 * a.I + nt * 128;
+            for (int kb = 0; kb < per_cta; ++kb) {
+                tma_prefetch_l2_2d(&tm_w1, kb * kBlockK, row0);
+                tma_prefetch_l2_2d(&tm_w1, kb * kBlockK, row0 + a.I);
+            }
+        }
+    }
+
     if (phase_mask & MXK_PHASE_ROUTE) route_phase(a, f, epoch, s_small);
     if (stamp && blockIdx.x == 0) { f->ticks[9] = gtimer_ns() - t0; f->ticks[14] -= t0; f->ticks[15] -= t0; }
 
