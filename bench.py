@@ -32,11 +32,11 @@ E_TOTAL, TOPK, H, I = 256, 8, 6144, 2048
 HBM_FALLBACK_GBS = 6650.0        # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 BF16_FALLBACK_TFLOPS = 1590.0
 NVLINK_GBS = 770.0               # measured peer copy per direction on this pool
-# DRAM traffic of k_gemm from the ncu capture summarised in profiles/k_gemm_decode_shard_E32_T16.md:
-# 1.1885 GB read+written per launch against 1.1732 GB algorithmic on the 32-expert shard.  The
+# DRAM traffic of k_mega from the ncu capture summarised in profiles/k_mega_decode_shard_E32_T16.md:
+# 1.1872 GB read+written per launch against 1.1757 GB algorithmic on the 32-expert shard.  The
 # benchmark's own launches stream more experts through the same code, so traffic is scaled from
 # that capture in proportion to the algorithmic bytes (weights dominate both).
-NCU_TRAFFIC_RATIO = 1.1885 / 1.1732
+NCU_TRAFFIC_RATIO = 1.1872 / 1.1757
 
 
 def load_peaks():
