@@ -91,7 +91,18 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
             raise_status(f, MXK_DEV_TIMEOUT_PIPE, 2);
     }
     __syncthreads();
-    // Row checksum word ~(sum + 1) at index EPR of each row sent (src/prologue.cuh:248-255).
+    // Barrier arrival: publish this launch's epoch into every peer's slot for this rank.  Every
+    // CTA fenced its table / count stores at world scope before arriving and this CTA acquired
+    // the arrivals above, so the flag itself needs no further fence (a second system-scope
+    // fence here would sit on the critical path of every rank).
+    for (int d = tid; d < a.R; d += nthr) {
+        uint32_t* xb = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) + a.L.xbar_off) +
+                       (size_t)a.rank * a.L.xbar_stride;
+        st_relaxed_sys(xb, (uint32_t)epoch);
+    }
+    // Row checksum word ~(sum + 1) at index EPR of each row sent (src/prologue.cuh:248-255).  The
+    // reference polls it to detect torn rows; here the barrier orders the rows, so the word is
+    // kept for layout parity only and is written off the critical path.
     for (int d = tid; d < a.R; d += nthr) {
         uint32_t csum = 0;
         for (int le = 0; le < a.EPR; ++le) csum += (uint32_t)ld_relaxed_gpu(rsc + d * a.EPR + le);
@@ -99,14 +110,6 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
                                                      a.L.expert_recv_counts_off) +
                          ((size_t)par * a.R + a.rank) * a.L.recv_stride;
         st_relaxed_sys(recv + a.EPR, ~(csum + 1u));
-    }
-    // Barrier arrival: publish this launch's epoch into every peer's slot for this rank.  The
-    // release of thread d covers its own checksum store; the other CTAs' stores were fenced
-    // before their arrival, which this CTA acquired above.
-    for (int d = tid; d < a.R; d += nthr) {
-        uint32_t* xb = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) + a.L.xbar_off) +
-                       (size_t)a.rank * a.L.xbar_stride;
-        st_release_sys(xb, (uint32_t)epoch);
     }
     if (tid == 0) {
         f->route_blocks_done = 0;
@@ -318,15 +321,18 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
         const uint4* srow = reinterpret_cast<const uint4*>(peer + a.x_off + (size_t)token * H);
         uint4* drow = reinterpret_cast<uint4*>(pool + (size_t)g * H);
         const int n16 = H / 16;
-        // batches of 8 loads in flight per lane before the first store (the strong loads are
-        // not reordered by the compiler, so issue order is what hides the NVLink latency)
-        for (int i0 = lane; i0 < n16; i0 += 32 * 8) {
-            uint4 v[8];
+        uint32_t wbits = 0;
+        if (lane == 0)  // issued first so that it travels with the row
+            wbits = ld_relaxed_sys(reinterpret_cast<const uint32_t*>(peer + a.weights_off) + (size_t)token * a.topk + k);
+        // up to 16 loads in flight per lane before the first store (the strong loads are not
+        // reordered by the compiler, so issue order is what hides the NVLink round trip)
+        for (int i0 = lane; i0 < n16; i0 += 32 * 16) {
+            uint4 v[16];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < 16; ++j)
                 if (i0 + 32 * j < n16) v[j] = ld_relaxed_sys_v4(srow + i0 + 32 * j);
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < 16; ++j)
                 if (i0 + 32 * j < n16) drow[i0 + 32 * j] = v[j];
         }
         if (a.scaled) {
@@ -334,10 +340,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
             for (int i = lane; i < a.L.sf_stride_h; i += 32)
                 pool_sf[(size_t)g * a.L.sf_stride_h + i] = i < kb ? ld_relaxed_sys_u8(ssf + i) : (uint8_t)127;
         }
-        if (lane == 0) {
-            const float w = __uint_as_float(ld_relaxed_sys(reinterpret_cast<const uint32_t*>(peer + a.weights_off) + (size_t)token * a.topk + k));
-            meta[g] = make_int4(src, token, k, __float_as_int(w));
-        }
+        if (lane == 0) meta[g] = make_int4(src, token, k, (int)wbits);
         // the row is complete: every lane makes its stores visible at GPU scope and to TMA
         // (a release by lane 0 alone does not cover the other lanes' stores), then count the row
         __threadfence();
