@@ -20,8 +20,8 @@
 // Warp roles (384 threads):
 //   warp 0      task scheduler + TMA producer (operand tiles, 4-stage ring)
 //   warp 1      MMA issuer (one lane), owns the TMEM allocation
-//   warp 2      scale-tile builder: global scale planes -> shared tiles for UTCCP
-//   warp 3      idle
+//   warps 2-3   scale-tile builders (even / odd groups): global scale planes -> shared
+//               tiles for UTCCP
 //   warps 4-11  epilogue: warp w reads TMEM lanes 32*(w%4).., column half (w-4)/4
 // ============================================================================
 #pragma once
@@ -69,7 +69,7 @@ __device__ void gemm_init_barriers(GemmSmem* S) {
     for (int s = 0; s < kSfRing; ++s) { mbar_init(&S->sf_full[s], 1); mbar_init(&S->sf_empty[s], 1); }
     mbar_init(&S->tmem_full, 1);
     mbar_init(&S->tmem_empty, kEpiWarps);
-    for (int s = 0; s < kTaskRing; ++s) { mbar_init(&S->task_full[s], 1); mbar_init(&S->task_empty[s], 2 + kEpiWarps); }
+    for (int s = 0; s < kTaskRing; ++s) { mbar_init(&S->task_full[s], 1); mbar_init(&S->task_empty[s], 3 + kEpiWarps); }
     S->abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -107,16 +107,30 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             uint32_t stage = 0, phase = 0;
             long long w_empty = 0, w_gate = 0, w_ring = 0;
             const uint64_t stream_policy = l2_policy_evict_first();
-            for (uint32_t it = 0;; ++it) {
-                const uint32_t slot = it % kTaskRing;
-                if (!MXK_TIMED(w_ring, mbar_wait(&S->task_empty[slot], ((it / kTaskRing) & 1) ^ 1, wait_ns, abort_flag))) {
-                    raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break;
+            // Claim the task of iteration `i` and publish it in the ring.  With many tasks per
+            // CTA the next task is published one iteration early, so that the scale-tile builder
+            // can work ahead across the task boundary; with few tasks per CTA (decode) claiming
+            // late keeps the tail of the dynamic queue balanced.
+            const bool lookahead = n_tasks > 8 * (int)gridDim.x;
+            bool ring_dead = false;
+            auto claim_publish = [&](uint32_t i) -> int4 {
+                const uint32_t slot = i % kTaskRing;
+                if (!MXK_TIMED(w_ring, mbar_wait(&S->task_empty[slot], ((i / kTaskRing) & 1) ^ 1, wait_ns, abort_flag))) {
+                    ring_dead = true;
+                    return make_int4(-1, 0, 0, 0);
                 }
-                const int t = it == 0 ? (int)blockIdx.x : (int)atomicAdd(&f->task_counter, 1u);
-                const int4 task = t < n_tasks ? ld_relaxed_gpu_v4(tasks + t) : make_int4(-1, 0, 0, 0);
-                S->task[slot] = task;
+                const int t = i == 0 ? (int)blockIdx.x : (int)atomicAdd(&f->task_counter, 1u);
+                const int4 tk = t < n_tasks ? ld_relaxed_gpu_v4(tasks + t) : make_int4(-1, 0, 0, 0);
+                S->task[slot] = tk;
                 mbar_arrive(&S->task_full[slot]);
+                return tk;
+            };
+            int4 pending = claim_publish(0);
+            for (uint32_t it = 0;; ++it) {
+                if (ring_dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break; }
+                const int4 task = pending;
                 if (task.x < 0) break;
+                if (lookahead) pending = claim_publish(it + 1);
                 const int4 win = ld_relaxed_gpu_v4(windows + task.y);
                 const int e = win.x, row0 = win.y;
                 const bool is_l2 = task.x == 1;
@@ -147,6 +161,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
                 if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; break; }
+                if (!lookahead) pending = claim_publish(it + 1);
             }
             atomicAdd(&f->ticks[0], (unsigned long long)w_empty);
             atomicAdd(&f->ticks[1], (unsigned long long)w_gate);
@@ -201,8 +216,10 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             atomicAdd(&f->ticks[3], (unsigned long long)w_drain);
             atomicAdd(&f->ticks[4], (unsigned long long)w_sf);
         }
-    } else if (warp == 2) {
-        // ------------------------------------------------------ scale-tile builder
+    } else if (warp == 2 || warp == 3) {
+        // ------------------------------------------------------ scale-tile builders
+        // Two warps share the work: warp 2 builds the even-numbered groups, warp 3 the odd ones.
+        const uint32_t my_parity = (uint32_t)(warp - 2);
         // Slot layout (what UTCCP 32x128b.warpx4 expects): tile byte 16*l + 4*j + i is the
         // scale of row l + 32*j for K block i of the group.  The two weight tiles repeat one
         // 4-byte word (a 128x128 block has one scale per K block).
@@ -276,11 +293,13 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 }
             };
             uint32_t wa[4], w0, w1;
-            load_group(0, wa, w0, w1);
+            int g = (int)((sfg ^ my_parity) & 1u);   // first group of this task that is mine
+            sfg += (uint32_t)g;
+            load_group(g, wa, w0, w1);
             bool dead = false;
-            for (int g = 0; g < ngroups; ++g, ++sfg) {
+            for (; g < ngroups; g += 2, sfg += 2) {
                 uint32_t na[4], n0, n1;
-                load_group(g + 1, na, n0, n1);
+                load_group(g + 2, na, n0, n1);
                 const uint32_t sslot = sfg % kSfRing;
                 bool free_ = true;
                 if (lane == 0) free_ = mbar_wait(&S->sf_empty[sslot], ((sfg / kSfRing) & 1) ^ 1, wait_ns, abort_flag);
@@ -297,6 +316,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 for (int j = 0; j < 4; ++j) wa[j] = na[j];
                 w0 = n0; w1 = n1;
             }
+            sfg -= (uint32_t)(g - ngroups);  // both warps leave the task with the same group count
             if (dead) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; } break; }
         }
     } else if (warp >= kFirstEpiWarp) {

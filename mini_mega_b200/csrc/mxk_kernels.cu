@@ -88,7 +88,7 @@ k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap 
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sf_tiles = tiles + kStages * kStageBytes;
     GemmSmem* S = reinterpret_cast<GemmSmem*>(sf_tiles + kSfRing * kSfSlotBytes);
-    __shared__ int s_small[64];
+    __shared__ int s_small[kRoutePer * 32];
     __shared__ float s_w[64];
     DevFlags* f = flags_of(a);
     const int warp = threadIdx.x >> 5;

@@ -23,7 +23,8 @@
 // Slots are handed out in ascending pair index idx = token*topk + k, so every
 // table row (and with it the pool row order) is deterministic; the reference
 // uses a shared-memory atomicAdd and accepts any order (src/prologue.cuh:164-180).
-__device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_wtot /*[32]*/) {
+constexpr int kRoutePer = 8;
+__device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_wtot /*[kRoutePer * warps]*/) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nthr = blockDim.x, nwarps = nthr >> 5;
     const int par = (int)(epoch & 1);
@@ -44,25 +45,41 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
         uint32_t* tbl = reinterpret_cast<uint32_t*>(peer_unk + a.L.src_index_table_off) +
                         (((size_t)par * a.EPR + le) * a.R + a.rank) * (size_t)a.slot_cap;
         int base = 0;
-        for (int p0 = 0; p0 < np; p0 += nthr) {
-            const int p = p0 + tid;
-            const bool hit = p < np && ti[p] == (int64_t)e;
-            const unsigned bal = __ballot_sync(0xFFFFFFFFu, hit);
-            if (lane == 0) s_wtot[warp] = __popc(bal);
+        // kRoutePer sub-chunks of blockDim pairs per iteration: the index loads of all sub-chunks
+        // are in flight together, then slots are handed out sub-chunk by sub-chunk (ascending idx)
+        for (int p0 = 0; p0 < np; p0 += nthr * kRoutePer) {
+            bool hit[kRoutePer];
+            unsigned bal[kRoutePer];
+            int64_t v[kRoutePer];
+#pragma unroll
+            for (int j = 0; j < kRoutePer; ++j) {
+                const int p = p0 + j * nthr + tid;
+                v[j] = p < np ? ti[p] : (int64_t)-2;
+            }
+#pragma unroll
+            for (int j = 0; j < kRoutePer; ++j) {
+                hit[j] = v[j] == (int64_t)e;
+                bal[j] = __ballot_sync(0xFFFFFFFFu, hit[j]);
+                if (lane == 0) s_wtot[j * nwarps + warp] = __popc(bal[j]);
+            }
             __syncthreads();
-            int wpre = 0, tot = 0;
-            for (int w = 0; w < nwarps; ++w) {
-                const int v = s_wtot[w];
-                wpre += (w < warp) ? v : 0;
-                tot += v;
+#pragma unroll
+            for (int j = 0; j < kRoutePer; ++j) {
+                int wpre = 0, tot = 0;
+                for (int w = 0; w < nwarps; ++w) {
+                    const int c = s_wtot[j * nwarps + w];
+                    wpre += (w < warp) ? c : 0;
+                    tot += c;
+                }
+                if (hit[j]) {
+                    const int p = p0 + j * nthr + tid;
+                    const int slot = base + wpre + __popc(bal[j] & ((1u << lane) - 1u));
+                    const bool ok = slot < a.slot_cap;  // over capacity: dropped (src/prologue.cuh:171-174)
+                    if (ok) st_relaxed_sys(tbl + slot, (uint32_t)p);
+                    pair_state[p] = ok ? 1 : 0;
+                }
+                base += tot;
             }
-            if (hit) {
-                const int slot = base + wpre + __popc(bal & ((1u << lane) - 1u));
-                const bool ok = slot < a.slot_cap;  // over capacity: dropped (src/prologue.cuh:171-174)
-                if (ok) st_relaxed_sys(tbl + slot, (uint32_t)p);
-                pair_state[p] = ok ? 1 : 0;
-            }
-            base += tot;
             __syncthreads();
         }
         if (tid == 0) {
