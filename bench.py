@@ -339,9 +339,8 @@ def gpu_arm(args):
                      "epi_wait_acc", "cta_life", "prod_wait_ring", "epi_busy"]
             print("ticks(% of CTA lifetime): " + " ".join(f"{n}={100.0 * tk[i] / life:.1f}" for i, n in enumerate(names)),
                   file=sys.stderr, flush=True)
-            print("phase ends (us since CTA start): route={:.1f} setup={:.1f} dispatch={:.1f} gemm={:.1f} reduce={:.1f} "
-                  "[route detail: local work {:.1f}, arrived {:.1f}]".format(
-                      *[tk[i] / 1e3 for i in range(9, 14)], tk[14] / 1e3, tk[15] / 1e3), file=sys.stderr, flush=True)
+            print("phase ends (us since CTA start): route={:.1f} setup={:.1f} dispatch={:.1f} gemm={:.1f} reduce={:.1f}".format(
+                *[tk[i] / 1e3 for i in range(9, 14)]), file=sys.stderr, flush=True)
             ts = buf.rwk[208:272].view(torch.int64).cpu().tolist()
             print("setup leader stamps (us after barrier): " + " ".join(f"{(ts[i] - ts[0]) / 1e3:.1f}" for i in range(1, 7)),
                   file=sys.stderr, flush=True)

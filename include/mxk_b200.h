@@ -59,9 +59,12 @@ typedef struct MxkLayout {
     int64_t topk_weights_off;   /* float  [max_tokens][topk]                      */
     /* unk */
     int64_t unk_bytes;
-    int64_t xbar_off;           /* uint32 [R][xbar_stride] arrival epoch per peer */
-    int64_t src_index_table_off;/* uint32 [2][EPR][R][slot_capacity]              */
-    int64_t expert_recv_counts_off; /* uint32 [2][R][recv_stride]                 */
+    int64_t xbar_off;           /* uint32 [R][xbar_stride] reserved (the barrier is carried
+                                   by the epoch tags of the two tables below)        */
+    int64_t src_index_table_off;/* uint64 [2][EPR][R][slot_capacity]: low word = pair
+                                   index token*topk+k, high word = launch epoch       */
+    int64_t expert_recv_counts_off; /* uint64 [2][R][recv_stride]: low word = count
+                                   (word EPR: checksum), high word = launch epoch     */
     int64_t combine_rows_off;   /* bf16   [topk][max_tokens][H]                   */
     int64_t combine_cnt_off;    /* uint32 [topk][max_tokens] arrivals per pair    */
     int32_t xbar_stride;        /* words between two peers' barrier slots         */

@@ -24,6 +24,19 @@
 // table row (and with it the pool row order) is deterministic; the reference
 // uses a shared-memory atomicAdd and accepts any order (src/prologue.cuh:164-180).
 constexpr int kRoutePer = 8;
+
+// Cross-rank words of the prologue are EPOCH-TAGGED 64-bit values {payload (low), epoch (high)}
+// written with one 8-byte store: a consumer polls the word itself until the tag is this launch's
+// epoch, so neither the producer nor the consumer needs a system-scope fence or a separate
+// flag on the critical path (the reference orders payload -> fence -> flag and adds a checksum
+// word against torn rows, src/flags.cuh:4, src/prologue.cuh:248-255,339-340).
+__device__ __forceinline__ uint64_t tagged(uint32_t payload, long long epoch) {
+    return ((uint64_t)(uint32_t)epoch << 32) | payload;
+}
+
+// Slots are handed out in ascending pair index idx = token*topk + k, so every table row (and
+// with it the pool row order) is deterministic; the reference uses a shared-memory atomicAdd
+// and accepts any order (src/prologue.cuh:164-180).
 __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_wtot /*[kRoutePer * warps]*/) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nthr = blockDim.x, nwarps = nthr >> 5;
@@ -33,16 +46,18 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     uint8_t* pair_state = a.rwk + a.L.pair_state_off;
     int* rsc = reinterpret_cast<int*>(a.rwk + a.L.route_slot_counts_off);
 
-    // Arrival counters of the rows peers will push to this rank in this launch.
-    // Safe to clear here: peers push only after this rank has arrived at the
-    // barrier below, and the previous launch's reduce has consumed them.
+    // Arrival counters of the rows peers will push to this rank in this launch.  Cleared before
+    // any count of this launch leaves the CTA: a peer can push only after it has seen ALL counts
+    // of this rank, and the previous launch's reduce has consumed the old values.
     unsigned* cnt = reinterpret_cast<unsigned*>(a.unk + a.L.combine_cnt_off);
     for (int i = blockIdx.x * nthr + tid; i < a.topk * a.cap; i += gridDim.x * nthr) cnt[i] = 0;
+    __threadfence();
+    __syncthreads();
 
     for (int e = blockIdx.x; e < a.E; e += gridDim.x) {
         const int dst = e / a.EPR, le = e % a.EPR;
         uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[dst]);
-        uint32_t* tbl = reinterpret_cast<uint32_t*>(peer_unk + a.L.src_index_table_off) +
+        uint64_t* tbl = reinterpret_cast<uint64_t*>(peer_unk + a.L.src_index_table_off) +
                         (((size_t)par * a.EPR + le) * a.R + a.rank) * (size_t)a.slot_cap;
         int base = 0;
         // kRoutePer sub-chunks of blockDim pairs per iteration: the index loads of all sub-chunks
@@ -75,7 +90,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
                     const int p = p0 + j * nthr + tid;
                     const int slot = base + wpre + __popc(bal[j] & ((1u << lane) - 1u));
                     const bool ok = slot < a.slot_cap;  // over capacity: dropped (src/prologue.cuh:171-174)
-                    if (ok) st_relaxed_sys(tbl + slot, (uint32_t)p);
+                    if (ok) st_relaxed_sys_u64(tbl + slot, tagged((uint32_t)p, epoch));
                     pair_state[p] = ok ? 1 : 0;
                 }
                 base += tot;
@@ -85,48 +100,37 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
         if (tid == 0) {
             const int c = base < a.slot_cap ? base : a.slot_cap;
             rsc[e] = c;
-            uint32_t* recv = reinterpret_cast<uint32_t*>(peer_unk + a.L.expert_recv_counts_off) +
+            uint64_t* recv = reinterpret_cast<uint64_t*>(peer_unk + a.L.expert_recv_counts_off) +
                              ((size_t)par * a.R + a.rank) * a.L.recv_stride;
-            st_relaxed_sys(recv + le, (uint32_t)c);
+            st_relaxed_sys_u64(recv + le, tagged((uint32_t)c, epoch));
         }
     }
     if (blockIdx.x == 0)  // invalid expert ids (negative / >= E) take no slot (src/prologue.cuh:166-167)
         for (int p = tid; p < np; p += nthr)
             if ((uint64_t)ti[p] >= (uint64_t)a.E) pair_state[p] = 0;
 
-    if (a.ticks && blockIdx.x == 0 && tid == 0) f->ticks[14] = gtimer_ns();
-    fence_world(a.R > 1);  // this thread's table / count stores are out before the CTA arrives
+    // Everything below is off the critical path (the counts are already on their way): make
+    // this CTA's local tables visible, arrive, and let CTA 0 close the launch bookkeeping.
+    __threadfence();
     __syncthreads();
     if (tid == 0) atomicAdd(&f->route_blocks_done, 1u);
     if (blockIdx.x != 0) return;
-    if (a.ticks && tid == 0) f->ticks[15] = gtimer_ns();
 
-    // ---- CTA 0: every CTA's tables are out; close the rows and signal the peers
     if (tid == 0) {
         const unsigned want = gridDim.x;
         if (!spin_until([&] { return ld_acquire_gpu(&f->route_blocks_done) >= want; }, a.local_wait_ns, nullptr))
             raise_status(f, MXK_DEV_TIMEOUT_PIPE, 2);
     }
     __syncthreads();
-    // Barrier arrival: publish this launch's epoch into every peer's slot for this rank.  Every
-    // CTA fenced its table / count stores at world scope before arriving and this CTA acquired
-    // the arrivals above, so the flag itself needs no further fence (a second system-scope
-    // fence here would sit on the critical path of every rank).
-    for (int d = tid; d < a.R; d += nthr) {
-        uint32_t* xb = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) + a.L.xbar_off) +
-                       (size_t)a.rank * a.L.xbar_stride;
-        st_relaxed_sys(xb, (uint32_t)epoch);
-    }
-    // Row checksum word ~(sum + 1) at index EPR of each row sent (src/prologue.cuh:248-255).  The
-    // reference polls it to detect torn rows; here the barrier orders the rows, so the word is
-    // kept for layout parity only and is written off the critical path.
+    // Row checksum word ~(sum + 1) at index EPR of each row sent (src/prologue.cuh:248-255), kept
+    // for layout parity with the reference; nothing here waits on it.
     for (int d = tid; d < a.R; d += nthr) {
         uint32_t csum = 0;
         for (int le = 0; le < a.EPR; ++le) csum += (uint32_t)ld_relaxed_gpu(rsc + d * a.EPR + le);
-        uint32_t* recv = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) +
+        uint64_t* recv = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) +
                                                      a.L.expert_recv_counts_off) +
                          ((size_t)par * a.R + a.rank) * a.L.recv_stride;
-        st_relaxed_sys(recv + a.EPR, ~(csum + 1u));
+        st_relaxed_sys_u64(recv + a.EPR, tagged(~(csum + 1u), epoch));
     }
     if (tid == 0) {
         f->route_blocks_done = 0;
@@ -135,7 +139,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     __syncthreads();
 }
 
-// CTA 0 builds the tables; `s_i` is scratch shared memory of 4*EPR + 2 ints.
+// CTA 0 builds the tables; `s_i` is scratch shared memory of 4*EPR + 2 + EPR*R ints.
 __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch, int* s_i) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int EPR = a.EPR, R = a.R;
@@ -145,26 +149,29 @@ __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch,
     int* s_base = s_first + EPR + 1;   // [EPR+1] first pool row of expert le
     const int par = (int)(epoch & 1);
 
-    // Cross-rank barrier: every rank has published its routes for this epoch.
-    for (int r = tid; r < R; r += nthr) {
-        const uint32_t* xb = reinterpret_cast<const uint32_t*>(a.unk + a.L.xbar_off) + (size_t)r * a.L.xbar_stride;
-        const bool ok = spin_until([&] { return (int32_t)(ld_relaxed_sys(xb) - (uint32_t)epoch) >= 0; },
+    // Cross-rank barrier = every (source rank, local expert) count word carries this epoch.
+    int* s_cnt = s_base + EPR + 1;     // [EPR][R]
+    const uint64_t* recv = reinterpret_cast<const uint64_t*>(a.unk + a.L.expert_recv_counts_off) +
+                           (size_t)par * R * a.L.recv_stride;
+    for (int i = tid; i < EPR * R; i += nthr) {
+        const int le = i / R, r = i % R;
+        const uint64_t* wp = recv + (size_t)r * a.L.recv_stride + le;
+        uint64_t w = 0;
+        const bool ok = spin_until([&] { w = ld_relaxed_sys_u64(wp); return (uint32_t)(w >> 32) == (uint32_t)epoch; },
                                    a.remote_wait_ns, nullptr);
-        if (!ok) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 0);
+        if (!ok) { raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 0); w = 0; }
+        s_cnt[i] = (int)(uint32_t)w;
     }
-    fence_world(a.R > 1);  // acquire side of the barrier, once for all polled flags
     __syncthreads();
     const bool ts = a.ticks != 0 && tid == 0;
     if (ts) f->dbg_ts[0] = gtimer_ns();
 
-    const uint32_t* recv = reinterpret_cast<const uint32_t*>(a.unk + a.L.expert_recv_counts_off) +
-                           (size_t)par * R * a.L.recv_stride;
     int* prefix = reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off);
     for (int le = tid; le < EPR; le += nthr) {
         int c = 0;
         for (int r = 0; r < R; ++r) {
             prefix[le * (R + 1) + r] = c;
-            c += (int)ld_relaxed_sys(recv + (size_t)r * a.L.recv_stride + le);
+            c += s_cnt[le * R + r];
         }
         prefix[le * (R + 1) + R] = c;
         s_tot[le] = c;
@@ -293,7 +300,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
     const int total = ld_relaxed_gpu(&f->total_rows);
     const int par = (int)(epoch & 1);
     const int R = a.R, EPR = a.EPR, H = a.H;
-    const uint32_t* tbl = reinterpret_cast<const uint32_t*>(a.unk + a.L.src_index_table_off) +
+    const uint64_t* tbl = reinterpret_cast<const uint64_t*>(a.unk + a.L.src_index_table_off) +
                           (size_t)par * EPR * R * a.slot_cap;
     uint8_t* pool = a.rwk + a.L.pool_off;
     uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
@@ -332,7 +339,17 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
             if (pf[mid] <= gl) slo = mid; else shi = mid;
         }
         const int src = slo, slot = gl - pf[src];
-        const uint32_t idx = ld_relaxed_sys(tbl + ((size_t)le * R + src) * a.slot_cap + slot);
+        // the pair index the source rank wrote for this slot (epoch-tagged: poll until it is this launch's)
+        uint64_t tw = 0;
+        {
+            const uint64_t* tp = tbl + ((size_t)le * R + src) * a.slot_cap + slot;
+            if (!spin_until([&] { tw = ld_relaxed_sys_u64(tp); return (uint32_t)(tw >> 32) == (uint32_t)epoch; },
+                            a.remote_wait_ns, nullptr)) {
+                if (lane == 0) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 2);
+                tw = 0;
+            }
+        }
+        const uint32_t idx = (uint32_t)tw;
         const int token = (int)(idx / (uint32_t)a.topk), k = (int)(idx % (uint32_t)a.topk);
         const uint8_t* peer = a.peer_bases[src];
         const uint4* srow = reinterpret_cast<const uint4*>(peer + a.x_off + (size_t)token * H);

@@ -192,12 +192,18 @@ class SymmBuffer:
             "pool_sf": (self.rwk, torch.uint8, (rows, L.sf_stride_h), L.pool_sf_off),
             "ffn": (self.rwk, torch.uint8, (rows + 128, I), L.ffn_off),
             "ffn_sf": (self.rwk, torch.uint8, (rows, L.sf_stride_i), L.ffn_sf_off),
-            "src_index_table": (self.unk, torch.int32, (2, EPR, R, slot), L.src_index_table_off),
-            "expert_recv_counts": (self.unk, torch.int32, (2, R, L.recv_stride), L.expert_recv_counts_off),
+            # epoch-tagged 64-bit words: [..., 0] = payload, [..., 1] = launch epoch
+            "src_index_table_raw": (self.unk, torch.int32, (2, EPR, R, slot, 2), L.src_index_table_off),
+            "expert_recv_counts_raw": (self.unk, torch.int32, (2, R, L.recv_stride, 2), L.expert_recv_counts_off),
             "combine_rows": (self.unk, torch.int16, (topk, cap, H), L.combine_rows_off),
             "combine_cnt": (self.unk, torch.int32, (topk, cap), L.combine_cnt_off),
             "xbar": (self.unk, torch.int32, (R, L.xbar_stride), L.xbar_off),
-        }[name]
+        }
+        if name in ("src_index_table", "expert_recv_counts"):      # payload words only
+            return self.table(name + "_raw")[..., 0]
+        if name in ("src_index_table_tags", "expert_recv_counts_tags"):
+            return self.table(name[:-5] + "_raw")[..., 1]
+        spec = spec[name]
         return _view(spec[0], spec[1], spec[2], int(spec[3]))
 
     def status(self) -> MxkStatus:
