@@ -287,6 +287,7 @@ def gpu_arm(args):
     cap = max(256, args.tpr) if not args.no_points else args.tpr
     lib = _lib.lib()
     buf = mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, H, I)
+    buf.cta_pair = args.cta_pair
     l1, l2 = mm.transform_weights_for_mega_moe(*make_weights(torch, epr, rank, dev))
     stream = torch.cuda.current_stream()
     hbm_gbs, bf16_tf, peak_kind = load_peaks()
@@ -337,7 +338,9 @@ def gpu_arm(args):
             life = max(tk[6], 1)
             names = ["prod_wait_stage", "prod_wait_gate", "mma_wait_tiles", "mma_wait_drain", "mma_wait_sf",
                      "epi_wait_acc", "cta_life", "prod_wait_ring", "epi_busy"]
-            print("ticks(% of CTA lifetime): " + " ".join(f"{n}={100.0 * tk[i] / life:.1f}" for i, n in enumerate(names)),
+            print("ticks(% of CTA lifetime): " + " ".join(f"{n}={100.0 * tk[i] / life:.1f}" for i, n in enumerate(names)) +
+                  f" epi_drain={100.0 * tk[15] / life:.1f}"
+                  f" sm_ghz_in_gemm={tk[6] / torch.cuda.get_device_properties(local).multi_processor_count / max(1.0, tk[12] - tk[11]):.3f}",
                   file=sys.stderr, flush=True)
             print("phase ends (us since CTA start): route={:.1f} setup={:.1f} dispatch={:.1f} gemm={:.1f} reduce={:.1f}".format(
                 *[tk[i] / 1e3 for i in range(9, 14)]), file=sys.stderr, flush=True)
@@ -472,6 +475,8 @@ def main():
     ap.add_argument("--tpr", type=int, default=0, help="tokens per rank; overrides --global-tokens")
     ap.add_argument("--experts", type=int, default=256, help="total experts (smaller for profiling captures)")
     ap.add_argument("--hidden", type=int, default=6144, help="H (7168 for the prefill-sized configuration)")
+    ap.add_argument("--cta-pair", type=int, default=0, choices=[0, 1, 2],
+                    help="GEMM tiling: 1 single CTAs, 2 CTA pairs with 256-row windows, 0 chosen by load")
     ap.add_argument("--ticks", action="store_true", help="print the GEMM kernel's wait-time breakdown to stderr")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-points", action="store_true", help="skip the 16/64/256 tokens-per-rank sweep")

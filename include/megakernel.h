@@ -71,6 +71,7 @@ struct MegaLaunchArgs {
     const uint8_t* w1_sf = nullptr;
     const uint8_t* w2_sf = nullptr;
     uint16_t* y_bf16 = nullptr;
+    int cta_pair = 0;   // 0 = choose by load, 1 = single CTAs, 2 = CTA pairs (256-row windows)
 };
 
 inline int& last_status() {
@@ -91,7 +92,7 @@ inline MxkLaunchArgs to_c(const MegaLaunchArgs& a) {
     c.max_spins = a.max_spins; c.skip_prologue = a.skip_prologue;
     c.experts_per_rank = a.experts_per_rank; c.topk = a.topk; c.hidden = a.hidden;
     c.intermediate = a.intermediate; c.max_tokens = a.max_tokens;
-    c.x_sf_off = a.x_sf_off; c.w1_sf = a.w1_sf; c.w2_sf = a.w2_sf; c.y_bf16 = a.y_bf16;
+    c.x_sf_off = a.x_sf_off; c.w1_sf = a.w1_sf; c.w2_sf = a.w2_sf; c.y_bf16 = a.y_bf16; c.cta_pair = a.cta_pair;
     return c;
 }
 

@@ -127,6 +127,10 @@ typedef struct MxkLaunchArgs {
     const uint8_t* w1_sf;      /* [EPR][2I/128][H/128] UE8M0 or NULL              */
     const uint8_t* w2_sf;      /* [EPR][H/128][I/128]  UE8M0 or NULL              */
     uint16_t* y_bf16;          /* optional bf16 [tokens][H]                       */
+    int32_t cta_pair;          /* GEMM tiling: 1 = one CTA per 128-row window, 2 = clusters
+                                  of two CTAs per 256-row window (2-CTA MMA; needs
+                                  win_cap 128 and an even grid), 0 = choose by load:
+                                  pairs when tokens*topk/experts_per_rank >= 256  */
 } MxkLaunchArgs;
 
 /* Host-readable copy of the device status header. */
@@ -144,7 +148,8 @@ typedef struct MxkStatus {
                               drain, 4 on scale tiles, 5 epilogue blocked on accumulators,
                               6 CTA lifetime, 7 producer blocked on the task ring,
                               8 epilogue busy; 9..13 phase ends in ns since CTA start
-                              (route, set-up, dispatch, GEMM, reduce)                 */
+                              (route, set-up, dispatch, GEMM, reduce); 15 epilogue
+                              draining accumulators (part of 8)                       */
 } MxkStatus;
 
 #define MXK_DEV_TIMEOUT_BARRIER 1

@@ -19,7 +19,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile csrc/mxk_kernels.cu for sm_100a into libmxk_b200.so (in-tree)."""
-    srcs = [os.path.join(SRC_DIR, f) for f in ("mxk_kernels.cu", "mxk_device.cuh")]
+    srcs = [os.path.join(SRC_DIR, f) for f in ("mxk_kernels.cu", "mxk_device.cuh", "mxk_phases.cuh", "mxk_gemm.cuh")]
     hdr = os.path.join(os.path.dirname(_HERE), "include", "mxk_b200.h")
     newest = max(os.path.getmtime(p) for p in srcs + [hdr])
     if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= newest:
@@ -64,6 +64,7 @@ class MxkLaunchArgs(C.Structure):
         ("experts_per_rank", C.c_int32), ("topk", C.c_int32), ("hidden", C.c_int32), ("intermediate", C.c_int32),
         ("max_tokens", C.c_int32),
         ("x_sf_off", C.c_int64), ("w1_sf", C.c_void_p), ("w2_sf", C.c_void_p), ("y_bf16", C.c_void_p),
+        ("cta_pair", C.c_int32),
     ]
 
 

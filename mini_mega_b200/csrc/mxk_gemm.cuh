@@ -30,12 +30,20 @@ constexpr int kStages = 4;
 constexpr int kABytes = kBlockM * kBlockK;           // 16 KB activation tile
 constexpr int kBBytes = kBlockN * kBlockK;           // 32 KB weight tile (two 128-row halves)
 constexpr int kStageBytes = kABytes + kBBytes;       // 48 KB
+// CTA-pair mode (cta_group::2): each CTA of a cluster of two stages its own 128 activation rows
+// and ONE 128-row half of the weight tile; the pair's MMA (M = 256, N = 256) reads both halves.
+// Per 128-row block of M each SM then moves 32 KB instead of 48 KB through shared memory.
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = 2 * kABytes;         // 32 KB
+constexpr int kMaxStages = kPairStages;
+static_assert(kPairStages * kPairStageBytes == kStages * kStageBytes, "both modes use the same tile region");
 constexpr int kTaskRing = 4;
 constexpr int kGemmThreads = 384;
 constexpr int kEpiWarps = 8;
 constexpr int kFirstEpiWarp = 4;
 constexpr int kTmemCols = 512;
-constexpr int kTmemSfCol = 256;       // scale tiles live behind the 256 accumulator columns
+constexpr int kTmemSfCol = 256;       // scale tiles live behind the 256 accumulator columns: ring slot s at
+                                      // columns 256 + 16*s (12 used: activation rows, weight halves 0 and 1)
 constexpr int kSfRing = 8;            // shared-memory scale-tile slots (one per 4 K blocks)
 constexpr int kSfSlotBytes = 3 * 512; // A rows, weight half 0, weight half 1
 constexpr int kPrefetchBytesPerCta = 704 * 1024;  // L2 prefetch during the prologue: 148 CTAs x 704 KB = 104 MB
@@ -45,14 +53,16 @@ constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align*/ + kSfRing * kSf
 // src/kernel.cuh:52-124): each role sums the cycles it spent blocked and adds them to
 // DevFlags::ticks at exit.  Slots: 0 producer/empty stage, 1 producer/L1->L2 gate, 2 MMA/full
 // stage, 3 MMA/accumulator drain, 4 MMA/scale tile, 5 epilogue/accumulators ready,
-// 6 CTA lifetime, 7 producer/task ring, 8 epilogue busy (drain to stores issued).
+// 6 CTA lifetime, 7 producer/task ring, 8 epilogue busy (drain to stores issued),
+// 15 epilogue accumulator drain (part of 8).
 #define MXK_TIMED(slot_var, expr) ([&] { if (!timed) return (expr); const long long t0_ = clock64(); const bool r_ = (expr); slot_var += clock64() - t0_; return r_; }())
 
 struct GemmSmem {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
-    uint64_t sf_full[kSfRing];
-    uint64_t sf_empty[kSfRing];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t sf_full[kSfRing];    // scale tiles of a group copied into tensor memory (commit of the copies)
+    uint64_t sf_empty[kSfRing];   // the group's MMAs retired: shared slot and TMEM columns reusable
+    uint64_t sf_peer[kSfRing];    // pair mode, leader only: the partner CTA has written its shared tile
     uint64_t tmem_full;
     uint64_t tmem_empty;
     uint64_t task_full[kTaskRing];
@@ -64,12 +74,15 @@ struct GemmSmem {
 };
 
 // Barrier initialisation (one thread) — part of the kernel prologue.
-__device__ void gemm_init_barriers(GemmSmem* S) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&S->full[s], 1); mbar_init(&S->empty[s], 1); }
-    for (int s = 0; s < kSfRing; ++s) { mbar_init(&S->sf_full[s], 1); mbar_init(&S->sf_empty[s], 1); }
+// In pair mode the barriers the MMA issuer waits on (scale tile ready, accumulators drained) and
+// the task-ring release live in the leader CTA and count the arrivals of both CTAs.
+__device__ void gemm_init_barriers(GemmSmem* S, const bool pair) {
+    const uint32_t ctas = pair ? 2u : 1u;
+    for (int s = 0; s < kMaxStages; ++s) { mbar_init(&S->full[s], 1); mbar_init(&S->empty[s], 1); }
+    for (int s = 0; s < kSfRing; ++s) { mbar_init(&S->sf_full[s], 1); mbar_init(&S->sf_empty[s], 1); mbar_init(&S->sf_peer[s], 1); }
     mbar_init(&S->tmem_full, 1);
-    mbar_init(&S->tmem_empty, kEpiWarps);
-    for (int s = 0; s < kTaskRing; ++s) { mbar_init(&S->task_full[s], 1); mbar_init(&S->task_empty[s], 3 + kEpiWarps); }
+    mbar_init(&S->tmem_empty, kEpiWarps * ctas);
+    for (int s = 0; s < kTaskRing; ++s) { mbar_init(&S->task_full[s], 1); mbar_init(&S->task_empty[s], (3 + kEpiWarps) * ctas); }
     S->abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -77,6 +90,7 @@ __device__ void gemm_init_barriers(GemmSmem* S) {
 
 // The GEMM phase of the persistent kernel; called by all threads of the CTA after the
 // set-up tables of this launch are visible.  Returns when every role has left its loop.
+template <bool kPair>
 __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t* sf_tiles, GemmSmem* S,
                            const uint32_t tmem_base, const CUtensorMap* tm_pool_p, const CUtensorMap* tm_ffn_p,
                            const CUtensorMap* tm_w1_p, const CUtensorMap* tm_w2_p) {
@@ -97,7 +111,25 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
     const uint32_t* pool_ready = reinterpret_cast<const uint32_t*>(a.rwk + a.L.pool_ready_off);
     const int kb1 = a.H / kBlockK, kb2 = a.I / kBlockK;
     const int nt1 = a.I / 128;
-    const uint32_t l1_need = (uint32_t)nt1 * kEpiWarps;   // arrivals that complete a window's ffn rows
+    const uint32_t l1_need = (uint32_t)nt1 * kEpiWarps * (kPair ? 2u : 1u);   // arrivals that complete a window's ffn rows
+    // Pair mode: CTA `crank` of the cluster owns rows [128*crank, 128*crank+128) of a 256-row
+    // window and weight half `crank`; rank 0 (the leader) claims tasks and issues the MMAs.
+    const uint32_t crank = kPair ? cluster_ctarank() : 0u;
+    const bool leader = crank == 0;
+    const int n_units = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;   // CTAs or CTA pairs pulling tasks
+    const int unit_id = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    constexpr int kNStages = kPair ? kPairStages : kStages;
+    constexpr int kStageB = kPair ? kPairStageBytes : kStageBytes;
+    // barrier helpers: in pair mode consumers release ring slots / scale tiles / accumulators on
+    // the leader's barriers (cluster address of rank 0; for the leader that is its own barrier)
+    auto wait_bar = [&](uint64_t* bar, uint32_t parity) -> bool {
+        if constexpr (kPair) return mbar_wait_cluster(bar, parity, wait_ns, abort_flag);
+        else return mbar_wait(bar, parity, wait_ns, abort_flag);
+    };
+    auto arrive_leader = [&](uint64_t* bar) {
+        if constexpr (kPair) mbar_arrive_cluster(mapa_u32(smem_u32(bar), 0));
+        else mbar_arrive(bar);
+    };
 
     if (warp == 0) {
         // ------------------------------------------------ scheduler + TMA producer
@@ -111,18 +143,34 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             // CTA the next task is published one iteration early, so that the scale-tile builder
             // can work ahead across the task boundary; with few tasks per CTA (decode) claiming
             // late keeps the tail of the dynamic queue balanced.
-            const bool lookahead = n_tasks > 8 * (int)gridDim.x;
+            const bool lookahead = n_tasks > 8 * n_units;
             bool ring_dead = false;
             auto claim_publish = [&](uint32_t i) -> int4 {
                 const uint32_t slot = i % kTaskRing;
-                if (!MXK_TIMED(w_ring, mbar_wait(&S->task_empty[slot], ((i / kTaskRing) & 1) ^ 1, wait_ns, abort_flag))) {
+                if constexpr (kPair) {
+                    if (!leader) {
+                        // the partner's producer consumes the leader's ring entries like any other role
+                        if (!MXK_TIMED(w_ring, wait_bar(&S->task_full[slot], (i / kTaskRing) & 1))) {
+                            ring_dead = true;
+                            return make_int4(-1, 0, 0, 0);
+                        }
+                        const int4 tk = S->task[slot];
+                        arrive_leader(&S->task_empty[slot]);
+                        return tk;
+                    }
+                }
+                if (!MXK_TIMED(w_ring, wait_bar(&S->task_empty[slot], ((i / kTaskRing) & 1) ^ 1))) {
                     ring_dead = true;
                     return make_int4(-1, 0, 0, 0);
                 }
-                const int t = i == 0 ? (int)blockIdx.x : (int)atomicAdd(&f->task_counter, 1u);
+                const int t = i == 0 ? unit_id : (int)atomicAdd(&f->task_counter, 1u);
                 const int4 tk = t < n_tasks ? ld_relaxed_gpu_v4(tasks + t) : make_int4(-1, 0, 0, 0);
                 S->task[slot] = tk;
                 mbar_arrive(&S->task_full[slot]);
+                if constexpr (kPair) {
+                    st_cluster_v4(mapa_u32(smem_u32(&S->task[slot]), 1), tk);
+                    mbar_arrive_cluster(mapa_u32(smem_u32(&S->task_full[slot]), 1));  // release: after the store
+                }
                 return tk;
             };
             int4 pending = claim_publish(0);
@@ -132,7 +180,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 if (task.x < 0) break;
                 if (lookahead) pending = claim_publish(it + 1);
                 const int4 win = ld_relaxed_gpu_v4(windows + task.y);
-                const int e = win.x, row0 = win.y;
+                const int e = win.x, row0 = win.y + 128 * (int)crank;
                 const bool is_l2 = task.x == 1;
                 if (is_l2) {  // every L1 tile of this window must have landed in ffn
                     if (!MXK_TIMED(w_gate, spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= l1_need; }, wait_ns, abort_flag))) {
@@ -153,12 +201,20 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 bool dead = false;
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!MXK_TIMED(w_empty, mbar_wait(&S->empty[stage], phase ^ 1, wait_ns, abort_flag))) { dead = true; break; }
-                    uint8_t* sa = tiles + stage * kStageBytes;
-                    mbar_expect_tx(&S->full[stage], kStageBytes);
-                    tma_load_2d(sa, ma, kb * kBlockK, row0, &S->full[stage]);
-                    tma_load_2d_hint(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[stage], stream_policy);
-                    tma_load_2d_hint(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[stage], stream_policy);
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    uint8_t* sa = tiles + stage * kStageB;
+                    if constexpr (kPair) {
+                        // both CTAs' bytes complete on the leader's barrier: 2 x (A 16 KB + weight half 16 KB)
+                        if (leader) mbar_expect_tx(&S->full[stage], 2 * kPairStageBytes);
+                        const uint32_t bar = mapa_u32(smem_u32(&S->full[stage]), 0);
+                        tma_load_2d_pair(sa, ma, kb * kBlockK, row0, bar);
+                        tma_load_2d_pair_hint(sa + kABytes, mb, kb * kBlockK, leader ? brow0 : brow1, bar, stream_policy);
+                    } else {
+                        mbar_expect_tx(&S->full[stage], kStageBytes);
+                        tma_load_2d(sa, ma, kb * kBlockK, row0, &S->full[stage]);
+                        tma_load_2d_hint(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[stage], stream_policy);
+                        tma_load_2d_hint(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[stage], stream_policy);
+                    }
+                    if (++stage == kNStages) { stage = 0; phase ^= 1; }
                 }
                 if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; break; }
                 if (!lookahead) pending = claim_publish(it + 1);
@@ -169,9 +225,20 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && leader) {
             uint32_t stage = 0, phase = 0, sfg = 0;
             long long w_full = 0, w_drain = 0, w_sf = 0;
+            bool stage_ready = false;   // full[stage] already seen complete by the early poll
+            bool sf_ready = false;      // likewise sf_full of the next group
+            const uint64_t tile_desc0 = umma_smem_desc_sw128(smem_u32(tiles));
+            const uint32_t idesc0 = umma_idesc_mx_e4m3(kPair ? 2 * kBlockM : kBlockM, kBlockN, 0, 0);
+            // the partner's copies of the barriers the MMAs release
+            uint32_t peer_empty0 = 0, peer_sf_empty0 = 0, peer_tmem_full = 0;
+            if constexpr (kPair) {
+                peer_empty0 = mapa_u32(smem_u32(&S->empty[0]), 1);
+                peer_sf_empty0 = mapa_u32(smem_u32(&S->sf_empty[0]), 1);
+                peer_tmem_full = mapa_u32(smem_u32(&S->tmem_full), 1);
+            }
             for (uint32_t it = 0;; ++it) {
                 const uint32_t slot = it % kTaskRing;
                 if (!mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag)) {
@@ -182,35 +249,69 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 if (task.x < 0) break;
                 const int nkb = task.x == 1 ? kb2 : kb1;
                 // the epilogue must have drained the previous task's accumulators
-                bool dead = !MXK_TIMED(w_drain, mbar_wait(&S->tmem_empty, (it & 1) ^ 1, wait_ns, abort_flag));
-                uint32_t sf_slot = 0, tsf = 0;
-                for (int kb = 0; kb < nkb && !dead; ++kb) {
-                    if ((kb & 3) == 0) {  // a new group of four K blocks: stage its scale tiles in TMEM
-                        sf_slot = sfg % kSfRing;
-                        if (!MXK_TIMED(w_sf, mbar_wait(&S->sf_full[sf_slot], (sfg / kSfRing) & 1, wait_ns, abort_flag))) { dead = true; break; }
-                        tc_fence_after();
-                        tsf = tmem_base + kTmemSfCol + (sfg & 1) * 16;
-                        const uint32_t ssf = smem_u32(sf_tiles + sf_slot * kSfSlotBytes);
-                        utccp_32x128b_warpx4(tsf, umma_smem_desc_sf(ssf));             // activation rows
-                        utccp_32x128b_warpx4(tsf + 4, umma_smem_desc_sf(ssf + 512));   // weight rows 0..127
-                        utccp_32x128b_warpx4(tsf + 8, umma_smem_desc_sf(ssf + 1024));  // weight rows 128..255
-                    }
-                    if (!MXK_TIMED(w_full, mbar_wait(&S->full[stage], phase, wait_ns, abort_flag))) { dead = true; break; }
-                    tc_fence_after();
-                    const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
-                    const uint64_t adesc = umma_smem_desc_sw128(sa);
-                    const uint64_t bdesc = umma_smem_desc_sw128(sa + kABytes);
-                    const uint32_t idesc = umma_idesc_mx_e4m3(kBlockM, kBlockN, kb & 3, kb & 3);
+                bool dead = !MXK_TIMED(w_drain, wait_bar(&S->tmem_empty, (it & 1) ^ 1));
+                // One K block is 512 tensor-pipe cycles; a barrier poll, a commit or a tensor-memory
+                // copy each cost this thread on the order of 100 cycles, so the issue path must stay
+                // short or the pipe runs dry: descriptors by addition, scale ids as constants, the
+                // next stage and the next scale group polled under the MMAs already queued, and the
+                // scale-tile copies issued by the builder warps instead of here.
+                uint32_t acc = 0;
+                for (int kb0 = 0; kb0 < nkb && !dead; kb0 += 4) {
+                    // a new group of four K blocks: its scale tiles were copied into TMEM slot
+                    // sf_slot by a builder warp
+                    const uint32_t sf_slot = sfg % kSfRing;
+                    if (!sf_ready && !MXK_TIMED(w_sf, wait_bar(&S->sf_full[sf_slot], (sfg / kSfRing) & 1))) { dead = true; break; }
+                    sf_ready = false;
+                    const uint32_t tsf = tmem_base + kTmemSfCol + sf_slot * 16;
+                    const uint32_t nsf_slot = (sfg + 1) % kSfRing, nsf_parity = ((sfg + 1) / kSfRing) & 1;
 #pragma unroll
-                    for (int k4 = 0; k4 < kBlockK / 32; ++k4)
-                        umma_mxf8(tmem_base, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, tsf, tsf + 4,
-                                  (kb > 0 || k4 > 0) ? 1u : 0u);
-                    umma_commit(&S->empty[stage]);  // stage reusable once these MMAs retire
-                    if ((kb & 3) == 3 || kb == nkb - 1) { umma_commit(&S->sf_empty[sf_slot]); ++sfg; }
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    for (int i = 0; i < 4; ++i) {
+                        if (kb0 + i >= nkb) break;
+                        if (!stage_ready && !MXK_TIMED(w_full, mbar_wait(&S->full[stage], phase, wait_ns, abort_flag))) { dead = true; break; }
+                        tc_fence_after();
+                        const uint64_t adesc = tile_desc0 + (uint64_t)(stage * (kStageB >> 4));
+                        const uint64_t bdesc = adesc + (uint64_t)(kABytes >> 4);
+                        const uint32_t idesc = idesc0 | ((uint32_t)i << 4) | ((uint32_t)i << 29);   // scale byte i of the group
+                        uint32_t nstage = stage + 1, nphase = phase;
+                        if (nstage == kNStages) { nstage = 0; nphase ^= 1; }
+                        if constexpr (kPair) {
+                            umma_mxf8_pair(tmem_base, adesc, bdesc, idesc, tsf, tsf + 4, acc);
+                            umma_mxf8_pair(tmem_base, adesc + 2, bdesc + 2, idesc, tsf, tsf + 4, 1u);
+                            stage_ready = mbar_try_wait(&S->full[nstage], nphase);   // poll the next stage under the MMAs
+                            if (i == 2) sf_ready = mbar_try_wait_cluster(&S->sf_full[nsf_slot], nsf_parity);
+                            umma_mxf8_pair(tmem_base, adesc + 4, bdesc + 4, idesc, tsf, tsf + 4, 1u);
+                            umma_mxf8_pair(tmem_base, adesc + 6, bdesc + 6, idesc, tsf, tsf + 4, 1u);
+                            // one commit per barrier and CTA: both producers / builders move on
+                            umma_commit_pair(smem_u32(&S->empty[stage]));
+                            umma_commit_pair(peer_empty0 + stage * 8);
+                        } else {
+                            umma_mxf8(tmem_base, adesc, bdesc, idesc, tsf, tsf + 4, acc);
+                            umma_mxf8(tmem_base, adesc + 2, bdesc + 2, idesc, tsf, tsf + 4, 1u);
+                            stage_ready = mbar_try_wait(&S->full[nstage], nphase);   // poll the next stage under the MMAs
+                            if (i == 2) sf_ready = mbar_try_wait(&S->sf_full[nsf_slot], nsf_parity);  // and the next group's scales
+                            umma_mxf8(tmem_base, adesc + 4, bdesc + 4, idesc, tsf, tsf + 4, 1u);
+                            umma_mxf8(tmem_base, adesc + 6, bdesc + 6, idesc, tsf, tsf + 4, 1u);
+                            umma_commit(&S->empty[stage]);  // stage reusable once these MMAs retire
+                        }
+                        acc = 1u;
+                        stage = nstage; phase = nphase;
+                    }
+                    if (dead) break;
+                    if constexpr (kPair) {
+                        umma_commit_pair(smem_u32(&S->sf_empty[sf_slot]));
+                        umma_commit_pair(peer_sf_empty0 + sf_slot * 8);
+                    } else {
+                        umma_commit(&S->sf_empty[sf_slot]);
+                    }
+                    ++sfg;
                 }
                 if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; break; }
-                umma_commit(&S->tmem_full);  // accumulators complete
+                if constexpr (kPair) {
+                    umma_commit_pair(smem_u32(&S->tmem_full));
+                    umma_commit_pair(peer_tmem_full);
+                } else {
+                    umma_commit(&S->tmem_full);  // accumulators complete
+                }
             }
             atomicAdd(&f->ticks[2], (unsigned long long)w_full);
             atomicAdd(&f->ticks[3], (unsigned long long)w_drain);
@@ -229,15 +330,15 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
         for (uint32_t it = 0;; ++it) {
             const uint32_t slot = it % kTaskRing;
             bool ok = true;
-            if (lane == 0) ok = mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag);
+            if (lane == 0) ok = wait_bar(&S->task_full[slot], (it / kTaskRing) & 1);
             ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
             if (!ok) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; } break; }
             const int4 task = S->task[slot];
             __syncwarp();
-            if (lane == 0) mbar_arrive(&S->task_empty[slot]);
+            if (lane == 0) arrive_leader(&S->task_empty[slot]);
             if (task.x < 0) break;
             const int4 win = ld_relaxed_gpu_v4(windows + task.y);
-            const int e = win.x, row0 = win.y, rows = task.w;
+            const int e = win.x, row0 = win.y + 128 * (int)crank, rows = task.w - 128 * (int)crank;
             const bool is_l2 = task.x == 1;
             const int nkb = is_l2 ? kb2 : kb1;
             const uint8_t* asf = nullptr;   // activation scale rows of this window
@@ -311,7 +412,36 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 dst[64 + lane] = make_uint4(w1, w1, w1, w1);
                 fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor-core copy
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&S->sf_full[sslot]);
+                if (lane == 0) {
+                    // copy the three tiles into the slot's TMEM columns; the commit reports them done
+                    const uint32_t tsf = tmem_base + kTmemSfCol + sslot * 16;
+                    const uint64_t sfdesc = umma_smem_desc_sf(smem_u32(dst));
+                    if constexpr (kPair) {
+                        if (leader) {  // one copy serves both CTAs: the partner's tile must be in place
+                            if (wait_bar(&S->sf_peer[sslot], (sfg / kSfRing) & 1)) {
+                                tc_fence_after();
+                                utccp_32x128b_warpx4_pair(tsf, sfdesc);
+                                utccp_32x128b_warpx4_pair(tsf + 4, sfdesc + (512 >> 4));
+                                utccp_32x128b_warpx4_pair(tsf + 8, sfdesc + (1024 >> 4));
+                                umma_commit_pair(smem_u32(&S->sf_full[sslot]));
+                            } else {
+                                free_ = false;
+                            }
+                        } else {
+                            arrive_leader(&S->sf_peer[sslot]);
+                        }
+                    } else {
+                        tc_fence_after();          // after the wait on sf_empty: the slot's last readers retired
+                        utccp_32x128b_warpx4(tsf, sfdesc);                    // activation rows
+                        utccp_32x128b_warpx4(tsf + 4, sfdesc + (512 >> 4));   // weight rows 0..127
+                        utccp_32x128b_warpx4(tsf + 8, sfdesc + (1024 >> 4));  // weight rows 128..255
+                        umma_commit(&S->sf_full[sslot]);
+                    }
+                }
+                if constexpr (kPair) {
+                    free_ = __shfl_sync(0xFFFFFFFFu, free_ ? 1 : 0, 0) != 0;
+                    if (!free_) { dead = true; break; }
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) wa[j] = na[j];
                 w0 = n0; w1 = n1;
@@ -327,19 +457,19 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
         uint8_t* ffn = a.rwk + a.L.ffn_off;
         uint8_t* ffn_sf = a.rwk + a.L.ffn_sf_off;
         const int4* meta = reinterpret_cast<const int4*>(a.rwk + a.L.row_meta_off);
-        long long w_acc = 0, t_busy = 0;
+        long long w_acc = 0, t_busy = 0, t_drain = 0;
         for (uint32_t it = 0;; ++it) {
             const uint32_t slot = it % kTaskRing;
             bool ok = true;
-            if (lane == 0) ok = mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag);
+            if (lane == 0) ok = wait_bar(&S->task_full[slot], (it / kTaskRing) & 1);
             ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
             if (!ok) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; } break; }
             const int4 task = S->task[slot];
             __syncwarp();
-            if (lane == 0) mbar_arrive(&S->task_empty[slot]);
+            if (lane == 0) arrive_leader(&S->task_empty[slot]);
             if (task.x < 0) break;
             const int4 win = ld_relaxed_gpu_v4(windows + task.y);
-            const int row0 = win.y, rows = task.w;
+            const int row0 = win.y + 128 * (int)crank, rows = task.w - 128 * (int)crank;
             const bool is_l2 = task.x == 1;
             const bool warp_active = q * 32 < rows;
             const bool row_valid = r < rows;
@@ -362,7 +492,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&S->tmem_empty);
+            if (lane == 0) arrive_leader(&S->tmem_empty);
+            if (timed) t_drain += clock64() - t_busy0;
 
             if (!is_l2) {
                 // ---- SwiGLU + per-row 1x128 requantisation to E4M3 -> ffn
@@ -450,6 +581,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
         if (warp == kFirstEpiWarp && lane == 0) {
             atomicAdd(&f->ticks[5], (unsigned long long)w_acc);
             atomicAdd(&f->ticks[8], (unsigned long long)t_busy);
+            atomicAdd(&f->ticks[15], (unsigned long long)t_drain);
         }
     }
     if (threadIdx.x == 0) atomicAdd(&f->ticks[6], (unsigned long long)(clock64() - t_start));

@@ -47,7 +47,7 @@ static_assert(sizeof(DevFlags) <= 1024, "status header must fit its 1 KB slot");
 
 struct KArgs {
     int R, rank, EPR, E, topk, H, I, cap, slot_cap, tokens, win_cap;
-    int gemm_grid, skip_combine, scaled, ticks;
+    int gemm_grid, skip_combine, scaled, ticks, pair;
     unsigned long long local_wait_ns, remote_wait_ns;
     uint8_t* rwk;
     uint8_t* unk;
@@ -80,10 +80,10 @@ __device__ __forceinline__ void raise_status(DevFlags* f, int code, int dbg_slot
 // The persistent kernel: one CTA per SM runs the phases selected by phase_mask in
 // layer order.  CTAs wait on each other (route arrival, set-up flag, L1->L2 and
 // pool counters), so the grid never exceeds the SM count and every CTA is resident.
-__global__ void __launch_bounds__(kGemmThreads, 1)
-k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap tm_pool,
-       const __grid_constant__ CUtensorMap tm_ffn, const __grid_constant__ CUtensorMap tm_w1,
-       const __grid_constant__ CUtensorMap tm_w2) {
+template <bool kPair>
+__device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, const CUtensorMap& tm_pool,
+                                          const CUtensorMap& tm_ffn, const CUtensorMap& tm_w1,
+                                          const CUtensorMap& tm_w2) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sf_tiles = tiles + kStages * kStageBytes;
@@ -99,15 +99,16 @@ k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap 
     const long long epoch = ld_relaxed_gpu(&f->current_time) + ((phase_mask & MXK_PHASE_ROUTE) ? 1 : 0);
 
     if (do_gemm) {
-        if (threadIdx.x == 0) gemm_init_barriers(S);
+        if (threadIdx.x == 0) gemm_init_barriers(S, kPair);
         for (int i = threadIdx.x; i < 2 * 2 * 128; i += blockDim.x) (&S->xch[0][0][0])[i] = 0ull;
         if (warp == 1) {
-            tmem_alloc(&S->tmem_base, kTmemCols);
-            tmem_relinquish();
+            if constexpr (kPair) { tmem_alloc_pair(&S->tmem_base, kTmemCols); tmem_relinquish_pair(); }
+            else { tmem_alloc(&S->tmem_base, kTmemCols); tmem_relinquish(); }
         }
         tc_fence_before();
     }
-    __syncthreads();
+    // pair mode: the partner's barriers must be initialised before anything arrives on them
+    if constexpr (kPair) cluster_sync_all(); else __syncthreads();
     uint32_t tmem_base = 0;
     if (do_gemm) {
         tc_fence_after();
@@ -156,19 +157,37 @@ k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap 
     if (stamp) atomicMax(&f->ticks[11], (unsigned long long)(gtimer_ns() - t0));
 
     if (do_gemm) {
-        if (tables_ok) gemm_phase(a, f, tiles, sf_tiles, S, tmem_base, &tm_pool, &tm_ffn, &tm_w1, &tm_w2);
+        if (tables_ok) gemm_phase<kPair>(a, f, tiles, sf_tiles, S, tmem_base, &tm_pool, &tm_ffn, &tm_w1, &tm_w2);
         if (S->abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain
         tc_fence_before();
-        __syncthreads();
+        // pair mode: neither CTA may free tensor memory or leave while its partner can still
+        // arrive on its barriers or its MMAs still write both halves
+        if constexpr (kPair) cluster_sync_all(); else __syncthreads();
         if (warp == 1) {
             __syncwarp();
-            tmem_dealloc(tmem_base, kTmemCols);
+            if constexpr (kPair) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
         }
     }
     if (stamp) atomicMax(&f->ticks[12], (unsigned long long)(gtimer_ns() - t0));
 
     if (phase_mask & MXK_PHASE_REDUCE) reduce_phase(a, f, s_small, s_w);
     if (stamp) atomicMax(&f->ticks[13], (unsigned long long)(gtimer_ns() - t0));
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap tm_pool,
+       const __grid_constant__ CUtensorMap tm_ffn, const __grid_constant__ CUtensorMap tm_w1,
+       const __grid_constant__ CUtensorMap tm_w2) {
+    mega_body<false>(a, phase_mask, tm_pool, tm_ffn, tm_w1, tm_w2);
+}
+
+// The same layer with the GEMM phase on CTA pairs (clusters of two, 2-CTA tcgen05 MMA with
+// M = 256): for windows of up to 256 rows, i.e. the compute-bound regime.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+k_mega_pair(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap tm_pool,
+            const __grid_constant__ CUtensorMap tm_ffn, const __grid_constant__ CUtensorMap tm_w1,
+            const __grid_constant__ CUtensorMap tm_w2) {
+    mega_body<true>(a, phase_mask, tm_pool, tm_ffn, tm_w1, tm_w2);
 }
 
 __global__ void k_empty() {}
@@ -358,6 +377,18 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     if (di.cc / 10 != 10) return fail(MXK_ERR_DEVICE, "this library runs on sm_100 (B200) only, device is sm_" + std::to_string(di.cc));
     int grid = la->grid > 0 ? la->grid : di.sm_count;
     if (grid > di.sm_count) grid = di.sm_count;  // CTAs wait on each other: all must be resident
+    // CTA-pair tiling pays once windows fill up (compute-bound regime); with few rows per
+    // expert a 256-row window would only halve the number of CTAs streaming weights
+    int pair = la->cta_pair;
+    if (pair < 0 || pair > 2) return fail(MXK_ERR_BAD_ARG, "cta_pair must be 0, 1 or 2");
+    if (pair == 0) pair = (win == 128 && grid >= 2 && (int64_t)la->tokens * g.topk >= 256ll * g.experts_per_rank) ? 2 : 1;
+    if (pair == 2) {
+        if (win != 128) return fail(MXK_ERR_BAD_ARG, "cta_pair = 2 needs win_cap = 128");
+        if (grid < 2) return fail(MXK_ERR_BAD_ARG, "cta_pair = 2 needs a grid of at least 2 CTAs");
+        grid &= ~1;
+        k->pair = 1;
+        k->win_cap = 256;   // rows per window of a CTA pair
+    }
     k->gemm_grid = grid;
     return 0;
 }
@@ -388,11 +419,36 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
     if (attr_dev != dev) {
         cudaError_t e = cudaFuncSetAttribute(k_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(k_mega)");
+        e = cudaFuncSetAttribute(k_mega_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(k_mega_pair)");
         attr_dev = dev;
     }
-    k_mega<<<k.gemm_grid, kGemmThreads, kGemmSmem, st>>>(k, mask, tm_pool, tm_ffn, tm_w1, tm_w2);
+    if (k.pair) {
+        // every CTA pair must be resident at once (CTAs wait on each other): ask the runtime how
+        // many clusters of two fit and never launch more
+        static thread_local int max_pairs = 0, pairs_dev = -1;
+        if (pairs_dev != dev) {
+            cudaLaunchConfig_t cfg;
+            std::memset(&cfg, 0, sizeof(cfg));
+            cfg.gridDim = dim3(2, 1, 1); cfg.blockDim = dim3(kGemmThreads, 1, 1); cfg.dynamicSmemBytes = kGemmSmem;
+            cudaLaunchAttribute at;
+            at.id = cudaLaunchAttributeClusterDimension;
+            at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+            cfg.attrs = &at; cfg.numAttrs = 1;
+            int n = 0;
+            cudaError_t e = cudaOccupancyMaxActiveClusters(&n, k_mega_pair, &cfg);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaOccupancyMaxActiveClusters(k_mega_pair)");
+            if (n < 1) return fail(MXK_ERR_DEVICE, "no CTA pair of k_mega_pair fits on this device");
+            max_pairs = n; pairs_dev = dev;
+        }
+        KArgs kk = k;
+        if (kk.gemm_grid > 2 * max_pairs) kk.gemm_grid = 2 * max_pairs;
+        k_mega_pair<<<kk.gemm_grid, kGemmThreads, kGemmSmem, st>>>(kk, mask, tm_pool, tm_ffn, tm_w1, tm_w2);
+    }
+    else
+        k_mega<<<k.gemm_grid, kGemmThreads, kGemmSmem, st>>>(k, mask, tm_pool, tm_ffn, tm_w1, tm_w2);
     cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : cuda_fail(e, "launch k_mega");
+    return e == cudaSuccess ? 0 : cuda_fail(e, k.pair ? "launch k_mega_pair" : "launch k_mega");
 }
 
 // ------------------------------------------------------------ static scratch

@@ -263,7 +263,7 @@ __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch,
         f->n_l1_tasks = n_l1;
         f->n_tasks = n_windows * (nt1 + nt2);
         f->total_rows = overflow ? 0 : total_rows;
-        f->task_counter = gridDim.x;  // first task of a CTA is its index
+        f->task_counter = a.pair ? gridDim.x >> 1 : gridDim.x;  // first task of a CTA (pair) is its index
     }
     __threadfence();
     __syncthreads();

@@ -213,7 +213,8 @@ class SymmBuffer:
 
     def launch_args(self, num_tokens: int, l1=None, l2=None, y_bf16: Optional[torch.Tensor] = None,
                     y_f32: Optional[torch.Tensor] = None, expert_window: Optional[int] = None,
-                    max_spins: int = 0, grid: int = 0, skip_combine: int = 0) -> MxkLaunchArgs:
+                    max_spins: int = 0, grid: int = 0, skip_combine: int = 0,
+                    cta_pair: Optional[int] = None) -> MxkLaunchArgs:
         L = self.layout
         a = MxkLaunchArgs()
         a.R, a.rank, a.tokens = self.world_size, self.rank, int(num_tokens)
@@ -236,6 +237,7 @@ class SymmBuffer:
             setattr(a, name + "_sf", None if sf is None else sf.data_ptr())
         a.y = None if y_f32 is None else y_f32.data_ptr()
         a.y_bf16 = None if y_bf16 is None else y_bf16.data_ptr()
+        a.cta_pair = int(getattr(self, "cta_pair", 0) if cta_pair is None else cta_pair)
         return a
 
     def destroy(self):
@@ -321,7 +323,7 @@ def _check_weights(sym_buffer: SymmBuffer, l1, l2):
 
 def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
                  cumulative_local_expert_recv_stats=None, activation: str = "swiglu", activation_clamp=None,
-                 expert_window: Optional[int] = None, max_spins: int = 0) -> None:
+                 expert_window: Optional[int] = None, max_spins: int = 0, cta_pair: Optional[int] = None) -> None:
     """One MoE layer: ``y[t] = sum_k w_k * W2_e SwiGLU(W1_e x_t)`` for this rank's
     ``y.shape[0]`` tokens, inputs taken from ``sym_buffer.x / x_sf / topk_idx / topk_weights``.
     Every rank of the group must call it the same number of times (a rank with zero
@@ -337,7 +339,7 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
     _check_weights(sym_buffer, l1_weights, l2_weights)
     lib = _lib.lib()
     a = sym_buffer.launch_args(num_tokens, l1_weights, l2_weights, y_bf16=y, expert_window=expert_window,
-                               max_spins=max_spins)
+                               max_spins=max_spins, cta_pair=cta_pair)
     if num_tokens == 0:  # nothing to reduce, but the rank still serves its experts
         check(lib.mxk_launch_compute(C.byref(a), _stream_ptr()), "mxk_launch_compute")
     else:

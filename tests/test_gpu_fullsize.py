@@ -104,9 +104,11 @@ def test_full_geometry_sample_and_properties():
         buf.destroy()
 
 
-def test_skewed_routing_full_width():
+@pytest.mark.parametrize("cta_pair", [1, 2])
+def test_skewed_routing_full_width(cta_pair):
     """Zipf(1.2)-skewed routing (the hottest expert gets many windows) at full H / I on a world of
-    32 experts: end-to-end against the oracle on every token."""
+    32 experts: end-to-end against the oracle on sampled tokens, with single-CTA windows of
+    128 rows and with CTA-pair windows of 256 rows."""
     import mini_mega_b200 as mm
     case_E, T = 32, 160
     rng = np.random.default_rng(11)
@@ -135,13 +137,14 @@ def test_skewed_routing_full_width():
         buf.topk_idx[:T].copy_(torch.from_numpy(idx))
         buf.topk_weights[:T].copy_(torch.from_numpy(w))
         y = torch.zeros((T, H), dtype=torch.bfloat16, device="cuda")
-        mm.fp8_mega_moe(y, l1, l2, buf)
+        mm.fp8_mega_moe(y, l1, l2, buf, cta_pair=cta_pair)
         torch.cuda.synchronize()
         st = buf.status()
-        assert st.status == 0
+        assert st.status == 0, f"device status {st.status} dbg {list(st.dbg)}"
         counts = np.bincount(idx.reshape(-1), minlength=case_E)
         assert counts.max() > 128, "the hottest expert should need more than one window"
-        assert st.n_windows == int(sum((c + 127) // 128 for c in counts))
+        win = 128 * cta_pair
+        assert st.n_windows == int(sum((c + win - 1) // win for c in counts))
         # oracle on 24 sampled tokens (all their experts)
         sample = rng.choice(T, 24, replace=False)
         want = np.zeros((len(sample), H), np.float32)

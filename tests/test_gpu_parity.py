@@ -78,12 +78,12 @@ def _reduce_check(world, r):
     assert np.array_equal(got16, orc.f32_to_bf16(want))
 
 
-def _run_case(case, expert_window=128, full_stage_checks=True, e2e_tol=1e-2):
+def _run_case(case, expert_window=128, full_stage_checks=True, e2e_tol=1e-2, cta_pair=None):
     from gpu_world import World, assert_status_ok, check_tables
     ref = orc.layer_world(case)
     w = World(case, expert_window=expert_window)
     try:
-        w.run()
+        w.run(cta_pair=cta_pair)
         assert_status_ok(w)
         check_tables(w, ref)
         for r in range(case.R):
@@ -98,10 +98,10 @@ def _run_case(case, expert_window=128, full_stage_checks=True, e2e_tol=1e-2):
     finally:
         w.destroy()
     if case.R == 1:
-        _run_fused(case, ref[0].y, expert_window, e2e_tol)
+        _run_fused(case, ref[0].y, expert_window, e2e_tol, cta_pair)
 
 
-def _run_fused(case, want_y, expert_window, e2e_tol):
+def _run_fused(case, want_y, expert_window, e2e_tol, cta_pair=None):
     """The same case through ONE launch of the whole layer (mxk_launch_full via fp8_mega_moe),
     twice on the same buffers: phases then overlap inside the persistent kernel."""
     import mini_mega_b200 as mm
@@ -114,7 +114,7 @@ def _run_fused(case, want_y, expert_window, e2e_tol):
         T = case.tokens[0]
         for _ in range(2):
             y = torch.zeros((T, case.H), dtype=torch.bfloat16, device="cuda")
-            mm.fp8_mega_moe(y, l1, l2, buf)
+            mm.fp8_mega_moe(y, l1, l2, buf, cta_pair=cta_pair)
             torch.cuda.synchronize()
             st = buf.status()
             assert st.status == 0, f"device status {st.status} dbg {list(st.dbg)}"
@@ -156,3 +156,12 @@ def test_reference_fixture_full_geometry():
     """The reference harness's own fixture at its frozen geometry (EPR=8, topk=8, H=6144,
     I=2048, balanced routes, WPROBE weights, byte-pattern x), R=1, 8 tokens."""
     _run_case(orc.gen_reference_fixture(1, 8, 8, 6144, 2048, 8, "balanced"))
+
+
+def test_cta_pair_mode():
+    """CTA-pair tiling (clusters of two CTAs, 256-row windows, 2-CTA MMA) forced on small cases:
+    windows of fewer than 128 rows (the partner CTA has no rows), of 128..256 rows, and several
+    windows per expert; with and without scale planes."""
+    _run_case(orc.gen_case(1, 8, 2, 512, 256, 32, seed=13, routing="logits", scaled=True), cta_pair=2)
+    _run_case(orc.gen_case(2, 2, 2, 512, 256, [300, 290], seed=14, routing="zipf", scaled=True), cta_pair=2)
+    _run_case(orc.gen_case(1, 4, 2, 1024, 512, 400, seed=15, routing="uniform", scaled=False), cta_pair=2)
