@@ -339,7 +339,7 @@ def gpu_arm(args):
             names = ["prod_wait_stage", "prod_wait_gate", "mma_wait_tiles", "mma_wait_drain", "mma_wait_sf",
                      "epi_wait_acc", "cta_life", "prod_wait_ring", "epi_busy"]
             print("ticks(% of CTA lifetime): " + " ".join(f"{n}={100.0 * tk[i] / life:.1f}" for i, n in enumerate(names)) +
-                  f" epi_drain={100.0 * tk[15] / life:.1f}"
+                  f" epi_drain={100.0 * tk[15] / life:.1f} epi_publish={100.0 * tk[14] / life:.1f}"
                   f" sm_ghz_in_gemm={tk[6] / torch.cuda.get_device_properties(local).multi_processor_count / max(1.0, tk[12] - tk[11]):.3f}",
                   file=sys.stderr, flush=True)
             print("phase ends (us since CTA start): route={:.1f} setup={:.1f} dispatch={:.1f} gemm={:.1f} reduce={:.1f}".format(

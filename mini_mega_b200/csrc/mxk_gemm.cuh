@@ -457,7 +457,32 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
         uint8_t* ffn = a.rwk + a.L.ffn_off;
         uint8_t* ffn_sf = a.rwk + a.L.ffn_sf_off;
         const int4* meta = reinterpret_cast<const int4*>(a.rwk + a.L.row_meta_off);
-        long long w_acc = 0, t_busy = 0, t_drain = 0;
+        long long w_acc = 0, t_busy = 0, t_drain = 0, t_pub = 0;
+        // Publishing a task's output (release of l1_done / combine_cnt) has to wait until the
+        // task's stores are performed.  It is deferred past the drain of the NEXT task's
+        // accumulators when those are already complete, so that the store latency hides
+        // behind work instead of holding the tensor memory; it is never held across a wait
+        // (an L2 task of this very CTA may be gated on it).
+        int pend_kind = 0;           // 0 none, 1 L1 window share (l1_done), 2 L2 row (combine_cnt)
+        uint32_t* pend_ptr = nullptr;
+        auto flush_publish = [&] {
+            if (pend_kind == 0) return;
+            const long long t_p0 = timed ? clock64() : 0;
+            if (pend_kind == 1) {
+                // every lane makes its own stores visible at GPU scope (and to the TMA reads of
+                // the L2 tasks) before lane 0 counts the warp's share as done
+                __threadfence();
+                fence_proxy_async_global();
+                __syncwarp();
+                if (lane == 0) red_release_gpu_add(pend_ptr, 1u);
+            } else if (pend_ptr) {
+                // release at system scope: this thread's row segment is visible before the count
+                if (a.R > 1) red_release_sys_add(pend_ptr, 1u); else red_release_gpu_add(pend_ptr, 1u);
+            }
+            pend_kind = 0;
+            pend_ptr = nullptr;
+            if (timed) t_pub += clock64() - t_p0;
+        };
         for (uint32_t it = 0;; ++it) {
             const uint32_t slot = it % kTaskRing;
             bool ok = true;
@@ -467,17 +492,22 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             const int4 task = S->task[slot];
             __syncwarp();
             if (lane == 0) arrive_leader(&S->task_empty[slot]);
-            if (task.x < 0) break;
+            if (task.x < 0) { flush_publish(); break; }
             const int4 win = ld_relaxed_gpu_v4(windows + task.y);
             const int row0 = win.y + 128 * (int)crank, rows = task.w - 128 * (int)crank;
             const bool is_l2 = task.x == 1;
             const bool warp_active = q * 32 < rows;
             const bool row_valid = r < rows;
 
-            bool got = true;
-            if (lane == 0) got = MXK_TIMED(w_acc, mbar_wait(&S->tmem_full, it & 1, wait_ns, abort_flag));
-            const long long t_busy0 = clock64();
+            bool got = false;
+            if (lane == 0) got = mbar_try_wait(&S->tmem_full, it & 1);
             got = __shfl_sync(0xFFFFFFFFu, got ? 1 : 0, 0) != 0;
+            if (!got) {   // about to block: publish first
+                flush_publish();
+                if (lane == 0) got = MXK_TIMED(w_acc, mbar_wait(&S->tmem_full, it & 1, wait_ns, abort_flag));
+                got = __shfl_sync(0xFFFFFFFFu, got ? 1 : 0, 0) != 0;
+            }
+            const long long t_busy0 = clock64();
             if (!got) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; } break; }
             tc_fence_after();
             // drain this warp's share of the accumulators into registers, then release TMEM
@@ -494,6 +524,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             __syncwarp();
             if (lane == 0) arrive_leader(&S->tmem_empty);
             if (timed) t_drain += clock64() - t_busy0;
+            flush_publish();   // the previous task's stores have had the drain to complete
 
             if (!is_l2) {
                 // ---- SwiGLU + per-row 1x128 requantisation to E4M3 -> ffn
@@ -542,12 +573,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                         if (a.scaled && half == 0) ffn_sf[(size_t)(row0 + r) * a.L.sf_stride_i + task.z] = (uint8_t)ex;
                     }
                 }
-                // publish: every lane makes its own stores visible at GPU scope (and to the TMA
-                // reads of the L2 tasks) before lane 0 counts the warp's share as done
-                __threadfence();
-                fence_proxy_async_global();
-                __syncwarp();
-                if (lane == 0) red_release_gpu_add(l1_done + task.y, 1u);
+                pend_kind = 1;
+                pend_ptr = l1_done + task.y;
             } else {
                 // ---- bf16 rows pushed to the source rank + per-pair arrival count
                 if (row_valid && !a.skip_combine) {
@@ -571,10 +598,9 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                         o.w = pack_bf16x2(__uint_as_float(vu[c * 8 + 6]), __uint_as_float(vu[c * 8 + 7]));
                         d1[c] = o;
                     }
-                    // release at system scope: this thread's row segment is visible before the count
-                    uint32_t* cnt = reinterpret_cast<uint32_t*>(peer_unk + a.L.combine_cnt_off) + (size_t)m.z * a.cap + m.y;
-                    if (a.R > 1) red_release_sys_add(cnt, 1u); else red_release_gpu_add(cnt, 1u);
+                    pend_ptr = reinterpret_cast<uint32_t*>(peer_unk + a.L.combine_cnt_off) + (size_t)m.z * a.cap + m.y;
                 }
+                pend_kind = 2;
             }
             t_busy += clock64() - t_busy0;
         }
@@ -582,6 +608,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             atomicAdd(&f->ticks[5], (unsigned long long)w_acc);
             atomicAdd(&f->ticks[8], (unsigned long long)t_busy);
             atomicAdd(&f->ticks[15], (unsigned long long)t_drain);
+            atomicAdd(&f->ticks[14], (unsigned long long)t_pub);
         }
     }
     if (threadIdx.x == 0) atomicAdd(&f->ticks[6], (unsigned long long)(clock64() - t_start));

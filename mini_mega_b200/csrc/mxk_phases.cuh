@@ -394,6 +394,83 @@ __device__ void reduce_phase(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, fl
     const uint16_t* rows = reinterpret_cast<const uint16_t*>(a.unk + a.L.combine_rows_off);
     const float* tw = reinterpret_cast<const float*>(a.self + a.weights_off);
     const uint32_t need = (uint32_t)(H / kBlockN) * 2u;
+    if (a.tokens > 2 * (int)gridDim.x && topk <= 32) {
+        // Many tokens per CTA: one WARP per token, so that the wait for a token's rows and the
+        // latency of its loads overlap across the warps of the CTA (a CTA-wide token would put
+        // a poll, a fence and two barriers between any two tokens).  Same arithmetic order.
+        const int lane = tid & 31, warp = tid >> 5, nw = nthr >> 5;
+        for (int t = blockIdx.x * nw + warp; t < a.tokens; t += (int)gridDim.x * nw) {
+            int ok = 0;
+            float w_mine = 0.0f;
+            if (lane < topk) {
+                ok = ld_relaxed_gpu_u8(pair_state + t * topk + lane);
+                if (ok && !a.skip_combine) {
+                    const uint32_t* c = cnt + (size_t)lane * a.cap + t;
+                    if (!spin_until([&] { return ld_relaxed_sys(c) >= need; }, a.remote_wait_ns, nullptr)) {
+                        raise_status(f, MXK_DEV_TIMEOUT_REDUCE, 4);
+                        ok = 0;
+                    }
+                    fence_world(a.R > 1);  // acquire: the counted row segments are visible
+                }
+                w_mine = tw[(size_t)t * topk + lane];
+            }
+            __syncwarp();  // the other lanes' loads are ordered after the polling lanes' acquires
+            const unsigned okmask = __ballot_sync(0xFFFFFFFFu, ok != 0);
+            // two column groups per pass: up to 16 row segments of 16 B in flight per lane
+            // (H/8 is a multiple of 32, so the second group's validity is uniform over the warp)
+            for (int c0 = lane; c0 < H / 8; c0 += 64) {
+                const bool two = c0 + 32 < H / 8;
+                float acc[2][8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[0][j] = acc[1][j] = 0.0f;
+                for (int k0 = 0; k0 < topk; k0 += 8) {
+                    uint4 v[2][8];
+                    float wk[8];
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        wk[kk] = __shfl_sync(0xFFFFFFFFu, w_mine, (k0 + kk) & 31);
+                        if (k0 + kk < topk && ((okmask >> (k0 + kk)) & 1u)) {
+                            const uint4* row = reinterpret_cast<const uint4*>(rows + ((size_t)(k0 + kk) * a.cap + t) * H);
+                            v[0][kk] = ld_relaxed_sys_v4(row + c0);
+                            if (two) v[1][kk] = ld_relaxed_sys_v4(row + c0 + 32);
+                        }
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        if (k0 + kk >= topk || !((okmask >> (k0 + kk)) & 1u)) continue;
+                        const float w = wk[kk];
+#pragma unroll
+                        for (int g = 0; g < 2; ++g) {
+                            if (g == 1 && !two) break;
+                            const uint32_t u[4] = {v[g][kk].x, v[g][kk].y, v[g][kk].z, v[g][kk].w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                acc[g][2 * j] = __fadd_rn(acc[g][2 * j], __fmul_rn(__uint_as_float(u[j] << 16), w));
+                                acc[g][2 * j + 1] = __fadd_rn(acc[g][2 * j + 1], __fmul_rn(__uint_as_float(u[j] & 0xFFFF0000u), w));
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    if (g == 1 && !two) break;
+                    const int c8 = c0 + 32 * g;
+                    if (a.y) {
+                        float4* o = reinterpret_cast<float4*>(a.y + (size_t)t * H + c8 * 8);
+                        o[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+                        o[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+                    }
+                    if (a.y_bf16) {
+                        uint4 o;
+                        o.x = pack_bf16x2(acc[g][0], acc[g][1]); o.y = pack_bf16x2(acc[g][2], acc[g][3]);
+                        o.z = pack_bf16x2(acc[g][4], acc[g][5]); o.w = pack_bf16x2(acc[g][6], acc[g][7]);
+                        *reinterpret_cast<uint4*>(a.y_bf16 + (size_t)t * H + c8 * 8) = o;
+                    }
+                }
+            }
+        }
+        return;
+    }
     for (int t = blockIdx.x; t < a.tokens; t += gridDim.x) {
         if (tid < topk) {
             int ok = ld_relaxed_gpu_u8(pair_state + t * topk + tid);
