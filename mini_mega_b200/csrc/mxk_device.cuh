@@ -388,6 +388,13 @@ __host__ __device__ constexpr uint32_t umma_idesc_mx_e4m3(int m, int n, uint32_t
     return (b_sf_id << 4) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(m >> 4) << 24) | (a_sf_id << 29);
 }
 
+// 32-byte global store (256-bit vector): one full sector per thread.
+__device__ __forceinline__ void st_global_v8(void* p, uint4 a, uint4 b) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+                 "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+
 // E4M3 pack with round-to-nearest-even and saturation to +-448 (NaN -> 0x7F).
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
     uint16_t lo, hi;

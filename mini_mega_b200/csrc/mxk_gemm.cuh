@@ -557,6 +557,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                     }
                     if (row_valid) {
                         uint4* dst = reinterpret_cast<uint4*>(ffn + (size_t)(row0 + r) * a.I + task.z * 128 + half * 64);
+                        uint4 prev = make_uint4(0, 0, 0, 0);
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             uint4 o;
@@ -568,7 +569,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                                               __uint_as_float(vg[c * 16 + 10]) * inv, __uint_as_float(vg[c * 16 + 11]) * inv);
                             o.w = pack_e4m3x4(__uint_as_float(vg[c * 16 + 12]) * inv, __uint_as_float(vg[c * 16 + 13]) * inv,
                                               __uint_as_float(vg[c * 16 + 14]) * inv, __uint_as_float(vg[c * 16 + 15]) * inv);
-                            dst[c] = o;
+                            if (c & 1) st_global_v8(dst + c - 1, prev, o); else prev = o;   // 32-byte stores
                         }
                         if (a.scaled && half == 0) ffn_sf[(size_t)(row0 + r) * a.L.sf_stride_i + task.z] = (uint8_t)ex;
                     }
@@ -584,19 +585,18 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                                      ((size_t)m.z * a.cap + m.y) * a.H + task.z * kBlockN + half * 64;
                     uint4* d0 = reinterpret_cast<uint4*>(crow);
                     uint4* d1 = reinterpret_cast<uint4*>(crow + 128);
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
+                    auto pack8 = [](const uint32_t* v) {
                         uint4 o;
-                        o.x = pack_bf16x2(__uint_as_float(vg[c * 8 + 0]), __uint_as_float(vg[c * 8 + 1]));
-                        o.y = pack_bf16x2(__uint_as_float(vg[c * 8 + 2]), __uint_as_float(vg[c * 8 + 3]));
-                        o.z = pack_bf16x2(__uint_as_float(vg[c * 8 + 4]), __uint_as_float(vg[c * 8 + 5]));
-                        o.w = pack_bf16x2(__uint_as_float(vg[c * 8 + 6]), __uint_as_float(vg[c * 8 + 7]));
-                        d0[c] = o;
-                        o.x = pack_bf16x2(__uint_as_float(vu[c * 8 + 0]), __uint_as_float(vu[c * 8 + 1]));
-                        o.y = pack_bf16x2(__uint_as_float(vu[c * 8 + 2]), __uint_as_float(vu[c * 8 + 3]));
-                        o.z = pack_bf16x2(__uint_as_float(vu[c * 8 + 4]), __uint_as_float(vu[c * 8 + 5]));
-                        o.w = pack_bf16x2(__uint_as_float(vu[c * 8 + 6]), __uint_as_float(vu[c * 8 + 7]));
-                        d1[c] = o;
+                        o.x = pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1]));
+                        o.y = pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3]));
+                        o.z = pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5]));
+                        o.w = pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7]));
+                        return o;
+                    };
+#pragma unroll
+                    for (int c = 0; c < 8; c += 2) {   // 32-byte stores: one full sector each
+                        st_global_v8(d0 + c, pack8(&vg[c * 8]), pack8(&vg[c * 8 + 8]));
+                        st_global_v8(d1 + c, pack8(&vu[c * 8]), pack8(&vu[c * 8 + 8]));
                     }
                     pend_ptr = reinterpret_cast<uint32_t*>(peer_unk + a.L.combine_cnt_off) + (size_t)m.z * a.cap + m.y;
                 }
