@@ -127,16 +127,29 @@ def make_weights(torch, epr, rank, device):
     return (w1, s1), (w2, s2)
 
 
+ROUTING = "uniform"   # set from --routing
+
+
 def make_inputs(torch, tokens, rank, seed):
     """Host-side (pinned) inputs of one step: x E4M3 + 1x128 scales, 8 distinct experts per token
-    uniformly at random, weights = softmax of N(0,1) logits."""
+    (uniformly at random, or without replacement from Zipf(1.2) over a seeded permutation of the
+    experts: the hottest expert then receives about ten times the mean), weights = softmax of
+    N(0,1) logits."""
     g = torch.Generator()
     g.manual_seed(seed * 7919 + rank)
     r = torch.randint(0, 256, (tokens, H), generator=g, dtype=torch.uint8)
     ex = torch.randint(3, 11, (tokens, H), generator=g, dtype=torch.uint8)
     x = ((r & 0x87) | (ex << 3)).pin_memory()
     x_sf = (torch.randint(0, 3, (tokens, H // 128), generator=g, dtype=torch.uint8) + (127 - 3)).pin_memory()
-    idx = torch.rand((tokens, E_TOTAL), generator=g).topk(TOPK, dim=1).indices.to(torch.int64).pin_memory()
+    if ROUTING == "zipf":
+        gp = torch.Generator()
+        gp.manual_seed(4242)                       # the same expert popularity on every rank and step
+        perm = torch.randperm(E_TOTAL, generator=gp)
+        p = 1.0 / torch.arange(1, E_TOTAL + 1, dtype=torch.float64) ** 1.2
+        draw = torch.multinomial((p / p.sum()).expand(tokens, E_TOTAL), TOPK, replacement=False, generator=g)
+        idx = perm[draw].to(torch.int64).pin_memory()
+    else:
+        idx = torch.rand((tokens, E_TOTAL), generator=g).topk(TOPK, dim=1).indices.to(torch.int64).pin_memory()
     w = torch.softmax(torch.randn((tokens, TOPK), generator=g), dim=1).float().pin_memory()
     return x, x_sf, idx, w
 
@@ -258,9 +271,11 @@ def cpu_arm(args, n_ranks):
 
 
 def workload_config(n, tokens):
-    return {"workload": f"MoE layer balanced: E={E_TOTAL} topk=8 H={H} I=2048 FP8 e4m3 + UE8M0 block "
+    kind = "balanced" if ROUTING == "uniform" else "skewed"
+    how = "uniform distinct routing" if ROUTING == "uniform" else "Zipf(1.2) distinct routing over a seeded expert permutation"
+    return {"workload": f"MoE layer {kind}: E={E_TOTAL} topk=8 H={H} I=2048 FP8 e4m3 + UE8M0 block "
                         f"scales, {n * tokens} tokens in total = {tokens} tokens/rank, EP={n} "
-                        f"({E_TOTAL // n} experts/GPU), uniform distinct routing",
+                        f"({E_TOTAL // n} experts/GPU), {how}",
             "tokens_per_rank": tokens, "global_tokens": n * tokens, "ep": n, "experts_per_gpu": E_TOTAL // n,
             "l2_policy": "inputs larger than L2 (expert weights streamed per layer >> 126 MB)"}
 
@@ -438,6 +453,23 @@ def gpu_arm(args):
     if rank == 0:
         # the layer is ONE kernel (k_mega); its duration is the step time measured above
         achieved = work["layer_bytes"] / (ms_step * 1e-3) / 1e9
+        _, bound = binding(work)
+        if bound == "tensor":   # prefill-sized run: the FP8 contraction binds, report it in TFLOP/s
+            tf = work["flops"] / (ms_step * 1e-3) / 1e12
+            roof = {"kernel": "k_mega", "bound": "tensor", "achieved": tf, "peak": 2.0 * bf16_tf, "unit": "TFLOP/s",
+                    "frac": tf / (2.0 * bf16_tf), "peak_kind": f"2 x bf16 dense GEMM peak of {peak_kind} (FP8 runs at twice the bf16 rate)",
+                    "frac_of_nominal_4500": tf / 4500.0, "traffic": None,
+                    "kernel_us": ms_step * 1e3, "gemm_phase_us": gemm_ms * 1e3,
+                    "gemm_phase_tflops": work["flops"] / (gemm_ms * 1e-3) / 1e12,
+                    "algorithmic_flops": work["flops"], "active_experts": work["active_experts"], "pairs": work["pairs"]}
+        else:
+            roof = {"kernel": "k_mega", "bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
+                    "frac": achieved / hbm_gbs, "peak_kind": f"of {peak_kind}",
+                    "traffic": int(work["layer_bytes"] * NCU_TRAFFIC_RATIO),
+                    "traffic_source": "ncu capture of the 32-expert shard scaled by algorithmic bytes",
+                    "kernel_us": ms_step * 1e3, "gemm_phase_us": gemm_ms * 1e3,
+                    "algorithmic_bytes": work["layer_bytes"], "active_experts": work["active_experts"],
+                    "pairs": work["pairs"]}
         line = {
             "metric": "tokens_per_s", "value": n * args.tpr / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": n,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -447,13 +479,7 @@ def gpu_arm(args):
             "e2e": {"value": n * args.tpr / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "gpu_launches": int(lib.mxk_kernels_per_layer()) * args.steps,
-            "roofline": {"kernel": "k_mega", "bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
-                         "frac": achieved / hbm_gbs, "peak_kind": f"of {peak_kind}",
-                         "traffic": int(work["layer_bytes"] * NCU_TRAFFIC_RATIO),
-                         "traffic_source": "ncu capture of the 32-expert shard scaled by algorithmic bytes",
-                         "kernel_us": ms_step * 1e3, "gemm_phase_us": gemm_ms * 1e3,
-                         "algorithmic_bytes": work["layer_bytes"], "active_experts": work["active_experts"],
-                         "pairs": work["pairs"]},
+            "roofline": roof,
             "points": points,
             "clocks": clocks,
         }
@@ -475,6 +501,8 @@ def main():
     ap.add_argument("--tpr", type=int, default=0, help="tokens per rank; overrides --global-tokens")
     ap.add_argument("--experts", type=int, default=256, help="total experts (smaller for profiling captures)")
     ap.add_argument("--hidden", type=int, default=6144, help="H (7168 for the prefill-sized configuration)")
+    ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"],
+                    help="expert choice per token: uniform (the baseline's balanced layer) or Zipf(1.2) skew")
     ap.add_argument("--cta-pair", type=int, default=0, choices=[0, 1, 2],
                     help="GEMM tiling: 1 single CTAs, 2 CTA pairs with 256-row windows, 0 chosen by load")
     ap.add_argument("--ticks", action="store_true", help="print the GEMM kernel's wait-time breakdown to stderr")
@@ -483,8 +511,8 @@ def main():
     args = ap.parse_args()
     if args.ticks:
         os.environ["MXK_TICKS"] = "1"
-    global E_TOTAL, H
-    E_TOTAL, H = args.experts, args.hidden
+    global E_TOTAL, H, ROUTING
+    E_TOTAL, H, ROUTING = args.experts, args.hidden, args.routing
     if args.tpr <= 0:
         args.tpr = max(1, args.global_tokens // max(1, args.gpus))
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

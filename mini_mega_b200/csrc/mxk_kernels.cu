@@ -94,7 +94,7 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
     const int warp = threadIdx.x >> 5;
     const bool do_gemm = (phase_mask & MXK_PHASE_GEMM) != 0;
 
-    // the launch counter is advanced by CTA 0 at the end of the route phase, after every
+    // the launch counter is advanced by the last CTA at the end of the route phase, after every
     // CTA has arrived there — i.e. after this read
     const long long epoch = ld_relaxed_gpu(&f->current_time) + ((phase_mask & MXK_PHASE_ROUTE) ? 1 : 0);
 
@@ -125,13 +125,15 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
     // While routing, barrier and dispatch run, HBM would sit idle: pull a slice of the expert
     // weights into L2 now (any W1 tile of a non-empty expert is needed later in this layer; the
     // streaming loads are evict-first, so these lines survive until their task comes up).
-    if (do_gemm && (phase_mask & MXK_PHASE_ROUTE) && threadIdx.x == 32) {
+    if (do_gemm && (phase_mask & MXK_PHASE_ROUTE) && warp == 1) {
+        // issued by all lanes of one warp (a lane per K block), so that the warp reaches the
+        // route phase's first barrier without delay
         const int nt1 = a.I / 128, nkb = a.H / kBlockK;
         const int per_cta = min(nkb, kPrefetchBytesPerCta / (2 * kABytes));
         for (int tile = blockIdx.x; tile < a.EPR * nt1 && tile < (int)gridDim.x; tile += gridDim.x) {
             const int e = tile / nt1, nt = tile % nt1;
             const int row0 = e * 2 * a.I + nt * 128;
-            for (int kb = 0; kb < per_cta; ++kb) {
+            for (int kb = (int)(threadIdx.x & 31); kb < per_cta; kb += 32) {
                 tma_prefetch_l2_2d(&tm_w1, kb * kBlockK, row0);
                 tma_prefetch_l2_2d(&tm_w1, kb * kBlockK, row0 + a.I);
             }

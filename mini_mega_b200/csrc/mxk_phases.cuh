@@ -5,8 +5,9 @@
 //
 //   route_phase     per-rank route build: deterministic slot per (token,k) pair,
 //                   scatter of pair indices into the owner ranks' tables, count
-//                   publish; CTA 0 then writes the row checksums, releases the
-//                   cross-rank barrier flags and advances the launch counter
+//                   publish as epoch-tagged words (they double as the cross-rank
+//                   barrier); the last CTA then writes the row checksums and
+//                   advances the launch counter
 //                   (reference: route_build_body / publish_counts_body /
 //                    xbar_route_ready_body, src/prologue.cuh:126-256, src/flags.cuh:284-377)
 //   setup_phase     CTA 0: barrier wait, prefix table, windows, cost-ordered task
@@ -105,16 +106,19 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
             st_relaxed_sys_u64(recv + le, tagged((uint32_t)c, epoch));
         }
     }
-    if (blockIdx.x == 0)  // invalid expert ids (negative / >= E) take no slot (src/prologue.cuh:166-167)
+    // The launch bookkeeping below belongs to the LAST CTA: CTA 0 goes straight on to poll the
+    // counts and build the tables, which is the critical path of the prologue.
+    const bool closer = blockIdx.x == gridDim.x - 1;
+    if (closer)  // invalid expert ids (negative / >= E) take no slot (src/prologue.cuh:166-167)
         for (int p = tid; p < np; p += nthr)
             if ((uint64_t)ti[p] >= (uint64_t)a.E) pair_state[p] = 0;
 
     // Everything below is off the critical path (the counts are already on their way): make
-    // this CTA's local tables visible, arrive, and let CTA 0 close the launch bookkeeping.
+    // this CTA's local tables visible, arrive, and let the last CTA close the launch bookkeeping.
     __threadfence();
     __syncthreads();
     if (tid == 0) atomicAdd(&f->route_blocks_done, 1u);
-    if (blockIdx.x != 0) return;
+    if (!closer) return;
 
     if (tid == 0) {
         const unsigned want = gridDim.x;
@@ -358,6 +362,14 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
         uint32_t wbits = 0;
         if (lane == 0)  // issued first so that it travels with the row
             wbits = ld_relaxed_sys(reinterpret_cast<const uint32_t*>(peer + a.weights_off) + (size_t)token * a.topk + k);
+        // the row's scale bytes too (up to 64 K blocks): requested before the row so that the whole
+        // row costs ONE round trip to the source rank
+        uint8_t sfb[2] = {127, 127};
+        if (a.scaled) {
+            const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
+            if (lane < kb) sfb[0] = ld_relaxed_sys_u8(ssf + lane);
+            if (lane + 32 < kb) sfb[1] = ld_relaxed_sys_u8(ssf + lane + 32);
+        }
         // up to 16 loads in flight per lane before the first store (the strong loads are not
         // reordered by the compiler, so issue order is what hides the NVLink round trip)
         for (int i0 = lane; i0 < n16; i0 += 32 * 16) {
@@ -372,7 +384,8 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
         if (a.scaled) {
             const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
             for (int i = lane; i < a.L.sf_stride_h; i += 32)
-                pool_sf[(size_t)g * a.L.sf_stride_h + i] = i < kb ? ld_relaxed_sys_u8(ssf + i) : (uint8_t)127;
+                pool_sf[(size_t)g * a.L.sf_stride_h + i] =
+                    i < 64 ? sfb[i >> 5] : (i < kb ? ld_relaxed_sys_u8(ssf + i) : (uint8_t)127);
         }
         if (lane == 0) meta[g] = make_int4(src, token, k, (int)wbits);
         // the row is complete: every lane makes its stores visible at GPU scope and to TMA

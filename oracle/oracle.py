@@ -356,6 +356,36 @@ def gen_case(R, EPR, topk, H, I, tokens, seed=0, routing="uniform", scaled=True,
     return Case(R, EPR, topk, H, I, cap, list(tokens), scaled, x, x_sf, ti, tw, w1, w1_sf, w2, w2_sf, name)
 
 
+def routes_from_counts(per_expert, R: int, tokens: int, topk: int) -> np.ndarray:
+    """Routes [R][tokens][topk] that reproduce recorded per-expert received-pair counts
+    (the replay of the reference's real-serving TK_INFO corpora, test/mega_common.cuh:460-482):
+    walking the global experts in order, the j-th pair overall goes to source rank j % R,
+    q = j / R, token q % tokens, top-k position q / tokens.  Raises if the counts do not
+    fill R*tokens*topk pairs or a token would name an expert twice."""
+    per_expert = np.asarray(per_expert, np.int64)
+    total = int(per_expert.sum())
+    if total != R * tokens * topk:
+        raise ValueError(f"counts hold {total} pairs, the world has {R * tokens * topk}")
+    ge = np.repeat(np.arange(per_expert.size, dtype=np.int64), per_expert)   # expert of pair j
+    j = np.arange(total)
+    src, q = j % R, j // R
+    out = np.zeros((R, tokens, topk), np.int64)
+    out[src, q % tokens, q // tokens] = ge
+    srt = np.sort(out, axis=2)
+    if (srt[:, :, 1:] == srt[:, :, :-1]).any():
+        raise ValueError("a token names an expert twice")
+    return out
+
+
+def with_routes(case: Case, routes: np.ndarray) -> Case:
+    """The same case with its top-k expert ids replaced by `routes` [R][tokens][topk]."""
+    ti = case.topk_idx.copy()
+    for r in range(case.R):
+        ti[r, : case.tokens[r]] = routes[r, : case.tokens[r]]
+    return Case(case.R, case.EPR, case.topk, case.H, case.I, case.cap, list(case.tokens), case.scaled, case.x,
+                case.x_sf, ti, case.topk_w, case.w1, case.w1_sf, case.w2, case.w2_sf, case.name)
+
+
 def gen_reference_fixture(R, EPR, topk, H, I, tokens, pattern="balanced", salt=0, cap=None) -> Case:
     """The reference harness's deterministic fixtures with run-time geometry:
     x byte (rank*37 + t*7 + c*3) & 0x3f and top-k weight 1 + 0.25*rank + 0.01*(i%7)

@@ -2,15 +2,17 @@
 
 Run in a container that has the reference checkout (default /root/reference):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py [/path/to/reference] [--only-tk-info]
 
-Two sources are used, neither copied into this repository:
+Three sources are used, none copied into this repository:
   * the reference's host-side C++ functions, compiled from its sources into
     oracle/_ref/libmoe_ref.so by oracle/Makefile (E4M3/bf16 codecs, ref_l1,
     ref_l2, ref_reduce, make_routes, gs_schedule_member, select_win, lpt_assign);
   * the reference's Python quantisers, imported by file path from
     torch/mxmegakernel/utils/math.py (ceil_to_ue8m0, per_token_cast_to_fp8,
     per_block_cast_to_fp8, cast_back_from_fp8).
+  * the reference's recorded route corpus test/76.real_decode/dataset.tk_info, of
+    which four launches' per-expert counts are kept (tk_info.npz).
 The fixtures are small .npz files; tests/test_oracle_golden.py checks the
 oracle against them on any machine.
 """
@@ -27,8 +29,38 @@ sys.path.insert(0, ROOT)
 from oracle import oracle as orc  # noqa: E402
 
 
+def make_tk_info(ref_root):
+    """A sample of the reference's real-decode route corpus (test/76.real_decode/dataset.tk_info:
+    per launch, the pairs each of 32 ranks x 8 experts received in live serving): the most
+    skewed, the median and the least skewed of the 4096-pair launches, and the most skewed
+    launch with fewer pairs.  Stored as counts per global expert [launches][256]."""
+    import collections
+    import re
+    launches = collections.OrderedDict()
+    with open(os.path.join(ref_root, "test", "76.real_decode", "dataset.tk_info"), errors="ignore") as fh:
+        for line in fh:
+            m = re.match(r"\[TK_INFO\] rank=(\d+) launch=(\d+) n=(\d+) : (.*)", line.strip())
+            if m:
+                launches.setdefault(int(m.group(2)), {})[int(m.group(1))] = [int(v) for v in m.group(4).split()]
+    full = {k: np.array([d[r] for r in range(32)], np.int32).reshape(-1) for k, d in launches.items()
+            if len(d) == 32 and all(len(v) == 8 for v in d.values())}
+    skew = lambda c: c.max() / c.mean()
+    big = sorted((k for k, c in full.items() if c.sum() == 4096), key=lambda k: skew(full[k]))
+    small = sorted((k for k, c in full.items() if c.sum() < 4096 and c.sum() % 64 == 0 and c.sum() >= 2048),
+                   key=lambda k: skew(full[k]))
+    pick = [big[-1], big[len(big) // 2], big[0], small[-1]]
+    np.savez_compressed(os.path.join(HERE, "tk_info.npz"), launch=np.array(pick, np.int32),
+                        counts=np.stack([full[k] for k in pick]))
+    print("tk_info launches", pick, "pairs", [int(full[k].sum()) for k in pick],
+          "max/mean", [round(float(skew(full[k])), 1) for k in pick])
+
+
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = next((a for a in sys.argv[1:] if not a.startswith("--")), "/root/reference")
+    if "--only-tk-info" in sys.argv:
+        make_tk_info(ref_root)
+        return
+    make_tk_info(ref_root)
     orc.build()
     R = orc.ref_lib()
     assert R is not None, "oracle/_ref/libmoe_ref.so missing: run make -C oracle with the reference present"

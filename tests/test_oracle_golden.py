@@ -154,3 +154,25 @@ def test_against_compiled_reference(orc):
     # codec spot checks
     for v in (0.3, -17.0, 500.0, 1e-3):
         assert R.ref_e4m3_quantize(v) == orc.lib().orc_e4m3_quantize(v)
+
+
+def test_recorded_route_corpus_replay(orc, golden_dir):
+    """routes_from_counts (reference: test/mega_common.cuh:460-482) on the sampled launches of the
+    real-decode corpus: the routes reproduce the recorded per-expert counts exactly (the
+    reference's route_count_deviation == 0, :485-495), no token names an expert twice, and the
+    prologue restatement then reports the same received counts on every owner rank."""
+    g = _load(golden_dir, "tk_info.npz")
+    R, EPR, topk = 8, 32, 8
+    for counts in g["counts"]:
+        tokens = int(counts.sum()) // (R * topk)
+        routes = orc.routes_from_counts(counts, R, tokens, topk)
+        assert routes.shape == (R, tokens, topk)
+        assert np.array_equal(np.bincount(routes.reshape(-1), minlength=R * EPR), counts)
+        srt = np.sort(routes, axis=2)
+        assert not (srt[:, :, 1:] == srt[:, :, :-1]).any()
+        case = orc.with_routes(orc.gen_case(R, EPR, topk, 128, 128, tokens, seed=3, scaled=False), routes)
+        ref = orc.route_world(case)
+        for r in range(R):
+            assert np.array_equal(ref[r].prefix_tbl[:, R], counts[r * EPR:(r + 1) * EPR])
+    with pytest.raises(ValueError):
+        orc.routes_from_counts(g["counts"][0], R, 63, topk)
