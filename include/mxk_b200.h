@@ -232,6 +232,15 @@ int64_t mxk_static_scratch_bytes(void);
  * MetaX lane order, src/megakernel.cu:66-105, src/megakernel.h:46-47). */
 int mxk_fill_weights(uint8_t* w, int64_t n_rows, int32_t k_cols, uint32_t seed, void* stream);
 
+/* bf16 activations -> E4M3 rows + one UE8M0 scale per 128 columns (x_sf [tokens][hidden/128]),
+ * the reference's activation quantiser per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=128)
+ * (torch/mxmegakernel/utils/math.py:26-36).  x_sf == NULL: plain saturating RNE cast, the
+ * reference kernel's own bf16 prefold for its scale-free arithmetic (src/prologue.cuh:105-122,
+ * MegaLaunchArgs::in_bf16).  A host that holds bf16 activations calls this on the launch stream
+ * with x_fp8 / x_sf pointing at this rank's x / x_sf regions of `sym`, then launches the layer:
+ * peers still pull one byte per element.  The launch structure's in_bf16 stays rejected. */
+int mxk_quantize_rows(const void* x_bf16, int32_t tokens, int32_t hidden, void* x_fp8, void* x_sf, void* stream);
+
 /* Registers / shared memory of every kernel, printed to stdout (reference:
  * dump_kernel_resources, src/megakernel.cu:270-282). */
 int mxk_dump_kernel_resources(void);

@@ -79,7 +79,7 @@ EXPORTS = [
     "mxk_last_error", "mxk_version", "mxk_compute_layout", "mxk_sym_bytes", "mxk_rwk_bytes", "mxk_unk_bytes",
     "mxk_launch_prelude", "mxk_launch_compute", "mxk_launch_reduce", "mxk_launch_full", "mxk_launch_empty",
     "mxk_kernels_per_layer", "mxk_launch_phases", "mxk_launch_full_static",
-    "mxk_static_scratch_bytes", "mxk_fill_weights", "mxk_dump_kernel_resources", "mxk_read_status", "mxk_select_win",
+    "mxk_static_scratch_bytes", "mxk_fill_weights", "mxk_quantize_rows", "mxk_dump_kernel_resources", "mxk_read_status", "mxk_select_win",
     "mxk_symm_alloc", "mxk_symm_free", "mxk_ipc_export", "mxk_ipc_import", "mxk_ipc_close",
 ]
 
@@ -111,6 +111,7 @@ def lib():
     L.mxk_launch_phases.argtypes = [C.POINTER(MxkLaunchArgs), C.c_int, C.c_void_p]
     L.mxk_launch_empty.argtypes = [C.c_int, C.c_int, C.c_int64, C.c_void_p]
     L.mxk_fill_weights.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_uint32, C.c_void_p]
+    L.mxk_quantize_rows.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
     L.mxk_read_status.argtypes = [C.c_void_p, C.POINTER(MxkStatus)]
     L.mxk_select_win.argtypes = [C.POINTER(C.c_uint32), C.c_int, C.c_int, C.c_int]
     L.mxk_symm_alloc.argtypes = [C.POINTER(C.c_void_p), C.c_int64]

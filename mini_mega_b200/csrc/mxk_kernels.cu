@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -193,6 +194,41 @@ k_mega_pair(const KArgs a, const int phase_mask, const __grid_constant__ CUtenso
 }
 
 __global__ void k_empty() {}
+
+// bf16 rows -> E4M3 + one UE8M0 scale per 128 columns, the reference's activation quantiser
+// (per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=128), torch/mxmegakernel/utils/math.py:26-36:
+// amax of the group clamped to 1e-4, sf = 2^ceil(log2(amax/448)), q = RNE(x / sf)); with
+// sf == nullptr a plain saturating RNE cast, which is what the reference kernel's bf16
+// prefold does (src/prologue.cuh:105-122).  One warp per 128-column group, 4 values per lane.
+__global__ void k_quant_rows(const uint16_t* __restrict__ x, int tokens, int H, uint8_t* __restrict__ q,
+                             uint8_t* __restrict__ sf) {
+    const int groups = H / 128;
+    const long long n = (long long)tokens * groups;
+    const int lane = threadIdx.x & 31;
+    const long long w0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nw = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long g = w0; g < n; g += nw) {
+        const long long t = g / groups;
+        const int c = (int)(g % groups);
+        const uint2 raw = *reinterpret_cast<const uint2*>(x + t * H + c * 128 + lane * 4);
+        const float v[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+                            __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
+        float inv = 1.0f;
+        if (sf) {
+            float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
+            const float s = fmaxf(amax, 1e-4f) / 448.0f;
+            const uint32_t bits = __float_as_uint(s);
+            uint32_t ex = ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) ? 1u : 0u);   // ceil to a power of two
+            ex = min(254u, max(1u, ex));
+            inv = __uint_as_float((254u - ex) << 23);
+            if (lane == 0) sf[t * groups + c] = (uint8_t)ex;
+        }
+        *reinterpret_cast<uint32_t*>(q + t * H + c * 128 + lane * 4) =
+            pack_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+    }
+}
 
 __global__ void k_fill_weights(uint8_t* w, long long n_rows, int k_cols, uint32_t seed) {
     const long long n = n_rows * k_cols;
@@ -589,9 +625,24 @@ int mxk_fill_weights(uint8_t* w, int64_t n_rows, int32_t k_cols, uint32_t seed, 
     return e == cudaSuccess ? 0 : cuda_fail(e, "launch fill_weights");
 }
 
+int mxk_quantize_rows(const void* x_bf16, int32_t tokens, int32_t hidden, void* x_fp8, void* x_sf, void* stream) {
+    if (!x_bf16 || !x_fp8 || tokens < 0 || hidden < 128 || hidden % 128)
+        return fail(MXK_ERR_BAD_ARG, "quantize_rows: null pointer, negative tokens or hidden not a multiple of 128");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 7) || (reinterpret_cast<uintptr_t>(x_fp8) & 3))
+        return fail(MXK_ERR_BAD_ARG, "quantize_rows: x_bf16 must be 8-byte and x_fp8 4-byte aligned");
+    if (tokens == 0) return 0;
+    const long long warps = (long long)tokens * (hidden / 128);
+    const int blocks = (int)std::min<long long>((warps + 7) / 8, 148 * 8);
+    k_quant_rows<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(x_bf16), tokens, hidden, static_cast<uint8_t*>(x_fp8), static_cast<uint8_t*>(x_sf));
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "launch k_quant_rows");
+}
+
 int mxk_dump_kernel_resources(void) {
     struct { const char* name; const void* fn; } ks[] = {
-        {"k_mega", (const void*)k_mega}, {"k_fill_weights", (const void*)k_fill_weights}};
+        {"k_mega", (const void*)k_mega}, {"k_mega_pair", (const void*)k_mega_pair},
+        {"k_quant_rows", (const void*)k_quant_rows}, {"k_fill_weights", (const void*)k_fill_weights}};
     for (auto& k : ks) {
         cudaFuncAttributes at;
         cudaError_t e = cudaFuncGetAttributes(&at, k.fn);

@@ -31,7 +31,7 @@ from ._lib import MxkLaunchArgs, MxkStatus, check, compute_layout
 EXPERT_WINDOW_MIN = 8
 EXPERT_WINDOW_MAX = 128
 EXPERT_WINDOW_MULTIPLE = 8
-_SUPPORTED_MMA_TYPES = ("fp8xfp8",)
+_SUPPORTED_MMA_TYPES = ("fp8xfp8", "bf16xfp8")
 
 
 class _DevMem:
@@ -144,8 +144,16 @@ class SymmBuffer:
         self._peer_bases = torch.tensor(sym_ptrs, dtype=torch.int64, device=f"cuda:{self.device}")
         self._unk_peers = torch.tensor(unk_ptrs, dtype=torch.int64, device=f"cuda:{self.device}")
 
-        self.x = _view(self.buffer, torch.float8_e4m3fn, (cap, self.hidden), int(L.x_off))
+        # fp8xfp8: `x` is the E4M3 region peers pull from.  bf16xfp8 (reference:
+        # torch/mxmegakernel/mega/__init__.py:244-246): `x` is a private bf16 tensor the caller
+        # fills; every layer call first quantises it into the E4M3 region `x_fp8` + `x_sf`
+        # (one byte per element still crosses NVLink).
+        self.x_fp8 = _view(self.buffer, torch.float8_e4m3fn, (cap, self.hidden), int(L.x_off))
         self.x_sf = _view(self.buffer, torch.uint8, (cap, self.hidden // 128), int(L.x_sf_off))
+        if mma_type == "bf16xfp8":
+            self.x = torch.zeros((cap, self.hidden), dtype=torch.bfloat16, device=f"cuda:{self.device}")
+        else:
+            self.x = self.x_fp8
         self.topk_idx = _view(self.buffer, torch.int64, (cap, self.num_topk), int(L.topk_idx_off))
         self.topk_weights = _view(self.buffer, torch.float32, (cap, self.num_topk), int(L.topk_weights_off))
         torch.cuda.synchronize()
@@ -303,9 +311,21 @@ def transform_weights_for_mega_moe(l1_weights: WeightArg, l2_weights: WeightArg,
     return l1, l2
 
 
+def _quantize_input(sym_buffer: "SymmBuffer", num_tokens: int, scaled: bool) -> None:
+    """bf16xfp8 buffers: quantise `x` (bf16) into the region peers pull from, on the launch stream."""
+    if sym_buffer.mma_type != "bf16xfp8" or num_tokens == 0:
+        return
+    check(_lib.lib().mxk_quantize_rows(sym_buffer.x.data_ptr(), int(num_tokens), sym_buffer.hidden,
+                                       sym_buffer.x_fp8.data_ptr(),
+                                       sym_buffer.x_sf.data_ptr() if scaled else None, _stream_ptr()),
+          "mxk_quantize_rows")
+
+
 def _check_buffer(sym_buffer: SymmBuffer, fn: str):
-    if sym_buffer.mma_type != "fp8xfp8":
-        raise ValueError(f"{fn} requires an fp8xfp8 SymmBuffer, got {sym_buffer.mma_type!r}")
+    # like the reference (torch/mxmegakernel/mega/__init__.py:615-618) the fp8 entry points take
+    # both buffer kinds; a bf16xfp8 buffer gets its input quantised first
+    if sym_buffer.mma_type not in ("fp8xfp8", "bf16xfp8"):
+        raise ValueError(f"{fn} requires an fp8xfp8 / bf16xfp8 SymmBuffer, got {sym_buffer.mma_type!r}")
 
 
 def _stream_ptr() -> int:
@@ -338,6 +358,7 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
         raise ValueError("y must be a contiguous bf16 [tokens, hidden] tensor")
     _check_weights(sym_buffer, l1_weights, l2_weights)
     lib = _lib.lib()
+    _quantize_input(sym_buffer, num_tokens, isinstance(l1_weights, tuple) and l1_weights[1] is not None)
     a = sym_buffer.launch_args(num_tokens, l1_weights, l2_weights, y_bf16=y, expert_window=expert_window,
                                max_spins=max_spins, cta_pair=cta_pair)
     if num_tokens == 0:  # nothing to reduce, but the rank still serves its experts
@@ -356,6 +377,7 @@ def fp8_mega_moe_compute(l1_weights, l2_weights, sym_buffer: SymmBuffer, num_tok
     if num_tokens < 0 or num_tokens > sym_buffer.num_max_tokens_per_rank:
         raise ValueError(f"num_tokens={num_tokens} exceeds capacity {sym_buffer.num_max_tokens_per_rank}")
     _check_weights(sym_buffer, l1_weights, l2_weights)
+    _quantize_input(sym_buffer, num_tokens, isinstance(l1_weights, tuple) and l1_weights[1] is not None)
     a = sym_buffer.launch_args(num_tokens, l1_weights, l2_weights, expert_window=expert_window,
                                max_spins=max_spins)
     check(_lib.lib().mxk_launch_compute(C.byref(a), _stream_ptr()), "mxk_launch_compute")
@@ -374,15 +396,20 @@ def fp8_mega_moe_reduce(y: torch.Tensor, sym_buffer: SymmBuffer, num_tokens: Opt
 
 
 def bf16_mega_moe(*args, **kwargs):
-    raise NotImplementedError("only fp8xfp8 is implemented")
+    raise NotImplementedError("only fp8xfp8 and bf16xfp8 are implemented")
 
 
-def bf16_fp8_mega_moe(*args, **kwargs):
-    raise NotImplementedError("only fp8xfp8 is implemented")
+def bf16_fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer, **kwargs) -> None:
+    """bf16 activations + FP8 weights (reference: torch/mxmegakernel/mega/__init__.py:719-757): the
+    caller fills ``sym_buffer.x`` (bf16); the rows are quantised on the device to E4M3 with 1x128
+    UE8M0 scales (plain cast when the weights carry no scale planes) and peers pull the bytes."""
+    if sym_buffer.mma_type != "bf16xfp8":
+        raise ValueError(f"bf16_fp8_mega_moe requires a bf16xfp8 SymmBuffer, got {sym_buffer.mma_type!r}")
+    fp8_mega_moe(y, l1_weights, l2_weights, sym_buffer, **kwargs)
 
 
 def fp8_fp4_mega_moe(*args, **kwargs):
-    raise NotImplementedError("only fp8xfp8 is implemented")
+    raise NotImplementedError("only fp8xfp8 and bf16xfp8 are implemented")
 
 
 def read_dbg_report(sym_buffer: SymmBuffer, hidden: int = 0, intermediate_hidden: int = 0):
