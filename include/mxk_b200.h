@@ -219,8 +219,10 @@ int mxk_launch_phases(const MxkLaunchArgs* a, int phase_mask, void* stream);
  * The first call on a device asks the CUDA runtime for the array's device address
  * (once per device, with that device current); make that first call outside any stream
  * capture.  All calls share the one array and it keeps the previous call's contents: the
- * status header and the barrier slot are cleared at the start of every call, everything
- * else is rewritten before it is read.  Two calls that overlap on the GPU (different
+ * status header behind the launch counter is cleared at the start of every call, the launch
+ * counter keeps running from call to call (the prologue's tables are tagged with it, so the
+ * previous call's words can never be taken for current ones), everything else is rewritten
+ * before it is read.  Two calls that overlap on the GPU (different
  * streams, or several threads) would race on the array: issue them on one stream or
  * serialise them yourself.  mxk_read_status cannot be used with it; a device-side expiry
  * shows up as wrong output only. */

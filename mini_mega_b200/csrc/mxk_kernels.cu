@@ -12,6 +12,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstddef>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -580,12 +581,14 @@ int mxk_launch_full_static(const MxkLaunchArgs* a, void* stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* unk = base + kStaticPtrBytes;
     uint8_t* rwk = unk + L.unk_bytes;
-    // The array keeps whatever the previous call left.  What the protocol needs at zero is
-    // the status header (launch counter, status word, expiry counters) and the barrier slot.
-    cudaError_t e = cudaMemsetAsync(rwk + L.flags_off, 0, 1024, st);
+    // The array keeps whatever the previous call left.  What the protocol needs at zero is the
+    // status header behind the launch counter (status word, expiry counters, work counters).  The
+    // launch counter itself — first word of the header, zero when the module is loaded — must
+    // keep running: the prologue's tables are tagged with it, and a counter that started over
+    // would make the previous call's words look current.
+    static_assert(offsetof(DevFlags, current_time) == 0 && sizeof(long long) == 8, "launch counter leads the header");
+    cudaError_t e = cudaMemsetAsync(rwk + L.flags_off + 8, 0, 1024 - 8, st);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status header)");
-    e = cudaMemsetAsync(unk + L.xbar_off, 0, (size_t)L.xbar_stride * 4, st);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(barrier slot)");
     void** sym_table = reinterpret_cast<void**>(base);
     void** unk_table = reinterpret_cast<void**>(base + 128);
     k_static_ptrs<<<1, 1, 0, st>>>(sym_table, unk_table, const_cast<uint8_t*>(a->self), unk);
