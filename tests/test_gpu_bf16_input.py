@@ -17,8 +17,9 @@ def _bf16_rows(T, H, seed):
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((T, H)).astype(np.float32) * np.exp(rng.uniform(-6, 6, (T, 1))).astype(np.float32)
     x[0, :128] = 0.0                 # all-zero group: amax clamps to 1e-4
-    x[1, 128:256] *= 1e4             # large group
-    x[2, 5] = 448.0 * 2.0 ** 3       # exactly representable maximum of its scale
+    if T > 2 and H >= 256:
+        x[1, 128:256] *= 1e4         # large group
+        x[2, 5] = 448.0 * 2.0 ** 3   # exactly representable maximum of its scale
     return torch.from_numpy(x).bfloat16()
 
 
