@@ -36,7 +36,7 @@ NVLINK_GBS = 770.0               # measured peer copy per direction on this pool
 # 1.1872 GB read+written per launch against 1.1757 GB algorithmic on the 32-expert shard.  The
 # benchmark's own launches stream more experts through the same code, so traffic is scaled from
 # that capture in proportion to the algorithmic bytes (weights dominate both).
-NCU_TRAFFIC_RATIO = 1.1872 / 1.1757
+NCU_TRAFFIC_RATIO = 1.1862 / 1.1757   # dram bytes of the captured decode shard / its algorithmic bytes (profiles/)
 
 
 def load_peaks():
