@@ -20,8 +20,8 @@
 // Warp roles (384 threads):
 //   warp 0      task scheduler + TMA producer (operand tiles, 4-stage ring)
 //   warp 1      MMA issuer (one lane), owns the TMEM allocation
-//   warps 2-3   scale-tile builders (even / odd groups): global scale planes -> shared
-//               tiles for UTCCP
+//   warps 2-3   scale-tile builders (even / odd tasks): global scale planes -> shared
+//               tiles -> tensor memory (tcgen05.cp)
 //   warps 4-11  epilogue: warp w reads TMEM lanes 32*(w%4).., column half (w-4)/4
 // ============================================================================
 #pragma once
@@ -319,7 +319,11 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
         }
     } else if (warp == 2 || warp == 3) {
         // ------------------------------------------------------ scale-tile builders
-        // Two warps share the work: warp 2 builds the even-numbered groups, warp 3 the odd ones.
+        // Two warps share the work by TASK: warp 2 builds the scale tiles of the even-numbered ring
+        // entries, warp 3 those of the odd ones.  Preparing a task is a chain of dependent global
+        // round trips (window record, gate counter, scale rows) that takes about as long as the MMAs
+        // of a short task; with alternating tasks each warp works one task ahead of the MMA issuer
+        // instead of in lock-step with it.  Both warps read every ring entry to keep the group count.
         const uint32_t my_parity = (uint32_t)(warp - 2);
         // Slot layout (what UTCCP 32x128b.warpx4 expects): tile byte 16*l + 4*j + i is the
         // scale of row l + 32*j for K block i of the group.  The two weight tiles repeat one
@@ -337,10 +341,12 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             __syncwarp();
             if (lane == 0) arrive_leader(&S->task_empty[slot]);
             if (task.x < 0) break;
-            const int4 win = ld_relaxed_gpu_v4(windows + task.y);
-            const int e = win.x, row0 = win.y + 128 * (int)crank, rows = task.w - 128 * (int)crank;
             const bool is_l2 = task.x == 1;
             const int nkb = is_l2 ? kb2 : kb1;
+            const int ngroups = (nkb + 3) >> 2;
+            if ((it & 1u) != my_parity) { sfg += (uint32_t)ngroups; continue; }   // the other warp's task
+            const int4 win = ld_relaxed_gpu_v4(windows + task.y);
+            const int e = win.x, row0 = win.y + 128 * (int)crank, rows = task.w - 128 * (int)crank;
             const uint8_t* asf = nullptr;   // activation scale rows of this window
             int asf_stride = 0;
             const uint8_t* wsf0 = nullptr;
@@ -373,7 +379,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             // Per group of four K blocks: 4 activation words per lane (rows l, l+32, l+64, l+96)
             // and one word per weight half.  The loads of group g+1 are issued before the wait
             // for group g's slot, so their latency hides behind the ring.
-            const int ngroups = (nkb + 3) >> 2;
+            const bool wsf_words = a.scaled && (nkb & 3) == 0 &&
+                                   ((reinterpret_cast<uintptr_t>(wsf0) | reinterpret_cast<uintptr_t>(wsf1)) & 3) == 0;
             auto load_group = [&](int g, uint32_t (&wa)[4], uint32_t& w0, uint32_t& w1) {
                 wa[0] = wa[1] = wa[2] = wa[3] = 0x7F7F7F7Fu;
                 w0 = w1 = 0x7F7F7F7Fu;
@@ -382,6 +389,11 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 for (int j = 0; j < 4; ++j) {
                     const int r = lane + 32 * j;
                     if (r < rows) wa[j] = ld_relaxed_gpu(reinterpret_cast<const uint32_t*>(asf + (size_t)r * asf_stride) + g);
+                }
+                if (wsf_words) {   // the four K blocks' weight scales are one aligned word per half
+                    w0 = __ldg(reinterpret_cast<const uint32_t*>(wsf0) + g);
+                    w1 = __ldg(reinterpret_cast<const uint32_t*>(wsf1) + g);
+                    return;
                 }
                 w0 = 0; w1 = 0;
 #pragma unroll
@@ -394,13 +406,11 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 }
             };
             uint32_t wa[4], w0, w1;
-            int g = (int)((sfg ^ my_parity) & 1u);   // first group of this task that is mine
-            sfg += (uint32_t)g;
-            load_group(g, wa, w0, w1);
+            load_group(0, wa, w0, w1);
             bool dead = false;
-            for (; g < ngroups; g += 2, sfg += 2) {
+            for (int g = 0; g < ngroups; ++g, ++sfg) {
                 uint32_t na[4], n0, n1;
-                load_group(g + 2, na, n0, n1);
+                load_group(g + 1, na, n0, n1);
                 const uint32_t sslot = sfg % kSfRing;
                 bool free_ = true;
                 if (lane == 0) free_ = mbar_wait(&S->sf_empty[sslot], ((sfg / kSfRing) & 1) ^ 1, wait_ns, abort_flag);
@@ -446,7 +456,6 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 for (int j = 0; j < 4; ++j) wa[j] = na[j];
                 w0 = n0; w1 = n1;
             }
-            sfg -= (uint32_t)(g - ngroups);  // both warps leave the task with the same group count
             if (dead) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; } break; }
         }
     } else if (warp >= kFirstEpiWarp) {
