@@ -173,24 +173,30 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 }
                 return tk;
             };
+            // The window record and the gate counter of a task are two dependent global round
+            // trips; with the look-ahead they are requested for the NEXT task while this task's
+            // loads are being issued, so that a task starts without them on its critical path.
+            auto gate_passed = [&](const int4& tk, const int4& wn) -> bool {   // one acquire load
+                return tk.x == 1 ? ld_acquire_gpu(l1_done + tk.y) >= l1_need
+                                 : ld_acquire_gpu(pool_ready + tk.y) >= (uint32_t)wn.z;
+            };
             int4 pending = claim_publish(0);
+            int4 pending_win = make_int4(0, 0, 0, 0);
+            bool pending_win_valid = false, pending_gate = false;
             for (uint32_t it = 0;; ++it) {
                 if (ring_dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break; }
                 const int4 task = pending;
                 if (task.x < 0) break;
+                const int4 win = pending_win_valid ? pending_win : ld_relaxed_gpu_v4(windows + task.y);
+                const bool gate_ok = pending_win_valid && pending_gate;
+                pending_win_valid = false;
                 if (lookahead) pending = claim_publish(it + 1);
-                const int4 win = ld_relaxed_gpu_v4(windows + task.y);
                 const int e = win.x, row0 = win.y + 128 * (int)crank;
                 const bool is_l2 = task.x == 1;
-                if (is_l2) {  // every L1 tile of this window must have landed in ffn
-                    if (!MXK_TIMED(w_gate, spin_until([&] { return ld_acquire_gpu(l1_done + task.y) >= l1_need; }, wait_ns, abort_flag))) {
-                        raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
-                    }
-                } else {      // every row of this window must have been pulled into the pool
-                    const uint32_t need_rows = (uint32_t)win.z;
-                    if (!MXK_TIMED(w_gate, spin_until([&] { return ld_acquire_gpu(pool_ready + task.y) >= need_rows; }, wait_ns, abort_flag))) {
-                        raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
-                    }
+                // L2: every L1 tile of this window must have landed in ffn; L1: every row of this
+                // window must have been pulled into the pool
+                if (!gate_ok && !MXK_TIMED(w_gate, spin_until([&] { return gate_passed(task, win); }, wait_ns, abort_flag))) {
+                    raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
                 }
                 fence_proxy_async_global();  // pool / ffn rows were written with ordinary stores
                 const CUtensorMap* ma = is_l2 ? &tm_ffn : &tm_pool;
@@ -200,6 +206,13 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 const int brow1 = is_l2 ? brow0 + 128 : brow0 + a.I;
                 bool dead = false;
                 for (int kb = 0; kb < nkb; ++kb) {
+                    if (lookahead && pending.x >= 0) {
+                        // request the next task's window record with the first stage, read its gate
+                        // two stages later (the record has arrived by then): each is one round trip
+                        // taken out of the slack of the stage ring instead of the next task's start
+                        if (kb == 0) { pending_win = ld_relaxed_gpu_v4(windows + pending.y); pending_win_valid = true; pending_gate = false; }
+                        else if (kb == 2) pending_gate = gate_passed(pending, pending_win);
+                    }
                     if (!MXK_TIMED(w_empty, mbar_wait(&S->empty[stage], phase ^ 1, wait_ns, abort_flag))) { dead = true; break; }
                     uint8_t* sa = tiles + stage * kStageB;
                     if constexpr (kPair) {
