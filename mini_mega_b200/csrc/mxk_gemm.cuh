@@ -536,10 +536,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             uint32_t vg[64], vu[64];
             if (warp_active) {
                 const uint32_t t0 = lane_addr + half * 64;
-                tmem_ld32(t0, *reinterpret_cast<uint32_t(*)[32]>(&vg[0]));
-                tmem_ld32(t0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&vg[32]));
-                tmem_ld32(t0 + 128, *reinterpret_cast<uint32_t(*)[32]>(&vu[0]));
-                tmem_ld32(t0 + 160, *reinterpret_cast<uint32_t(*)[32]>(&vu[32]));
+                tmem_ld64(t0, vg);
+                tmem_ld64(t0 + 128, vu);
                 tmem_wait_ld();
             }
             tc_fence_before();
