@@ -47,7 +47,8 @@ constexpr int kTmemSfCol = 256;       // scale tiles live behind the 256 accumul
 constexpr int kSfRing = 8;            // shared-memory scale-tile slots (one per 4 K blocks)
 constexpr int kSfSlotBytes = 3 * 512; // A rows, weight half 0, weight half 1
 constexpr int kPrefetchBytesPerCta = 704 * 1024;  // L2 prefetch during the prologue: 148 CTAs x 704 KB = 104 MB
-constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align*/ + kSfRing * kSfSlotBytes + 8192 /*control*/;
+constexpr int kPubDepth = 8;          // combine-row arrival counts a thread may hold back before one fence releases them
+constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align*/ + kSfRing * kSfSlotBytes + 16384 /*control*/;
 
 // Wait-time accounting (reference: clock64 phase stamps in local_flags.pre_ticks,
 // src/kernel.cuh:52-124): each role sums the cycles it spent blocked and adds them to
@@ -69,9 +70,12 @@ struct GemmSmem {
     uint64_t task_empty[kTaskRing];
     int4 task[kTaskRing];
     unsigned long long xch[2][2][128];  // amax exchange between the two column halves
+    uint32_t pubq[kPubDepth][kEpiWarps * 32];   // per epilogue thread: queued arrival counts, (rank << 24) | (k * cap + token)
     uint32_t tmem_base;
     int abort_flag;
 };
+
+static_assert(sizeof(GemmSmem) <= 16384, "control block must fit the space reserved behind the tile rings");
 
 // Barrier initialisation (one thread) — part of the kernel prologue.
 // In pair mode the barriers the MMA issuer waits on (scale tile ready, accumulators drained) and
@@ -485,26 +489,43 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
         // accumulators when those are already complete, so that the store latency hides
         // behind work instead of holding the tensor memory; it is never held across a wait
         // (an L2 task of this very CTA may be gated on it).
-        int pend_kind = 0;           // 0 none, 1 L1 window share (l1_done), 2 L2 row (combine_cnt)
+        //
+        // The arrival counts of pushed combine rows (L2 tasks) are batched on top of that: a fence
+        // that makes a thread's row segments visible to another GPU costs several microseconds
+        // whatever it has to wait for, more than the MMAs of an L2 task, so a thread queues up to
+        // kPubDepth counts and releases them with ONE fence followed by relaxed adds — when the
+        // queue is full (after a drain, before the next stores are issued), or before it blocks.
+        // Holding them back cannot stall this kernel: only the reduce phase waits for them.
+        int pend_l1 = 0;             // an L1 window share (l1_done) awaits its publish
         uint32_t* pend_ptr = nullptr;
-        auto flush_publish = [&] {
-            if (pend_kind == 0) return;
+        int pub_n = 0;               // queued row counts of this thread
+        const int tq = (int)threadIdx.x - kFirstEpiWarp * 32;
+        auto flush_l1 = [&] {
+            if (!pend_l1) return;
             const long long t_p0 = timed ? clock64() : 0;
-            if (pend_kind == 1) {
-                // every lane makes its own stores visible at GPU scope (and to the TMA reads of
-                // the L2 tasks) before lane 0 counts the warp's share as done
-                __threadfence();
-                fence_proxy_async_global();
-                __syncwarp();
-                if (lane == 0) red_release_gpu_add(pend_ptr, 1u);
-            } else if (pend_ptr) {
-                // release at system scope: this thread's row segment is visible before the count
-                if (a.R > 1) red_release_sys_add(pend_ptr, 1u); else red_release_gpu_add(pend_ptr, 1u);
-            }
-            pend_kind = 0;
-            pend_ptr = nullptr;
+            // every lane makes its own stores visible at GPU scope (and to the TMA reads of
+            // the L2 tasks) before lane 0 counts the warp's share as done
+            __threadfence();
+            fence_proxy_async_global();
+            __syncwarp();
+            if (lane == 0) red_release_gpu_add(pend_ptr, 1u);
+            pend_l1 = 0;
             if (timed) t_pub += clock64() - t_p0;
         };
+        auto flush_rows = [&] {
+            if (pub_n == 0) return;
+            const long long t_p0 = timed ? clock64() : 0;
+            fence_world(a.R > 1);   // every row segment this thread has stored is visible before the counts
+            for (int i = 0; i < pub_n; ++i) {
+                const uint32_t en = S->pubq[i][tq];
+                uint32_t* cnt = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[en >> 24]) + a.L.combine_cnt_off) +
+                                (en & 0xFFFFFFu);
+                if (a.R > 1) red_relaxed_sys_add(cnt, 1u); else red_relaxed_gpu_add(cnt, 1u);
+            }
+            pub_n = 0;
+            if (timed) t_pub += clock64() - t_p0;
+        };
+        auto flush_publish = [&] { flush_l1(); flush_rows(); };
         for (uint32_t it = 0;; ++it) {
             const uint32_t slot = it % kTaskRing;
             bool ok = true;
@@ -544,7 +565,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             __syncwarp();
             if (lane == 0) arrive_leader(&S->tmem_empty);
             if (timed) t_drain += clock64() - t_busy0;
-            flush_publish();   // the previous task's stores have had the drain to complete
+            flush_l1();        // the previous task's stores have had the drain to complete
+            if (pub_n == kPubDepth) flush_rows();
 
             if (!is_l2) {
                 // ---- SwiGLU + per-row 1x128 requantisation to E4M3 -> ffn
@@ -594,7 +616,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                         if (a.scaled && half == 0) ffn_sf[(size_t)(row0 + r) * a.L.sf_stride_i + task.z] = (uint8_t)ex;
                     }
                 }
-                pend_kind = 1;
+                pend_l1 = 1;
                 pend_ptr = l1_done + task.y;
             } else {
                 // ---- bf16 rows pushed to the source rank + per-pair arrival count
@@ -618,9 +640,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                         st_global_v8(d0 + c, pack8(&vg[c * 8]), pack8(&vg[c * 8 + 8]));
                         st_global_v8(d1 + c, pack8(&vu[c * 8]), pack8(&vu[c * 8 + 8]));
                     }
-                    pend_ptr = reinterpret_cast<uint32_t*>(peer_unk + a.L.combine_cnt_off) + (size_t)m.z * a.cap + m.y;
+                    S->pubq[pub_n++][tq] = ((uint32_t)m.x << 24) | (uint32_t)(m.z * a.cap + m.y);
                 }
-                pend_kind = 2;
             }
             t_busy += clock64() - t_busy0;
         }

@@ -393,6 +393,8 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     int win = la->win_cap ? la->win_cap : 128;
     // same rule as the reference binding: window in [8,128], multiple of 8 (torch/csrc/apis/mega.hpp:230-233)
     if (win < 8 || win > 128 || win % 8) return fail(MXK_ERR_BAD_ARG, "win_cap must be a multiple of 8 in [8,128]");
+    if ((int64_t)g.topk * g.max_tokens > 0xFFFFFF || g.R > 255)
+        return fail(MXK_ERR_BAD_ARG, "topk * max_tokens must fit 24 bits and R 8 bits (arrival-count queue entries)");
     if ((la->w1_sf == nullptr) != (la->w2_sf == nullptr)) return fail(MXK_ERR_BAD_ARG, "w1_sf and w2_sf must both be set or both be null");
     k->R = g.R; k->rank = g.rank; k->EPR = g.experts_per_rank; k->E = g.R * g.experts_per_rank;
     k->topk = g.topk; k->H = g.hidden; k->I = g.intermediate; k->cap = g.max_tokens;
