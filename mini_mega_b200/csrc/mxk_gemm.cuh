@@ -494,7 +494,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
         // that makes a thread's row segments visible to another GPU costs several microseconds
         // whatever it has to wait for, more than the MMAs of an L2 task, so a thread queues up to
         // kPubDepth counts and releases them with ONE fence followed by relaxed adds — when the
-        // queue is full (after a drain, before the next stores are issued), or before it blocks.
+        // queue is full (after a drain, before the next stores are issued) or the task queue ends.
         // Holding them back cannot stall this kernel: only the reduce phase waits for them.
         int pend_l1 = 0;             // an L1 window share (l1_done) awaits its publish
         uint32_t* pend_ptr = nullptr;
@@ -545,8 +545,9 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             bool got = false;
             if (lane == 0) got = mbar_try_wait(&S->tmem_full, it & 1);
             got = __shfl_sync(0xFFFFFFFFu, got ? 1 : 0, 0) != 0;
-            if (!got) {   // about to block: publish first
-                flush_publish();
+            if (!got) {   // about to block: publish the L1 share first (an L2 task may be gated on it);
+                          // queued row counts stay queued until eight are together or the queue ends
+                flush_l1();
                 if (lane == 0) got = MXK_TIMED(w_acc, mbar_wait(&S->tmem_full, it & 1, wait_ns, abort_flag));
                 got = __shfl_sync(0xFFFFFFFFu, got ? 1 : 0, 0) != 0;
             }
