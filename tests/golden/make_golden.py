@@ -1,6 +1,6 @@
 """Generate the golden fixtures under tests/golden/ from the REFERENCE itself.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run in a container that has the reference checkout (its path is the first argument):
 
     python tests/golden/make_golden.py [/path/to/reference] [--only-tk-info]
 
