@@ -10,10 +10,16 @@ H=6144, I=2048, FP8 E4M3 with UE8M0 block scales (128x128 weights, 1x128 activat
 split expert-parallel over the N GPUs: 256/N experts and 128/N tokens per rank.  At N=8
 this is exactly "16 tokens per rank, EP over 8 GPUs, 32 experts/GPU"; at N=1 the same job
 runs on one GPU (strong scaling).  A step is one layer.
-`value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the same through
-the public call with host buffers (pinned H2D of x / scales / routing and D2H of y
-inside the timed region).  `points` repeats the device-resident measurement at 16, 64
-and 256 tokens per rank.  Rank 0 prints ONE JSON line.
+
+`value` is whole-job tokens/s with inputs resident in HBM (eager launches, CUDA events);
+`e2e` is the same through the public call with host buffers (one pinned H2D of the packed
+inputs and the D2H of y inside the timed region).  `points` repeats the device-resident
+measurement at 16, 64 and 256 tokens per rank, with Zipf(1.2)-skewed routing at 256 tokens
+per rank, and on the prefill-sized layer (H=7168, 4096 tokens per rank); every point is
+also timed the reference's way, as one CUDA graph of 20 layer nodes replayed
+(test/mybench.cu:230-257).  `parity` checks, after the timed region and on every rank, the
+integer tables of the last layer against the CPU oracle's routing model and y of sampled
+tokens against the oracle's arithmetic.  Rank 0 prints ONE JSON line.
 """
 import argparse
 import ctypes as C
@@ -29,14 +35,16 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 E_TOTAL, TOPK, H, I = 256, 8, 6144, 2048
-HBM_FALLBACK_GBS = 6650.0        # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+HBM_FALLBACK_GBS = 6650.0        # used only without MEASURED_PEAKS.json
 BF16_FALLBACK_TFLOPS = 1590.0
-NVLINK_GBS = 770.0               # measured peer copy per direction on this pool
-# DRAM traffic of k_mega from the ncu capture summarised in profiles/k_mega_decode_shard_E32_T16.md:
-# 1.1872 GB read+written per launch against 1.1757 GB algorithmic on the 32-expert shard.  The
-# benchmark's own launches stream more experts through the same code, so traffic is scaled from
-# that capture in proportion to the algorithmic bytes (weights dominate both).
-NCU_TRAFFIC_RATIO = 1.1862 / 1.1757   # dram bytes of the captured decode shard / its algorithmic bytes (profiles/)
+HBM_NOMINAL_GBS = 8000.0         # the HBM figure the 70 % decode target is quoted on
+FP8_NOMINAL_TFLOPS = 4500.0      # dense FP8 peak the 60 % prefill target is quoted on
+NVLINK_GBS = 770.0               # peer copy per direction (nominal 900)
+# DRAM bytes of k_mega per launch over its algorithmic bytes, from the ncu capture of the
+# 32-expert decode shard; the benchmark's own launches stream more experts through the same
+# code, so traffic is scaled from that capture in proportion to the algorithmic bytes.
+NCU_TRAFFIC_RATIO = 1.1862 / 1.1757
+GRAPH_NODES, GRAPH_WARM, GRAPH_TIMED = 20, 2, 3
 
 
 def load_peaks():
@@ -98,12 +106,12 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- workload
-def make_weights(torch, epr, rank, device):
+def make_weights(torch, epr, rank, device, hidden):
     """Seeded synthetic expert weights of this rank, directly as E4M3 bytes + UE8M0 exponents
     (random sign / mantissa, exponent field 3..10, block scale 2^-9): same shapes and value range
     as N(0, 0.02) weights quantised per 128x128 block, without materialising FP32 tensors."""
     g = torch.Generator(device=device)
-    g.manual_seed(1000 + rank)
+    g.manual_seed(1000 + rank + 7 * hidden)
 
     def fp8_bytes(shape):
         n = 1
@@ -118,30 +126,27 @@ def make_weights(torch, epr, rank, device):
             out[o:o + m] = (r & 0x87) | (ex << 3)
         return out.view(*shape)
 
-    w1 = fp8_bytes((epr, 2 * I, H))
-    w2 = fp8_bytes((epr, H, I))
-    s1 = torch.full((epr, 2 * I // 128, H // 128), 127 - 9, dtype=torch.uint8, device=device)
-    s2 = torch.full((epr, H // 128, I // 128), 127 - 9, dtype=torch.uint8, device=device)
+    w1 = fp8_bytes((epr, 2 * I, hidden))
+    w2 = fp8_bytes((epr, hidden, I))
+    s1 = torch.full((epr, 2 * I // 128, hidden // 128), 127 - 9, dtype=torch.uint8, device=device)
+    s2 = torch.full((epr, hidden // 128, I // 128), 127 - 9, dtype=torch.uint8, device=device)
     s1 += torch.randint(0, 3, s1.shape, generator=g, device=device, dtype=torch.uint8)
     s2 += torch.randint(0, 3, s2.shape, generator=g, device=device, dtype=torch.uint8)
     return (w1, s1), (w2, s2)
 
 
-ROUTING = "uniform"   # set from --routing
-
-
-def make_inputs(torch, tokens, rank, seed):
+def make_inputs(torch, tokens, rank, seed, hidden, routing):
     """Host-side (pinned) inputs of one step: x E4M3 + 1x128 scales, 8 distinct experts per token
     (uniformly at random, or without replacement from Zipf(1.2) over a seeded permutation of the
     experts: the hottest expert then receives about ten times the mean), weights = softmax of
     N(0,1) logits."""
     g = torch.Generator()
     g.manual_seed(seed * 7919 + rank)
-    r = torch.randint(0, 256, (tokens, H), generator=g, dtype=torch.uint8)
-    ex = torch.randint(3, 11, (tokens, H), generator=g, dtype=torch.uint8)
+    r = torch.randint(0, 256, (tokens, hidden), generator=g, dtype=torch.uint8)
+    ex = torch.randint(3, 11, (tokens, hidden), generator=g, dtype=torch.uint8)
     x = ((r & 0x87) | (ex << 3)).pin_memory()
-    x_sf = (torch.randint(0, 3, (tokens, H // 128), generator=g, dtype=torch.uint8) + (127 - 3)).pin_memory()
-    if ROUTING == "zipf":
+    x_sf = (torch.randint(0, 3, (tokens, hidden // 128), generator=g, dtype=torch.uint8) + (127 - 3)).pin_memory()
+    if routing == "zipf":
         gp = torch.Generator()
         gp.manual_seed(4242)                       # the same expert popularity on every rank and step
         perm = torch.randperm(E_TOTAL, generator=gp)
@@ -154,7 +159,7 @@ def make_inputs(torch, tokens, rank, seed):
     return x, x_sf, idx, w
 
 
-def algorithmic_work(idx_all, n_ranks, rank, tokens):
+def algorithmic_work(idx_all, n_ranks, rank, tokens, hidden):
     """Per-GPU algorithmic bytes / flops of one layer for the routing actually drawn.
     idx_all: [n_ranks*tokens, topk] global expert ids of every rank's tokens."""
     epr = E_TOTAL // n_ranks
@@ -163,14 +168,19 @@ def algorithmic_work(idx_all, n_ranks, rank, tokens):
     P = int(mine.sum())                                   # routed pairs landing on this GPU
     active = int(idx_all[mine].unique().numel())          # local experts with >= 1 row
     src_rank = (idx_all.new_tensor(range(idx_all.shape[0])) // tokens)[:, None].expand_as(idx_all)
-    P_remote = int((mine & (src_rank != rank)).sum())
-    w_bytes = active * (2 * I * H + H * I + (2 * I // 128) * (H // 128) + (H // 128) * (I // 128))
-    gemm_bytes = w_bytes + P * (H + H // 128) + 2 * P * (I + I // 128) + P * 2 * H
-    layer_bytes = gemm_bytes + P * (H + H // 128) + tokens * TOPK * 2 * H + tokens * 2 * H
-    flops = P * 6 * H * I
-    nvl = max(P_remote * (H + H // 128), P_remote * 2 * H)
+    P_remote_in = int((mine & (src_rank != rank)).sum())              # pairs pulled / pushed in from peers
+    P_remote_out = int(((src_rank == rank) & (owner != rank)).sum())  # this rank's pairs served elsewhere
+    kb = hidden // 128
+    w_bytes = active * (2 * I * hidden + hidden * I + (2 * I // 128) * kb + kb * (I // 128))
+    gemm_bytes = w_bytes + P * (hidden + kb) + 2 * P * (I + I // 128) + P * 2 * hidden
+    layer_bytes = gemm_bytes + P * (hidden + kb) + tokens * TOPK * 2 * hidden + tokens * 2 * hidden
+    flops = P * 6 * hidden * I
+    nvl_in = P_remote_in * (hidden + kb) + P_remote_out * 2 * hidden      # dispatch in + combine rows coming back
+    nvl_out = P_remote_out * (hidden + kb) + P_remote_in * 2 * hidden     # dispatch out + combine rows pushed
     return {"pairs": P, "active_experts": active, "weight_bytes": w_bytes, "gemm_bytes": gemm_bytes,
-            "layer_bytes": layer_bytes, "flops": flops, "nvlink_bytes": nvl}
+            "layer_bytes": layer_bytes, "flops": flops, "nvlink_bytes": max(nvl_in, nvl_out),
+            "nvlink_in": nvl_in, "nvlink_out": nvl_out,
+            "dispatch_in": P_remote_in * (hidden + kb), "combine_out": P_remote_in * 2 * hidden}
 
 
 # ----------------------------------------------------------------------------- CPU arm
@@ -189,21 +199,21 @@ class CpuLayer:
         self.rows, self.tokens, self.experts = rows_per_expert, tokens, experts
         self.R = orc.ref_lib()
         rng = np.random.default_rng(5)
-        self.x = rng.integers(0, 0x40, (experts, rows_per_expert, H)).astype(np.uint8)
-        self.comb = orc.f32_to_bf16(rng.standard_normal((TOPK, tokens, H)).astype(np.float32))
+        self.x = rng.integers(0, 0x40, (experts, rows_per_expert, 6144)).astype(np.uint8)
+        self.comb = orc.f32_to_bf16(rng.standard_normal((TOPK, tokens, 6144)).astype(np.float32))
         self.tidx = rng.integers(0, E_TOTAL, (tokens, TOPK)).astype(np.int64)
         self.tw = rng.random((tokens, TOPK)).astype(np.float32)
         R = self.R
-        self.kind = "reference" if (R is not None and R.ref_const(2) == H and R.ref_const(3) == I and
+        self.kind = "reference" if (R is not None and R.ref_const(2) == 6144 and R.ref_const(3) == I and
                                     R.ref_const(1) == TOPK and R.ref_const(0) >= experts) else "port"
-        w1 = orc.fill_weights(experts * 2 * I, H, 17).reshape(experts, 2 * I, H)
-        w2 = orc.fill_weights(experts * H, I, 91).reshape(experts, H, I)
+        w1 = orc.fill_weights(experts * 2 * I, 6144, 17).reshape(experts, 2 * I, 6144)
+        w2 = orc.fill_weights(experts * 6144, I, 91).reshape(experts, 6144, I)
         if self.kind == "reference":
-            self.w1 = np.zeros((experts, 2 * I * H), np.uint8)
-            self.w2 = np.zeros((experts, H * I), np.uint8)
+            self.w1 = np.zeros((experts, 2 * I * 6144), np.uint8)
+            self.w2 = np.zeros((experts, 6144 * I), np.uint8)
             for e in range(experts):
-                R.ref_pack_lane(np.ascontiguousarray(w1[e]), 2 * I, H, self.w1[e])
-                R.ref_pack_lane(np.ascontiguousarray(w2[e]), H, I, self.w2[e])
+                R.ref_pack_lane(np.ascontiguousarray(w1[e]), 2 * I, 6144, self.w1[e])
+                R.ref_pack_lane(np.ascontiguousarray(w2[e]), 6144, I, self.w2[e])
         else:
             self.w1, self.w2 = w1, w2
 
@@ -215,7 +225,7 @@ class CpuLayer:
             if self.kind == "reference":
                 ffn = np.zeros((self.rows, I), np.float32)
                 q = np.zeros((self.rows, I), np.uint8)
-                out = np.zeros((self.rows, H), np.float32)
+                out = np.zeros((self.rows, 6144), np.float32)
                 R.ref_l1_rows(self.x[e], self.w1.reshape(-1), e, self.rows, ffn.reshape(-1), th)
                 R.ref_quantize(ffn.reshape(-1), self.rows * I, q.reshape(-1))
                 R.ref_l2_rows(q, self.w2.reshape(-1), e, self.rows, out.reshape(-1), th)
@@ -224,7 +234,7 @@ class CpuLayer:
                 q, _ = orc.requant(h, False)
                 orc.l2(q, None, self.w2[e], None, th)
         if self.kind == "reference":
-            y = np.zeros((self.tokens, H), np.float32)
+            y = np.zeros((self.tokens, 6144), np.float32)
             R.ref_reduce_tokens(self.comb.view(np.uint8).reshape(-1), self.tidx, self.tw, self.tokens, E_TOTAL,
                                 self.tokens, y.reshape(-1), th)
         else:
@@ -247,6 +257,13 @@ def cpu_sample_shape(tpr):
     return rows, min(tpr, 16)
 
 
+def cpu_labels(tpr, rows, experts, n_ranks):
+    """How the CPU number relates to the job: whether the timed sample was scaled up to the rank's
+    share, and that an N-rank job is priced as N hosts working in parallel."""
+    return {"extrapolated": experts * rows != tpr * TOPK, "extrapolation_factor": (tpr * TOPK) / (experts * rows),
+            "hosts_assumed": n_ranks}
+
+
 def cpu_arm(args, n_ranks):
     """`--impl reference`: every step is one pass of the CPU path over the bounded sample."""
     threads = os.cpu_count() or 1
@@ -258,30 +275,296 @@ def cpu_arm(args, n_ranks):
     scale = (args.tpr * TOPK) / (layer.experts * rows)
     layer_s = sum(secs) / len(secs) * scale             # one rank's share; ranks run in parallel
     value = n_ranks * args.tpr / layer_s
+    cpu = {"value": value, "unit": "tokens/s", "cores": threads, "kind": layer.kind, "sample": layer.describe(args.tpr)}
+    cpu.update(cpu_labels(args.tpr, rows, layer.experts, n_ranks))
     line = {
         "impl": "reference", "metric": "tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": n_ranks,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": layer_s * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-        "config": workload_config(n_ranks, args.tpr),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": layer.kind,
-                         "sample": layer.describe(args.tpr)},
+        "config": workload_config(n_ranks, args.tpr, args.hidden, args.routing),
+        "cpu_baseline": cpu,
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n, tokens):
-    kind = "balanced" if ROUTING == "uniform" else "skewed"
-    how = "uniform distinct routing" if ROUTING == "uniform" else "Zipf(1.2) distinct routing over a seeded expert permutation"
-    return {"workload": f"MoE layer {kind}: E={E_TOTAL} topk=8 H={H} I=2048 FP8 e4m3 + UE8M0 block "
+def workload_config(n, tokens, hidden, routing):
+    kind = "balanced" if routing == "uniform" else "skewed"
+    how = "uniform distinct routing" if routing == "uniform" else "Zipf(1.2) distinct routing over a seeded expert permutation"
+    return {"workload": f"MoE layer {kind}: E={E_TOTAL} topk=8 H={hidden} I=2048 FP8 e4m3 + UE8M0 block "
                         f"scales, {n * tokens} tokens in total = {tokens} tokens/rank, EP={n} "
                         f"({E_TOTAL // n} experts/GPU), {how}",
             "tokens_per_rank": tokens, "global_tokens": n * tokens, "ep": n, "experts_per_gpu": E_TOTAL // n,
-            "l2_policy": "inputs larger than L2 (expert weights streamed per layer >> 126 MB)"}
+            "l2_policy": "inputs larger than L2 (expert weights streamed per layer >> 126 MB)",
+            "timing": "eager launches, CUDA events on the launching stream, max over ranks; us_per_layer_graph: "
+                      f"one CUDA graph of {GRAPH_NODES} layer nodes, {GRAPH_WARM} warm replays, {GRAPH_TIMED} timed"}
 
 
 # ----------------------------------------------------------------------------- CUDA arm
+class Job:
+    """One geometry on this rank: symmetric buffers, this rank's expert weights, helpers that load
+    inputs and time layers.  `hidden` 6144 = the decode layer, 7168 = the prefill-sized layer."""
+
+    def __init__(self, torch, dist, mm, lib, n, rank, dev, group, hidden, cap, cta_pair, dispatch_mode):
+        self.torch, self.dist, self.mm, self.lib = torch, dist, mm, lib
+        self.n, self.rank, self.dev, self.hidden, self.cap = n, rank, dev, hidden, cap
+        self.epr = E_TOTAL // n
+        self.buf = mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, hidden, I, dispatch_mode=dispatch_mode)
+        self.buf.cta_pair = cta_pair
+        self.weights = make_weights(torch, self.epr, rank, dev, hidden)
+        self.l1, self.l2 = mm.transform_weights_for_mega_moe(*self.weights)
+        self.stream = torch.cuda.current_stream()
+        self.inputs = None
+        self.push = bool(self.buf.layout.push_eligible) if dispatch_mode == 0 else dispatch_mode == 2
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.n > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, v):
+        if self.n == 1:
+            return v
+        t = self.torch.tensor([v], dtype=self.torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def gather(self, t_host):
+        """Every rank's copy of a host tensor, concatenated in rank order (host)."""
+        if self.n == 1:
+            return t_host.clone()
+        t = t_host.to(self.dev)
+        out = [self.torch.empty_like(t) for _ in range(self.n)]
+        self.dist.all_gather(out, t)
+        return self.torch.cat(out).cpu()
+
+    def load(self, tokens, seed, routing="uniform"):
+        torch, buf = self.torch, self.buf
+        x, x_sf, idx, w = make_inputs(torch, tokens, self.rank, seed, self.hidden, routing)
+        buf.x.view(torch.uint8)[:tokens].copy_(x)
+        buf.x_sf[:tokens].copy_(x_sf)
+        buf.topk_idx[:tokens].copy_(idx)
+        buf.topk_weights[:tokens].copy_(w)
+        self.inputs = (tokens, x, x_sf, idx, w)
+        self.y = torch.zeros((tokens, self.hidden), dtype=torch.bfloat16, device=self.dev)
+        return self.gather(idx)
+
+    def layer(self, y=None):
+        self.mm.fp8_mega_moe(self.y if y is None else y, self.l1, self.l2, self.buf)
+
+    def check_status(self, what):
+        st = self.buf.status()
+        assert st.status == 0, f"{what}: device status {st.status} dbg {list(st.dbg)}"
+        return st
+
+    def time_eager(self, steps, warmup):
+        torch = self.torch
+        for _ in range(warmup):
+            self.layer()
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(self.stream)
+        for _ in range(steps):
+            self.layer()
+        e1.record(self.stream)
+        self.barrier()
+        ms = self.max_over_ranks(e0.elapsed_time(e1)) / steps
+        self.check_status("eager layers")
+        return ms
+
+    def time_graph(self):
+        """The reference's method (test/mybench.cu:230-257): one graph of GRAPH_NODES identical layer
+        nodes, warm replays, then timed replays bracketed by one event pair; per layer =
+        elapsed / (nodes * replays), host barrier outside the window."""
+        torch = self.torch
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(self.stream)
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(GRAPH_NODES):
+                    self.layer()
+        for _ in range(GRAPH_WARM):
+            g.replay()
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(self.stream)
+        for _ in range(GRAPH_TIMED):
+            g.replay()
+        e1.record(self.stream)
+        self.barrier()
+        ms = self.max_over_ranks(e0.elapsed_time(e1)) / (GRAPH_NODES * GRAPH_TIMED)
+        self.check_status("graph replay")
+        del g
+        return ms
+
+    def time_gemm_phase(self, steps, warmup):
+        """Average duration of the GEMM phase launched alone (events bracket it on the launching stream)."""
+        torch, lib = self.torch, self.lib
+        from mini_mega_b200 import _lib
+        a = self.buf.launch_args(self.inputs[0], self.l1, self.l2, y_bf16=self.y)
+        evs = []
+        for i in range(warmup + steps):
+            _lib.check(lib.mxk_launch_phases(C.byref(a), 1 | 2 | 4, self.stream.cuda_stream), "prologue+dispatch")
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.stream)
+            _lib.check(lib.mxk_launch_phases(C.byref(a), 8, self.stream.cuda_stream), "gemm")
+            e1.record(self.stream)
+            _lib.check(lib.mxk_launch_phases(C.byref(a), 16, self.stream.cuda_stream), "reduce")
+            if i >= warmup:
+                evs.append((e0, e1))
+        self.barrier()
+        return self.max_over_ranks(sum(a_.elapsed_time(b_) for a_, b_ in evs) / len(evs))
+
+    def time_e2e(self, steps, warmup):
+        """Public call with HOST buffers.  Push-mode buffers take the step's inputs as ONE packed
+        pinned image (SymmBuffer.packed_layout) and one copy; pull-mode buffers as four copies into
+        the regular regions.  y comes back with one D2H copy.  All inside the timed region."""
+        torch, buf = self.torch, self.buf
+        tokens, x, x_sf, idx, w = self.inputs
+        y_host = torch.empty((tokens, self.hidden), dtype=torch.bfloat16).pin_memory()
+        packed = self.push
+        if packed:
+            xo, so, io, wo, total = buf.packed_layout(tokens)
+            img = torch.zeros(total, dtype=torch.uint8).pin_memory()
+            img[xo:xo + x.numel()] = x.reshape(-1)
+            img[so:so + x_sf.numel()] = x_sf.reshape(-1)
+            img[io:io + idx.numel() * 8] = idx.reshape(-1).view(torch.uint8)
+            img[wo:wo + w.numel() * 4] = w.reshape(-1).view(torch.uint8)
+            dst = buf.buffer[:total]
+            h2d = total
+
+            def step():
+                dst.copy_(img, non_blocking=True)
+                self.mm.fp8_mega_moe(self.y, self.l1, self.l2, buf, packed_inputs=True)
+                y_host.copy_(self.y, non_blocking=True)
+        else:
+            h2d = x.numel() + x_sf.numel() + idx.numel() * 8 + w.numel() * 4
+
+            def step():
+                buf.x.view(torch.uint8)[:tokens].copy_(x, non_blocking=True)
+                buf.x_sf[:tokens].copy_(x_sf, non_blocking=True)
+                buf.topk_idx[:tokens].copy_(idx, non_blocking=True)
+                buf.topk_weights[:tokens].copy_(w, non_blocking=True)
+                self.mm.fp8_mega_moe(self.y, self.l1, self.l2, buf)
+                y_host.copy_(self.y, non_blocking=True)
+
+        for _ in range(warmup):
+            step()
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(self.stream)
+        for _ in range(steps):
+            step()
+        e1.record(self.stream)
+        self.barrier()
+        ms = self.max_over_ranks(e0.elapsed_time(e1)) / steps
+        self.check_status("end-to-end layers")
+        if packed:   # leave the regular regions as the resident runs expect them
+            buf.x.view(torch.uint8)[:tokens].copy_(x)
+            buf.x_sf[:tokens].copy_(x_sf)
+            buf.topk_idx[:tokens].copy_(idx)
+            buf.topk_weights[:tokens].copy_(w)
+        return ms, h2d, y_host.numel() * 2, y_host
+
+    def phase_stamps(self, layers=3):
+        """A few untimed layers with the kernel's phase stamps switched on: per-rank time at which the
+        GEMM phase and the whole layer ended (ns since kernel start), gathered over the ranks."""
+        torch = self.torch
+        before = self.lib.mxk_set_ticks(1)
+        for _ in range(layers):
+            self.layer()
+        self.torch.cuda.synchronize()
+        st = self.buf.status()
+        self.lib.mxk_set_ticks(before if before in (0, 1) else -1)
+        mine = torch.tensor([float(st.ticks[i]) for i in range(9, 14)], dtype=torch.float64)
+        allr = self.gather(mine.view(1, 5))
+        return allr, st
+
+    def destroy(self):
+        self.buf.destroy()
+        self.weights = self.l1 = self.l2 = None
+
+
+def parity_leg(job, routing_all, np):
+    """After the timed region: the last layer's integer tables on this rank against the oracle's
+    routing model of the whole world, the dispatched rows against the ranks' inputs, and y of two
+    sampled tokens per rank against the oracle's arithmetic on the owners' weights.  The oracle is
+    the checker here, outside any timed region."""
+    from oracle import oracle as orc
+    torch, dist, buf, n, rank = job.torch, job.dist, job.buf, job.n, job.rank
+    tokens, x, x_sf, idx, w = job.inputs
+    Hh, epr = job.hidden, job.epr
+    job.y.zero_()
+    job.layer()
+    torch.cuda.synchronize()
+    st = job.check_status("parity layer")
+    x_all = job.gather(x).numpy().reshape(n, tokens, Hh)
+    sf_all = job.gather(x_sf).numpy().reshape(n, tokens, Hh // 128)
+    idx_all = routing_all.numpy().reshape(n, tokens, TOPK)
+    case = orc.Case(n, epr, TOPK, Hh, I, tokens, [tokens] * n, True, x_all, sf_all, idx_all,
+                    np.zeros((n, tokens, TOPK), np.float32), None, None, None, None, "bench")
+    ref = orc.route_world(case, slot_cap=job.cap)[rank]
+    rows = ref.meta.shape[0]
+    ok = np.array_equal(buf.table("route_slot_counts").cpu().numpy(), ref.route_slot_counts)
+    ok &= np.array_equal(buf.table("prefix_tbl").cpu().numpy(), ref.prefix_tbl)
+    ok &= np.array_equal(buf.table("expert_row_base").cpu().numpy(), ref.row_base)
+    ok &= np.array_equal(buf.table("row_meta")[:rows, :3].cpu().numpy(), ref.meta)
+    ok &= int(st.total_rows) == rows
+    pool = buf.table("pool")[:rows].cpu().numpy()
+    psf = buf.table("pool_sf")[:rows, : Hh // 128].cpu().numpy()
+    ok &= np.array_equal(pool, x_all[ref.meta[:, 0], ref.meta[:, 1]])
+    ok &= np.array_equal(psf, sf_all[ref.meta[:, 0], ref.meta[:, 1]])
+    # y of sampled tokens: the owners of their experts send the weights (device to device)
+    (w1, s1), (w2, s2) = job.weights
+    sample = sorted({0, tokens - 1})
+    worst, checked = 0.0, 0
+    y_host = job.y.float().cpu().numpy()
+    for r in range(n):
+        for t in sample:
+            acc = np.zeros(Hh, np.float32)
+            for k in range(TOPK):
+                e = int(idx_all[r, t, k])
+                owner, le = e // epr, e % epr
+                parts = None
+                if n == 1:
+                    parts = [w1[le], s1[le], w2[le], s2[le]]
+                else:
+                    if rank == owner:
+                        parts = [w1[le].contiguous(), s1[le].contiguous(), w2[le].contiguous(), s2[le].contiguous()]
+                    else:
+                        parts = [torch.empty_like(w1[0]), torch.empty_like(s1[0]), torch.empty_like(w2[0]), torch.empty_like(s2[0])]
+                    for p_ in parts:
+                        dist.broadcast(p_, src=owner)
+                if rank != r:
+                    continue
+                a1, b1, a2, b2 = (p_.cpu().numpy() for p_ in parts)
+                h = orc.l1(x_all[r, t:t + 1], sf_all[r, t:t + 1], a1, b1)
+                q, sf = orc.requant(h, True)
+                o = orc.bf16_to_f32(orc.f32_to_bf16(orc.l2(q, sf, a2, b2)))[0]
+                acc = acc + o * np.float32(w[t, k])
+            if rank == r:
+                worst = max(worst, float(orc.rel_l2(y_host[t:t + 1], acc[None])))
+                checked += 1
+    res = torch.tensor([1.0 if ok else 0.0, worst, float(checked)], dtype=torch.float64, device=job.dev)
+    if n > 1:
+        mn = res.clone()
+        dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        mx = res.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = res.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ok_all, worst_all, checked_all = bool(mn[0].item() > 0.5), float(mx[1].item()), int(sm[2].item())
+    else:
+        ok_all, worst_all, checked_all = bool(ok), worst, checked
+    return {"tables_exact": ok_all, "max_rel_l2": worst_all, "tokens_checked": checked_all, "tolerance": 1e-2,
+            "ranks": n, "tables": "route_slot_counts, prefix_tbl, expert_row_base, row_meta, pool bytes + scales",
+            "passed": bool(ok_all and worst_all <= 1e-2)}
+
+
 def gpu_arm(args):
+    import numpy as np
     import torch
     import torch.distributed as dist
 
@@ -298,117 +581,11 @@ def gpu_arm(args):
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     assert args.gpus == n, f"--gpus {args.gpus} but WORLD_SIZE={n}"
-    epr = E_TOTAL // n
-    cap = max(256, args.tpr) if not args.no_points else args.tpr
     lib = _lib.lib()
-    buf = mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, H, I)
-    buf.cta_pair = args.cta_pair
-    l1, l2 = mm.transform_weights_for_mega_moe(*make_weights(torch, epr, rank, dev))
-    stream = torch.cuda.current_stream()
     hbm_gbs, bf16_tf, peak_kind = load_peaks()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if n > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(v):
-        if n == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def all_routing(idx_host, tokens):
-        if n == 1:
-            return idx_host.clone()
-        t = idx_host.to(dev)
-        out = [torch.empty_like(t) for _ in range(n)]
-        dist.all_gather(out, t)
-        return torch.cat(out).cpu()
-
-    def resident_run(tokens, steps, warmup, seed):
-        """Inputs already in the symmetric buffer; K eager layers timed with CUDA events."""
-        x, x_sf, idx, w = make_inputs(torch, tokens, rank, seed)
-        buf.x.view(torch.uint8)[:tokens].copy_(x)
-        buf.x_sf[:tokens].copy_(x_sf)
-        buf.topk_idx[:tokens].copy_(idx)
-        buf.topk_weights[:tokens].copy_(w)
-        y = torch.zeros((tokens, H), dtype=torch.bfloat16, device=dev)
-        for _ in range(warmup):
-            mm.fp8_mega_moe(y, l1, l2, buf)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
-            mm.fp8_mega_moe(y, l1, l2, buf)
-        e1.record(stream)
-        barrier()
-        ms = max_over_ranks(e0.elapsed_time(e1))
-        st = buf.status()
-        assert st.status == 0, f"device status {st.status} dbg {list(st.dbg)}"
-        if args.ticks and rank == 0:
-            tk = list(st.ticks)
-            life = max(tk[6], 1)
-            names = ["prod_wait_stage", "prod_wait_gate", "mma_wait_tiles", "mma_wait_drain", "mma_wait_sf",
-                     "epi_wait_acc", "cta_life", "prod_wait_ring", "epi_busy"]
-            print("ticks(% of CTA lifetime): " + " ".join(f"{n}={100.0 * tk[i] / life:.1f}" for i, n in enumerate(names)) +
-                  f" epi_drain={100.0 * tk[15] / life:.1f} epi_publish={100.0 * tk[14] / life:.1f}"
-                  f" sm_ghz_in_gemm={tk[6] / torch.cuda.get_device_properties(local).multi_processor_count / max(1.0, tk[12] - tk[11]):.3f}",
-                  file=sys.stderr, flush=True)
-            print("phase ends (us since CTA start): route={:.1f} setup={:.1f} dispatch={:.1f} gemm={:.1f} reduce={:.1f}".format(
-                *[tk[i] / 1e3 for i in range(9, 14)]), file=sys.stderr, flush=True)
-            ts = buf.rwk[208:272].view(torch.int64).cpu().tolist()
-            print("setup leader stamps (us after barrier): " + " ".join(f"{(ts[i] - ts[0]) / 1e3:.1f}" for i in range(1, 7)),
-                  file=sys.stderr, flush=True)
-        return ms / steps, all_routing(idx, tokens), y
-
-    def gemm_kernel_ms(tokens, steps, warmup):
-        """Average k_gemm duration: events bracket the GEMM phase alone on the launching stream."""
-        y = torch.zeros((tokens, H), dtype=torch.bfloat16, device=dev)
-        a = buf.launch_args(tokens, l1, l2, y_bf16=y)
-        evs = []
-        for i in range(warmup + steps):
-            _lib.check(lib.mxk_launch_phases(C.byref(a), 1 | 2 | 4, stream.cuda_stream), "prologue+dispatch")
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            _lib.check(lib.mxk_launch_phases(C.byref(a), 8, stream.cuda_stream), "gemm")
-            e1.record(stream)
-            _lib.check(lib.mxk_launch_phases(C.byref(a), 16, stream.cuda_stream), "reduce")
-            if i >= warmup:
-                evs.append((e0, e1))
-        barrier()
-        return max_over_ranks(sum(a_.elapsed_time(b_) for a_, b_ in evs) / len(evs))
-
-    def e2e_run(tokens, steps, warmup, seed):
-        """Public call with HOST buffers: pinned H2D of the step's inputs and D2H of y each step."""
-        x, x_sf, idx, w = make_inputs(torch, tokens, rank, seed)
-        y = torch.zeros((tokens, H), dtype=torch.bfloat16, device=dev)
-        y_host = torch.empty((tokens, H), dtype=torch.bfloat16).pin_memory()
-
-        def step():
-            buf.x.view(torch.uint8)[:tokens].copy_(x, non_blocking=True)
-            buf.x_sf[:tokens].copy_(x_sf, non_blocking=True)
-            buf.topk_idx[:tokens].copy_(idx, non_blocking=True)
-            buf.topk_weights[:tokens].copy_(w, non_blocking=True)
-            mm.fp8_mega_moe(y, l1, l2, buf)
-            y_host.copy_(y, non_blocking=True)
-
-        for _ in range(warmup):
-            step()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
-            step()
-        e1.record(stream)
-        barrier()
-        ms = max_over_ranks(e0.elapsed_time(e1)) / steps
-        h2d = x.numel() + x_sf.numel() + idx.numel() * 8 + w.numel() * 4
-        return ms, h2d, y_host.numel() * 2
-
     fp8_peak = 2.0 * bf16_tf * 1e12
+    cap = max(256, args.tpr) if not args.no_points else args.tpr
+    job = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, cap, args.cta_pair, args.dispatch_mode)
 
     def binding(work):
         t_h = work["layer_bytes"] / (hbm_gbs * 1e9)
@@ -417,27 +594,85 @@ def gpu_arm(args):
         t = max(t_h, t_f, t_n)
         return t, ("hbm" if t == t_h else "tensor" if t == t_f else "nvlink")
 
+    def nominal(work):
+        return max(work["layer_bytes"] / (HBM_NOMINAL_GBS * 1e9), work["flops"] / (FP8_NOMINAL_TFLOPS * 1e12),
+                   work["nvlink_bytes"] / (900.0 * 1e9))
+
+    def point(name, jb, tpr, ms, ms_graph, wk, extra=None):
+        t_roof, bound = binding(wk)
+        p = {"name": name, "tokens_per_rank": tpr, "hidden": jb.hidden, "us_per_layer": ms * 1e3,
+             "us_per_layer_graph": None if ms_graph is None else ms_graph * 1e3,
+             "tokens_per_s_per_gpu": tpr / (ms * 1e-3), "bound": bound, "roofline_us": t_roof * 1e6,
+             "roofline_frac": t_roof / (ms * 1e-3), "frac_of_nominal": nominal(wk) / (ms * 1e-3),
+             "active_experts": wk["active_experts"], "pairs": wk["pairs"],
+             "prologue": "push" if jb.push else "pull"}
+        if bound == "tensor":
+            p["tflops_per_gpu"] = wk["flops"] / (ms * 1e-3) / 1e12
+        if extra:
+            p.update(extra)
+        return p
+
+    def run_graph(jb):
+        return None if args.no_graph else jb.time_graph()
+
     # ---- headline: timed region with clock sampling ----
+    routing = job.load(args.tpr, seed=1, routing=args.routing)
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    ms_step, routing, _ = resident_run(args.tpr, args.steps, args.warmup, seed=1)
+    ms_step = job.time_eager(args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
-    work = algorithmic_work(routing, n, rank, args.tpr)
-    gemm_ms = gemm_kernel_ms(args.tpr, max(3, min(args.steps, 20)), 3)
-    e2e_ms, h2d, d2h = e2e_run(args.tpr, args.steps, args.warmup, seed=1)
+    work = algorithmic_work(routing, n, rank, args.tpr, args.hidden)
+    ms_graph = run_graph(job)
+    gemm_ms = job.time_gemm_phase(max(3, min(args.steps, 20)), 3)
+    e2e_ms, h2d, d2h, _ = job.time_e2e(args.steps, args.warmup)
+    stamps, st_ticks = job.phase_stamps()
+    disp_ns = float(st_ticks.ticks[11]) - float(st_ticks.ticks[10])   # rank 0: set-up end -> dispatch end
 
     points = []
     for tpr in (() if args.no_points else (16, 64, 256)):
-        if tpr == args.tpr:
-            ms, wk = ms_step, work
+        if tpr == args.tpr and args.routing == "uniform":
+            ms, mg, wk = ms_step, ms_graph, work
         else:
-            ms, rt, _ = resident_run(tpr, max(3, min(args.steps, 20)), 3, seed=2)
-            wk = algorithmic_work(rt, n, rank, tpr)
-        t_roof, bound = binding(wk)
-        points.append({"tokens_per_rank": tpr, "us_per_layer": ms * 1e3, "tokens_per_s_per_gpu": tpr / (ms * 1e-3),
-                       "bound": bound, "roofline_us": t_roof * 1e6, "roofline_frac": t_roof / (ms * 1e-3),
-                       "active_experts": wk["active_experts"], "pairs": wk["pairs"]})
+            rt = job.load(tpr, seed=2)
+            ms = job.time_eager(max(3, min(args.steps, 20)), 3)
+            mg = run_graph(job)
+            wk = algorithmic_work(rt, n, rank, tpr, args.hidden)
+        points.append(point(f"balanced_tpr{tpr}", job, tpr, ms, mg, wk))
+    if not args.no_points:
+        # BASELINE skew configuration: Zipf(1.2) routing, 256 tokens per rank
+        rt = job.load(256, seed=3, routing="zipf")
+        ms = job.time_eager(max(3, min(args.steps, 20)), 3)
+        mg = run_graph(job)
+        wk = algorithmic_work(rt, n, rank, 256, args.hidden)
+        sk, _ = job.phase_stamps()
+        gemm_end = sk[:, 3]
+        points.append(point("skew_zipf1.2_tpr256", job, 256, ms, mg, wk, {
+            "rank_gemm_end_us_max": float(gemm_end.max()) / 1e3, "rank_gemm_end_us_mean": float(gemm_end.mean()) / 1e3,
+            "rank_time_max_over_mean": float(gemm_end.max() / max(gemm_end.mean(), 1.0))}))
+
+    # ---- parity of the headline configuration (outside every timed region) ----
+    parity = None
+    if not args.no_parity:
+        routing = job.load(args.tpr, seed=1, routing=args.routing)
+        parity = parity_leg(job, routing, np)
+
+    # ---- prefill-sized layer: H=7168, 4096 tokens per rank ----
+    if not args.no_points and args.hidden == 6144:
+        job.destroy()
+        torch.cuda.empty_cache()
+        pj = Job(torch, dist, mm, lib, n, rank, dev, group, 7168, 4096, args.cta_pair, args.dispatch_mode)
+        rt = pj.load(4096, seed=4)
+        ms = pj.time_eager(5, 3)
+        mg = run_graph(pj)
+        wk = algorithmic_work(rt, n, rank, 4096, 7168)
+        pst, _ = pj.phase_stamps(2)
+        points.append(point("prefill_h7168_tpr4096", pj, 4096, ms, mg, wk, {
+            "frac_of_nominal_fp8_4500": wk["flops"] / (ms * 1e-3) / 1e12 / FP8_NOMINAL_TFLOPS,
+            "phase_end_us_rank0": [float(v) / 1e3 for v in pst[0].tolist()]}))
+        pj.destroy()
+    else:
+        job.destroy()
 
     cpu = None
     if rank == 0 and n == 1 and not args.no_cpu:
@@ -449,6 +684,7 @@ def gpu_arm(args):
         layer_s = sum(secs) / len(secs) * (args.tpr * TOPK) / (layer.experts * rows)
         cpu = {"value": args.tpr / layer_s, "unit": "tokens/s", "cores": threads, "kind": layer.kind,
                "sample": layer.describe(args.tpr), "ms_per_layer": layer_s * 1e3}
+        cpu.update(cpu_labels(args.tpr, rows, layer.experts, 1))
 
     if rank == 0:
         # the layer is ONE kernel (k_mega); its duration is the step time measured above
@@ -458,13 +694,14 @@ def gpu_arm(args):
             tf = work["flops"] / (ms_step * 1e-3) / 1e12
             roof = {"kernel": "k_mega", "bound": "tensor", "achieved": tf, "peak": 2.0 * bf16_tf, "unit": "TFLOP/s",
                     "frac": tf / (2.0 * bf16_tf), "peak_kind": f"2 x bf16 dense GEMM peak of {peak_kind} (FP8 runs at twice the bf16 rate)",
-                    "frac_of_nominal_4500": tf / 4500.0, "traffic": None,
+                    "frac_of_nominal_4500": tf / FP8_NOMINAL_TFLOPS, "traffic": None,
                     "kernel_us": ms_step * 1e3, "gemm_phase_us": gemm_ms * 1e3,
                     "gemm_phase_tflops": work["flops"] / (gemm_ms * 1e-3) / 1e12,
                     "algorithmic_flops": work["flops"], "active_experts": work["active_experts"], "pairs": work["pairs"]}
         else:
             roof = {"kernel": "k_mega", "bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
                     "frac": achieved / hbm_gbs, "peak_kind": f"of {peak_kind}",
+                    "frac_of_nominal_8000": achieved / HBM_NOMINAL_GBS,
                     "traffic": int(work["layer_bytes"] * NCU_TRAFFIC_RATIO),
                     "traffic_source": "ncu capture of the 32-expert shard scaled by algorithmic bytes",
                     "kernel_us": ms_step * 1e3, "gemm_phase_us": gemm_ms * 1e3,
@@ -474,21 +711,34 @@ def gpu_arm(args):
             "metric": "tokens_per_s", "value": n * args.tpr / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": n,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-            "config": workload_config(n, args.tpr),
+            "config": workload_config(n, args.tpr, args.hidden, args.routing),
             "us_per_layer": ms_step * 1e3,
+            "us_per_layer_graph": None if ms_graph is None else ms_graph * 1e3,
             "e2e": {"value": n * args.tpr / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "copies_per_step": "1 H2D (packed image) + 1 D2H" if job.push else "4 H2D + 1 D2H"},
             "gpu_launches": int(lib.mxk_kernels_per_layer()) * args.steps,
             "roofline": roof,
+            "nvlink": {"algorithmic_bytes_in": work["nvlink_in"], "algorithmic_bytes_out": work["nvlink_out"],
+                       "dispatch_bytes_in": work["dispatch_in"], "combine_bytes_out": work["combine_out"],
+                       "dispatch_phase_us_rank0": disp_ns / 1e3,
+                       "dispatch_gbs_rank0": (work["dispatch_in"] / disp_ns) if disp_ns > 0 else None,
+                       "peak_gbs_per_direction": NVLINK_GBS, "note": "bytes per GPU and layer on rank 0's routing; "
+                       "dispatch time = set-up end to dispatch end from the kernel's phase stamps"},
+            "phase_end_us_by_rank": [[float(v) / 1e3 for v in row] for row in stamps.tolist()],
+            "prologue": "push" if job.push else "pull",
             "points": points,
             "clocks": clocks,
         }
+        if parity is not None:
+            line["parity"] = parity
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
-    buf.destroy()
     if n > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity["passed"]:
+        sys.exit(3)
 
 
 def main():
@@ -505,14 +755,16 @@ def main():
                     help="expert choice per token: uniform (the baseline's balanced layer) or Zipf(1.2) skew")
     ap.add_argument("--cta-pair", type=int, default=0, choices=[0, 1, 2],
                     help="GEMM tiling: 1 single CTAs, 2 CTA pairs with 256-row windows, 0 chosen by load")
-    ap.add_argument("--ticks", action="store_true", help="print the GEMM kernel's wait-time breakdown to stderr")
+    ap.add_argument("--dispatch-mode", type=int, default=0, choices=[0, 1, 2],
+                    help="prologue protocol: 1 pull, 2 push, 0 chosen by geometry")
+    ap.add_argument("--ticks", action="store_true", help="print the kernel's wait-time breakdown and time line to stderr")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
-    ap.add_argument("--no-points", action="store_true", help="skip the 16/64/256 tokens-per-rank sweep")
+    ap.add_argument("--no-points", action="store_true", help="skip the sweep points (16/64/256 tokens per rank, skew, prefill)")
+    ap.add_argument("--no-graph", action="store_true", help="skip the CUDA-graph timings")
+    ap.add_argument("--no-parity", action="store_true", help="skip the parity leg")
     args = ap.parse_args()
-    if args.ticks:
-        os.environ["MXK_TICKS"] = "1"
-    global E_TOTAL, H, ROUTING
-    E_TOTAL, H, ROUTING = args.experts, args.hidden, args.routing
+    global E_TOTAL
+    E_TOTAL = args.experts
     if args.tpr <= 0:
         args.tpr = max(1, args.global_tokens // max(1, args.gpus))
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -521,7 +773,68 @@ def main():
             return  # rank 0 alone runs the CPU arm
         cpu_arm(args, args.gpus)
         return
+    if args.ticks:
+        ticks_run(args)
+        return
     gpu_arm(args)
+
+
+def ticks_run(args):
+    """`--ticks`: a short device-resident run with the kernel's accounting switched on; prints the
+    roles' blocked time and the time line of the first and the last CTA to stderr, and a small
+    JSON line with the layer time (not a benchmark value: the accounting itself costs time)."""
+    import torch
+    import torch.distributed as dist
+
+    import mini_mega_b200 as mm
+    from mini_mega_b200 import _lib
+    n = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if n > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    lib = _lib.lib()
+    job = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, args.tpr, args.cta_pair, args.dispatch_mode)
+    job.load(args.tpr, seed=1, routing=args.routing)
+    ms_plain = job.time_eager(args.steps, args.warmup)
+    lib.mxk_set_ticks(1)
+    ms = job.time_eager(args.steps, args.warmup)
+    st = job.buf.status()
+    lib.mxk_set_ticks(-1)
+    for r in range(n):
+        if n > 1:
+            dist.barrier()
+        if r != rank:
+            continue
+        tk = list(st.ticks)
+        life = max(tk[6], 1)
+        names = ["prod_wait_stage", "prod_wait_gate", "mma_wait_tiles", "mma_wait_drain", "mma_wait_sf",
+                 "epi_wait_acc", "cta_life", "prod_wait_ring", "epi_busy"]
+        sms = torch.cuda.get_device_properties(local).multi_processor_count
+        print(f"[rank {rank}] ticks(% of CTA lifetime): " + " ".join(f"{nm}={100.0 * tk[i] / life:.1f}" for i, nm in enumerate(names)) +
+              f" epi_drain={100.0 * tk[15] / life:.1f} epi_publish={100.0 * tk[14] / life:.1f}"
+              f" sm_ghz_in_gemm={tk[6] / sms / max(1.0, tk[12] - tk[11]):.3f}", file=sys.stderr, flush=True)
+        print(f"[rank {rank}] phase ends (us since CTA start): route={tk[9] / 1e3:.1f} setup={tk[10] / 1e3:.1f} "
+              f"dispatch={tk[11] / 1e3:.1f} gemm={tk[12] / 1e3:.1f} reduce={tk[13] / 1e3:.1f}", file=sys.stderr, flush=True)
+        tr = list(st.trace)
+        lab = ["entry", "init", "pushed", "route_end", "barrier", "tables", "setup_end", "dispatch_end", "gate0", "tma0",
+               "tile0", "gemm_end", "reduce_end"]
+        for base, who in ((0, "first CTA"), (32, "last CTA")):
+            t0 = tr[base]
+            print(f"[rank {rank}] {who} time line (us): " +
+                  " ".join(f"{lab[i]}={(tr[base + i] - t0) / 1e3:.1f}" for i in range(1, 13) if tr[base + i] >= t0 and tr[base + i] != 0),
+                  file=sys.stderr, flush=True)
+    if rank == 0:
+        print(json.dumps({"ticks_run": True, "us_per_layer_plain": ms_plain * 1e3, "us_per_layer_with_accounting": ms * 1e3,
+                          "n_gpus": n, "tokens_per_rank": args.tpr, "hidden": args.hidden, "experts": E_TOTAL,
+                          "prologue": "push" if job.push else "pull"}), flush=True)
+    job.destroy()
+    if n > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

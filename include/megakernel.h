@@ -72,6 +72,7 @@ struct MegaLaunchArgs {
     const uint8_t* w2_sf = nullptr;
     uint16_t* y_bf16 = nullptr;
     int cta_pair = 0;   // 0 = choose by load, 1 = single CTAs, 2 = CTA pairs (256-row windows)
+    int dispatch_mode = 0;   // prologue protocol, the same on every rank: 0 = by geometry, 1 = pull, 2 = push
 };
 
 inline int& last_status() {
@@ -92,7 +93,7 @@ inline MxkLaunchArgs to_c(const MegaLaunchArgs& a) {
     c.max_spins = a.max_spins; c.skip_prologue = a.skip_prologue;
     c.experts_per_rank = a.experts_per_rank; c.topk = a.topk; c.hidden = a.hidden;
     c.intermediate = a.intermediate; c.max_tokens = a.max_tokens;
-    c.x_sf_off = a.x_sf_off; c.w1_sf = a.w1_sf; c.w2_sf = a.w2_sf; c.y_bf16 = a.y_bf16; c.cta_pair = a.cta_pair;
+    c.x_sf_off = a.x_sf_off; c.w1_sf = a.w1_sf; c.w2_sf = a.w2_sf; c.y_bf16 = a.y_bf16; c.cta_pair = a.cta_pair; c.dispatch_mode = a.dispatch_mode;
     return c;
 }
 

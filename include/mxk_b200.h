@@ -59,15 +59,12 @@ typedef struct MxkLayout {
     int64_t topk_weights_off;   /* float  [max_tokens][topk]                      */
     /* unk */
     int64_t unk_bytes;
-    int64_t xbar_off;           /* uint32 [R][xbar_stride] reserved (the barrier is carried
-                                   by the epoch tags of the two tables below)        */
     int64_t src_index_table_off;/* uint64 [2][EPR][R][slot_capacity]: low word = pair
                                    index token*topk+k, high word = launch epoch       */
     int64_t expert_recv_counts_off; /* uint64 [2][R][recv_stride]: low word = count
                                    (word EPR: checksum), high word = launch epoch     */
     int64_t combine_rows_off;   /* bf16   [topk][max_tokens][H]                   */
     int64_t combine_cnt_off;    /* uint32 [topk][max_tokens] arrivals per pair    */
-    int32_t xbar_stride;        /* words between two peers' barrier slots         */
     int32_t recv_stride;        /* words per expert_recv_counts row (>= EPR+1)    */
     /* rwk */
     int64_t rwk_bytes;
@@ -78,7 +75,7 @@ typedef struct MxkLayout {
     int64_t expert_row_base_off;/* int32  [EPR+1] first pool row of each expert   */
     int64_t windows_off;        /* int32  [max_windows][4] expert,row0,rows,-     */
     int64_t tasks_off;          /* int32  [max_tasks][4]   kind,window,ntile,rows */
-    int64_t l1_done_off;        /* uint32 [max_windows]                           */
+    int64_t l1_done_off;        /* uint32 [2][max_windows] (copy = launch parity)  */
     int64_t row_meta_off;       /* int32  [pool_rows][4] src,token,k,weight bits  */
     int64_t pool_off;           /* uint8  [pool_rows+128][H]   dispatched rows    */
     int64_t pool_sf_off;        /* uint8  [pool_rows][sf_stride_h]                */
@@ -89,8 +86,18 @@ typedef struct MxkLayout {
     int32_t sf_stride_i;        /* bytes per ffn_sf row  (I/128 rounded to 16)    */
     int32_t max_windows;
     int32_t max_tasks;
-    int64_t pool_ready_off;     /* uint32 [max_windows] rows of a window dispatched   */
+    int64_t pool_ready_off;     /* uint32 [2][max_windows] rows of a window dispatched
+                                   (copy = launch parity, like l1_done)                */
     int64_t expert_first_win_off; /* int32 [EPR] first window id of each expert      */
+    /* push-mode prologue (small batches): every rank stores its tokens' routing, top-k
+     * weights, scales and E4M3 rows into the owner ranks' staging area as epoch-tagged
+     * 64-bit words {payload u32, epoch u32}; 0 bytes when the geometry is not eligible */
+    int64_t xin_off;            /* unk: uint64 [2][R][xin_src_words]                  */
+    int64_t xin_src_words;      /* words per (parity, source rank): 16 header words
+                                   (word 0 = token count) + max_tokens * xin_row_words */
+    int32_t xin_row_words;      /* per token: topk ids, topk weights, ceil(H/512) scale
+                                   words (padded to even), H/4 row words              */
+    int32_t push_eligible;      /* 1: this geometry may run the push-mode prologue    */
 } MxkLayout;
 
 /* One launch.  Field names follow fp8mega::MegaLaunchArgs (reference
@@ -131,6 +138,12 @@ typedef struct MxkLaunchArgs {
                                   of two CTAs per 256-row window (2-CTA MMA; needs
                                   win_cap 128 and an even grid), 0 = choose by load:
                                   pairs when tokens*topk/experts_per_rank >= 256  */
+    int32_t dispatch_mode;     /* prologue protocol, THE SAME ON EVERY RANK of a launch:
+                                  1 = pull (route scatter, count barrier, owner ranks pull
+                                  rows; reference r19_pull_flags), 2 = push (source ranks
+                                  store ids + rows into the owners' staging area, every CTA
+                                  derives the tables itself; needs layout.push_eligible),
+                                  0 = push when the geometry is eligible, else pull       */
 } MxkLaunchArgs;
 
 /* Host-readable copy of the device status header. */
@@ -150,6 +163,13 @@ typedef struct MxkStatus {
                               8 epilogue busy; 9..13 phase ends in ns since CTA start
                               (route, set-up, dispatch, GEMM, reduce); 15 epilogue
                               draining accumulators (part of 8)                       */
+    uint64_t trace[64];    /* MXK_TICKS=1: globaltimer stamps (ns) of the last layer, CTA 0
+                              in [0,32) and the last CTA in [32,64): 0 kernel entry, 1 barriers /
+                              tensor memory ready, 2 route or push issued, 3 route phase left,
+                              4 barrier seen (all sources arrived), 5 tables built, 6 set-up
+                              left, 7 dispatch left, 8 first task's gate passed, 9 first
+                              operand tile requested, 10 first tile landed, 11 GEMM phase left,
+                              12 reduce left                                               */
 } MxkStatus;
 
 #define MXK_DEV_TIMEOUT_BARRIER 1
@@ -218,14 +238,15 @@ int mxk_launch_phases(const MxkLaunchArgs* a, int phase_mask, void* stream);
  *
  * The first call on a device asks the CUDA runtime for the array's device address
  * (once per device, with that device current); make that first call outside any stream
- * capture.  All calls share the one array and it keeps the previous call's contents: the
- * status header behind the launch counter is cleared at the start of every call, the launch
- * counter keeps running from call to call (the prologue's tables are tagged with it, so the
- * previous call's words can never be taken for current ones), everything else is rewritten
- * before it is read.  Two calls that overlap on the GPU (different
- * streams, or several threads) would race on the array: issue them on one stream or
- * serialise them yourself.  mxk_read_status cannot be used with it; a device-side expiry
- * shows up as wrong output only. */
+ * capture.  All calls share the one array and it keeps the previous call's contents.  Calls
+ * with one geometry continue on it exactly like launches on a caller-owned workspace; the
+ * launch counter (first word of rwk, at a fixed place whatever the geometry) keeps running
+ * from call to call, because the prologue's words are tagged with it.  When a call's geometry
+ * differs from the previous call's on that device, everything behind the counter is cleared on
+ * the caller's stream first (cudaMemsetAsync allocates nothing), since the old tables lie at
+ * other offsets.  Two calls that overlap on the GPU (different streams, or several threads)
+ * would race on the array: issue them on one stream or serialise them yourself.  The status
+ * of the last call is read with mxk_read_status_static(). */
 int mxk_launch_full_static(const MxkLaunchArgs* a, void* stream);
 int64_t mxk_static_scratch_bytes(void);
 
@@ -249,6 +270,16 @@ int mxk_dump_kernel_resources(void);
 
 /* Synchronous read of the status header of an rwk block. */
 int mxk_read_status(const void* rwk, MxkStatus* out);
+/* The same for the workspace of mxk_launch_full_static on the current device. */
+int mxk_read_status_static(MxkStatus* out);
+/* Where MxkStatus.ticks sits inside rwk (byte offset) and how many 64-bit counters there are
+ * (reference: mxk_rwk_ticks_off / mxk_ticks_count, torch/csrc/flags_bridge.cu:44-51). */
+int64_t mxk_rwk_ticks_off(void);
+int64_t mxk_ticks_count(void);
+/* Wait-time accounting and phase stamps of the kernel (MxkStatus.ticks / trace) for the launches
+ * that follow: 1 on, 0 off, -1 back to the MXK_TICKS environment variable.  Returns the setting
+ * that was in force (reference: the -DR24_DIAG_PHASE build switch, src/flags_defs.cuh:93-109). */
+int mxk_set_ticks(int on);
 
 /* Window chooser kept for the callers that bind it (reference: mxk_select_win,
  * torch/csrc/flags_bridge.cu:31-38 -> src/win_select.cuh:95-128). */

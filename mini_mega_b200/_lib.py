@@ -38,9 +38,9 @@ class MxkLayout(C.Structure):
     _fields_ = [
         ("sym_bytes", C.c_int64), ("x_off", C.c_int64), ("x_sf_off", C.c_int64), ("topk_idx_off", C.c_int64),
         ("topk_weights_off", C.c_int64),
-        ("unk_bytes", C.c_int64), ("xbar_off", C.c_int64), ("src_index_table_off", C.c_int64),
+        ("unk_bytes", C.c_int64), ("src_index_table_off", C.c_int64),
         ("expert_recv_counts_off", C.c_int64), ("combine_rows_off", C.c_int64), ("combine_cnt_off", C.c_int64),
-        ("xbar_stride", C.c_int32), ("recv_stride", C.c_int32),
+        ("recv_stride", C.c_int32),
         ("rwk_bytes", C.c_int64), ("flags_off", C.c_int64), ("route_slot_counts_off", C.c_int64),
         ("pair_state_off", C.c_int64), ("prefix_tbl_off", C.c_int64), ("expert_row_base_off", C.c_int64),
         ("windows_off", C.c_int64), ("tasks_off", C.c_int64), ("l1_done_off", C.c_int64),
@@ -48,6 +48,8 @@ class MxkLayout(C.Structure):
         ("ffn_sf_off", C.c_int64), ("pool_rows", C.c_int64),
         ("sf_stride_h", C.c_int32), ("sf_stride_i", C.c_int32), ("max_windows", C.c_int32), ("max_tasks", C.c_int32),
         ("pool_ready_off", C.c_int64), ("expert_first_win_off", C.c_int64),
+        ("xin_off", C.c_int64), ("xin_src_words", C.c_int64), ("xin_row_words", C.c_int32),
+        ("push_eligible", C.c_int32),
     ]
 
 
@@ -64,14 +66,14 @@ class MxkLaunchArgs(C.Structure):
         ("experts_per_rank", C.c_int32), ("topk", C.c_int32), ("hidden", C.c_int32), ("intermediate", C.c_int32),
         ("max_tokens", C.c_int32),
         ("x_sf_off", C.c_int64), ("w1_sf", C.c_void_p), ("w2_sf", C.c_void_p), ("y_bf16", C.c_void_p),
-        ("cta_pair", C.c_int32),
+        ("cta_pair", C.c_int32), ("dispatch_mode", C.c_int32),
     ]
 
 
 class MxkStatus(C.Structure):
     _fields_ = [("launches", C.c_int64), ("status", C.c_int32), ("n_tasks", C.c_int32), ("n_l1_tasks", C.c_int32),
                 ("n_windows", C.c_int32), ("total_rows", C.c_int32), ("dbg", C.c_int32 * 8),
-                ("ticks", C.c_uint64 * 16)]
+                ("ticks", C.c_uint64 * 16), ("trace", C.c_uint64 * 64)]
 
 
 # every symbol include/mxk_b200.h declares; tests check that the library exports them
@@ -79,7 +81,8 @@ EXPORTS = [
     "mxk_last_error", "mxk_version", "mxk_compute_layout", "mxk_sym_bytes", "mxk_rwk_bytes", "mxk_unk_bytes",
     "mxk_launch_prelude", "mxk_launch_compute", "mxk_launch_reduce", "mxk_launch_full", "mxk_launch_empty",
     "mxk_kernels_per_layer", "mxk_launch_phases", "mxk_launch_full_static",
-    "mxk_static_scratch_bytes", "mxk_fill_weights", "mxk_quantize_rows", "mxk_dump_kernel_resources", "mxk_read_status", "mxk_select_win",
+    "mxk_static_scratch_bytes", "mxk_fill_weights", "mxk_quantize_rows", "mxk_dump_kernel_resources", "mxk_read_status",
+    "mxk_read_status_static", "mxk_rwk_ticks_off", "mxk_ticks_count", "mxk_set_ticks", "mxk_select_win",
     "mxk_symm_alloc", "mxk_symm_free", "mxk_ipc_export", "mxk_ipc_import", "mxk_ipc_close",
 ]
 
@@ -113,6 +116,10 @@ def lib():
     L.mxk_fill_weights.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_uint32, C.c_void_p]
     L.mxk_quantize_rows.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
     L.mxk_read_status.argtypes = [C.c_void_p, C.POINTER(MxkStatus)]
+    L.mxk_read_status_static.argtypes = [C.POINTER(MxkStatus)]
+    L.mxk_rwk_ticks_off.restype = C.c_int64
+    L.mxk_ticks_count.restype = C.c_int64
+    L.mxk_set_ticks.argtypes = [C.c_int]
     L.mxk_select_win.argtypes = [C.POINTER(C.c_uint32), C.c_int, C.c_int, C.c_int]
     L.mxk_symm_alloc.argtypes = [C.POINTER(C.c_void_p), C.c_int64]
     L.mxk_symm_free.argtypes = [C.c_void_p]

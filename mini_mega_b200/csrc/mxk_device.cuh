@@ -67,6 +67,15 @@ __device__ __forceinline__ uint64_t ld_relaxed_sys_u64(const uint64_t* p) {
 __device__ __forceinline__ void st_relaxed_sys_u64(uint64_t* p, uint64_t v) {
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// two 64-bit words with one 16-byte access; each word is read / written whole
+__device__ __forceinline__ void st_relaxed_sys_v2_u64(uint64_t* p, uint64_t a, uint64_t b) {
+    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ ulonglong2 ld_relaxed_sys_v2_u64(const uint64_t* p) {
+    ulonglong2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint8_t ld_relaxed_gpu_u8(const uint8_t* p) {
     uint32_t v;
     asm volatile("ld.relaxed.gpu.global.u8 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

@@ -48,7 +48,8 @@ constexpr int kSfRing = 8;            // shared-memory scale-tile slots (one per
 constexpr int kSfSlotBytes = 3 * 512; // A rows, weight half 0, weight half 1
 constexpr int kPrefetchBytesPerCta = 704 * 1024;  // L2 prefetch during the prologue: 148 CTAs x 704 KB = 104 MB
 constexpr int kPubDepth = 8;          // combine-row arrival counts a thread may hold back before one fence releases them
-constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align*/ + kSfRing * kSfSlotBytes + 16384 /*control*/;
+constexpr int kControlBytes = 20480;  // barriers, task ring, exchange words, count queues, push-mode tables
+constexpr int kGemmSmem = kStages * kStageBytes + 1024 /*align*/ + kSfRing * kSfSlotBytes + kControlBytes;
 
 // Wait-time accounting (reference: clock64 phase stamps in local_flags.pre_ticks,
 // src/kernel.cuh:52-124): each role sums the cycles it spent blocked and adds them to
@@ -73,9 +74,38 @@ struct GemmSmem {
     uint32_t pubq[kPubDepth][kEpiWarps * 32];   // per epilogue thread: queued arrival counts, (rank << 24) | (k * cap + token)
     uint32_t tmem_base;
     int abort_flag;
+    PushTabs tabs;                // push mode: this launch's tables, built by every CTA for itself
 };
 
-static_assert(sizeof(GemmSmem) <= 16384, "control block must fit the space reserved behind the tile rings");
+static_assert(sizeof(GemmSmem) <= kControlBytes, "control block must fit the space reserved behind the tile rings");
+static_assert(kGemmSmem + 2048 <= 227 * 1024, "dynamic + static shared memory of the kernel within the 227 KB of a CTA");
+
+// Push mode: task `t` of the queue and window `w`, computed from the tables in shared memory
+// (pull mode reads the same records from the lists CTA 0 wrote to global memory).  Task order:
+// L1 tasks then L2 tasks; per sorted expert position p its windows x n-tiles, windows fastest.
+__device__ __forceinline__ int tabs_pos_of_window(const PushTabs* T, int EPR, int w) {
+    int lo = 0, hi = EPR;   // largest p with first[p] <= w (empty experts sit at the end)
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (T->first[mid] <= w) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+__device__ __forceinline__ int4 tabs_window(const PushTabs* T, const KArgs& a, int w) {
+    const int p = tabs_pos_of_window(T, a.EPR, w);
+    const int e = T->order[p], wl = w - T->first[p];
+    return make_int4(e, T->base[e] + wl * a.win_cap, min(a.win_cap, T->tot[e] - wl * a.win_cap), 0);
+}
+__device__ __forceinline__ int4 tabs_task(const PushTabs* T, const KArgs& a, int t) {
+    const int kind = t >= T->n_l1 ? 1 : 0;
+    const int nt = kind ? a.H / kBlockN : a.I / 128;
+    const int tt = kind ? t - T->n_l1 : t;
+    const int p = tabs_pos_of_window(T, a.EPR, tt / nt);
+    const int fw = T->first[p], nw = T->first[p + 1] - fw;
+    const int i = tt - fw * nt;
+    const int w = i % nw;
+    return make_int4(kind, fw + w, i / nw, min(a.win_cap, T->tot[T->order[p]] - w * a.win_cap));
+}
 
 // Barrier initialisation (one thread) — part of the kernel prologue.
 // In pair mode the barriers the MMA issuer waits on (scale tile ready, accumulators drained) and
@@ -95,7 +125,8 @@ __device__ void gemm_init_barriers(GemmSmem* S, const bool pair) {
 // The GEMM phase of the persistent kernel; called by all threads of the CTA after the
 // set-up tables of this launch are visible.  Returns when every role has left its loop.
 template <bool kPair>
-__device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t* sf_tiles, GemmSmem* S,
+__device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, const PushTabs* tabs,
+                           unsigned long long* trace, uint8_t* tiles, uint8_t* sf_tiles, GemmSmem* S,
                            const uint32_t tmem_base, const CUtensorMap* tm_pool_p, const CUtensorMap* tm_ffn_p,
                            const CUtensorMap* tm_w1_p, const CUtensorMap* tm_w2_p) {
     const CUtensorMap& tm_pool = *tm_pool_p;
@@ -108,11 +139,15 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
     const bool timed = a.ticks != 0;
     const long long t_start = clock64();
 
-    const int n_tasks = ld_relaxed_gpu(&f->n_tasks);  // written by the set-up phase of this same kernel
+    const int par = (int)(epoch & 1);
+    // pull mode: written by the set-up phase of this same kernel (CTA 0); push mode: own tables
+    const int n_tasks = tabs ? tabs->n_tasks : ld_relaxed_gpu(&f->n_tasks);
     const int4* tasks = reinterpret_cast<const int4*>(a.rwk + a.L.tasks_off);
     const int4* windows = reinterpret_cast<const int4*>(a.rwk + a.L.windows_off);
-    uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
-    const uint32_t* pool_ready = reinterpret_cast<const uint32_t*>(a.rwk + a.L.pool_ready_off);
+    auto get_task = [&](int t) -> int4 { return tabs ? tabs_task(tabs, a, t) : ld_relaxed_gpu_v4(tasks + t); };
+    auto get_window = [&](int w) -> int4 { return tabs ? tabs_window(tabs, a, w) : ld_relaxed_gpu_v4(windows + w); };
+    uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off) + (size_t)par * a.L.max_windows;
+    const uint32_t* pool_ready = reinterpret_cast<const uint32_t*>(a.rwk + a.L.pool_ready_off) + (size_t)par * a.L.max_windows;
     const int kb1 = a.H / kBlockK, kb2 = a.I / kBlockK;
     const int nt1 = a.I / 128;
     const uint32_t l1_need = (uint32_t)nt1 * kEpiWarps * (kPair ? 2u : 1u);   // arrivals that complete a window's ffn rows
@@ -167,8 +202,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                     ring_dead = true;
                     return make_int4(-1, 0, 0, 0);
                 }
-                const int t = i == 0 ? unit_id : (int)atomicAdd(&f->task_counter, 1u);
-                const int4 tk = t < n_tasks ? ld_relaxed_gpu_v4(tasks + t) : make_int4(-1, 0, 0, 0);
+                const int t = i == 0 ? unit_id : n_units + (int)atomicAdd(&f->task_ctr[par], 1u);
+                const int4 tk = t < n_tasks ? get_task(t) : make_int4(-1, 0, 0, 0);
                 S->task[slot] = tk;
                 mbar_arrive(&S->task_full[slot]);
                 if constexpr (kPair) {
@@ -191,7 +226,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 if (ring_dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 3); *abort_flag = 1; break; }
                 const int4 task = pending;
                 if (task.x < 0) break;
-                const int4 win = pending_win_valid ? pending_win : ld_relaxed_gpu_v4(windows + task.y);
+                const int4 win = pending_win_valid ? pending_win : get_window(task.y);
                 const bool gate_ok = pending_win_valid && pending_gate;
                 pending_win_valid = false;
                 if (lookahead) pending = claim_publish(it + 1);
@@ -202,6 +237,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                 if (!gate_ok && !MXK_TIMED(w_gate, spin_until([&] { return gate_passed(task, win); }, wait_ns, abort_flag))) {
                     raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
                 }
+                if (trace && it == 0) trace[8] = gtimer_ns();
                 fence_proxy_async_global();  // pool / ffn rows were written with ordinary stores
                 const CUtensorMap* ma = is_l2 ? &tm_ffn : &tm_pool;
                 const CUtensorMap* mb = is_l2 ? &tm_w2 : &tm_w1;
@@ -214,7 +250,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                         // request the next task's window record with the first stage, read its gate
                         // two stages later (the record has arrived by then): each is one round trip
                         // taken out of the slack of the stage ring instead of the next task's start
-                        if (kb == 0) { pending_win = ld_relaxed_gpu_v4(windows + pending.y); pending_win_valid = true; pending_gate = false; }
+                        if (kb == 0) { pending_win = get_window(pending.y); pending_win_valid = true; pending_gate = false; }
                         else if (kb == 2) pending_gate = gate_passed(pending, pending_win);
                     }
                     if (!MXK_TIMED(w_empty, mbar_wait(&S->empty[stage], phase ^ 1, wait_ns, abort_flag))) { dead = true; break; }
@@ -231,6 +267,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                         tma_load_2d_hint(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[stage], stream_policy);
                         tma_load_2d_hint(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[stage], stream_policy);
                     }
+                    if (trace && it == 0 && kb == 0) trace[9] = gtimer_ns();
                     if (++stage == kNStages) { stage = 0; phase ^= 1; }
                 }
                 if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; break; }
@@ -285,6 +322,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
                     for (int i = 0; i < 4; ++i) {
                         if (kb0 + i >= nkb) break;
                         if (!stage_ready && !MXK_TIMED(w_full, mbar_wait(&S->full[stage], phase, wait_ns, abort_flag))) { dead = true; break; }
+                        if (trace && it == 0 && kb0 + i == 0) trace[10] = gtimer_ns();
                         tc_fence_after();
                         const uint64_t adesc = tile_desc0 + (uint64_t)(stage * (kStageB >> 4));
                         const uint64_t bdesc = adesc + (uint64_t)(kABytes >> 4);
@@ -362,7 +400,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             const int nkb = is_l2 ? kb2 : kb1;
             const int ngroups = (nkb + 3) >> 2;
             if ((it & 1u) != my_parity) { sfg += (uint32_t)ngroups; continue; }   // the other warp's task
-            const int4 win = ld_relaxed_gpu_v4(windows + task.y);
+            const int4 win = get_window(task.y);
             const int e = win.x, row0 = win.y + 128 * (int)crank, rows = task.w - 128 * (int)crank;
             const uint8_t* asf = nullptr;   // activation scale rows of this window
             int asf_stride = 0;
@@ -536,7 +574,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, uint8_t* tiles, uint8_t*
             __syncwarp();
             if (lane == 0) arrive_leader(&S->task_empty[slot]);
             if (task.x < 0) { flush_publish(); break; }
-            const int4 win = ld_relaxed_gpu_v4(windows + task.y);
+            const int4 win = get_window(task.y);
             const int row0 = win.y + 128 * (int)crank, rows = task.w - 128 * (int)crank;
             const bool is_l2 = task.x == 1;
             const bool warp_active = q * 32 < rows;

@@ -35,21 +35,27 @@ constexpr uint64_t kDefaultRemoteWaitNs = 20000000000ull;  // 20 s
 struct DevFlags {  // head of rwk (flags_off)
     long long current_time;      // completed prologues; the running launch is +1
     unsigned route_blocks_done;
-    unsigned task_counter;
-    unsigned pad0_[2];
+    unsigned clear_blocks_done;  // arrivals at the grid barrier behind a full clear of combine_cnt
+    unsigned task_ctr[2];        // claimed tasks beyond the first per CTA, by launch parity (the
+                                 // copy of the other parity is reset for the next launch)
     int n_tasks, n_l1_tasks, n_windows, total_rows;
     int status;
     int dbg[8];
     unsigned long long ticks[16];
     unsigned long long dbg_ts[8];  // set-up leader time stamps (diagnostic, MXK_TICKS=1)
-    unsigned setup_epoch;        // epoch whose tables CTA 0 has published; alone in its 128-byte
-    unsigned pad2_[31];          // line: every CTA polls it while CTA 0 writes the fields above
+    unsigned setup_epoch;        // epoch whose tables CTA 0 has published; every CTA polls it
+    unsigned pad2_[31];          // while CTA 0 writes the fields above
+    unsigned reduce_blocks_done; // CTAs that have finished the reduce phase of this launch
+    unsigned cnt_clean_epoch;    // launch whose reduce has consumed AND zeroed every arrival count
+    unsigned long long trace[64];  // MxkStatus.trace
 };
 static_assert(sizeof(DevFlags) <= 1024, "status header must fit its 1 KB slot");
+static_assert(offsetof(DevFlags, ticks) % 8 == 0 && offsetof(DevFlags, trace) % 8 == 0, "64-bit fields aligned");
 
 struct KArgs {
     int R, rank, EPR, E, topk, H, I, cap, slot_cap, tokens, win_cap;
     int gemm_grid, skip_combine, scaled, ticks, pair;
+    int push;                    // push-mode prologue (see push_phase)
     unsigned long long local_wait_ns, remote_wait_ns;
     uint8_t* rwk;
     uint8_t* unk;
@@ -96,6 +102,13 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
     const int warp = threadIdx.x >> 5;
     const bool do_gemm = (phase_mask & MXK_PHASE_GEMM) != 0;
 
+    // Time line of the first and the last CTA (MxkStatus.trace), MXK_TICKS=1 only.
+    unsigned long long* trace = nullptr;
+    if (a.ticks != 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) trace = f->trace + (blockIdx.x == 0 ? 0 : 32);
+    const bool stamp = a.ticks != 0 && threadIdx.x == 0;
+    const uint64_t t0 = stamp ? gtimer_ns() : 0;
+    if (trace && threadIdx.x == 0) trace[0] = t0;
+
     // the launch counter is advanced by the last CTA at the end of the route phase, after every
     // CTA has arrived there — i.e. after this read
     const long long epoch = ld_relaxed_gpu(&f->current_time) + ((phase_mask & MXK_PHASE_ROUTE) ? 1 : 0);
@@ -116,11 +129,10 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
         tc_fence_after();
         tmem_base = S->tmem_base;
     }
+    if (trace && threadIdx.x == 0) trace[1] = gtimer_ns();
 
     // Phase stamps in ns since this CTA started (MxkStatus.ticks 9..13: end of route, set-up,
     // dispatch, GEMM, reduce; CTA 0 for the first two, maximum over CTAs for the rest).
-    const bool stamp = a.ticks != 0 && threadIdx.x == 0;
-    const uint64_t t0 = stamp ? gtimer_ns() : 0;
     if (stamp && blockIdx.x == 0 && (phase_mask & MXK_PHASE_SETUP))
         for (int i = 0; i < 16; ++i) f->ticks[i] = 0;  // other CTAs add to them only after the set-up flag
 
@@ -142,26 +154,55 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
         }
     }
 
-    if (phase_mask & MXK_PHASE_ROUTE) route_phase(a, f, epoch, s_small);
+    const PushScratch sc = push_scratch(tiles);   // push mode: the tile region is scratch until the GEMM phase
+    if (phase_mask & MXK_PHASE_ROUTE) {
+        ensure_counts_clean(a, f, epoch);
+        if (a.push) {
+            push_phase(a, f, epoch, sc.wid);
+            if (trace && threadIdx.x == 0) trace[2] = gtimer_ns();
+            __syncthreads();   // the scratch is reused below
+            route_phase(a, f, epoch, s_small, true);
+        } else {
+            route_phase(a, f, epoch, s_small, false);
+        }
+    }
     if (stamp && blockIdx.x == 0) f->ticks[9] = gtimer_ns() - t0;
+    if (trace && threadIdx.x == 0) trace[3] = gtimer_ns();
 
     bool tables_ok = true;
-    if (phase_mask & MXK_PHASE_SETUP) {
-        // the tile region is idle until the GEMM phase: CTA 0 borrows it as scratch
-        if (blockIdx.x == 0) setup_phase_leader(a, f, epoch, reinterpret_cast<int*>(tiles));
-        else tables_ok = setup_phase_wait(a, f, epoch, s_small);
-        __syncthreads();
-    }
-    if (stamp && blockIdx.x == 0) f->ticks[10] = gtimer_ns() - t0;
-
-    if ((phase_mask & MXK_PHASE_DISPATCH) && tables_ok) {
-        dispatch_phase(a, f, epoch, reinterpret_cast<int*>(tiles));  // tile region still idle: scratch
-        __syncthreads();
+    const PushTabs* tabs = nullptr;
+    if (a.push) {
+        if (phase_mask & (MXK_PHASE_SETUP | MXK_PHASE_DISPATCH | MXK_PHASE_GEMM)) {
+            const bool setup = (phase_mask & MXK_PHASE_SETUP) != 0, disp = (phase_mask & MXK_PHASE_DISPATCH) != 0;
+            tables_ok = push_tables(a, f, epoch, sc, &S->tabs, setup);
+            tabs = &S->tabs;
+            if (trace && threadIdx.x == 0) trace[5] = gtimer_ns();
+            if (stamp && blockIdx.x == 0) f->ticks[10] = gtimer_ns() - t0;
+            if (tables_ok && (setup || disp)) push_dispatch(a, f, epoch, sc, tabs, setup, disp);
+            fence_proxy_async_smem();   // the scratch becomes TMA destination next
+            __syncthreads();
+        }
+    } else {
+        if (phase_mask & MXK_PHASE_SETUP) {
+            // the tile region is idle until the GEMM phase: CTA 0 borrows it as scratch
+            if (blockIdx.x == 0) setup_phase_leader(a, f, epoch, reinterpret_cast<int*>(tiles));
+            else tables_ok = setup_phase_wait(a, f, epoch, s_small);
+            __syncthreads();
+        }
+        if (stamp && blockIdx.x == 0) f->ticks[10] = gtimer_ns() - t0;
+        if (trace && threadIdx.x == 0) trace[6] = gtimer_ns();
+        if ((phase_mask & MXK_PHASE_DISPATCH) && tables_ok) {
+            dispatch_phase(a, f, epoch, reinterpret_cast<int*>(tiles));  // tile region still idle: scratch
+            fence_proxy_async_smem();
+            __syncthreads();
+        }
     }
     if (stamp) atomicMax(&f->ticks[11], (unsigned long long)(gtimer_ns() - t0));
+    if (trace && threadIdx.x == 0) trace[7] = gtimer_ns();
 
     if (do_gemm) {
-        if (tables_ok) gemm_phase<kPair>(a, f, tiles, sf_tiles, S, tmem_base, &tm_pool, &tm_ffn, &tm_w1, &tm_w2);
+        if (tables_ok)
+            gemm_phase<kPair>(a, f, epoch, tabs, trace, tiles, sf_tiles, S, tmem_base, &tm_pool, &tm_ffn, &tm_w1, &tm_w2);
         if (S->abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain
         tc_fence_before();
         // pair mode: neither CTA may free tensor memory or leave while its partner can still
@@ -173,9 +214,11 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
         }
     }
     if (stamp) atomicMax(&f->ticks[12], (unsigned long long)(gtimer_ns() - t0));
+    if (trace && threadIdx.x == 0) trace[11] = gtimer_ns();
 
-    if (phase_mask & MXK_PHASE_REDUCE) reduce_phase(a, f, s_small, s_w);
+    if (phase_mask & MXK_PHASE_REDUCE) reduce_phase(a, f, epoch, s_small, s_w);
     if (stamp) atomicMax(&f->ticks[13], (unsigned long long)(gtimer_ns() - t0));
+    if (trace && threadIdx.x == 0) trace[12] = gtimer_ns();
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -280,13 +323,20 @@ int compute_layout(const MxkGeom* g, MxkLayout* L) {
     L->sym_bytes = o;
     // unk
     o = 0;
-    L->xbar_stride = 32;  // 128 B apart: one line per writing peer
-    L->xbar_off = take(R * L->xbar_stride * 4);
     L->recv_stride = (int32_t)align_up(EPR + 1, 64);
     L->src_index_table_off = take(2 * EPR * R * slot * 8);
     L->expert_recv_counts_off = take(2 * R * (int64_t)L->recv_stride * 8);
     L->combine_rows_off = take(topk * cap * H * 2);
     L->combine_cnt_off = take(topk * cap * 4);
+    // push-mode staging area, only for geometries whose world routing fits a CTA's shared memory
+    L->push_eligible = (R <= kPushMaxR && EPR <= kPushMaxEPR && R * cap * topk <= kPushMaxPairs &&
+                        EPR * (R + 1) <= kPushMaxCnt) ? 1 : 0;
+    {
+        const int64_t sfw = (((H / 128) + 3) / 4 + 1) & ~(int64_t)1;
+        L->xin_row_words = (int32_t)(2 * topk + sfw + H / 4);
+        L->xin_src_words = 16 + cap * (int64_t)L->xin_row_words;
+        L->xin_off = take(L->push_eligible ? 2 * R * L->xin_src_words * 8 : 0);
+    }
     L->unk_bytes = o;
     // rwk
     o = 0;
@@ -307,8 +357,8 @@ int compute_layout(const MxkGeom* g, MxkLayout* L) {
     L->expert_row_base_off = take((EPR + 1) * 4);
     L->windows_off = take((int64_t)L->max_windows * 16);
     L->tasks_off = take((int64_t)L->max_tasks * 16);
-    L->l1_done_off = take((int64_t)L->max_windows * 4);
-    L->pool_ready_off = take((int64_t)L->max_windows * 4);
+    L->l1_done_off = take(2 * (int64_t)L->max_windows * 4);
+    L->pool_ready_off = take(2 * (int64_t)L->max_windows * 4);
     L->expert_first_win_off = take(EPR * 4);
     L->row_meta_off = take(L->pool_rows * 16);
     L->pool_off = take((L->pool_rows + 128) * H);
@@ -349,6 +399,13 @@ int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t k) {
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(MXK_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed, CUresult " + std::to_string((int)r));
     return 0;
+}
+
+// Wait-time accounting and phase stamps: MXK_TICKS=1 in the environment, or mxk_set_ticks().
+int g_ticks_override = -1;
+int ticks_enabled() {
+    static const int ticks_env = [] { const char* e = std::getenv("MXK_TICKS"); return e && e[0] == '1' ? 1 : 0; }();
+    return g_ticks_override >= 0 ? g_ticks_override : ticks_env;
 }
 
 struct DeviceInfo { int sm_count = 0; int cc = 0; bool ok = false; };
@@ -396,15 +453,19 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     if ((int64_t)g.topk * g.max_tokens > 0xFFFFFF || g.R > 255)
         return fail(MXK_ERR_BAD_ARG, "topk * max_tokens must fit 24 bits and R 8 bits (arrival-count queue entries)");
     if ((la->w1_sf == nullptr) != (la->w2_sf == nullptr)) return fail(MXK_ERR_BAD_ARG, "w1_sf and w2_sf must both be set or both be null");
+    // set-up and dispatch borrow the operand-tile region of shared memory for their tables
+    if ((4ll * g.experts_per_rank + 2 + (int64_t)g.experts_per_rank * (g.R + 1)) * 4 > (int64_t)kStages * kStageBytes)
+        return fail(MXK_ERR_BAD_ARG, "experts_per_rank * (R + 1) tables exceed the shared-memory scratch of the prologue");
+    if (la->dispatch_mode < 0 || la->dispatch_mode > 2) return fail(MXK_ERR_BAD_ARG, "dispatch_mode must be 0, 1 or 2");
+    if (la->dispatch_mode == 2 && !k->L.push_eligible)
+        return fail(MXK_ERR_BAD_ARG, "dispatch_mode = 2 (push) needs R <= 64, experts_per_rank <= 256 and R * max_tokens * topk <= 16384");
+    k->push = la->dispatch_mode == 2 || (la->dispatch_mode == 0 && k->L.push_eligible);
     k->R = g.R; k->rank = g.rank; k->EPR = g.experts_per_rank; k->E = g.R * g.experts_per_rank;
     k->topk = g.topk; k->H = g.hidden; k->I = g.intermediate; k->cap = g.max_tokens;
     k->slot_cap = g.slot_capacity ? g.slot_capacity : g.max_tokens;
     k->tokens = la->tokens; k->win_cap = win;
     k->skip_combine = la->skip_combine; k->scaled = la->w1_sf != nullptr;
-    {
-        static const int ticks_env = [] { const char* e = std::getenv("MXK_TICKS"); return e && e[0] == '1' ? 1 : 0; }();
-        k->ticks = ticks_env;  // MXK_TICKS=1: the GEMM kernel accounts its wait cycles (MxkStatus.ticks)
-    }
+    k->ticks = ticks_enabled();  // the kernel accounts its wait cycles and stamps its phases (MxkStatus.ticks / trace)
     k->local_wait_ns = la->max_spins > 0 ? (unsigned long long)la->max_spins * 250ull : kDefaultLocalWaitNs;
     k->remote_wait_ns = la->max_spins > 0 ? (unsigned long long)la->max_spins * 250ull : kDefaultRemoteWaitNs;
     k->rwk = static_cast<uint8_t*>(la->rwk); k->unk = static_cast<uint8_t*>(la->unk);
@@ -442,18 +503,41 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
     if ((mask & MXK_PHASE_REDUCE) && !k.y && !k.y_bf16) return fail(MXK_ERR_BAD_ARG, "y or y_bf16 must be non-null");
     if ((mask & MXK_PHASE_REDUCE) && k.tokens == 0) mask &= ~MXK_PHASE_REDUCE;  // nothing to reduce on this rank
     if (mask == 0) return 0;
-    CUtensorMap tm_pool, tm_ffn, tm_w1, tm_w2;
-    std::memset(&tm_pool, 0, sizeof(tm_pool));
-    std::memset(&tm_ffn, 0, sizeof(tm_ffn));
-    std::memset(&tm_w1, 0, sizeof(tm_w1));
-    std::memset(&tm_w2, 0, sizeof(tm_w2));
+    // The four tensor maps depend only on (workspace, weights, geometry): a serving loop launches the
+    // same ones every layer, so the last few sets are kept per thread instead of being re-encoded.
+    struct MapSet { const void* rwk; const void* w1; const void* w2; int64_t rows; int H, I, EPR; CUtensorMap m[4]; };
+    static thread_local MapSet cache[4];
+    static thread_local int cache_n = 0, cache_next = 0;
+    CUtensorMap zero_maps[4];
+    const CUtensorMap* maps = zero_maps;
     if (mask & MXK_PHASE_GEMM) {
         if (!k.w1 || !k.w2) return fail(MXK_ERR_BAD_ARG, "w1 / w2 must be non-null");
-        if (int rc = make_map(&tm_pool, k.rwk + k.L.pool_off, k.L.pool_rows + 128, k.H)) return rc;
-        if (int rc = make_map(&tm_ffn, k.rwk + k.L.ffn_off, k.L.pool_rows + 128, k.I)) return rc;
-        if (int rc = make_map(&tm_w1, k.w1, (int64_t)k.EPR * 2 * k.I, k.H)) return rc;
-        if (int rc = make_map(&tm_w2, k.w2, (int64_t)k.EPR * k.H, k.I)) return rc;
+        const MapSet* hit = nullptr;
+        for (int i = 0; i < cache_n; ++i) {
+            const MapSet& c = cache[i];
+            if (c.rwk == k.rwk && c.w1 == k.w1 && c.w2 == k.w2 && c.rows == k.L.pool_rows && c.H == k.H && c.I == k.I && c.EPR == k.EPR) {
+                hit = &c;
+                break;
+            }
+        }
+        if (!hit) {
+            MapSet n;
+            std::memset(&n, 0, sizeof(n));
+            n.rwk = k.rwk; n.w1 = k.w1; n.w2 = k.w2; n.rows = k.L.pool_rows; n.H = k.H; n.I = k.I; n.EPR = k.EPR;
+            if (int rc = make_map(&n.m[0], k.rwk + k.L.pool_off, k.L.pool_rows + 128, k.H)) return rc;
+            if (int rc = make_map(&n.m[1], k.rwk + k.L.ffn_off, k.L.pool_rows + 128, k.I)) return rc;
+            if (int rc = make_map(&n.m[2], k.w1, (int64_t)k.EPR * 2 * k.I, k.H)) return rc;
+            if (int rc = make_map(&n.m[3], k.w2, (int64_t)k.EPR * k.H, k.I)) return rc;
+            cache[cache_next] = n;
+            hit = &cache[cache_next];
+            cache_next = (cache_next + 1) % 4;
+            if (cache_n < 4) ++cache_n;
+        }
+        maps = hit->m;
+    } else {
+        std::memset(zero_maps, 0, sizeof(zero_maps));
     }
+    const CUtensorMap &tm_pool = maps[0], &tm_ffn = maps[1], &tm_w1 = maps[2], &tm_w2 = maps[3];
     static thread_local int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -507,7 +591,7 @@ __global__ void k_static_ptrs(void** sym_table, void** unk_table, void* sym, voi
 
 // Device address of g_static_scratch on the current device.  In host code the array's
 // name is only a stand-in, so the address is asked from the runtime once per device.
-int static_scratch_base(uint8_t** out) {
+int static_scratch_base(uint8_t** out, int* dev_out) {
     static uint8_t* base[kStaticMaxDevices] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -520,6 +604,7 @@ int static_scratch_base(uint8_t** out) {
         base[dev] = static_cast<uint8_t*>(p);
     }
     *out = base[dev];
+    *dev_out = dev;
     return 0;
 }
 
@@ -579,18 +664,32 @@ int mxk_launch_full_static(const MxkLaunchArgs* a, void* stream) {
         return fail(MXK_ERR_BAD_ARG, "workspace of this geometry needs " + std::to_string(need) +
                                          " bytes, the static scratch holds " + std::to_string(kStaticScratchBytes));
     uint8_t* base = nullptr;
-    if (int rc = static_scratch_base(&base)) return rc;
+    int dev = 0;
+    if (int rc = static_scratch_base(&base, &dev)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    uint8_t* unk = base + kStaticPtrBytes;
-    uint8_t* rwk = unk + L.unk_bytes;
-    // The array keeps whatever the previous call left.  What the protocol needs at zero is the
-    // status header behind the launch counter (status word, expiry counters, work counters).  The
-    // launch counter itself — first word of the header, zero when the module is loaded — must
-    // keep running: the prologue's tables are tagged with it, and a counter that started over
-    // would make the previous call's words look current.
+    // Layout of the array: the two pointer tables, then rwk, then unk.  rwk comes first so that its
+    // status header — whose first word is the launch counter — sits at the same address whatever
+    // the geometry: the counter is zero when the module is loaded and must keep running from call
+    // to call, because the prologue's words are tagged with it and a counter that started over
+    // would make an earlier call's words look current.
     static_assert(offsetof(DevFlags, current_time) == 0 && sizeof(long long) == 8, "launch counter leads the header");
-    cudaError_t e = cudaMemsetAsync(rwk + L.flags_off + 8, 0, 1024 - 8, st);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status header)");
+    uint8_t* rwk = base + kStaticPtrBytes;
+    uint8_t* unk = rwk + L.rwk_bytes;
+    // The array keeps whatever the previous call left.  Calls of one geometry continue on it like
+    // launches on an ordinary workspace.  A call with ANOTHER geometry finds the tables of the old
+    // one at different offsets, so everything behind the launch counter is cleared first (the
+    // memset runs on the caller's stream, before this call's kernel and after the previous one).
+    static MxkGeom last_geom[kStaticMaxDevices] = {};
+    cudaError_t e;
+    if (std::memcmp(&last_geom[dev], &g, sizeof(g)) != 0) {
+        e = cudaMemsetAsync(rwk + 8, 0, need - kStaticPtrBytes - 8, st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(static workspace)");
+        last_geom[dev] = g;
+    } else {
+        // a device-side failure of an earlier call must not be reported for this one
+        e = cudaMemsetAsync(rwk + offsetof(DevFlags, status), 0, sizeof(int) * 9, st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status words)");
+    }
     void** sym_table = reinterpret_cast<void**>(base);
     void** unk_table = reinterpret_cast<void**>(base + 128);
     k_static_ptrs<<<1, 1, 0, st>>>(sym_table, unk_table, const_cast<uint8_t*>(a->self), unk);
@@ -605,6 +704,12 @@ int mxk_launch_full_static(const MxkLaunchArgs* a, void* stream) {
     if (int rc = build_kargs(&b, &k)) return rc;
     if (!k.y && !k.y_bf16) return fail(MXK_ERR_BAD_ARG, "y or y_bf16 must be non-null");
     return launch_mega(k, kPhaseAll, st);
+}
+int mxk_read_status_static(MxkStatus* out) {
+    uint8_t* base = nullptr;
+    int dev = 0;
+    if (int rc = static_scratch_base(&base, &dev)) return rc;
+    return mxk_read_status(base + kStaticPtrBytes, out);
 }
 int64_t mxk_static_scratch_bytes(void) { return (int64_t)kStaticScratchBytes; }
 
@@ -669,8 +774,20 @@ int mxk_read_status(const void* rwk, MxkStatus* out) {
     out->n_tasks = f.n_tasks; out->n_l1_tasks = f.n_l1_tasks; out->n_windows = f.n_windows; out->total_rows = f.total_rows;
     for (int i = 0; i < 8; ++i) out->dbg[i] = f.dbg[i];
     for (int i = 0; i < 16; ++i) out->ticks[i] = f.ticks[i];
+    for (int i = 0; i < 64; ++i) out->trace[i] = f.trace[i];
     return 0;
 }
+
+// Byte offset of the per-layer wait / phase counters (MxkStatus.ticks) inside rwk and their
+// number, for hosts that copy them back themselves (reference: pre_ticks readers,
+// torch/csrc/flags_bridge.cu:44-51).
+int mxk_set_ticks(int on) {
+    const int before = ticks_enabled();
+    g_ticks_override = on < 0 ? -1 : (on ? 1 : 0);
+    return before;
+}
+int64_t mxk_rwk_ticks_off(void) { return (int64_t)offsetof(DevFlags, ticks); }   // flags_off is 0 in every layout
+int64_t mxk_ticks_count(void) { return 16; }
 
 // Window chooser, restated from the reference's cost model with its own
 // calibration table (src/win_select.cuh:45-128): argmin over {32,48,64,96,128}

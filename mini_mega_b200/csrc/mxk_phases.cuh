@@ -18,6 +18,13 @@
 //                   (reference: r19_pull_flags, src/compute_big.cuh:1691-1946)
 //   reduce_phase    top-k weighted sum at the source rank
 //                   (reference: reduce_tile_body, src/combine.cuh:488-656)
+//
+// Small batches run the PUSH-mode prologue instead of route scatter / barrier / pull
+// (three dependent trips over NVLink): push_phase stores every token's routing, weights,
+// scales and E4M3 row into the staging area of the ranks that own its experts; push_tables
+// lets EVERY CTA derive the world's routing tables from those words in shared memory (no
+// leader CTA, no flag); push_dispatch copies the rows from the staging area into the pool.
+// The tables that result are the same, bit for bit, as the pull-mode ones.
 // ============================================================================
 #pragma once
 
@@ -38,7 +45,34 @@ __device__ __forceinline__ uint64_t tagged(uint32_t payload, long long epoch) {
 // Slots are handed out in ascending pair index idx = token*topk + k, so every table row (and
 // with it the pool row order) is deterministic; the reference uses a shared-memory atomicAdd
 // and accepts any order (src/prologue.cuh:164-180).
-__device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_wtot /*[kRoutePer * warps]*/) {
+// Arrival counters of the rows peers push to this rank (combine_cnt) must be zero before any
+// peer can push for this launch.  The reduce phase zeroes every count it has consumed and the
+// last CTA to leave it records the launch in cnt_clean_epoch; when the previous launch did that
+// (the normal case) nothing has to be cleared here.  Otherwise — a compute launch without a
+// reduce, a reduce that gave up — the whole grid clears the table and meets at a barrier before
+// anything of this launch leaves the rank: a peer can push only after it has seen this rank's
+// routing, and that is published behind the barrier.
+__device__ void ensure_counts_clean(const KArgs& a, DevFlags* f, long long epoch) {
+    if (ld_relaxed_gpu(&f->cnt_clean_epoch) == (uint32_t)(epoch - 1)) return;   // uniform over the grid
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    unsigned* cnt = reinterpret_cast<unsigned*>(a.unk + a.L.combine_cnt_off);
+    for (int i = blockIdx.x * nthr + tid; i < a.topk * a.cap; i += gridDim.x * nthr) cnt[i] = 0;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        atomicAdd(&f->clear_blocks_done, 1u);
+        const unsigned want = gridDim.x;
+        if (!spin_until([&] { return ld_acquire_gpu(&f->clear_blocks_done) >= want; }, a.local_wait_ns, nullptr))
+            raise_status(f, MXK_DEV_TIMEOUT_PIPE, 2);
+    }
+    __syncthreads();
+}
+
+// `local_only` (push mode): only this rank's own tables are written — route_slot_counts and the
+// accepted-pair map; nothing is scattered to the owner ranks, they derive their tables from the
+// pushed routing words.
+__device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_wtot /*[kRoutePer * warps]*/,
+                            const bool local_only) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nthr = blockDim.x, nwarps = nthr >> 5;
     const int par = (int)(epoch & 1);
@@ -46,14 +80,6 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     const int64_t* ti = a.topk_idx;
     uint8_t* pair_state = a.rwk + a.L.pair_state_off;
     int* rsc = reinterpret_cast<int*>(a.rwk + a.L.route_slot_counts_off);
-
-    // Arrival counters of the rows peers will push to this rank in this launch.  Cleared before
-    // any count of this launch leaves the CTA: a peer can push only after it has seen ALL counts
-    // of this rank, and the previous launch's reduce has consumed the old values.
-    unsigned* cnt = reinterpret_cast<unsigned*>(a.unk + a.L.combine_cnt_off);
-    for (int i = blockIdx.x * nthr + tid; i < a.topk * a.cap; i += gridDim.x * nthr) cnt[i] = 0;
-    __threadfence();
-    __syncthreads();
 
     for (int e = blockIdx.x; e < a.E; e += gridDim.x) {
         const int dst = e / a.EPR, le = e % a.EPR;
@@ -91,7 +117,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
                     const int p = p0 + j * nthr + tid;
                     const int slot = base + wpre + __popc(bal[j] & ((1u << lane) - 1u));
                     const bool ok = slot < a.slot_cap;  // over capacity: dropped (src/prologue.cuh:171-174)
-                    if (ok) st_relaxed_sys_u64(tbl + slot, tagged((uint32_t)p, epoch));
+                    if (ok && !local_only) st_relaxed_sys_u64(tbl + slot, tagged((uint32_t)p, epoch));
                     pair_state[p] = ok ? 1 : 0;
                 }
                 base += tot;
@@ -101,9 +127,11 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
         if (tid == 0) {
             const int c = base < a.slot_cap ? base : a.slot_cap;
             rsc[e] = c;
-            uint64_t* recv = reinterpret_cast<uint64_t*>(peer_unk + a.L.expert_recv_counts_off) +
-                             ((size_t)par * a.R + a.rank) * a.L.recv_stride;
-            st_relaxed_sys_u64(recv + le, tagged((uint32_t)c, epoch));
+            if (!local_only) {
+                uint64_t* recv = reinterpret_cast<uint64_t*>(peer_unk + a.L.expert_recv_counts_off) +
+                                 ((size_t)par * a.R + a.rank) * a.L.recv_stride;
+                st_relaxed_sys_u64(recv + le, tagged((uint32_t)c, epoch));
+            }
         }
     }
     // The launch bookkeeping below belongs to the LAST CTA: CTA 0 goes straight on to poll the
@@ -128,7 +156,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     __syncthreads();
     // Row checksum word ~(sum + 1) at index EPR of each row sent (src/prologue.cuh:248-255), kept
     // for layout parity with the reference; nothing here waits on it.
-    for (int d = tid; d < a.R; d += nthr) {
+    for (int d = tid; d < a.R && !local_only; d += nthr) {
         uint32_t csum = 0;
         for (int le = 0; le < a.EPR; ++le) csum += (uint32_t)ld_relaxed_gpu(rsc + d * a.EPR + le);
         uint64_t* recv = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) +
@@ -138,12 +166,149 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     }
     if (tid == 0) {
         f->route_blocks_done = 0;
-        f->current_time = epoch;  // every CTA has read the old value before arriving above
+        f->clear_blocks_done = 0;  // every CTA is past the clear barrier, if there was one
+        // a rank without tokens receives no rows and runs no reduce: its (all-zero) table stays clean
+        if (a.tokens == 0) f->cnt_clean_epoch = (uint32_t)epoch;
+        f->current_time = epoch;   // every CTA has read the old value before arriving above
     }
     __syncthreads();
 }
 
-// CTA 0 builds the tables; `s_i` is scratch shared memory of 4*EPR + 2 + EPR*R ints.
+// From the per-(local expert, source rank) counts s_cnt[EPR][R] of this launch: the prefix table
+// (written to `prefix`, [EPR][R+1], shared or global memory), rows per expert, the experts ranked
+// by descending row count (ties by index: the hottest experts' windows are claimed first so the
+// dynamic queue ends on the cheap ones — LPT order), the first window of every sorted position and
+// the first pool row of every expert (reference: task_setup_body, src/prologue.cuh:423-452).
+// Called by all threads of a CTA; the results are valid after it returns.
+__device__ void build_tables(const KArgs& a, const int* s_cnt, int* prefix, int* s_tot /*[EPR]*/,
+                             int* s_order /*[EPR]*/, int* s_first /*[EPR+1]*/, int* s_base /*[EPR+1]*/) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int EPR = a.EPR, R = a.R;
+    for (int le = tid; le < EPR; le += nthr) {
+        int c = 0;
+        for (int r = 0; r < R; ++r) {
+            prefix[le * (R + 1) + r] = c;
+            c += s_cnt[le * R + r];
+        }
+        prefix[le * (R + 1) + R] = c;
+        s_tot[le] = c;
+    }
+    __syncthreads();
+    for (int le = tid; le < EPR; le += nthr) {
+        const int c = s_tot[le];
+        int rk = 0;
+        for (int j = 0; j < EPR; ++j) {
+            const int cj = s_tot[j];
+            rk += (cj > c || (cj == c && j < le)) ? 1 : 0;
+        }
+        s_order[rk] = le;
+    }
+    __syncthreads();
+    if (tid < 32) {
+        // exclusive scans by warp 0: pool rows in expert-index order, windows in sorted order
+        const int lane = tid;
+        int carry_rows = 0, carry_win = 0;
+        for (int b = 0; b < EPR; b += 32) {
+            const int i = b + lane;
+            const int c = i < EPR ? s_tot[i] : 0;
+            const int cs = i < EPR ? s_tot[s_order[i]] : 0;
+            const int w = cs > 0 ? (cs + a.win_cap - 1) / a.win_cap : 0;
+            int ic = c, iw = w;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int uc = __shfl_up_sync(0xFFFFFFFFu, ic, d), uw = __shfl_up_sync(0xFFFFFFFFu, iw, d);
+                if (lane >= d) { ic += uc; iw += uw; }
+            }
+            if (i < EPR) { s_base[i] = carry_rows + ic - c; s_first[i] = carry_win + iw - w; }
+            carry_rows += __shfl_sync(0xFFFFFFFFu, ic, 31);
+            carry_win += __shfl_sync(0xFFFFFFFFu, iw, 31);
+        }
+        if (lane == 0) { s_base[EPR] = carry_rows; s_first[EPR] = carry_win; }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ bool tables_overflow(const KArgs& a, int n_windows, int total_rows) {
+    const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
+    return n_windows > a.L.max_windows || (long long)n_windows * (nt1 + nt2) > a.L.max_tasks || total_rows > a.L.pool_rows;
+}
+
+// CTA 0 writes the tables of this launch to global memory (row bases, windows, the task list — L1
+// tasks then L2 tasks, each (expert, n-tile, window) with windows fastest so that concurrent CTAs
+// share a weight tile in L2), clears the gate counters, and publishes the set-up flag.
+__device__ void publish_tables(const KArgs& a, DevFlags* f, long long epoch, const int* s_tot, const int* s_order,
+                               const int* s_first, const int* s_base) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int EPR = a.EPR;
+    const int par = (int)(epoch & 1);
+    const bool ts = a.ticks != 0 && tid == 0;
+    int* row_base = reinterpret_cast<int*>(a.rwk + a.L.expert_row_base_off);
+    int* first_win = reinterpret_cast<int*>(a.rwk + a.L.expert_first_win_off);
+    for (int le = tid; le <= EPR; le += nthr) row_base[le] = s_base[le];
+    for (int p = tid; p < EPR; p += nthr) first_win[s_order[p]] = s_first[p];
+
+    int n_windows = s_first[EPR];
+    const int total_rows = s_base[EPR];
+    const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
+    const bool overflow = tables_overflow(a, n_windows, total_rows);
+    if (overflow) n_windows = 0;
+    int4* windows = reinterpret_cast<int4*>(a.rwk + a.L.windows_off);
+    int4* tasks = reinterpret_cast<int4*>(a.rwk + a.L.tasks_off);
+    uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
+    uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off);
+    // The gate counters exist once per launch parity.  This launch's copy was cleared while the
+    // previous launch ran (push mode counts rows into it without waiting for this CTA); the other
+    // copy, last used by the previous launch, is cleared here for the next one.
+    {
+        const int prev_windows = min(max(ld_relaxed_gpu(&f->n_windows), 0), a.L.max_windows);
+        uint32_t* l1_o = l1_done + (size_t)(par ^ 1) * a.L.max_windows;
+        uint32_t* pr_o = pool_ready + (size_t)(par ^ 1) * a.L.max_windows;
+        for (int i = tid; i < prev_windows; i += nthr) { l1_o[i] = 0; pr_o[i] = 0; }
+    }
+    __syncthreads();   // n_windows of the previous launch was read by every thread above
+    l1_done += (size_t)par * a.L.max_windows;
+    pool_ready += (size_t)par * a.L.max_windows;
+    const int n_l1 = n_windows * nt1;
+    if (!overflow) {
+        // one warp per expert (sorted position p), lanes over its windows and tasks
+        const int lane = tid & 31, wid = tid >> 5, nwarps = nthr >> 5;
+        for (int p = wid; p < EPR; p += nwarps) {
+            const int e = s_order[p], c = s_tot[e];
+            const int fw = s_first[p], nw = s_first[p + 1] - fw;
+            if (nw == 0) break;  // sorted: every later expert is empty too
+            for (int w = lane; w < nw; w += 32) {
+                const int rows = min(a.win_cap, c - w * a.win_cap);
+                windows[fw + w] = make_int4(e, s_base[e] + w * a.win_cap, rows, 0);
+                if (!a.push) { l1_done[fw + w] = 0; pool_ready[fw + w] = 0; }
+            }
+            for (int i = lane; i < nt1 * nw; i += 32) {
+                const int nt = i / nw, w = i % nw;
+                tasks[fw * nt1 + i] = make_int4(0, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
+            }
+            for (int i = lane; i < nt2 * nw; i += 32) {
+                const int nt = i / nw, w = i % nw;
+                tasks[n_l1 + fw * nt2 + i] = make_int4(1, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
+            }
+        }
+    }
+    if (ts) f->dbg_ts[4] = gtimer_ns();
+    if (tid == 0) {
+        if (overflow) raise_status(f, MXK_DEV_BAD_TABLE, 3);
+        f->n_windows = n_windows;
+        f->n_l1_tasks = n_l1;
+        f->n_tasks = n_windows * (nt1 + nt2);
+        f->total_rows = overflow ? 0 : total_rows;
+        f->task_ctr[par ^ 1] = 0;   // the next launch's claim counter
+    }
+    __threadfence();
+    __syncthreads();
+    if (ts) f->dbg_ts[5] = gtimer_ns();
+    if (tid == 0) st_release_gpu(&f->setup_epoch, (uint32_t)epoch);
+    if (ts) f->dbg_ts[6] = gtimer_ns();
+}
+
+// Pull mode, CTA 0: wait for every source rank's counts (this IS the cross-rank barrier), build
+// and publish the tables; `s_i` is scratch shared memory of 4*EPR + 2 + EPR*R ints.
 __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch, int* s_i) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int EPR = a.EPR, R = a.R;
@@ -169,111 +334,9 @@ __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch,
     __syncthreads();
     const bool ts = a.ticks != 0 && tid == 0;
     if (ts) f->dbg_ts[0] = gtimer_ns();
-
-    int* prefix = reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off);
-    for (int le = tid; le < EPR; le += nthr) {
-        int c = 0;
-        for (int r = 0; r < R; ++r) {
-            prefix[le * (R + 1) + r] = c;
-            c += s_cnt[le * R + r];
-        }
-        prefix[le * (R + 1) + R] = c;
-        s_tot[le] = c;
-    }
-    __syncthreads();
-    if (ts) f->dbg_ts[1] = gtimer_ns();
-    // Experts by descending row count, ties by index: the hottest experts' windows
-    // are claimed first so the dynamic queue ends on the cheap ones (LPT order).
-    for (int le = tid; le < EPR; le += nthr) {
-        const int c = s_tot[le];
-        int rk = 0;
-        for (int j = 0; j < EPR; ++j) {
-            const int cj = s_tot[j];
-            rk += (cj > c || (cj == c && j < le)) ? 1 : 0;
-        }
-        s_order[rk] = le;
-    }
-    __syncthreads();
-    if (ts) f->dbg_ts[2] = gtimer_ns();
-    if (tid < 32) {
-        // exclusive scans by warp 0: pool rows in expert-index order, windows in sorted order
-        const int lane = tid;
-        int carry_rows = 0, carry_win = 0;
-        for (int b = 0; b < EPR; b += 32) {
-            const int i = b + lane;
-            const int c = i < EPR ? s_tot[i] : 0;
-            const int cs = i < EPR ? s_tot[s_order[i]] : 0;
-            const int w = cs > 0 ? (cs + a.win_cap - 1) / a.win_cap : 0;
-            int ic = c, iw = w;
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const int uc = __shfl_up_sync(0xFFFFFFFFu, ic, d), uw = __shfl_up_sync(0xFFFFFFFFu, iw, d);
-                if (lane >= d) { ic += uc; iw += uw; }
-            }
-            if (i < EPR) { s_base[i] = carry_rows + ic - c; s_first[i] = carry_win + iw - w; }
-            carry_rows += __shfl_sync(0xFFFFFFFFu, ic, 31);
-            carry_win += __shfl_sync(0xFFFFFFFFu, iw, 31);
-        }
-        if (lane == 0) { s_base[EPR] = carry_rows; s_first[EPR] = carry_win; }
-    }
-    __syncthreads();
+    build_tables(a, s_cnt, reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off), s_tot, s_order, s_first, s_base);
     if (ts) f->dbg_ts[3] = gtimer_ns();
-    int* row_base = reinterpret_cast<int*>(a.rwk + a.L.expert_row_base_off);
-    int* first_win = reinterpret_cast<int*>(a.rwk + a.L.expert_first_win_off);
-    for (int le = tid; le <= EPR; le += nthr) row_base[le] = s_base[le];
-    for (int p = tid; p < EPR; p += nthr) first_win[s_order[p]] = s_first[p];
-
-    int n_windows = s_first[EPR];
-    const int total_rows = s_base[EPR];
-    const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
-    bool overflow = false;
-    if (n_windows > a.L.max_windows || (long long)n_windows * (nt1 + nt2) > a.L.max_tasks ||
-        total_rows > a.L.pool_rows) {
-        overflow = true;
-        n_windows = 0;
-    }
-    int4* windows = reinterpret_cast<int4*>(a.rwk + a.L.windows_off);
-    int4* tasks = reinterpret_cast<int4*>(a.rwk + a.L.tasks_off);
-    uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off);
-    uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off);
-    const int n_l1 = n_windows * nt1;
-    if (!overflow) {
-        // one warp per expert (sorted position p), lanes over its windows and tasks
-        const int lane = tid & 31, wid = tid >> 5, nwarps = nthr >> 5;
-        for (int p = wid; p < EPR; p += nwarps) {
-            const int e = s_order[p], c = s_tot[e];
-            const int fw = s_first[p], nw = s_first[p + 1] - fw;
-            if (nw == 0) break;  // sorted: every later expert is empty too
-            for (int w = lane; w < nw; w += 32) {
-                const int rows = min(a.win_cap, c - w * a.win_cap);
-                windows[fw + w] = make_int4(e, s_base[e] + w * a.win_cap, rows, 0);
-                l1_done[fw + w] = 0;
-                pool_ready[fw + w] = 0;
-            }
-            for (int i = lane; i < nt1 * nw; i += 32) {
-                const int nt = i / nw, w = i % nw;
-                tasks[fw * nt1 + i] = make_int4(0, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
-            }
-            for (int i = lane; i < nt2 * nw; i += 32) {
-                const int nt = i / nw, w = i % nw;
-                tasks[n_l1 + fw * nt2 + i] = make_int4(1, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
-            }
-        }
-    }
-    if (ts) f->dbg_ts[4] = gtimer_ns();
-    if (tid == 0) {
-        if (overflow) raise_status(f, MXK_DEV_BAD_TABLE, 3);
-        f->n_windows = n_windows;
-        f->n_l1_tasks = n_l1;
-        f->n_tasks = n_windows * (nt1 + nt2);
-        f->total_rows = overflow ? 0 : total_rows;
-        f->task_counter = a.pair ? gridDim.x >> 1 : gridDim.x;  // first task of a CTA (pair) is its index
-    }
-    __threadfence();
-    __syncthreads();
-    if (ts) f->dbg_ts[5] = gtimer_ns();
-    if (tid == 0) st_release_gpu(&f->setup_epoch, (uint32_t)epoch);
-    if (ts) f->dbg_ts[6] = gtimer_ns();
+    publish_tables(a, f, epoch, s_tot, s_order, s_first, s_base);
 }
 
 // Every other CTA waits until CTA 0 has published the tables of this epoch.
@@ -309,7 +372,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
     uint8_t* pool = a.rwk + a.L.pool_off;
     uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
     int4* meta = reinterpret_cast<int4*>(a.rwk + a.L.row_meta_off);
-    uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off);
+    uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off) + (size_t)par * a.L.max_windows;
     const int kb = H / 128;
     if (blockIdx.x * nwarps_cta >= total) return;  // no row for this CTA (uniform per CTA)
 
@@ -353,7 +416,11 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
                 tw = 0;
             }
         }
-        const uint32_t idx = (uint32_t)tw;
+        uint32_t idx = (uint32_t)tw;
+        if (idx >= (uint32_t)(a.cap * a.topk)) {   // not a pair index of this geometry: never form an address from it
+            if (lane == 0) raise_status(f, MXK_DEV_BAD_TABLE, 3);
+            idx = 0;
+        }
         const int token = (int)(idx / (uint32_t)a.topk), k = (int)(idx % (uint32_t)a.topk);
         const uint8_t* peer = a.peer_bases[src];
         const uint4* srow = reinterpret_cast<const uint4*>(peer + a.x_off + (size_t)token * H);
@@ -397,13 +464,322 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
     }
 }
 
+// ============================================================ push-mode prologue
+// Staging area `xin` in unk, per launch parity and source rank: 16 header words (word 0 = token
+// count of the source in this launch) followed by one row per token:
+//   [topk routing words][topk weight words][sfw scale words][H/4 row words]
+// Every word is {payload u32, epoch u32}, stored with 8-byte (or 2 x 8-byte) stores: the reader
+// polls the word itself until the tag is this launch's epoch, so the data needs neither a fence
+// nor a flag.  Routing and weight words go to every rank, scale and row words only to the ranks
+// that own one of the token's experts.  Two parities are enough for the same reason as in the
+// pull-mode tables: no rank can finish launch N+1 before every rank has pushed for N+1.
+constexpr int kPushMaxEPR = 256;       // local experts whose tables fit the control block
+constexpr int kPushMaxR = 64;
+constexpr int kPushMaxPairs = 16384;   // routing words of the whole world kept in shared memory per CTA
+constexpr int kPushMaxCnt = 4096;      // EPR * (R + 1)
+
+struct PushTabs {   // tables of this launch, in the control block of shared memory for the whole kernel
+    int n_tasks, n_l1, n_windows, total_rows;
+    int tot[kPushMaxEPR];         // rows of local expert le
+    int order[kPushMaxEPR];       // expert at sorted position p (descending rows)
+    int first[kPushMaxEPR + 1];   // first window of sorted position p
+    int base[kPushMaxEPR + 1];    // first pool row of local expert le
+};
+
+struct PushScratch {   // carved from the operand-tile region, which is idle until the GEMM phase
+    int* wid;      // [kPushMaxPairs] routing word of world pair i (expert id or -1), sources in rank order
+    int* cnt;      // [EPR][R]
+    int* prefix;   // [EPR][R+1]
+    int* fw_e;     // [EPR] first window of local expert le
+    int* tok;      // [R] tokens of source r in this launch
+    int* sb;       // [R+1] first world pair of source r
+    int* flag;     // [1] every source arrived in time
+};
+__device__ __forceinline__ PushScratch push_scratch(uint8_t* tiles) {
+    PushScratch sc;
+    sc.wid = reinterpret_cast<int*>(tiles);
+    sc.cnt = sc.wid + kPushMaxPairs;
+    sc.prefix = sc.cnt + kPushMaxCnt;
+    sc.fw_e = sc.prefix + kPushMaxCnt + kPushMaxEPR;
+    sc.tok = sc.fw_e + kPushMaxEPR;
+    sc.sb = sc.tok + kPushMaxR;
+    sc.flag = sc.sb + kPushMaxR + 1;
+    return sc;
+}
+__device__ __forceinline__ int xin_sf_words(int H) { return (((H / 128) + 3) / 4 + 1) & ~1; }   // even: rows stay 16-byte aligned
+__device__ __forceinline__ uint64_t* xin_block(const KArgs& a, void* unk_base, int par, int src) {
+    return reinterpret_cast<uint64_t*>(static_cast<uint8_t*>(unk_base) + a.L.xin_off) +
+           ((size_t)par * a.R + src) * (size_t)a.L.xin_src_words;
+}
+// largest r with sb[r] <= i (sources without tokens share their successor's start)
+__device__ __forceinline__ int push_src_of(const int* sb, int R, int i) {
+    int lo = 0, hi = R;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (sb[mid] <= i) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// Source side: store this rank's tokens into the owners' staging areas.  Work unit = (token,
+// destination rank), spread over the grid.  `s_ids` is scratch for tokens*topk ints.
+__device__ void push_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_ids) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int par = (int)(epoch & 1), R = a.R, topk = a.topk, H = a.H, EPR = a.EPR;
+    const int np = a.tokens * topk;
+    if (blockIdx.x == 0 && tid < R)   // header: how many rows the destination has to expect from this rank
+        st_relaxed_sys_u64(xin_block(a, a.unk_peers[tid], par, a.rank), tagged((uint32_t)a.tokens, epoch));
+    for (int p = tid; p < np; p += nthr) {   // invalid ids (negative / >= E) travel as -1 (src/prologue.cuh:166-167)
+        const int64_t v = a.topk_idx[p];
+        s_ids[p] = (uint64_t)v < (uint64_t)a.E ? (int)v : -1;
+    }
+    __syncthreads();
+    const int sfw = xin_sf_words(H), kb = H / 128, row_words = a.L.xin_row_words;
+    const uint32_t* wts = reinterpret_cast<const uint32_t*>(a.self + a.weights_off);
+    const uint8_t* xsf = a.self + a.x_sf_off;
+    for (int u = blockIdx.x; u < a.tokens * R; u += gridDim.x) {
+        const int t = u / R, d = (u + t) % R;
+        bool routed = false;
+        for (int k = 0; k < topk; ++k) {
+            const int e = s_ids[t * topk + k];
+            routed |= e >= 0 && e / EPR == d;
+        }
+        uint64_t* row = xin_block(a, a.unk_peers[d], par, a.rank) + 16 + (size_t)t * row_words;
+        if (tid < topk) st_relaxed_sys_u64(row + tid, tagged((uint32_t)s_ids[t * topk + tid], epoch));
+        else if (tid < 2 * topk) st_relaxed_sys_u64(row + tid, tagged(wts[(size_t)t * topk + tid - topk], epoch));
+        if (!routed) continue;
+        if (a.scaled && tid >= 128 && tid < 128 + sfw) {   // four scale bytes per word, 127 (x1.0) beyond H/128
+            const int i = tid - 128;
+            uint32_t w = 0;
+            for (int j = 0; j < 4; ++j) {
+                const int b = 4 * i + j;
+                w |= (uint32_t)(b < kb ? xsf[(size_t)t * kb + b] : (uint8_t)127) << (8 * j);
+            }
+            st_relaxed_sys_u64(row + 2 * topk + i, tagged(w, epoch));
+        }
+        const uint2* xs = reinterpret_cast<const uint2*>(a.self + a.x_off + (size_t)t * H);
+        uint64_t* xd = row + 2 * topk + sfw;
+        for (int i = tid; i < H / 8; i += nthr) {
+            const uint2 v = xs[i];
+            st_relaxed_sys_v2_u64(xd + 2 * i, tagged(v.x, epoch), tagged(v.y, epoch));
+        }
+    }
+}
+
+// Owner side, EVERY CTA: wait for all sources' routing words of this launch (this is the
+// cross-rank barrier), count the pairs per (local expert, source) and build the tables in shared
+// memory.  With `publish`, CTA 0 also writes them to global memory in the pull-mode formats
+// (prefix table, received counts + checksum word, row bases, windows, tasks, status header).
+// Returns false when a source did not arrive in time or the tables overflow the buffers.
+__device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const PushScratch& sc, PushTabs* T,
+                            const bool publish) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int par = (int)(epoch & 1), R = a.R, topk = a.topk, EPR = a.EPR;
+    const uint32_t ep = (uint32_t)epoch;
+    const uint64_t* mine = xin_block(a, a.unk, par, 0);
+    const size_t src_words = (size_t)a.L.xin_src_words;
+    const int row_words = a.L.xin_row_words;
+    if (tid == 0) *sc.flag = 1;
+    for (int i = tid; i < EPR * R; i += nthr) sc.cnt[i] = 0;
+    __syncthreads();
+    for (int r = tid; r < R; r += nthr) {
+        const uint64_t* hp = mine + r * src_words;
+        uint64_t w = 0;
+        if (!spin_until([&] { w = ld_relaxed_sys_u64(hp); return (uint32_t)(w >> 32) == ep; }, a.remote_wait_ns, nullptr)) {
+            if (blockIdx.x == 0) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 0);
+            *sc.flag = 0;
+            w = 0;
+        }
+        sc.tok[r] = min((int)(uint32_t)w, a.cap);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int c = 0;
+        for (int r = 0; r < R; ++r) { sc.sb[r] = c; c += sc.tok[r] * topk; }
+        sc.sb[R] = c;
+    }
+    __syncthreads();
+    const int W = sc.sb[R];   // <= R * cap * topk <= kPushMaxPairs
+    for (int i0 = tid; i0 < W; i0 += nthr * 4) {   // four polls in flight per thread
+        const uint64_t* ptr[4];
+        uint64_t w[4];
+        int src[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = i0 + j * nthr;
+            if (i < W) {
+                src[j] = push_src_of(sc.sb, R, i);
+                const int q = i - sc.sb[src[j]];
+                ptr[j] = mine + src[j] * src_words + 16 + (size_t)(q / topk) * row_words + q % topk;
+                w[j] = ld_relaxed_sys_u64(ptr[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = i0 + j * nthr;
+            if (i >= W) continue;
+            uint64_t t = w[j];
+            const uint64_t* tp = ptr[j];
+            if ((uint32_t)(t >> 32) != ep &&
+                !spin_until([&] { t = ld_relaxed_sys_u64(tp); return (uint32_t)(t >> 32) == ep; }, a.remote_wait_ns, nullptr)) {
+                if (blockIdx.x == 0) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 0);
+                *sc.flag = 0;
+                t = 0xFFFFFFFFull;
+            }
+            const int e = (int)(uint32_t)t;
+            sc.wid[i] = e;
+            if (e >= 0 && e / EPR == a.rank) atomicAdd(&sc.cnt[(e % EPR) * R + src[j]], 1);
+        }
+    }
+    __syncthreads();
+    const bool ts = a.ticks != 0 && tid == 0 && blockIdx.x == 0;
+    if (ts) f->dbg_ts[0] = gtimer_ns();
+    // pairs beyond the slot capacity of a (source, expert) row are dropped (src/prologue.cuh:171-174)
+    for (int i = tid; i < EPR * R; i += nthr) sc.cnt[i] = min(sc.cnt[i], a.slot_cap);
+    __syncthreads();
+    build_tables(a, sc.cnt, sc.prefix, T->tot, T->order, T->first, T->base);
+    if (ts) f->dbg_ts[3] = gtimer_ns();
+    const int n_windows = T->first[EPR], total_rows = T->base[EPR];
+    const bool overflow = tables_overflow(a, n_windows, total_rows);
+    if (tid == 0) {
+        const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
+        T->n_windows = overflow ? 0 : n_windows;
+        T->n_l1 = overflow ? 0 : n_windows * nt1;
+        T->n_tasks = overflow ? 0 : n_windows * (nt1 + nt2);
+        T->total_rows = overflow ? 0 : total_rows;
+    }
+    for (int p = tid; p < EPR; p += nthr) sc.fw_e[T->order[p]] = T->first[p];
+    if (publish && blockIdx.x == 0) {
+        int* g_prefix = reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off);
+        for (int i = tid; i < EPR * (R + 1); i += nthr) g_prefix[i] = sc.prefix[i];
+        uint64_t* recv = reinterpret_cast<uint64_t*>(a.unk + a.L.expert_recv_counts_off) + (size_t)par * R * a.L.recv_stride;
+        for (int i = tid; i < EPR * R; i += nthr) {
+            const int le = i / R, r = i % R;
+            recv[(size_t)r * a.L.recv_stride + le] = tagged((uint32_t)sc.cnt[i], epoch);
+        }
+        for (int r = tid; r < R; r += nthr) {   // the reference's checksum word of a count row (src/prologue.cuh:248-255)
+            uint32_t csum = 0;
+            for (int le = 0; le < EPR; ++le) csum += (uint32_t)sc.cnt[le * R + r];
+            recv[(size_t)r * a.L.recv_stride + EPR] = tagged(~(csum + 1u), epoch);
+        }
+        publish_tables(a, f, epoch, T->tot, T->order, T->first, T->base);
+    }
+    __syncthreads();
+    return *sc.flag != 0 && !overflow;
+}
+
+// Owner side: one WARP per world pair whose expert lives here.  Its slot inside the (expert,
+// source) row is the number of earlier pairs of the same source with the same expert — the
+// ascending-pair-index order of the pull-mode route — which fixes the pool row; the warp then
+// copies the row's words from the staging area into the pool (tags stripped), the scale bytes and
+// the staged (source, token, k, weight), and counts the row into its window's pool_ready.
+// `do_tables`: also write the pair index into src_index_table (same words a pull-mode source writes).
+__device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, const PushScratch& sc, const PushTabs* T,
+                              const bool do_tables, const bool do_rows) {
+    const int lane = threadIdx.x & 31;
+    const int nwarps_cta = blockDim.x >> 5;
+    const int gwarp = blockIdx.x * nwarps_cta + (threadIdx.x >> 5);
+    const int nwarps = gridDim.x * nwarps_cta;
+    const int par = (int)(epoch & 1), R = a.R, topk = a.topk, EPR = a.EPR, H = a.H;
+    const uint32_t ep = (uint32_t)epoch;
+    const int W = sc.sb[R];
+    const uint64_t* mine = xin_block(a, a.unk, par, 0);
+    const size_t src_words = (size_t)a.L.xin_src_words;
+    const int row_words = a.L.xin_row_words, sfw = xin_sf_words(H), sfw_real = (H / 128 + 3) / 4;
+    uint64_t* tbl = reinterpret_cast<uint64_t*>(a.unk + a.L.src_index_table_off) + (size_t)par * EPR * R * a.slot_cap;
+    uint8_t* pool = a.rwk + a.L.pool_off;
+    uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
+    int4* meta = reinterpret_cast<int4*>(a.rwk + a.L.row_meta_off);
+    uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off) + (size_t)par * a.L.max_windows;
+    for (int i = gwarp; i < W; i += nwarps) {
+        const int e = sc.wid[i];
+        if (e < 0 || e / EPR != a.rank) continue;   // uniform over the warp
+        const int src = push_src_of(sc.sb, R, i);
+        const int p = i - sc.sb[src], le = e % EPR;
+        int c = 0;
+        for (int j = lane; j < p; j += 32) c += sc.wid[sc.sb[src] + j] == e ? 1 : 0;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, d);
+        const int slot = c;
+        if (slot >= a.slot_cap) continue;           // over capacity: dropped
+        const int gl = sc.prefix[le * (R + 1) + src] + slot;
+        const int g = T->base[le] + gl;
+        if (do_tables && lane == 0) tbl[((size_t)le * R + src) * a.slot_cap + slot] = tagged((uint32_t)p, epoch);
+        if (!do_rows) continue;
+        const int token = p / topk, k = p % topk;
+        const uint64_t* row = mine + src * src_words + 16 + (size_t)token * row_words;
+        bool ok = true;
+        auto poll = [&](const uint64_t* wp) -> uint32_t {
+            uint64_t w = ld_relaxed_sys_u64(wp);
+            if ((uint32_t)(w >> 32) != ep &&
+                !spin_until([&] { w = ld_relaxed_sys_u64(wp); return (uint32_t)(w >> 32) == ep; }, a.remote_wait_ns, nullptr))
+                ok = false;
+            return (uint32_t)w;
+        };
+        uint32_t wbits = 0;
+        if (lane == 0) wbits = poll(row + topk + k);
+        if (a.scaled) {
+            uint32_t* dsf = reinterpret_cast<uint32_t*>(pool_sf + (size_t)g * a.L.sf_stride_h);
+            for (int j = lane; j < a.L.sf_stride_h / 4; j += 32)
+                dsf[j] = j < sfw_real ? poll(row + 2 * topk + j) : 0x7F7F7F7Fu;
+        }
+        // row words, two per 16-byte load, eight loads in flight per lane
+        const uint64_t* xs = row + 2 * topk + sfw;
+        uint2* drow = reinterpret_cast<uint2*>(pool + (size_t)g * H);
+        const int n16 = H / 8;
+        for (int u0 = lane; u0 < n16; u0 += 32 * 8) {
+            ulonglong2 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (u0 + 32 * j < n16) v[j] = ld_relaxed_sys_v2_u64(xs + 2 * (u0 + 32 * j));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int u = u0 + 32 * j;
+                if (u >= n16) continue;
+                ulonglong2 t = v[j];
+                if (((uint32_t)(t.x >> 32) != ep || (uint32_t)(t.y >> 32) != ep) &&
+                    !spin_until([&] { t = ld_relaxed_sys_v2_u64(xs + 2 * u);
+                                      return (uint32_t)(t.x >> 32) == ep && (uint32_t)(t.y >> 32) == ep; },
+                                a.remote_wait_ns, nullptr))
+                    ok = false;
+                drow[u] = make_uint2((uint32_t)t.x, (uint32_t)t.y);
+            }
+        }
+        if (!__all_sync(0xFFFFFFFFu, ok ? 1 : 0) && lane == 0) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 2);
+        if (lane == 0) meta[g] = make_int4(src, token, k, (int)wbits);
+        // the row is complete: every lane makes its stores visible at GPU scope and to TMA, then count it
+        __threadfence();
+        fence_proxy_async_global();
+        __syncwarp();
+        if (lane == 0) red_release_gpu_add(pool_ready + sc.fw_e[le] + gl / a.win_cap, 1u);
+    }
+}
+
 // y[t] = sum over k (ascending, FP32, product then sum) of w_k * bf16 row_k
 // (reference: src/combine.cuh:601-627, src/bench_check.cuh:484-499).
-__device__ void reduce_phase(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, float* s_w /*[64]*/) {
+//
+// Every arrival count a token has waited for is zeroed once it is complete (all `need` adds of this
+// launch have landed by then, and peers push again only after this rank's next launch has
+// published its routing); the last CTA to finish records the launch in cnt_clean_epoch, which lets
+// the next launch skip the clear of the table (ensure_counts_clean).
+__device__ void reduce_tokens(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, float* s_w /*[64]*/);
+__device__ void reduce_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_ok, float* s_w) {
+    reduce_tokens(a, f, s_ok, s_w);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();   // this CTA's zeroed counts before its arrival
+        if (atomicAdd(&f->reduce_blocks_done, 1u) == gridDim.x - 1) {
+            f->reduce_blocks_done = 0;
+            __threadfence();
+            if (ld_relaxed_gpu(&f->status) == 0) f->cnt_clean_epoch = (uint32_t)epoch;
+        }
+    }
+}
+__device__ void reduce_tokens(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, float* s_w /*[64]*/) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int H = a.H, topk = a.topk;
     const uint8_t* pair_state = a.rwk + a.L.pair_state_off;
-    const uint32_t* cnt = reinterpret_cast<const uint32_t*>(a.unk + a.L.combine_cnt_off);
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(a.unk + a.L.combine_cnt_off);
     const uint16_t* rows = reinterpret_cast<const uint16_t*>(a.unk + a.L.combine_rows_off);
     const float* tw = reinterpret_cast<const float*>(a.self + a.weights_off);
     const uint32_t need = (uint32_t)(H / kBlockN) * 2u;
@@ -418,10 +794,12 @@ __device__ void reduce_phase(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, fl
             if (lane < topk) {
                 ok = ld_relaxed_gpu_u8(pair_state + t * topk + lane);
                 if (ok && !a.skip_combine) {
-                    const uint32_t* c = cnt + (size_t)lane * a.cap + t;
+                    uint32_t* c = cnt + (size_t)lane * a.cap + t;
                     if (!spin_until([&] { return ld_relaxed_sys(c) >= need; }, a.remote_wait_ns, nullptr)) {
                         raise_status(f, MXK_DEV_TIMEOUT_REDUCE, 4);
                         ok = 0;
+                    } else {
+                        *c = 0;
                     }
                     fence_world(a.R > 1);  // acquire: the counted row segments are visible
                 }
@@ -488,10 +866,12 @@ __device__ void reduce_phase(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, fl
         if (tid < topk) {
             int ok = ld_relaxed_gpu_u8(pair_state + t * topk + tid);
             if (ok && !a.skip_combine) {
-                const uint32_t* c = cnt + (size_t)tid * a.cap + t;
+                uint32_t* c = cnt + (size_t)tid * a.cap + t;
                 if (!spin_until([&] { return ld_relaxed_sys(c) >= need; }, a.remote_wait_ns, nullptr)) {
                     raise_status(f, MXK_DEV_TIMEOUT_REDUCE, 4);
                     ok = 0;
+                } else {
+                    *c = 0;
                 }
                 fence_world(a.R > 1);  // acquire: the counted row segments are visible
             }

@@ -80,7 +80,7 @@ class SymmBuffer:
     def __init__(self, group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int, hidden: int,
                  intermediate_hidden: int, num_shared_experts: int = 0, mma_type: str = "fp8xfp8",
                  activation: str = "swiglu", grid_num_tokens: Optional[int] = None,
-                 expert_window: Optional[int] = None, slot_capacity: int = 0,
+                 expert_window: Optional[int] = None, slot_capacity: int = 0, dispatch_mode: int = 0,
                  _local_world: Optional[Tuple[int, int]] = None):
         if activation != "swiglu":
             raise ValueError(f"Only `swiglu` activation is supported, got `{activation}`")
@@ -111,6 +111,7 @@ class SymmBuffer:
         self.mma_type, self.activation = mma_type, activation
         self.expert_window = int(expert_window)
         self.slot_capacity = int(slot_capacity)
+        self.dispatch_mode = int(dispatch_mode)
         self.launch_count = 0
         self.device = torch.cuda.current_device()
         self.layout = compute_layout(world_size, rank, self.num_experts_per_rank, self.num_topk, self.hidden,
@@ -205,7 +206,6 @@ class SymmBuffer:
             "expert_recv_counts_raw": (self.unk, torch.int32, (2, R, L.recv_stride, 2), L.expert_recv_counts_off),
             "combine_rows": (self.unk, torch.int16, (topk, cap, H), L.combine_rows_off),
             "combine_cnt": (self.unk, torch.int32, (topk, cap), L.combine_cnt_off),
-            "xbar": (self.unk, torch.int32, (R, L.xbar_stride), L.xbar_off),
         }
         if name in ("src_index_table", "expert_recv_counts"):      # payload words only
             return self.table(name + "_raw")[..., 0]
@@ -213,6 +213,21 @@ class SymmBuffer:
             return self.table(name[:-5] + "_raw")[..., 1]
         spec = spec[name]
         return _view(spec[0], spec[1], spec[2], int(spec[3]))
+
+    def packed_layout(self, num_tokens: int):
+        """Offsets of a PACKED input image for `num_tokens` tokens: x, x_sf, topk_idx and
+        topk_weights back to back (each region 256-byte aligned) from the start of the symmetric
+        block, so that a host can bring a step's inputs over with ONE copy instead of four.
+        Returns (x_off, x_sf_off, topk_idx_off, topk_weights_off, total_bytes).  Peers that pull
+        rows address them with their own launch's offsets: either every rank packs for the same
+        token count, or the buffer runs the push-mode prologue (which never reads a peer's block)."""
+        T, H, topk = int(num_tokens), self.hidden, self.num_topk
+        a256 = lambda v: (v + 255) // 256 * 256   # noqa: E731
+        x_off = 0
+        x_sf_off = a256(x_off + T * H)
+        idx_off = a256(x_sf_off + T * (H // 128))
+        w_off = a256(idx_off + T * topk * 8)
+        return x_off, x_sf_off, idx_off, w_off, w_off + T * topk * 4
 
     def status(self) -> MxkStatus:
         st = MxkStatus()
@@ -222,7 +237,8 @@ class SymmBuffer:
     def launch_args(self, num_tokens: int, l1=None, l2=None, y_bf16: Optional[torch.Tensor] = None,
                     y_f32: Optional[torch.Tensor] = None, expert_window: Optional[int] = None,
                     max_spins: int = 0, grid: int = 0, skip_combine: int = 0,
-                    cta_pair: Optional[int] = None) -> MxkLaunchArgs:
+                    cta_pair: Optional[int] = None, dispatch_mode: Optional[int] = None,
+                    packed: bool = False) -> MxkLaunchArgs:
         L = self.layout
         a = MxkLaunchArgs()
         a.R, a.rank, a.tokens = self.world_size, self.rank, int(num_tokens)
@@ -234,6 +250,8 @@ class SymmBuffer:
         a.topk_idx = None
         a.topk_idx_off, a.x_off, a.weights_off = L.topk_idx_off, L.x_off, L.topk_weights_off
         a.x_sf_off = L.x_sf_off
+        if packed:   # inputs were copied in as one packed image, see packed_layout()
+            a.x_off, a.x_sf_off, a.topk_idx_off, a.weights_off, _ = self.packed_layout(num_tokens)
         a.experts_per_rank, a.topk = self.num_experts_per_rank, self.num_topk
         a.hidden, a.intermediate, a.max_tokens = self.hidden, self.intermediate_hidden, self.num_max_tokens_per_rank
         a.max_spins, a.skip_combine = int(max_spins), int(skip_combine)
@@ -246,6 +264,9 @@ class SymmBuffer:
         a.y = None if y_f32 is None else y_f32.data_ptr()
         a.y_bf16 = None if y_bf16 is None else y_bf16.data_ptr()
         a.cta_pair = int(getattr(self, "cta_pair", 0) if cta_pair is None else cta_pair)
+        # prologue protocol (0 automatic, 1 pull, 2 push): a property of the buffer because every
+        # rank of a launch must use the same one
+        a.dispatch_mode = int(self.dispatch_mode if dispatch_mode is None else dispatch_mode)
         return a
 
     def destroy(self):
@@ -266,12 +287,13 @@ def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_ran
                                  hidden: int, intermediate_hidden: int, num_shared_experts: int = 0,
                                  use_fp8_dispatch: Optional[bool] = None, mma_type: str = "fp8xfp8",
                                  activation: str = "swiglu", num_tokens: Optional[int] = None,
-                                 expert_window: Optional[int] = None, slot_capacity: int = 0) -> SymmBuffer:
+                                 expert_window: Optional[int] = None, slot_capacity: int = 0,
+                                 dispatch_mode: int = 0) -> SymmBuffer:
     if use_fp8_dispatch is not None:
         assert use_fp8_dispatch == (mma_type.split("x")[0] == "fp8")
     return SymmBuffer(group, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
                       num_shared_experts, mma_type=mma_type, activation=activation, grid_num_tokens=num_tokens,
-                      expert_window=expert_window, slot_capacity=slot_capacity)
+                      expert_window=expert_window, slot_capacity=slot_capacity, dispatch_mode=dispatch_mode)
 
 
 WeightArg = Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]
@@ -343,9 +365,11 @@ def _check_weights(sym_buffer: SymmBuffer, l1, l2):
 
 def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
                  cumulative_local_expert_recv_stats=None, activation: str = "swiglu", activation_clamp=None,
-                 expert_window: Optional[int] = None, max_spins: int = 0, cta_pair: Optional[int] = None) -> None:
+                 expert_window: Optional[int] = None, max_spins: int = 0, cta_pair: Optional[int] = None,
+                 packed_inputs: bool = False) -> None:
     """One MoE layer: ``y[t] = sum_k w_k * W2_e SwiGLU(W1_e x_t)`` for this rank's
-    ``y.shape[0]`` tokens, inputs taken from ``sym_buffer.x / x_sf / topk_idx / topk_weights``.
+    ``y.shape[0]`` tokens, inputs taken from ``sym_buffer.x / x_sf / topk_idx / topk_weights``
+    (or, with ``packed_inputs``, from the packed image described by ``SymmBuffer.packed_layout``).
     Every rank of the group must call it the same number of times (a rank with zero
     tokens still launches so that it joins the barrier and serves its experts)."""
     _check_buffer(sym_buffer, "fp8_mega_moe")
@@ -360,7 +384,7 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
     lib = _lib.lib()
     _quantize_input(sym_buffer, num_tokens, isinstance(l1_weights, tuple) and l1_weights[1] is not None)
     a = sym_buffer.launch_args(num_tokens, l1_weights, l2_weights, y_bf16=y, expert_window=expert_window,
-                               max_spins=max_spins, cta_pair=cta_pair)
+                               max_spins=max_spins, cta_pair=cta_pair, packed=packed_inputs)
     if num_tokens == 0:  # nothing to reduce, but the rank still serves its experts
         check(lib.mxk_launch_compute(C.byref(a), _stream_ptr()), "mxk_launch_compute")
     else:

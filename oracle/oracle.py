@@ -356,6 +356,48 @@ def gen_case(R, EPR, topk, H, I, tokens, seed=0, routing="uniform", scaled=True,
     return Case(R, EPR, topk, H, I, cap, list(tokens), scaled, x, x_sf, ti, tw, w1, w1_sf, w2, w2_sf, name)
 
 
+def gen_case_bytes(R, EPR, topk, H, I, tokens, seed=0, routing="uniform", cap=None, name="") -> Case:
+    """Seeded synthetic layer drawn directly as E4M3 bytes + UE8M0 exponents (random sign and
+    mantissa, exponent field 3..10, scale bytes near 2^-9 for weights and 2^-3 for activations):
+    same shapes and value range as quantised N(0,0.02) weights / N(0,1) activations, without
+    FP32 tensors or a quantisation pass, so that full-width worlds generate in seconds."""
+    rng = np.random.default_rng(seed)
+    E = R * EPR
+    if isinstance(tokens, int):
+        tokens = [tokens] * R
+    cap = cap or max(max(tokens), 1)
+
+    def fp8(shape):
+        n = int(np.prod(shape))
+        raw = rng.bit_generator.random_raw((2 * n + 7) // 8).view(np.uint8)   # raw 64-bit words: fastest source
+        return ((raw[:n] & 0x87) | (((raw[n:] & 7) + 3) << 3)).reshape(shape)
+
+    x = fp8((R, cap, H))
+    x_sf = (rng.integers(0, 3, (R, cap, H // 128)) + 124).astype(np.uint8)
+    ti = np.zeros((R, cap, topk), np.int64)
+    tw = np.zeros((R, cap, topk), np.float32)
+    perm = rng.permutation(E)
+    for r in range(R):
+        T = tokens[r]
+        if T == 0:
+            continue
+        ti[r, :T] = gen_routing(routing, rng, T, E, topk, perm)
+        lg = rng.standard_normal((T, topk)).astype(np.float32)
+        ex = np.exp(lg - lg.max(axis=1, keepdims=True))
+        tw[r, :T] = (ex / ex.sum(axis=1, keepdims=True)).astype(np.float32)
+    # one random block per weight kind; expert e holds it rotated by a prime multiple of e bytes
+    # (distinct per expert, and a full-width world of 1.2 GB generates in a few seconds)
+    b1, b2 = fp8((2 * I * H,)), fp8((H * I,))
+    w1 = np.empty((E, 2 * I, H), np.uint8)
+    w2 = np.empty((E, H, I), np.uint8)
+    for e in range(E):
+        w1[e] = np.roll(b1, e * 7919).reshape(2 * I, H)
+        w2[e] = np.roll(b2, e * 4099).reshape(H, I)
+    w1_sf = (rng.integers(0, 3, (E, 2 * I // 128, H // 128)) + 118).astype(np.uint8)
+    w2_sf = (rng.integers(0, 3, (E, H // 128, I // 128)) + 118).astype(np.uint8)
+    return Case(R, EPR, topk, H, I, cap, list(tokens), True, x, x_sf, ti, tw, w1, w1_sf, w2, w2_sf, name)
+
+
 def routes_from_counts(per_expert, R: int, tokens: int, topk: int) -> np.ndarray:
     """Routes [R][tokens][topk] that reproduce recorded per-expert received-pair counts
     (the replay of the reference's real-serving TK_INFO corpora, test/mega_common.cuh:460-482):

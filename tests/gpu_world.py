@@ -38,10 +38,11 @@ def load_inputs(case, bufs):
 
 
 class World:
-    def __init__(self, case, slot_capacity=0, expert_window=128):
+    def __init__(self, case, slot_capacity=0, expert_window=128, dispatch_mode=0):
         self.case = case
         self.bufs = mm.SymmBuffer.local_world(case.R, case.E, case.cap, case.topk, case.H, case.I,
-                                              slot_capacity=slot_capacity, expert_window=expert_window)
+                                              slot_capacity=slot_capacity, expert_window=expert_window,
+                                              dispatch_mode=dispatch_mode)
         self.weights = [dev_weights(case, r) for r in range(case.R)]
         self.y = [torch.zeros((max(case.tokens[r], 1), case.H), dtype=torch.bfloat16, device="cuda")
                   for r in range(case.R)]

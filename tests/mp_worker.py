@@ -1,8 +1,12 @@
 """Worker of the multi-process tests (one process per rank).
 
-mode "gpu":  real expert-parallel layer over NCCL-bootstrapped IPC buffers, one GPU per rank;
-             three launches on the same buffers with different inputs (exercises the epoch-parity
-             tables, counter reset and ragged / empty ranks); y checked against the oracle.
+mode "gpu":  real expert-parallel layer over NCCL-bootstrapped IPC buffers, one GPU per rank, once
+             with the pull-mode and once with the push-mode prologue: three launches on the same
+             buffers with different inputs (exercises the epoch-parity tables, counter reset and
+             ragged / empty ranks), integer tables exact, y checked against the oracle; then five
+             layers captured in one CUDA graph and replayed three times on every rank (no host
+             reset in between: stale flags or tags across ranks would show), each node's y equal
+             to the eager result bit for bit (reference: test/check.cu:533-745).
 mode "gloo": CPU ranks: each rank derives its own routing share, ranks exchange them like the
              device scatter does, and the assembled tables must equal the whole-world oracle.
 """
@@ -34,47 +38,77 @@ def run_gpu():
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
     group = dist.group.WORLD
-    buf = None
     worst = 0.0
-    for ci, case in enumerate(cases(world)):
-        if buf is None:
-            buf = mm.get_symm_buffer_for_mega_moe(group, case.E, case.cap, case.topk, case.H, case.I)
-        T = case.tokens[rank]
-        buf.x.view(torch.uint8).copy_(torch.from_numpy(case.x[rank]))
-        buf.x_sf.copy_(torch.from_numpy(case.x_sf[rank]))
-        buf.topk_idx.copy_(torch.from_numpy(case.topk_idx[rank]))
-        buf.topk_weights.copy_(torch.from_numpy(case.topk_w[rank]))
-        sl = slice(rank * case.EPR, (rank + 1) * case.EPR)
-        l1, l2 = mm.transform_weights_for_mega_moe(
-            (torch.from_numpy(case.w1[sl]).cuda(), torch.from_numpy(case.w1_sf[sl]).cuda()),
-            (torch.from_numpy(case.w2[sl]).cuda(), torch.from_numpy(case.w2_sf[sl]).cuda()))
-        y = torch.zeros((T, case.H), dtype=torch.bfloat16, device="cuda")
-        torch.cuda.synchronize()
+    all_cases = cases(world)
+    refs = [orc.layer_world(c) for c in all_cases]
+    for mode in (1, 2):
+        buf = None
+        launches = 0
+        for ci, case in enumerate(all_cases):
+            if buf is None:
+                buf = mm.get_symm_buffer_for_mega_moe(group, case.E, case.cap, case.topk, case.H, case.I,
+                                                      dispatch_mode=mode)
+            T = case.tokens[rank]
+            buf.x.view(torch.uint8).copy_(torch.from_numpy(case.x[rank]))
+            buf.x_sf.copy_(torch.from_numpy(case.x_sf[rank]))
+            buf.topk_idx.copy_(torch.from_numpy(case.topk_idx[rank]))
+            buf.topk_weights.copy_(torch.from_numpy(case.topk_w[rank]))
+            sl = slice(rank * case.EPR, (rank + 1) * case.EPR)
+            l1, l2 = mm.transform_weights_for_mega_moe(
+                (torch.from_numpy(case.w1[sl]).cuda(), torch.from_numpy(case.w1_sf[sl]).cuda()),
+                (torch.from_numpy(case.w2[sl]).cuda(), torch.from_numpy(case.w2_sf[sl]).cuda()))
+            y = torch.zeros((T, case.H), dtype=torch.bfloat16, device="cuda")
+            torch.cuda.synchronize()
+            dist.barrier()
+            mm.fp8_mega_moe(y, l1, l2, buf)
+            launches += 1
+            torch.cuda.synchronize()
+            st = buf.status()
+            assert st.status == 0, f"rank {rank} mode {mode} case {ci}: device status {st.status} dbg {list(st.dbg)}"
+            ref = refs[ci]
+            # integer tables of this rank: bit-exact
+            par = int(st.launches & 1)
+            s = ref[rank]
+            assert np.array_equal(buf.table("route_slot_counts").cpu().numpy(), s.route_slot_counts)
+            assert np.array_equal(buf.table("prefix_tbl").cpu().numpy(), s.prefix_tbl)
+            tbl = buf.table("src_index_table")[par].cpu().numpy().astype(np.uint32)
+            for le in range(case.EPR):     # rows are defined up to their count; later slots keep older launches
+                for src in range(world):
+                    n = int(s.prefix_tbl[le, src + 1] - s.prefix_tbl[le, src])
+                    assert np.array_equal(tbl[le, src, :n], s.src_index_table[le, src, :n]), (mode, ci, le, src)
+            rows = s.meta.shape[0]
+            assert np.array_equal(buf.table("row_meta")[:rows, :3].cpu().numpy(), s.meta)
+            assert np.array_equal(buf.table("pool")[:rows].cpu().numpy(), s.pool)
+            if T:
+                err = orc.rel_l2(y.float().cpu().numpy(), ref[rank].y)
+                worst = max(worst, err)
+                assert err <= 1e-2, f"rank {rank} mode {mode} case {ci}: relative L2 {err}"
+            dist.barrier()
+        # graph of five layers on the last case's inputs, replayed three times
+        y_eager = y.clone()
+        ys = [torch.zeros_like(y_eager) for _ in range(5)]
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for yy in ys:
+                    mm.fp8_mega_moe(yy, l1, l2, buf)
+        for rep in range(3):
+            for yy in ys:
+                yy.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            g.replay()
+            torch.cuda.synchronize()
+            st = buf.status()
+            assert st.status == 0, f"rank {rank} mode {mode} replay {rep}: device status {st.status} dbg {list(st.dbg)}"
+            for ni, yy in enumerate(ys):
+                assert torch.equal(yy.view(torch.int16), y_eager.view(torch.int16)), (mode, rep, ni)
+        assert buf.status().launches == launches + 15
         dist.barrier()
-        mm.fp8_mega_moe(y, l1, l2, buf)
-        torch.cuda.synchronize()
-        st = buf.status()
-        assert st.status == 0, f"rank {rank} case {ci}: device status {st.status} dbg {list(st.dbg)}"
-        ref = orc.layer_world(case)
-        # integer tables of this rank: bit-exact
-        par = int(st.launches & 1)
-        s = ref[rank]
-        assert np.array_equal(buf.table("route_slot_counts").cpu().numpy(), s.route_slot_counts)
-        assert np.array_equal(buf.table("prefix_tbl").cpu().numpy(), s.prefix_tbl)
-        tbl = buf.table("src_index_table")[par].cpu().numpy().astype(np.uint32)
-        for le in range(case.EPR):     # rows are defined up to their count; later slots keep older launches
-            for src in range(world):
-                n = int(s.prefix_tbl[le, src + 1] - s.prefix_tbl[le, src])
-                assert np.array_equal(tbl[le, src, :n], s.src_index_table[le, src, :n]), (ci, le, src)
-        rows = s.meta.shape[0]
-        assert np.array_equal(buf.table("row_meta")[:rows, :3].cpu().numpy(), s.meta)
-        assert np.array_equal(buf.table("pool")[:rows].cpu().numpy(), s.pool)
-        if T:
-            err = orc.rel_l2(y.float().cpu().numpy(), ref[rank].y)
-            worst = max(worst, err)
-            assert err <= 1e-2, f"rank {rank} case {ci}: relative L2 {err}"
-        dist.barrier()
-    buf.destroy()
+        del g
+        buf.destroy()
     print(f"MP_OK rank={rank} worst_rel_l2={worst:.3e}", flush=True)
     dist.destroy_process_group()
 

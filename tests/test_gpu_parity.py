@@ -78,10 +78,13 @@ def _reduce_check(world, r):
     assert np.array_equal(got16, orc.f32_to_bf16(want))
 
 
-def _run_case(case, expert_window=128, full_stage_checks=True, e2e_tol=1e-2, cta_pair=None):
+MODES = [1, 2]   # prologue protocol: 1 = pull (route scatter, barrier, owner pulls), 2 = push (sources store rows)
+
+
+def _run_case(case, expert_window=128, full_stage_checks=True, e2e_tol=1e-2, cta_pair=None, dispatch_mode=0, ref=None):
     from gpu_world import World, assert_status_ok, check_tables
-    ref = orc.layer_world(case)
-    w = World(case, expert_window=expert_window)
+    ref = ref or orc.layer_world(case)
+    w = World(case, expert_window=expert_window, dispatch_mode=dispatch_mode)
     try:
         w.run(cta_pair=cta_pair)
         assert_status_ok(w)
@@ -98,21 +101,21 @@ def _run_case(case, expert_window=128, full_stage_checks=True, e2e_tol=1e-2, cta
     finally:
         w.destroy()
     if case.R == 1:
-        _run_fused(case, ref[0].y, expert_window, e2e_tol, cta_pair)
+        _run_fused(case, ref[0].y, expert_window, e2e_tol, cta_pair, dispatch_mode)
 
 
-def _run_fused(case, want_y, expert_window, e2e_tol, cta_pair=None):
+def _run_fused(case, want_y, expert_window, e2e_tol, cta_pair=None, dispatch_mode=0):
     """The same case through ONE launch of the whole layer (mxk_launch_full via fp8_mega_moe),
     twice on the same buffers: phases then overlap inside the persistent kernel."""
     import mini_mega_b200 as mm
     from gpu_world import dev_weights, load_inputs
     buf = mm.get_symm_buffer_for_mega_moe(None, case.E, case.cap, case.topk, case.H, case.I,
-                                          expert_window=expert_window)
+                                          expert_window=expert_window, dispatch_mode=dispatch_mode)
     try:
         load_inputs(case, [buf])
         l1, l2 = dev_weights(case, 0)
         T = case.tokens[0]
-        for _ in range(2):
+        for _ in range(3):
             y = torch.zeros((T, case.H), dtype=torch.bfloat16, device="cuda")
             mm.fp8_mega_moe(y, l1, l2, buf, cta_pair=cta_pair)
             torch.cuda.synchronize()
@@ -124,32 +127,40 @@ def _run_fused(case, want_y, expert_window, e2e_tol, cta_pair=None):
         buf.destroy()
 
 
-def test_toy_scaled():
+@pytest.mark.parametrize("mode", MODES)
+def test_toy_scaled(mode):
     """BASELINE config 0: E=8, topk=2, H=512, I=256, T=32, world=1, UE8M0 block scales,
     top-k of router logits."""
-    _run_case(orc.gen_case(1, 8, 2, 512, 256, 32, seed=1, routing="logits", scaled=True))
+    _run_case(orc.gen_case(1, 8, 2, 512, 256, 32, seed=1, routing="logits", scaled=True), dispatch_mode=mode)
 
 
-def test_toy_reference_mode():
+@pytest.mark.parametrize("mode", MODES)
+def test_toy_reference_mode(mode):
     """Same shape without scale planes: the reference kernel's own arithmetic (scale == 1)."""
-    _run_case(orc.gen_case(1, 8, 2, 512, 256, 32, seed=2, routing="logits", scaled=False))
+    _run_case(orc.gen_case(1, 8, 2, 512, 256, 32, seed=2, routing="logits", scaled=False), dispatch_mode=mode)
 
 
-def test_multi_rank_world_scaled():
+@pytest.mark.parametrize("mode", MODES)
+def test_multi_rank_world_scaled(mode):
     """4 ranks x 4 experts, ragged token counts including an empty rank."""
-    _run_case(orc.gen_case(4, 4, 4, 1024, 512, [24, 0, 7, 33], seed=3, routing="uniform", scaled=True, cap=40))
+    _run_case(orc.gen_case(4, 4, 4, 1024, 512, [24, 0, 7, 33], seed=3, routing="uniform", scaled=True, cap=40),
+              dispatch_mode=mode)
 
 
-def test_multi_window_skew():
+@pytest.mark.parametrize("mode", MODES)
+def test_multi_window_skew(mode):
     """Zipf routing on few experts: several 128-row windows per expert, and a 64-row window run."""
     case = orc.gen_case(2, 2, 2, 512, 256, [150, 130], seed=4, routing="zipf", scaled=True)
-    _run_case(case)
-    _run_case(case, expert_window=64)
+    ref = orc.layer_world(case)
+    _run_case(case, dispatch_mode=mode, ref=ref)
+    _run_case(case, expert_window=64, dispatch_mode=mode, ref=ref)
 
 
-def test_invalid_ids():
+@pytest.mark.parametrize("mode", MODES)
+def test_invalid_ids(mode):
     """Negative expert ids are skipped everywhere (src/prologue.cuh:166-167, src/combine.cuh reduce)."""
-    _run_case(orc.gen_case(2, 4, 4, 512, 256, [20, 12], seed=5, routing="uniform", scaled=True, invalid_frac=0.15))
+    _run_case(orc.gen_case(2, 4, 4, 512, 256, [20, 12], seed=5, routing="uniform", scaled=True, invalid_frac=0.15),
+              dispatch_mode=mode)
 
 
 def test_reference_fixture_full_geometry():
@@ -161,7 +172,29 @@ def test_reference_fixture_full_geometry():
 def test_cta_pair_mode():
     """CTA-pair tiling (clusters of two CTAs, 256-row windows, 2-CTA MMA) forced on small cases:
     windows of fewer than 128 rows (the partner CTA has no rows), of 128..256 rows, and several
-    windows per expert; with and without scale planes."""
+    windows per expert; with and without scale planes; pull- and push-mode prologue."""
     _run_case(orc.gen_case(1, 8, 2, 512, 256, 32, seed=13, routing="logits", scaled=True), cta_pair=2)
-    _run_case(orc.gen_case(2, 2, 2, 512, 256, [300, 290], seed=14, routing="zipf", scaled=True), cta_pair=2)
-    _run_case(orc.gen_case(1, 4, 2, 1024, 512, 400, seed=15, routing="uniform", scaled=False), cta_pair=2)
+    _run_case(orc.gen_case(2, 2, 2, 512, 256, [300, 290], seed=14, routing="zipf", scaled=True), cta_pair=2, dispatch_mode=1)
+    _run_case(orc.gen_case(1, 4, 2, 1024, 512, 400, seed=15, routing="uniform", scaled=False), cta_pair=2, dispatch_mode=2)
+
+
+def test_prefill_geometry_h7168():
+    """BASELINE config 4's geometry (H=7168, I=2048: 56 K blocks = 14 scale groups per L1 task, scale
+    rows of 56 live bytes in a stride of 64) on a small world: 8 experts, top-4, 600 tokens, so that the
+    hottest expert fills more than two 128-row windows (and more than one 256-row window of a CTA
+    pair).  Full stage checks with single CTAs and with CTA pairs, pull and push prologue."""
+    case = orc.gen_case_bytes(1, 8, 4, 7168, 2048, 600, seed=41, routing="zipf")
+    ref = orc.layer_world(case, threads=16)
+    counts = np.bincount(case.topk_idx[0, :600].reshape(-1), minlength=8)
+    assert counts.max() > 256
+    for cta_pair, mode in ((1, 1), (2, 1), (1, 2), (2, 2)):
+        _run_case(case, cta_pair=cta_pair, dispatch_mode=mode, ref=ref)
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_decode_world_full_width(mode):
+    """The EP=8 decode shape as a multi-rank world at full width: 8 ranks x 4 experts, H=6144,
+    I=2048, top-8, 16 tokens per rank (32 rows per expert on average).  Tables exact on every rank,
+    stage checks, y within 1e-2."""
+    case = orc.gen_case_bytes(8, 4, 8, 6144, 2048, 16, seed=42)
+    _run_case(case, dispatch_mode=mode, ref=orc.layer_world(case, threads=16))

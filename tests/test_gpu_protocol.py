@@ -12,8 +12,9 @@ from oracle import oracle as orc
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("mode", [1, 2])
 @pytest.mark.parametrize("pattern", ["balanced", "hot", "mixed-invalid"])
-def test_prelude_tables_on_reference_patterns(pattern):
+def test_prelude_tables_on_reference_patterns(pattern, mode):
     """L0 check of the reference (test/check.cu:168-198): after the prologue alone, slot counts,
     source tables, received counts + checksum and prefix tables are exact on every rank —
     'hot' overflows the slot capacity (pairs dropped), 'mixed-invalid' carries ids of -1."""
@@ -21,7 +22,7 @@ def test_prelude_tables_on_reference_patterns(pattern):
     R, EPR, topk, tokens = 2, 8, 8, 16
     case = orc.gen_reference_fixture(R, EPR, topk, 512, 256, tokens, pattern, salt=1)
     ref = orc.route_world(case)                 # slot capacity = max_tokens, like the reference
-    w = World(case)
+    w = World(case, dispatch_mode=mode)         # 1 = pull-mode prologue, 2 = push-mode prologue
     try:
         w.run(phases=(1, 2))                    # route for every rank, then set-up for every rank
         check_tables(w, ref)
@@ -51,7 +52,8 @@ def test_prelude_tables_on_reference_patterns(pattern):
         w.destroy()
 
 
-def test_barrier_wait_expires_and_context_survives():
+@pytest.mark.parametrize("mode", [1, 2])
+def test_barrier_wait_expires_and_context_survives(mode):
     """A rank whose peer never arrives: the barrier wait runs out after max_spins*250 ns, the
     kernel records MXK_DEV_TIMEOUT_BARRIER and returns; nothing hangs or traps and the same
     process then runs a correct layer."""
@@ -59,7 +61,7 @@ def test_barrier_wait_expires_and_context_survives():
     from gpu_world import World
     from mini_mega_b200 import _lib
     case = orc.gen_case(2, 4, 2, 512, 256, [8, 8], seed=7, scaled=True)
-    w = World(case)
+    w = World(case, dispatch_mode=mode)
     try:
         lib = _lib.lib()
         a = w.args(0, max_spins=4000)   # 1 ms
@@ -86,14 +88,15 @@ def test_barrier_wait_expires_and_context_survives():
         buf.destroy()
 
 
-def test_graph_replay_matches_eager():
+@pytest.mark.parametrize("mode", [1, 2])
+def test_graph_replay_matches_eager(mode):
     """Reference graph check (test/check.cu:533-745): N layer launches captured in one CUDA graph
     with no host reset between nodes; every replay must reproduce the eager result (the
     launch counter and table parity live on the device)."""
     import mini_mega_b200 as mm
     from gpu_world import dev_weights, load_inputs
     case = orc.gen_case(1, 8, 4, 1024, 512, 48, seed=9, routing="uniform", scaled=True)
-    buf = mm.get_symm_buffer_for_mega_moe(None, case.E, case.cap, case.topk, case.H, case.I)
+    buf = mm.get_symm_buffer_for_mega_moe(None, case.E, case.cap, case.topk, case.H, case.I, dispatch_mode=mode)
     try:
         load_inputs(case, [buf])
         l1, l2 = dev_weights(case, 0)
@@ -123,11 +126,12 @@ def test_graph_replay_matches_eager():
         buf.destroy()
 
 
-def test_split_compute_then_reduce():
+@pytest.mark.parametrize("mode", [1, 2])
+def test_split_compute_then_reduce(mode):
     import mini_mega_b200 as mm
     from gpu_world import dev_weights, load_inputs
     case = orc.gen_case(1, 8, 2, 512, 256, 24, seed=10, routing="logits", scaled=True)
-    buf = mm.get_symm_buffer_for_mega_moe(None, case.E, case.cap, case.topk, case.H, case.I)
+    buf = mm.get_symm_buffer_for_mega_moe(None, case.E, case.cap, case.topk, case.H, case.I, dispatch_mode=mode)
     try:
         load_inputs(case, [buf])
         l1, l2 = dev_weights(case, 0)
@@ -141,3 +145,29 @@ def test_split_compute_then_reduce():
         assert torch.equal(y_full.view(torch.int16), y_split.view(torch.int16))
     finally:
         buf.destroy()
+
+
+def test_compute_without_reduce_then_full_layer():
+    """A compute launch that is never followed by its reduce leaves arrival counts behind; the next
+    layer must notice (the count table is not marked clean) and clear them before peers push."""
+    import mini_mega_b200 as mm
+    from gpu_world import dev_weights, load_inputs
+    case = orc.gen_case(1, 8, 2, 512, 256, 24, seed=12, routing="logits", scaled=True)
+    want = orc.layer_world(case)[0].y
+    for mode in (1, 2):
+        buf = mm.get_symm_buffer_for_mega_moe(None, case.E, case.cap, case.topk, case.H, case.I, dispatch_mode=mode)
+        try:
+            load_inputs(case, [buf])
+            l1, l2 = dev_weights(case, 0)
+            y = torch.zeros((24, 512), dtype=torch.bfloat16, device="cuda")
+            mm.fp8_mega_moe(y, l1, l2, buf)
+            mm.fp8_mega_moe_compute(l1, l2, buf, 24)      # rows pushed, counts raised, nobody reduces
+            assert int(buf.table("combine_cnt").sum()) > 0
+            y.zero_()
+            mm.fp8_mega_moe(y, l1, l2, buf)
+            torch.cuda.synchronize()
+            assert buf.status().status == 0
+            assert orc.rel_l2(y.float().cpu().numpy(), want) <= 1e-2
+            assert int(buf.table("combine_cnt").sum()) == 0   # consumed counts are zeroed by the reduce
+        finally:
+            buf.destroy()
