@@ -98,6 +98,10 @@ typedef struct MxkLayout {
     int32_t xin_row_words;      /* per token: topk ids, topk weights, ceil(H/512) scale
                                    words (padded to even), H/4 row words              */
     int32_t push_eligible;      /* 1: this geometry may run the push-mode prologue    */
+    int64_t route_scratch_off;  /* rwk: int32 [route_scratch_ctas][E] pairs per (CTA slice, expert),
+                                   scratch of the one-pass route build for large batches */
+    int32_t route_scratch_ctas;
+    int32_t reserved0_;
 } MxkLayout;
 
 /* One launch.  Field names follow fp8mega::MegaLaunchArgs (reference
@@ -284,6 +288,31 @@ int mxk_set_ticks(int on);
 /* Window chooser kept for the callers that bind it (reference: mxk_select_win,
  * torch/csrc/flags_bridge.cu:31-38 -> src/win_select.cuh:95-128). */
 int mxk_select_win(const uint32_t* counts, int E, int cap_hint, int win_min);
+
+/* Skew-aware schedulers as pure functions (host entry points; the kernels call the same source).
+ *   mxk_group_ranks         ranks per helper group of the reference's build (kGroupRanks,
+ *                           torch/csrc/flags_bridge.cu:15)
+ *   mxk_gs_schedule_member  the (group expert, window) units one member of a helper group computes:
+ *                           deterministic LPT, cost = ceil(rows / 16), ties to the owner then the
+ *                           lowest member (reference: gs_schedule_member, src/group_sched.cuh:164-205).
+ *                           rows_of_ge [group_ranks * EPR], ge = member * EPR + local expert.
+ *                           Returns the member's window count (at most cap entries are written).
+ *   mxk_gs_group_skewed     1 when max * n_experts > skew_num * sum (reference: MX_GS_SKEW_NUM = 2,
+ *                           src/group_sched.cuh:26-28)
+ *   mxk_lpt_assign          LPT over (expert, window, slice) tasks with cost = rows (reference:
+ *                           enumerate_group_tasks / lpt_assign, src/balance_partition.cuh:62-115);
+ *                           tasks [n][3] and member_of [n] in assignment order, load [n_members].
+ *   mxk_gs_schedule_on_device  the member lists of a whole group computed by a kernel (host arrays
+ *                           in and out, [group_ranks][cap]); host and device results must agree,
+ *                           as in the reference's check (test/check.cu:287-315). */
+int mxk_group_ranks(void);
+int mxk_gs_schedule_member(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int member,
+                           int32_t* out_ge, int32_t* out_w, int cap);
+int mxk_gs_group_skewed(const int32_t* rows_of_ge, int n_experts, int skew_num);
+int mxk_lpt_assign(const int32_t* counts, const int32_t* experts, int n_experts, int win_cap, int n_slice, int n_members,
+                   int32_t* tasks, int32_t* member_of, int64_t* load, int cap);
+int mxk_gs_schedule_on_device(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int32_t* out_ge,
+                              int32_t* out_w, int32_t* out_n, int cap);
 
 /* Symmetric-memory helpers (reference SymmBuffer C++ side,
  * torch/csrc/apis/mega.hpp:86-195): device allocation that can be exported to

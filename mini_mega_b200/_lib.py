@@ -19,7 +19,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile csrc/mxk_kernels.cu for sm_100a into libmxk_b200.so (in-tree)."""
-    srcs = [os.path.join(SRC_DIR, f) for f in ("mxk_kernels.cu", "mxk_device.cuh", "mxk_phases.cuh", "mxk_gemm.cuh")]
+    srcs = [os.path.join(SRC_DIR, f) for f in ("mxk_kernels.cu", "mxk_device.cuh", "mxk_phases.cuh", "mxk_gemm.cuh",
+                                               "mxk_sched.cuh")]
     hdr = os.path.join(os.path.dirname(_HERE), "include", "mxk_b200.h")
     newest = max(os.path.getmtime(p) for p in srcs + [hdr])
     if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= newest:
@@ -50,6 +51,7 @@ class MxkLayout(C.Structure):
         ("pool_ready_off", C.c_int64), ("expert_first_win_off", C.c_int64),
         ("xin_off", C.c_int64), ("xin_src_words", C.c_int64), ("xin_row_words", C.c_int32),
         ("push_eligible", C.c_int32),
+        ("route_scratch_off", C.c_int64), ("route_scratch_ctas", C.c_int32), ("reserved0_", C.c_int32),
     ]
 
 
@@ -83,6 +85,7 @@ EXPORTS = [
     "mxk_kernels_per_layer", "mxk_launch_phases", "mxk_launch_full_static",
     "mxk_static_scratch_bytes", "mxk_fill_weights", "mxk_quantize_rows", "mxk_dump_kernel_resources", "mxk_read_status",
     "mxk_read_status_static", "mxk_rwk_ticks_off", "mxk_ticks_count", "mxk_set_ticks", "mxk_select_win",
+    "mxk_group_ranks", "mxk_gs_schedule_member", "mxk_gs_group_skewed", "mxk_lpt_assign", "mxk_gs_schedule_on_device",
     "mxk_symm_alloc", "mxk_symm_free", "mxk_ipc_export", "mxk_ipc_import", "mxk_ipc_close",
 ]
 
@@ -120,6 +123,11 @@ def lib():
     L.mxk_rwk_ticks_off.restype = C.c_int64
     L.mxk_ticks_count.restype = C.c_int64
     L.mxk_set_ticks.argtypes = [C.c_int]
+    i32p = C.POINTER(C.c_int32)
+    L.mxk_gs_schedule_member.argtypes = [i32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p, i32p, C.c_int]
+    L.mxk_gs_group_skewed.argtypes = [i32p, C.c_int, C.c_int]
+    L.mxk_lpt_assign.argtypes = [i32p, i32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p, i32p, C.POINTER(C.c_int64), C.c_int]
+    L.mxk_gs_schedule_on_device.argtypes = [i32p, C.c_int, C.c_int, C.c_int, i32p, i32p, i32p, C.c_int]
     L.mxk_select_win.argtypes = [C.POINTER(C.c_uint32), C.c_int, C.c_int, C.c_int]
     L.mxk_symm_alloc.argtypes = [C.POINTER(C.c_void_p), C.c_int64]
     L.mxk_symm_free.argtypes = [C.c_void_p]

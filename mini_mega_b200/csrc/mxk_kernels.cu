@@ -20,6 +20,7 @@
 
 #include "../../include/mxk_b200.h"
 #include "mxk_device.cuh"
+#include "mxk_sched.cuh"
 
 namespace {
 
@@ -36,6 +37,8 @@ struct DevFlags {  // head of rwk (flags_off)
     long long current_time;      // completed prologues; the running launch is +1
     unsigned route_blocks_done;
     unsigned clear_blocks_done;  // arrivals at the grid barrier behind a full clear of combine_cnt
+    unsigned route_sync;         // arrivals at the grid barrier of the one-pass route
+    unsigned pad0_;
     unsigned task_ctr[2];        // claimed tasks beyond the first per CTA, by launch parity (the
                                  // copy of the other parity is reset for the next launch)
     int n_tasks, n_l1_tasks, n_windows, total_rows;
@@ -161,9 +164,9 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
             push_phase(a, f, epoch, sc.wid);
             if (trace && threadIdx.x == 0) trace[2] = gtimer_ns();
             __syncthreads();   // the scratch is reused below
-            route_phase(a, f, epoch, s_small, true);
+            route_phase(a, f, epoch, s_small, reinterpret_cast<int*>(tiles), kStages * kStageBytes / 4, true);
         } else {
-            route_phase(a, f, epoch, s_small, false);
+            route_phase(a, f, epoch, s_small, reinterpret_cast<int*>(tiles), kStages * kStageBytes / 4, false);
         }
     }
     if (stamp && blockIdx.x == 0) f->ticks[9] = gtimer_ns() - t0;
@@ -238,6 +241,16 @@ k_mega_pair(const KArgs a, const int phase_mask, const __grid_constant__ CUtenso
 }
 
 __global__ void k_empty() {}
+
+// The cross-rank window scheduler on the device: thread m computes member m's list (the same pure
+// function the host entry point calls; reference check.cu:287-315 re-runs it on the host to find
+// which windows a rank computes, which doubles as a host/device determinism test).
+__global__ void k_sched_members(const int* rows_of_ge, int EPR, int group_ranks, int win_cap, int* out_ge, int* out_w,
+                                int* out_n, int cap) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= group_ranks) return;
+    out_n[m] = sched_member_windows(rows_of_ge, EPR, group_ranks, win_cap, m, out_ge + (size_t)m * cap, out_w + (size_t)m * cap, cap);
+}
 
 // bf16 rows -> E4M3 + one UE8M0 scale per 128 columns, the reference's activation quantiser
 // (per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=128), torch/mxmegakernel/utils/math.py:26-36:
@@ -353,6 +366,8 @@ int compute_layout(const MxkGeom* g, MxkLayout* L) {
     L->flags_off = take(1024);
     L->route_slot_counts_off = take(E * 4);
     L->pair_state_off = take(cap * topk);
+    L->route_scratch_ctas = 256;   // per-slice expert counts of the one-pass route build, [CTAs][E]
+    L->route_scratch_off = take((int64_t)L->route_scratch_ctas * E * 4);
     L->prefix_tbl_off = take(EPR * (R + 1) * 4);
     L->expert_row_base_off = take((EPR + 1) * 4);
     L->windows_off = take((int64_t)L->max_windows * 16);
@@ -781,6 +796,54 @@ int mxk_read_status(const void* rwk, MxkStatus* out) {
 // Byte offset of the per-layer wait / phase counters (MxkStatus.ticks) inside rwk and their
 // number, for hosts that copy them back themselves (reference: pre_ticks readers,
 // torch/csrc/flags_bridge.cu:44-51).
+// ---- skew-aware schedulers (pure functions of mxk_sched.cuh) -----------------------------
+int mxk_group_ranks(void) { return 4; }   // ranks per helper group the reference builds with (kGroupRanks)
+static int sched_args_ok(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap) {
+    if (!rows_of_ge || EPR < 1 || group_ranks < 1 || group_ranks > kSchedMaxGroupRanks || win_cap < 1)
+        return fail(MXK_ERR_BAD_ARG, "scheduler: null counts, EPR < 1, window < 1 or group size outside [1,16]");
+    return 0;
+}
+int mxk_gs_schedule_member(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int member,
+                           int32_t* out_ge, int32_t* out_w, int cap) {
+    if (sched_args_ok(rows_of_ge, EPR, group_ranks, win_cap)) return MXK_ERR_BAD_ARG;
+    if (member < 0 || member >= group_ranks || cap < 0 || (cap > 0 && (!out_ge || !out_w)))
+        return fail(MXK_ERR_BAD_ARG, "scheduler: member outside the group or null output");
+    return sched_member_windows(rows_of_ge, EPR, group_ranks, win_cap, member, out_ge, out_w, cap);
+}
+int mxk_gs_group_skewed(const int32_t* rows_of_ge, int n_experts, int skew_num) {
+    if (!rows_of_ge || n_experts < 1) return fail(MXK_ERR_BAD_ARG, "scheduler: null counts");
+    return sched_group_skewed(rows_of_ge, n_experts, skew_num) ? 1 : 0;
+}
+int mxk_lpt_assign(const int32_t* counts, const int32_t* experts, int n_experts, int win_cap, int n_slice, int n_members,
+                   int32_t* tasks, int32_t* member_of, int64_t* load, int cap) {
+    if (!counts || !experts || !tasks || !member_of || !load || n_experts < 1 || win_cap < 1 || n_slice < 1 || n_members < 1 || cap < 0)
+        return fail(MXK_ERR_BAD_ARG, "lpt_assign: null pointer or non-positive size");
+    static_assert(sizeof(long long) == sizeof(int64_t), "64-bit loads");
+    return sched_lpt_assign(counts, experts, n_experts, win_cap, n_slice, n_members, tasks, member_of,
+                            reinterpret_cast<long long*>(load), cap);
+}
+int mxk_gs_schedule_on_device(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int32_t* out_ge,
+                              int32_t* out_w, int32_t* out_n, int cap) {
+    if (sched_args_ok(rows_of_ge, EPR, group_ranks, win_cap)) return MXK_ERR_BAD_ARG;
+    if (!out_ge || !out_w || !out_n || cap < 1) return fail(MXK_ERR_BAD_ARG, "scheduler: null output");
+    const size_t n_in = (size_t)EPR * group_ranks * 4, n_out = (size_t)group_ranks * cap * 4;
+    int *d_in = nullptr, *d_ge = nullptr, *d_w = nullptr, *d_n = nullptr;
+    cudaError_t e = cudaMalloc(&d_in, n_in);
+    if (e == cudaSuccess) e = cudaMalloc(&d_ge, n_out);
+    if (e == cudaSuccess) e = cudaMalloc(&d_w, n_out);
+    if (e == cudaSuccess) e = cudaMalloc(&d_n, (size_t)group_ranks * 4);
+    if (e == cudaSuccess) e = cudaMemcpy(d_in, rows_of_ge, n_in, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) {
+        k_sched_members<<<1, 32>>>(d_in, EPR, group_ranks, win_cap, d_ge, d_w, d_n, cap);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(out_ge, d_ge, n_out, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemcpy(out_w, d_w, n_out, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemcpy(out_n, d_n, (size_t)group_ranks * 4, cudaMemcpyDeviceToHost);
+    cudaFree(d_in); cudaFree(d_ge); cudaFree(d_w); cudaFree(d_n);
+    return e == cudaSuccess ? 0 : cuda_fail(e, "scheduler on device");
+}
+
 int mxk_set_ticks(int on) {
     const int before = ticks_enabled();
     g_ticks_override = on < 0 ? -1 : (on ? 1 : 0);

@@ -68,11 +68,100 @@ __device__ void ensure_counts_clean(const KArgs& a, DevFlags* f, long long epoch
     __syncthreads();
 }
 
+// Route build for LARGE batches in one pass over the pairs (the per-expert scan of route_phase
+// below costs every CTA a full pass per expert it owns).  CTA c takes the c-th slice of this
+// rank's pairs, ranks every pair among the earlier pairs of its slice with the same expert and
+// counts the slice's pairs per expert; the slice counts go to a [grid][E] table in global memory,
+// the grid meets at a barrier, and the exclusive sum over the earlier slices turns a pair's rank
+// into its slot — the same ascending-pair-index order as the per-expert scan.  `s_i` is scratch
+// of 2 * slice + 2 * E ints.  Returns false when the shapes do not fit (the caller then scans).
+__device__ bool route_onepass(const KArgs& a, DevFlags* f, long long epoch, int* s_i, int scratch_ints,
+                              const bool local_only) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int par = (int)(epoch & 1);
+    const int np = a.tokens * a.topk, E = a.E, G = (int)gridDim.x, c = (int)blockIdx.x;
+    const int S = (np + G - 1) / G;
+    if (E > 2048 || G > a.L.route_scratch_ctas || 2 * S + 2 * E > scratch_ints) return false;   // uniform over the grid
+    int* s_id = s_i;            // [S] expert of the slice's pair, -1 = invalid
+    int* s_rank = s_id + S;     // [S] earlier pairs of the slice with the same expert
+    int* s_hist = s_rank + S;   // [E] pairs of the slice per expert
+    int* s_base = s_hist + E;   // [E] pairs of the earlier slices per expert
+    const int p0 = min(np, c * S), n = min(np, p0 + S) - p0;
+    const int64_t* ti = a.topk_idx;
+    uint8_t* pair_state = a.rwk + a.L.pair_state_off;
+    int* rsc = reinterpret_cast<int*>(a.rwk + a.L.route_slot_counts_off);
+    int* g_cnt = reinterpret_cast<int*>(a.rwk + a.L.route_scratch_off);   // [G][E]
+    for (int e = tid; e < E; e += nthr) s_hist[e] = 0;
+    for (int i = tid; i < n; i += nthr) {
+        const int64_t v = ti[p0 + i];
+        s_id[i] = (uint64_t)v < (uint64_t)E ? (int)v : -1;   // invalid ids take no slot (src/prologue.cuh:166-167)
+    }
+    __syncthreads();
+    for (int i = tid; i < n; i += nthr) {
+        const int id = s_id[i];
+        int r = 0;
+        if (id >= 0) {
+            for (int j = 0; j < i; ++j) r += s_id[j] == id ? 1 : 0;
+            atomicAdd(&s_hist[id], 1);
+        }
+        s_rank[i] = r;
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += nthr) g_cnt[(size_t)c * E + e] = s_hist[e];
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        atomicAdd(&f->route_sync, 1u);
+        const unsigned want = (unsigned)G;
+        if (!spin_until([&] { return ld_acquire_gpu(&f->route_sync) >= want; }, a.local_wait_ns, nullptr))
+            raise_status(f, MXK_DEV_TIMEOUT_PIPE, 2);
+    }
+    __syncthreads();
+    // pairs of the earlier slices per expert (coalesced over the experts); the experts this CTA
+    // owns (e = c, c + G, ...) also get their totals, their count is published from here
+    for (int e = tid; e < E; e += nthr) {
+        int before = 0, total = 0;
+        for (int cc = 0; cc < G; ++cc) {
+            const int v = ld_relaxed_gpu(g_cnt + (size_t)cc * E + e);
+            before += cc < c ? v : 0;
+            total += v;
+        }
+        s_base[e] = before;
+        if (e % G == c) {
+            const int cnt = total < a.slot_cap ? total : a.slot_cap;
+            rsc[e] = cnt;
+            if (!local_only) {
+                uint64_t* recv = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[e / a.EPR]) +
+                                                             a.L.expert_recv_counts_off) +
+                                 ((size_t)par * a.R + a.rank) * a.L.recv_stride;
+                st_relaxed_sys_u64(recv + e % a.EPR, tagged((uint32_t)cnt, epoch));
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n; i += nthr) {
+        const int id = s_id[i], p = p0 + i;
+        bool ok = false;
+        if (id >= 0) {
+            const int slot = s_base[id] + s_rank[i];
+            ok = slot < a.slot_cap;   // over capacity: dropped (src/prologue.cuh:171-174)
+            if (ok && !local_only) {
+                uint64_t* tbl = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[id / a.EPR]) +
+                                                            a.L.src_index_table_off) +
+                                (((size_t)par * a.EPR + id % a.EPR) * a.R + a.rank) * (size_t)a.slot_cap;
+                st_relaxed_sys_u64(tbl + slot, tagged((uint32_t)p, epoch));
+            }
+        }
+        pair_state[p] = ok ? 1 : 0;
+    }
+    return true;
+}
+
 // `local_only` (push mode): only this rank's own tables are written — route_slot_counts and the
 // accepted-pair map; nothing is scattered to the owner ranks, they derive their tables from the
 // pushed routing words.
 __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_wtot /*[kRoutePer * warps]*/,
-                            const bool local_only) {
+                            int* s_big, int s_big_ints /* large scratch for the one-pass variant */, const bool local_only) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nthr = blockDim.x, nwarps = nthr >> 5;
     const int par = (int)(epoch & 1);
@@ -81,7 +170,9 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     uint8_t* pair_state = a.rwk + a.L.pair_state_off;
     int* rsc = reinterpret_cast<int*>(a.rwk + a.L.route_slot_counts_off);
 
-    for (int e = blockIdx.x; e < a.E; e += gridDim.x) {
+    // many pairs: one pass over this rank's pairs instead of one scan per expert
+    const bool onepass = np > kRoutePer * nthr && route_onepass(a, f, epoch, s_big, s_big_ints, local_only);
+    for (int e = blockIdx.x; e < a.E && !onepass; e += gridDim.x) {
         const int dst = e / a.EPR, le = e % a.EPR;
         uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[dst]);
         uint64_t* tbl = reinterpret_cast<uint64_t*>(peer_unk + a.L.src_index_table_off) +
@@ -137,7 +228,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     // The launch bookkeeping below belongs to the LAST CTA: CTA 0 goes straight on to poll the
     // counts and build the tables, which is the critical path of the prologue.
     const bool closer = blockIdx.x == gridDim.x - 1;
-    if (closer)  // invalid expert ids (negative / >= E) take no slot (src/prologue.cuh:166-167)
+    if (closer && !onepass)  // invalid expert ids (negative / >= E) take no slot (src/prologue.cuh:166-167)
         for (int p = tid; p < np; p += nthr)
             if ((uint64_t)ti[p] >= (uint64_t)a.E) pair_state[p] = 0;
 
@@ -167,6 +258,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     if (tid == 0) {
         f->route_blocks_done = 0;
         f->clear_blocks_done = 0;  // every CTA is past the clear barrier, if there was one
+        f->route_sync = 0;         // and past the barrier of the one-pass route
         // a rank without tokens receives no rows and runs no reduce: its (all-zero) table stays clean
         if (a.tokens == 0) f->cnt_clean_epoch = (uint32_t)epoch;
         f->current_time = epoch;   // every CTA has read the old value before arriving above

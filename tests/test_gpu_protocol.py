@@ -53,6 +53,33 @@ def test_prelude_tables_on_reference_patterns(pattern, mode):
 
 
 @pytest.mark.parametrize("mode", [1, 2])
+def test_large_batch_route_tables(mode):
+    """More pairs per rank than one scan step covers (the route build then works in one pass over
+    the pairs: slice ranks, per-slice expert counts, grid barrier, exclusive sums), with a slot
+    capacity below the per-expert load (drops) and invalid ids: every table still exact."""
+    from gpu_world import World, check_tables
+    case = orc.gen_case(2, 4, 8, 512, 256, [500, 410], seed=17, routing="uniform", scaled=True, invalid_frac=0.05)
+    ref = orc.route_world(case, slot_cap=300)
+    w = World(case, slot_capacity=300, dispatch_mode=mode)
+    try:
+        w.run(phases=(1, 2))
+        check_tables(w, ref)
+        for r in range(2):
+            assert w.bufs[r].status().status == 0
+            T = case.tokens[r]
+            idx = case.topk_idx[r, :T].reshape(-1)
+            seen, want = {}, np.zeros(T * 8, np.uint8)
+            for p, e in enumerate(idx):
+                if 0 <= e < 8:
+                    seen[e] = seen.get(e, 0) + 1
+                    want[p] = 1 if seen[e] <= 300 else 0
+            assert np.array_equal(w.table(r, "pair_state")[: T * 8], want)
+            assert (want == 0).sum() > 100   # the capacity really dropped pairs
+    finally:
+        w.destroy()
+
+
+@pytest.mark.parametrize("mode", [1, 2])
 def test_barrier_wait_expires_and_context_survives(mode):
     """A rank whose peer never arrives: the barrier wait runs out after max_spins*250 ns, the
     kernel records MXK_DEV_TIMEOUT_BARRIER and returns; nothing hangs or traps and the same
