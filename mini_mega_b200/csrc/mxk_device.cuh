@@ -38,6 +38,11 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ long long ld_acquire_gpu_s64(const long long* p) {
+    long long v;
+    asm volatile("ld.acquire.gpu.global.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
 // Strong (coherent) loads for data produced by other SMs / other GPUs while this kernel
 // runs.  Weak loads — including ld.global.cg — were observed to return stale bytes right
 // after an acquire of the producer's counter; strong loads are ordered by that acquire.

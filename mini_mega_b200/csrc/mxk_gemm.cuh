@@ -126,7 +126,7 @@ __device__ void gemm_init_barriers(GemmSmem* S, const bool pair) {
 // set-up tables of this launch are visible.  Returns when every role has left its loop.
 template <bool kPair>
 __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, const PushTabs* tabs,
-                           unsigned long long* trace, uint8_t* tiles, uint8_t* sf_tiles, GemmSmem* S,
+                           unsigned long long* trace, int* deferred_route_smem, uint8_t* tiles, uint8_t* sf_tiles, GemmSmem* S,
                            const uint32_t tmem_base, const CUtensorMap* tm_pool_p, const CUtensorMap* tm_ffn_p,
                            const CUtensorMap* tm_w1_p, const CUtensorMap* tm_w2_p) {
     const CUtensorMap& tm_pool = *tm_pool_p;
@@ -151,6 +151,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
     const int kb1 = a.H / kBlockK, kb2 = a.I / kBlockK;
     const int nt1 = a.I / 128;
     const uint32_t l1_need = (uint32_t)nt1 * kEpiWarps * (kPair ? 2u : 1u);   // arrivals that complete a window's ffn rows
+    const uint32_t row_parts = tabs ? (uint32_t)tabs->parts : 1u;             // pool_ready arrivals per dispatched row
     // Pair mode: CTA `crank` of the cluster owns rows [128*crank, 128*crank+128) of a 256-row
     // window and weight half `crank`; rank 0 (the leader) claims tasks and issues the MMAs.
     const uint32_t crank = kPair ? cluster_ctarank() : 0u;
@@ -217,7 +218,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
             // loads are being issued, so that a task starts without them on its critical path.
             auto gate_passed = [&](const int4& tk, const int4& wn) -> bool {   // one acquire load
                 return tk.x == 1 ? ld_acquire_gpu(l1_done + tk.y) >= l1_need
-                                 : ld_acquire_gpu(pool_ready + tk.y) >= (uint32_t)wn.z;
+                                 : ld_acquire_gpu(pool_ready + tk.y) >= (uint32_t)wn.z * row_parts;
             };
             int4 pending = claim_publish(0);
             int4 pending_win = make_int4(0, 0, 0, 0);
@@ -421,7 +422,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                 } else {
                     // pool scales are written by the dispatch phase of this same kernel
                     bool ready = true;
-                    const uint32_t need_rows = (uint32_t)win.z;
+                    const uint32_t need_rows = (uint32_t)win.z * row_parts;
                     ready = spin_until([&] { return ld_acquire_gpu(pool_ready + task.y) >= need_rows; }, wait_ns, abort_flag);
                     ready = __all_sync(0xFFFFFFFFu, ready ? 1 : 0) != 0;
                     if (!ready) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; } break; }
@@ -522,6 +523,11 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
         uint8_t* ffn_sf = a.rwk + a.L.ffn_sf_off;
         const int4* meta = reinterpret_cast<const int4*>(a.rwk + a.L.row_meta_off);
         long long w_acc = 0, t_busy = 0, t_drain = 0, t_pub = 0;
+        // Push mode, fused launch: this rank's own route bookkeeping (slot counts, accepted-pair map,
+        // launch counter), done here by the eight epilogue warps while the first accumulators fill.
+        if (deferred_route_smem)
+            route_phase(a, f, epoch, deferred_route_smem, nullptr, 0, true,
+                        Team{(int)threadIdx.x - kFirstEpiWarp * 32, kEpiWarps * 32, 1});
         // Publishing a task's output (release of l1_done / combine_cnt) has to wait until the
         // task's stores are performed.  It is deferred past the drain of the NEXT task's
         // accumulators when those are already complete, so that the store latency hides

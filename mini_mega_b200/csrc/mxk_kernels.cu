@@ -115,6 +115,7 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
     // the launch counter is advanced by the last CTA at the end of the route phase, after every
     // CTA has arrived there — i.e. after this read
     const long long epoch = ld_relaxed_gpu(&f->current_time) + ((phase_mask & MXK_PHASE_ROUTE) ? 1 : 0);
+    const uint32_t clean_epoch = ld_relaxed_gpu(&f->cnt_clean_epoch);   // see ensure_counts_clean
 
     if (do_gemm) {
         if (threadIdx.x == 0) gemm_init_barriers(S, kPair);
@@ -158,15 +159,20 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
     }
 
     const PushScratch sc = push_scratch(tiles);   // push mode: the tile region is scratch until the GEMM phase
+    const Team cta_team{(int)threadIdx.x, (int)blockDim.x, 0};
+    // Push mode keeps only this rank's own bookkeeping in the route build (slot counts, accepted-pair
+    // map, launch counter); nothing before the reduce phase needs it, so in a fused launch the
+    // epilogue warps do it while they wait for the first accumulators (gemm_phase).
+    const bool defer_route = a.push && do_gemm && (phase_mask & MXK_PHASE_ROUTE);
     if (phase_mask & MXK_PHASE_ROUTE) {
-        ensure_counts_clean(a, f, epoch);
+        ensure_counts_clean(a, f, epoch, clean_epoch);
         if (a.push) {
             push_phase(a, f, epoch, sc.wid);
             if (trace && threadIdx.x == 0) trace[2] = gtimer_ns();
             __syncthreads();   // the scratch is reused below
-            route_phase(a, f, epoch, s_small, reinterpret_cast<int*>(tiles), kStages * kStageBytes / 4, true);
+            if (!defer_route) route_phase(a, f, epoch, s_small, reinterpret_cast<int*>(tiles), kStages * kStageBytes / 4, true, cta_team);
         } else {
-            route_phase(a, f, epoch, s_small, reinterpret_cast<int*>(tiles), kStages * kStageBytes / 4, false);
+            route_phase(a, f, epoch, s_small, reinterpret_cast<int*>(tiles), kStages * kStageBytes / 4, false, cta_team);
         }
     }
     if (stamp && blockIdx.x == 0) f->ticks[9] = gtimer_ns() - t0;
@@ -177,11 +183,13 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
     if (a.push) {
         if (phase_mask & (MXK_PHASE_SETUP | MXK_PHASE_DISPATCH | MXK_PHASE_GEMM)) {
             const bool setup = (phase_mask & MXK_PHASE_SETUP) != 0, disp = (phase_mask & MXK_PHASE_DISPATCH) != 0;
-            tables_ok = push_tables(a, f, epoch, sc, &S->tabs, setup);
+            tables_ok = push_tables(a, f, epoch, sc, &S->tabs);
             tabs = &S->tabs;
             if (trace && threadIdx.x == 0) trace[5] = gtimer_ns();
             if (stamp && blockIdx.x == 0) f->ticks[10] = gtimer_ns() - t0;
             if (tables_ok && (setup || disp)) push_dispatch(a, f, epoch, sc, tabs, setup, disp);
+            if (trace && threadIdx.x == 0) trace[6] = gtimer_ns();
+            if (setup && blockIdx.x == 0) push_publish(a, f, epoch, sc, tabs);   // raises the status itself on overflow
             fence_proxy_async_smem();   // the scratch becomes TMA destination next
             __syncthreads();
         }
@@ -205,7 +213,10 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
 
     if (do_gemm) {
         if (tables_ok)
-            gemm_phase<kPair>(a, f, epoch, tabs, trace, tiles, sf_tiles, S, tmem_base, &tm_pool, &tm_ffn, &tm_w1, &tm_w2);
+            gemm_phase<kPair>(a, f, epoch, tabs, trace, defer_route ? s_small : nullptr, tiles, sf_tiles, S, tmem_base, &tm_pool,
+                              &tm_ffn, &tm_w1, &tm_w2);
+        else if (defer_route)   // no GEMM phase after all (tables failed): the launch bookkeeping still has to happen
+            route_phase(a, f, epoch, s_small, nullptr, 0, true, cta_team);
         if (S->abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain
         tc_fence_before();
         // pair mode: neither CTA may free tensor memory or leave while its partner can still

@@ -45,6 +45,17 @@ __device__ __forceinline__ uint64_t tagged(uint32_t payload, long long epoch) {
 // Slots are handed out in ascending pair index idx = token*topk + k, so every table row (and
 // with it the pool row order) is deterministic; the reference uses a shared-memory atomicAdd
 // and accepts any order (src/prologue.cuh:164-180).
+// The route build can be run by the whole CTA or by a team of its warps (the epilogue warps of the
+// GEMM phase, while they wait for the first accumulators): thread numbering and the barrier are
+// the team's.
+struct Team {
+    int tid, nthr, bar;   // bar 0 = the CTA barrier, else a named barrier of `nthr` threads
+    __device__ __forceinline__ void sync() const {
+        if (bar == 0) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(nthr) : "memory");
+    }
+};
+
 // Arrival counters of the rows peers push to this rank (combine_cnt) must be zero before any
 // peer can push for this launch.  The reduce phase zeroes every count it has consumed and the
 // last CTA to leave it records the launch in cnt_clean_epoch; when the previous launch did that
@@ -52,8 +63,8 @@ __device__ __forceinline__ uint64_t tagged(uint32_t payload, long long epoch) {
 // reduce, a reduce that gave up — the whole grid clears the table and meets at a barrier before
 // anything of this launch leaves the rank: a peer can push only after it has seen this rank's
 // routing, and that is published behind the barrier.
-__device__ void ensure_counts_clean(const KArgs& a, DevFlags* f, long long epoch) {
-    if (ld_relaxed_gpu(&f->cnt_clean_epoch) == (uint32_t)(epoch - 1)) return;   // uniform over the grid
+__device__ void ensure_counts_clean(const KArgs& a, DevFlags* f, long long epoch, uint32_t clean_epoch) {
+    if (clean_epoch == (uint32_t)(epoch - 1)) return;   // uniform over the grid
     const int tid = threadIdx.x, nthr = blockDim.x;
     unsigned* cnt = reinterpret_cast<unsigned*>(a.unk + a.L.combine_cnt_off);
     for (int i = blockIdx.x * nthr + tid; i < a.topk * a.cap; i += gridDim.x * nthr) cnt[i] = 0;
@@ -161,9 +172,10 @@ __device__ bool route_onepass(const KArgs& a, DevFlags* f, long long epoch, int*
 // accepted-pair map; nothing is scattered to the owner ranks, they derive their tables from the
 // pushed routing words.
 __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_wtot /*[kRoutePer * warps]*/,
-                            int* s_big, int s_big_ints /* large scratch for the one-pass variant */, const bool local_only) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nthr = blockDim.x, nwarps = nthr >> 5;
+                            int* s_big, int s_big_ints /* large scratch for the one-pass variant */, const bool local_only,
+                            const Team team) {
+    const int tid = team.tid, lane = tid & 31, warp = tid >> 5;
+    const int nthr = team.nthr, nwarps = nthr >> 5;
     const int par = (int)(epoch & 1);
     const int np = a.tokens * a.topk;
     const int64_t* ti = a.topk_idx;
@@ -171,7 +183,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     int* rsc = reinterpret_cast<int*>(a.rwk + a.L.route_slot_counts_off);
 
     // many pairs: one pass over this rank's pairs instead of one scan per expert
-    const bool onepass = np > kRoutePer * nthr && route_onepass(a, f, epoch, s_big, s_big_ints, local_only);
+    const bool onepass = team.bar == 0 && np > kRoutePer * nthr && route_onepass(a, f, epoch, s_big, s_big_ints, local_only);
     for (int e = blockIdx.x; e < a.E && !onepass; e += gridDim.x) {
         const int dst = e / a.EPR, le = e % a.EPR;
         uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[dst]);
@@ -195,7 +207,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
                 bal[j] = __ballot_sync(0xFFFFFFFFu, hit[j]);
                 if (lane == 0) s_wtot[j * nwarps + warp] = __popc(bal[j]);
             }
-            __syncthreads();
+            team.sync();
 #pragma unroll
             for (int j = 0; j < kRoutePer; ++j) {
                 int wpre = 0, tot = 0;
@@ -213,7 +225,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
                 }
                 base += tot;
             }
-            __syncthreads();
+            team.sync();
         }
         if (tid == 0) {
             const int c = base < a.slot_cap ? base : a.slot_cap;
@@ -235,7 +247,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     // Everything below is off the critical path (the counts are already on their way): make
     // this CTA's local tables visible, arrive, and let the last CTA close the launch bookkeeping.
     __threadfence();
-    __syncthreads();
+    team.sync();
     if (tid == 0) atomicAdd(&f->route_blocks_done, 1u);
     if (!closer) return;
 
@@ -244,7 +256,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
         if (!spin_until([&] { return ld_acquire_gpu(&f->route_blocks_done) >= want; }, a.local_wait_ns, nullptr))
             raise_status(f, MXK_DEV_TIMEOUT_PIPE, 2);
     }
-    __syncthreads();
+    team.sync();
     // Row checksum word ~(sum + 1) at index EPR of each row sent (src/prologue.cuh:248-255), kept
     // for layout parity with the reference; nothing here waits on it.
     for (int d = tid; d < a.R && !local_only; d += nthr) {
@@ -261,9 +273,10 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
         f->route_sync = 0;         // and past the barrier of the one-pass route
         // a rank without tokens receives no rows and runs no reduce: its (all-zero) table stays clean
         if (a.tokens == 0) f->cnt_clean_epoch = (uint32_t)epoch;
+        __threadfence();           // the reduce phase takes the counter as "every CTA's route tables are written"
         f->current_time = epoch;   // every CTA has read the old value before arriving above
     }
-    __syncthreads();
+    team.sync();
 }
 
 // From the per-(local expert, source rank) counts s_cnt[EPR][R] of this launch: the prefix table
@@ -572,6 +585,7 @@ constexpr int kPushMaxCnt = 4096;      // EPR * (R + 1)
 
 struct PushTabs {   // tables of this launch, in the control block of shared memory for the whole kernel
     int n_tasks, n_l1, n_windows, total_rows;
+    int parts;                    // warps that share the copy of one pool row (each counts into pool_ready)
     int tot[kPushMaxEPR];         // rows of local expert le
     int order[kPushMaxEPR];       // expert at sorted position p (descending rows)
     int first[kPushMaxEPR + 1];   // first window of sorted position p
@@ -615,56 +629,73 @@ __device__ __forceinline__ int push_src_of(const int* sb, int R, int i) {
 
 // Source side: store this rank's tokens into the owners' staging areas.  Work unit = (token,
 // destination rank), spread over the grid.  `s_ids` is scratch for tokens*topk ints.
+// Every global load of a unit (row, weights, scales, peer pointer) is issued before anything
+// waits, and for the CTA's first unit even before the routing words are in shared memory: the
+// whole phase costs one memory round trip plus the stores.
 __device__ void push_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_ids) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int par = (int)(epoch & 1), R = a.R, topk = a.topk, H = a.H, EPR = a.EPR;
     const int np = a.tokens * topk;
-    if (blockIdx.x == 0 && tid < R)   // header: how many rows the destination has to expect from this rank
-        st_relaxed_sys_u64(xin_block(a, a.unk_peers[tid], par, a.rank), tagged((uint32_t)a.tokens, epoch));
+    const int sfw = xin_sf_words(H), kb = H / 128, row_words = a.L.xin_row_words, n16 = H / 8;
+    const uint32_t* wts = reinterpret_cast<const uint32_t*>(a.self + a.weights_off);
+    const uint8_t* xsf = a.self + a.x_sf_off;
+    constexpr int kMaxPer = 3;   // 16-byte units of a row per thread: H <= 8192 -> 1024 units over 384 threads
+    struct Unit { uint2 x[kMaxPer]; uint32_t w, sf; void* peer; };
+    auto load_unit = [&](int u, Unit& un) {
+        const int t = u / R, d = (u + t) % R;
+        const uint2* xs = reinterpret_cast<const uint2*>(a.self + a.x_off + (size_t)t * H);
+#pragma unroll
+        for (int j = 0; j < kMaxPer; ++j)
+            if (tid + j * nthr < n16) un.x[j] = xs[tid + j * nthr];
+        un.w = (tid >= topk && tid < 2 * topk) ? wts[(size_t)t * topk + tid - topk] : 0u;
+        un.sf = 0;
+        if (a.scaled && tid >= 128 && tid < 128 + sfw) {   // four scale bytes per word, 127 (x1.0) beyond H/128
+            const int i = tid - 128;
+            for (int j = 0; j < 4; ++j) {
+                const int b = 4 * i + j;
+                un.sf |= (uint32_t)(b < kb ? xsf[(size_t)t * kb + b] : (uint8_t)127) << (8 * j);
+            }
+        }
+        un.peer = a.unk_peers[d];
+    };
+    const int n_units = a.tokens * R;
+    Unit un;
+    if ((int)blockIdx.x < n_units) load_unit(blockIdx.x, un);
+    void* hdr_peer = (blockIdx.x == gridDim.x - 1 && tid < R) ? a.unk_peers[tid] : nullptr;
     for (int p = tid; p < np; p += nthr) {   // invalid ids (negative / >= E) travel as -1 (src/prologue.cuh:166-167)
         const int64_t v = a.topk_idx[p];
         s_ids[p] = (uint64_t)v < (uint64_t)a.E ? (int)v : -1;
     }
+    if (hdr_peer)   // header: how many rows the destination has to expect from this rank
+        st_relaxed_sys_u64(xin_block(a, hdr_peer, par, a.rank), tagged((uint32_t)a.tokens, epoch));
     __syncthreads();
-    const int sfw = xin_sf_words(H), kb = H / 128, row_words = a.L.xin_row_words;
-    const uint32_t* wts = reinterpret_cast<const uint32_t*>(a.self + a.weights_off);
-    const uint8_t* xsf = a.self + a.x_sf_off;
-    for (int u = blockIdx.x; u < a.tokens * R; u += gridDim.x) {
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
         const int t = u / R, d = (u + t) % R;
         bool routed = false;
         for (int k = 0; k < topk; ++k) {
             const int e = s_ids[t * topk + k];
             routed |= e >= 0 && e / EPR == d;
         }
-        uint64_t* row = xin_block(a, a.unk_peers[d], par, a.rank) + 16 + (size_t)t * row_words;
+        uint64_t* row = xin_block(a, un.peer, par, a.rank) + 16 + (size_t)t * row_words;
         if (tid < topk) st_relaxed_sys_u64(row + tid, tagged((uint32_t)s_ids[t * topk + tid], epoch));
-        else if (tid < 2 * topk) st_relaxed_sys_u64(row + tid, tagged(wts[(size_t)t * topk + tid - topk], epoch));
-        if (!routed) continue;
-        if (a.scaled && tid >= 128 && tid < 128 + sfw) {   // four scale bytes per word, 127 (x1.0) beyond H/128
-            const int i = tid - 128;
-            uint32_t w = 0;
-            for (int j = 0; j < 4; ++j) {
-                const int b = 4 * i + j;
-                w |= (uint32_t)(b < kb ? xsf[(size_t)t * kb + b] : (uint8_t)127) << (8 * j);
+        else if (tid < 2 * topk) st_relaxed_sys_u64(row + tid, tagged(un.w, epoch));
+        if (routed) {
+            if (a.scaled && tid >= 128 && tid < 128 + sfw) st_relaxed_sys_u64(row + 2 * topk + tid - 128, tagged(un.sf, epoch));
+            uint64_t* xd = row + 2 * topk + sfw;
+#pragma unroll
+            for (int j = 0; j < kMaxPer; ++j) {
+                const int i = tid + j * nthr;
+                if (i < n16) st_relaxed_sys_v2_u64(xd + 2 * i, tagged(un.x[j].x, epoch), tagged(un.x[j].y, epoch));
             }
-            st_relaxed_sys_u64(row + 2 * topk + i, tagged(w, epoch));
         }
-        const uint2* xs = reinterpret_cast<const uint2*>(a.self + a.x_off + (size_t)t * H);
-        uint64_t* xd = row + 2 * topk + sfw;
-        for (int i = tid; i < H / 8; i += nthr) {
-            const uint2 v = xs[i];
-            st_relaxed_sys_v2_u64(xd + 2 * i, tagged(v.x, epoch), tagged(v.y, epoch));
-        }
+        if (u + (int)gridDim.x < n_units) load_unit(u + gridDim.x, un);
     }
 }
 
 // Owner side, EVERY CTA: wait for all sources' routing words of this launch (this is the
 // cross-rank barrier), count the pairs per (local expert, source) and build the tables in shared
-// memory.  With `publish`, CTA 0 also writes them to global memory in the pull-mode formats
-// (prefix table, received counts + checksum word, row bases, windows, tasks, status header).
-// Returns false when a source did not arrive in time or the tables overflow the buffers.
-__device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const PushScratch& sc, PushTabs* T,
-                            const bool publish) {
+// memory.  Returns false when a source did not arrive in time or the tables overflow the buffers.
+__device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const PushScratch& sc, PushTabs* T) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int par = (int)(epoch & 1), R = a.R, topk = a.topk, EPR = a.EPR;
     const uint32_t ep = (uint32_t)epoch;
@@ -673,7 +704,6 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
     const int row_words = a.L.xin_row_words;
     if (tid == 0) *sc.flag = 1;
     for (int i = tid; i < EPR * R; i += nthr) sc.cnt[i] = 0;
-    __syncthreads();
     for (int r = tid; r < R; r += nthr) {
         const uint64_t* hp = mine + r * src_words;
         uint64_t w = 0;
@@ -685,10 +715,10 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
         sc.tok[r] = min((int)(uint32_t)w, a.cap);
     }
     __syncthreads();
-    if (tid == 0) {
+    for (int r = tid; r <= R; r += nthr) {   // first world pair of source r
         int c = 0;
-        for (int r = 0; r < R; ++r) { sc.sb[r] = c; c += sc.tok[r] * topk; }
-        sc.sb[R] = c;
+        for (int q = 0; q < r; ++q) c += sc.tok[q];
+        sc.sb[r] = c * topk;
     }
     __syncthreads();
     const int W = sc.sb[R];   // <= R * cap * topk <= kPushMaxPairs
@@ -739,42 +769,54 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
         T->n_l1 = overflow ? 0 : n_windows * nt1;
         T->n_tasks = overflow ? 0 : n_windows * (nt1 + nt2);
         T->total_rows = overflow ? 0 : total_rows;
+        // a pool row is copied by `parts` warps when there are warps to spare, so that the copy of a
+        // row costs one round trip to the staging area instead of several
+        const int nwarps = (int)gridDim.x * (nthr >> 5);
+        T->parts = W <= nwarps ? 4 : (W <= 2 * nwarps ? 2 : 1);
     }
     for (int p = tid; p < EPR; p += nthr) sc.fw_e[T->order[p]] = T->first[p];
-    if (publish && blockIdx.x == 0) {
-        int* g_prefix = reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off);
-        for (int i = tid; i < EPR * (R + 1); i += nthr) g_prefix[i] = sc.prefix[i];
-        uint64_t* recv = reinterpret_cast<uint64_t*>(a.unk + a.L.expert_recv_counts_off) + (size_t)par * R * a.L.recv_stride;
-        for (int i = tid; i < EPR * R; i += nthr) {
-            const int le = i / R, r = i % R;
-            recv[(size_t)r * a.L.recv_stride + le] = tagged((uint32_t)sc.cnt[i], epoch);
-        }
-        for (int r = tid; r < R; r += nthr) {   // the reference's checksum word of a count row (src/prologue.cuh:248-255)
-            uint32_t csum = 0;
-            for (int le = 0; le < EPR; ++le) csum += (uint32_t)sc.cnt[le * R + r];
-            recv[(size_t)r * a.L.recv_stride + EPR] = tagged(~(csum + 1u), epoch);
-        }
-        publish_tables(a, f, epoch, T->tot, T->order, T->first, T->base);
-    }
     __syncthreads();
     return *sc.flag != 0 && !overflow;
 }
 
-// Owner side: one WARP per world pair whose expert lives here.  Its slot inside the (expert,
-// source) row is the number of earlier pairs of the same source with the same expert — the
-// ascending-pair-index order of the pull-mode route — which fixes the pool row; the warp then
-// copies the row's words from the staging area into the pool (tags stripped), the scale bytes and
-// the staged (source, token, k, weight), and counts the row into its window's pool_ready.
+// CTA 0, after its share of the dispatch: the tables of this launch in global memory, in the
+// pull-mode formats (prefix table, received counts + checksum word, row bases, windows, tasks,
+// status header).  Nothing in the kernel waits for them.
+__device__ void push_publish(const KArgs& a, DevFlags* f, long long epoch, const PushScratch& sc, const PushTabs* T) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int par = (int)(epoch & 1), R = a.R, EPR = a.EPR;
+    int* g_prefix = reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off);
+    for (int i = tid; i < EPR * (R + 1); i += nthr) g_prefix[i] = sc.prefix[i];
+    uint64_t* recv = reinterpret_cast<uint64_t*>(a.unk + a.L.expert_recv_counts_off) + (size_t)par * R * a.L.recv_stride;
+    for (int i = tid; i < EPR * R; i += nthr) {
+        const int le = i / R, r = i % R;
+        recv[(size_t)r * a.L.recv_stride + le] = tagged((uint32_t)sc.cnt[i], epoch);
+    }
+    for (int r = tid; r < R; r += nthr) {   // the reference's checksum word of a count row (src/prologue.cuh:248-255)
+        uint32_t csum = 0;
+        for (int le = 0; le < EPR; ++le) csum += (uint32_t)sc.cnt[le * R + r];
+        recv[(size_t)r * a.L.recv_stride + EPR] = tagged(~(csum + 1u), epoch);
+    }
+    publish_tables(a, f, epoch, T->tot, T->order, T->first, T->base);
+}
+
+// Owner side: one WARP per (world pair whose expert lives here, part of its row).  The pair's slot
+// inside the (expert, source) row is the number of earlier pairs of the same source with the same
+// expert — the ascending-pair-index order of the pull-mode route — which fixes the pool row; the
+// warp then copies its part of the row's words from the staging area into the pool (tags
+// stripped); part 0 also stores the scale bytes and the staged (source, token, k, weight).  Every
+// part counts itself into the window's pool_ready.
 // `do_tables`: also write the pair index into src_index_table (same words a pull-mode source writes).
 __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, const PushScratch& sc, const PushTabs* T,
                               const bool do_tables, const bool do_rows) {
     const int lane = threadIdx.x & 31;
     const int nwarps_cta = blockDim.x >> 5;
-    const int gwarp = blockIdx.x * nwarps_cta + (threadIdx.x >> 5);
     const int nwarps = gridDim.x * nwarps_cta;
+    // CTA 0 publishes the tables afterwards: it takes the last items, the last CTA the first ones
+    const int gwarp = ((int)gridDim.x - 1 - (int)blockIdx.x) * nwarps_cta + (threadIdx.x >> 5);
     const int par = (int)(epoch & 1), R = a.R, topk = a.topk, EPR = a.EPR, H = a.H;
     const uint32_t ep = (uint32_t)epoch;
-    const int W = sc.sb[R];
+    const int W = sc.sb[R], P = T->parts;
     const uint64_t* mine = xin_block(a, a.unk, par, 0);
     const size_t src_words = (size_t)a.L.xin_src_words;
     const int row_words = a.L.xin_row_words, sfw = xin_sf_words(H), sfw_real = (H / 128 + 3) / 4;
@@ -783,11 +825,27 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
     uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
     int4* meta = reinterpret_cast<int4*>(a.rwk + a.L.row_meta_off);
     uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off) + (size_t)par * a.L.max_windows;
-    for (int i = gwarp; i < W; i += nwarps) {
+    const int n16 = H / 8, per_part = n16 / P;   // H % 256 == 0: per_part is a multiple of 8
+    for (int it = gwarp; it < W * P; it += nwarps) {
+        const int i = it / P, part = it % P;
         const int e = sc.wid[i];
         if (e < 0 || e / EPR != a.rank) continue;   // uniform over the warp
         const int src = push_src_of(sc.sb, R, i);
         const int p = i - sc.sb[src], le = e % EPR;
+        const int token = p / topk, k = p % topk;
+        const uint64_t* row = mine + src * src_words + 16 + (size_t)token * row_words;
+        // this part's row words first (two per 16-byte load, up to eight loads in flight per lane):
+        // they do not depend on the slot, which is counted while they travel
+        const uint64_t* xs = row + 2 * topk + sfw;
+        const int u_lo = part * per_part, u_hi = u_lo + per_part;
+        ulonglong2 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (do_rows && u_lo + lane + 32 * j < u_hi) v[j] = ld_relaxed_sys_v2_u64(xs + 2 * (u_lo + lane + 32 * j));
+        uint64_t wword = 0, sfword = 0;
+        const bool lead = do_rows && part == 0;
+        if (lead && lane == 0) wword = ld_relaxed_sys_u64(row + topk + k);
+        if (lead && a.scaled && lane < sfw_real) sfword = ld_relaxed_sys_u64(row + 2 * topk + lane);
         int c = 0;
         for (int j = lane; j < p; j += 32) c += sc.wid[sc.sb[src] + j] == e ? 1 : 0;
 #pragma unroll
@@ -796,38 +854,26 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
         if (slot >= a.slot_cap) continue;           // over capacity: dropped
         const int gl = sc.prefix[le * (R + 1) + src] + slot;
         const int g = T->base[le] + gl;
-        if (do_tables && lane == 0) tbl[((size_t)le * R + src) * a.slot_cap + slot] = tagged((uint32_t)p, epoch);
+        if (do_tables && part == 0 && lane == 0) tbl[((size_t)le * R + src) * a.slot_cap + slot] = tagged((uint32_t)p, epoch);
         if (!do_rows) continue;
-        const int token = p / topk, k = p % topk;
-        const uint64_t* row = mine + src * src_words + 16 + (size_t)token * row_words;
         bool ok = true;
-        auto poll = [&](const uint64_t* wp) -> uint32_t {
-            uint64_t w = ld_relaxed_sys_u64(wp);
+        auto settle = [&](const uint64_t* wp, uint64_t w) -> uint32_t {   // the word, polled until it is this launch's
             if ((uint32_t)(w >> 32) != ep &&
                 !spin_until([&] { w = ld_relaxed_sys_u64(wp); return (uint32_t)(w >> 32) == ep; }, a.remote_wait_ns, nullptr))
                 ok = false;
             return (uint32_t)w;
         };
-        uint32_t wbits = 0;
-        if (lane == 0) wbits = poll(row + topk + k);
-        if (a.scaled) {
-            uint32_t* dsf = reinterpret_cast<uint32_t*>(pool_sf + (size_t)g * a.L.sf_stride_h);
-            for (int j = lane; j < a.L.sf_stride_h / 4; j += 32)
-                dsf[j] = j < sfw_real ? poll(row + 2 * topk + j) : 0x7F7F7F7Fu;
-        }
-        // row words, two per 16-byte load, eight loads in flight per lane
-        const uint64_t* xs = row + 2 * topk + sfw;
         uint2* drow = reinterpret_cast<uint2*>(pool + (size_t)g * H);
-        const int n16 = H / 8;
-        for (int u0 = lane; u0 < n16; u0 += 32 * 8) {
-            ulonglong2 v[8];
+        for (int u0 = u_lo + lane; u0 < u_hi; u0 += 32 * 8) {
+            if (u0 != u_lo + lane) {   // rows wider than 8 x 32 units per part: further batches
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (u0 + 32 * j < n16) v[j] = ld_relaxed_sys_v2_u64(xs + 2 * (u0 + 32 * j));
+                for (int j = 0; j < 8; ++j)
+                    if (u0 + 32 * j < u_hi) v[j] = ld_relaxed_sys_v2_u64(xs + 2 * (u0 + 32 * j));
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int u = u0 + 32 * j;
-                if (u >= n16) continue;
+                if (u >= u_hi) continue;
                 ulonglong2 t = v[j];
                 if (((uint32_t)(t.x >> 32) != ep || (uint32_t)(t.y >> 32) != ep) &&
                     !spin_until([&] { t = ld_relaxed_sys_v2_u64(xs + 2 * u);
@@ -837,9 +883,17 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
                 drow[u] = make_uint2((uint32_t)t.x, (uint32_t)t.y);
             }
         }
+        if (lead) {
+            if (a.scaled) {
+                uint32_t* dsf = reinterpret_cast<uint32_t*>(pool_sf + (size_t)g * a.L.sf_stride_h);
+                if (lane < a.L.sf_stride_h / 4)   // sf_stride_h <= 64 bytes: one word per lane
+                    dsf[lane] = lane < sfw_real ? settle(row + 2 * topk + lane, sfword) : 0x7F7F7F7Fu;
+            }
+            if (lane == 0) meta[g] = make_int4(src, token, k, (int)settle(row + topk + k, wword));
+        }
         if (!__all_sync(0xFFFFFFFFu, ok ? 1 : 0) && lane == 0) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 2);
-        if (lane == 0) meta[g] = make_int4(src, token, k, (int)wbits);
-        // the row is complete: every lane makes its stores visible at GPU scope and to TMA, then count it
+        // this part of the row is complete: every lane makes its stores visible at GPU scope and to
+        // TMA, then the part is counted
         __threadfence();
         fence_proxy_async_global();
         __syncwarp();
@@ -856,6 +910,12 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
 // the next launch skip the clear of the table (ensure_counts_clean).
 __device__ void reduce_tokens(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, float* s_w /*[64]*/);
 __device__ void reduce_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_ok, float* s_w) {
+    // the accepted-pair map is written by the route build of every CTA; the launch counter moves
+    // once all of them have arrived (long ago, normally)
+    if (threadIdx.x == 0 &&
+        !spin_until([&] { return ld_acquire_gpu_s64(&f->current_time) >= epoch; }, a.local_wait_ns, nullptr))
+        raise_status(f, MXK_DEV_TIMEOUT_PIPE, 2);
+    __syncthreads();
     reduce_tokens(a, f, s_ok, s_w);
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -891,9 +951,11 @@ __device__ void reduce_tokens(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, f
                         raise_status(f, MXK_DEV_TIMEOUT_REDUCE, 4);
                         ok = 0;
                     } else {
+                        // acquire: the counted row segments are visible (the pushers release their rows
+                        // with a fence before the relaxed adds); then the count is consumed
+                        (void)(a.R > 1 ? ld_acquire_sys(c) : ld_acquire_gpu(c));
                         *c = 0;
                     }
-                    fence_world(a.R > 1);  // acquire: the counted row segments are visible
                 }
                 w_mine = tw[(size_t)t * topk + lane];
             }
@@ -963,9 +1025,9 @@ __device__ void reduce_tokens(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, f
                     raise_status(f, MXK_DEV_TIMEOUT_REDUCE, 4);
                     ok = 0;
                 } else {
+                    (void)(a.R > 1 ? ld_acquire_sys(c) : ld_acquire_gpu(c));   // acquire: the counted row segments are visible
                     *c = 0;
                 }
-                fence_world(a.R > 1);  // acquire: the counted row segments are visible
             }
             s_ok[tid] = ok;
             s_w[tid] = tw[(size_t)t * topk + tid];
