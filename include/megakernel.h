@@ -73,6 +73,13 @@ struct MegaLaunchArgs {
     uint16_t* y_bf16 = nullptr;
     int cta_pair = 0;   // 0 = choose by load, 1 = single CTAs, 2 = CTA pairs (256-row windows)
     int dispatch_mode = 0;   // prologue protocol, the same on every rank: 0 = by geometry, 1 = pull, 2 = push
+    // cross-rank helper scheduling (reference: MX_GROUP_SCHED with rwk->ld.w1g / w2g): group size, skew
+    // threshold (0 = the reference's 2, negative = always) and the group-replicated weights
+    int group_ranks = 0, group_skew_num = 0;
+    const uint8_t* w1_group = nullptr;
+    const uint8_t* w2_group = nullptr;
+    const uint8_t* w1_sf_group = nullptr;
+    const uint8_t* w2_sf_group = nullptr;
 };
 
 inline int& last_status() {
@@ -94,6 +101,8 @@ inline MxkLaunchArgs to_c(const MegaLaunchArgs& a) {
     c.experts_per_rank = a.experts_per_rank; c.topk = a.topk; c.hidden = a.hidden;
     c.intermediate = a.intermediate; c.max_tokens = a.max_tokens;
     c.x_sf_off = a.x_sf_off; c.w1_sf = a.w1_sf; c.w2_sf = a.w2_sf; c.y_bf16 = a.y_bf16; c.cta_pair = a.cta_pair; c.dispatch_mode = a.dispatch_mode;
+    c.group_ranks = a.group_ranks; c.group_skew_num = a.group_skew_num;
+    c.w1_group = a.w1_group; c.w2_group = a.w2_group; c.w1_sf_group = a.w1_sf_group; c.w2_sf_group = a.w2_sf_group;
     return c;
 }
 

@@ -124,7 +124,7 @@ typedef struct MxkLaunchArgs {
     const int64_t* topk_idx;   /* optional; NULL => self + topk_idx_off           */
     const uint8_t* w1;         /* [EPR][2I][H] E4M3 row-major, gate rows then up  */
     const uint8_t* w2;         /* [EPR][H][I]  E4M3 row-major                     */
-    int32_t group_weights_ready; /* accepted; cross-rank helper scheduling unused */
+    int32_t group_weights_ready; /* != 0: w1_group / w2_group below hold the helper group's weights */
     int64_t topk_idx_off, x_off, weights_off;
     int32_t in_bf16;           /* must be 0                                       */
     int32_t skip_combine;      /* >0: L2 results are not pushed (diagnostic)      */
@@ -148,6 +148,24 @@ typedef struct MxkLaunchArgs {
                                   store ids + rows into the owners' staging area, every CTA
                                   derives the tables itself; needs layout.push_eligible),
                                   0 = push when the geometry is eligible, else pull       */
+    /* ---- cross-rank helper scheduling for skewed routing (reference: MX_GROUP_SCHED,
+     * src/compute.cuh:700-835; group-replicated weights rwk->ld.w1g / w2g,
+     * src/flags_defs.cuh:160-169, gated by group_weights_ready above) ----
+     * Ranks form interleaved helper groups of group_ranks (group = rank % (R / group_ranks),
+     * member = rank / (R / group_ranks)); every member holds the weights of ALL the group's
+     * experts in the order ge = member * experts_per_rank + local expert.  When a launch finds
+     * its group's load skewed, the (expert, window) units of the group are spread over the
+     * members by the deterministic LPT of mxk_gs_schedule_member and a member computes windows
+     * of other members' experts from its replica, pushing the results to the source ranks as
+     * usual.  Needs group_weights_ready != 0, the push-mode prologue, R % group_ranks == 0 and
+     * the inputs in their regular regions of sym; the same on every rank. */
+    int32_t group_ranks;       /* 0 / 1 = no helper groups                                  */
+    int32_t group_skew_num;    /* skew test max * n > num * sum: 0 = the reference's 2,
+                                  negative = helpers on in every launch                     */
+    const uint8_t* w1_group;   /* [group_ranks * EPR][2I][H]                                */
+    const uint8_t* w2_group;   /* [group_ranks * EPR][H][I]                                 */
+    const uint8_t* w1_sf_group;/* [group_ranks * EPR][2I/128][H/128] or NULL                */
+    const uint8_t* w2_sf_group;/* [group_ranks * EPR][H/128][I/128]  or NULL                */
 } MxkLaunchArgs;
 
 /* Host-readable copy of the device status header. */
@@ -155,6 +173,8 @@ typedef struct MxkStatus {
     int64_t launches;      /* completed prologues (reference current_time)       */
     int32_t status;        /* 0 = ok, else the first MXK_DEV_* code raised       */
     int32_t n_tasks, n_l1_tasks, n_windows, total_rows;
+    int32_t helper_on;     /* 1: the last launch ran this rank's member list of the helper group
+                              (n_windows / total_rows then count the windows and rows it computed) */
     int32_t dbg[8];        /* expiry counters, slot meaning as the reference:
                               0 barrier, 2 route, 3 task queue, 4 L1->L2 gate /
                               reduce wait, 5 pipeline barrier, 6 TMEM barrier    */

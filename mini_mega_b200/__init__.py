@@ -14,6 +14,7 @@ from .mega import (  # noqa: F401
     fp8_mega_moe,
     fp8_mega_moe_compute,
     fp8_mega_moe_reduce,
+    gather_group_weights,
     get_symm_buffer_for_mega_moe,
     get_symm_buffer_size_for_mega_moe,
     get_token_alignment_for_mega_moe,

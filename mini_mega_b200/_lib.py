@@ -69,12 +69,14 @@ class MxkLaunchArgs(C.Structure):
         ("max_tokens", C.c_int32),
         ("x_sf_off", C.c_int64), ("w1_sf", C.c_void_p), ("w2_sf", C.c_void_p), ("y_bf16", C.c_void_p),
         ("cta_pair", C.c_int32), ("dispatch_mode", C.c_int32),
+        ("group_ranks", C.c_int32), ("group_skew_num", C.c_int32),
+        ("w1_group", C.c_void_p), ("w2_group", C.c_void_p), ("w1_sf_group", C.c_void_p), ("w2_sf_group", C.c_void_p),
     ]
 
 
 class MxkStatus(C.Structure):
     _fields_ = [("launches", C.c_int64), ("status", C.c_int32), ("n_tasks", C.c_int32), ("n_l1_tasks", C.c_int32),
-                ("n_windows", C.c_int32), ("total_rows", C.c_int32), ("dbg", C.c_int32 * 8),
+                ("n_windows", C.c_int32), ("total_rows", C.c_int32), ("helper_on", C.c_int32), ("dbg", C.c_int32 * 8),
                 ("ticks", C.c_uint64 * 16), ("trace", C.c_uint64 * 64)]
 
 

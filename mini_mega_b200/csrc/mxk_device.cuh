@@ -81,6 +81,11 @@ __device__ __forceinline__ ulonglong2 ld_relaxed_sys_v2_u64(const uint64_t* p) {
     asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ uint2 ld_relaxed_sys_v2_u32(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint8_t ld_relaxed_gpu_u8(const uint8_t* p) {
     uint32_t v;
     asm volatile("ld.relaxed.gpu.global.u8 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

@@ -91,15 +91,20 @@ __device__ __forceinline__ int tabs_pos_of_window(const PushTabs* T, int EPR, in
     }
     return lo;
 }
+// The expert index of a window addresses the weight arrays: with helper groups configured these
+// are the group's replicated arrays (ge = member * EPR + local expert), else this rank's own.
 __device__ __forceinline__ int4 tabs_window(const PushTabs* T, const KArgs& a, int w) {
+    if (T->helper) return make_int4(T->gw[w] >> 16, T->rr[w] >> 10, T->rr[w] & 1023, 0);
     const int p = tabs_pos_of_window(T, a.EPR, w);
     const int e = T->order[p], wl = w - T->first[p];
-    return make_int4(e, T->base[e] + wl * a.win_cap, min(a.win_cap, T->tot[e] - wl * a.win_cap), 0);
+    return make_int4(a.ge_base + e, T->base[e] + wl * a.win_cap, min(a.win_cap, T->tot[e] - wl * a.win_cap), 0);
 }
 __device__ __forceinline__ int4 tabs_task(const PushTabs* T, const KArgs& a, int t) {
     const int kind = t >= T->n_l1 ? 1 : 0;
     const int nt = kind ? a.H / kBlockN : a.I / 128;
     const int tt = kind ? t - T->n_l1 : t;
+    if (T->helper)   // the member's window list: window-major, n-tile minor
+        return make_int4(kind, tt / nt, tt % nt, T->rr[tt / nt] & 1023);
     const int p = tabs_pos_of_window(T, a.EPR, tt / nt);
     const int fw = T->first[p], nw = T->first[p + 1] - fw;
     const int i = tt - fw * nt;

@@ -42,6 +42,7 @@ struct DevFlags {  // head of rwk (flags_off)
     unsigned task_ctr[2];        // claimed tasks beyond the first per CTA, by launch parity (the
                                  // copy of the other parity is reset for the next launch)
     int n_tasks, n_l1_tasks, n_windows, total_rows;
+    int helper_on;               // the last launch ran the member's window list of the helper group
     int status;
     int dbg[8];
     unsigned long long ticks[16];
@@ -59,6 +60,10 @@ struct KArgs {
     int R, rank, EPR, E, topk, H, I, cap, slot_cap, tokens, win_cap;
     int gemm_grid, skip_combine, scaled, ticks, pair;
     int push;                    // push-mode prologue (see push_phase)
+    int group_ranks;             // members of a helper group (1 = none); helper scheduling needs push mode
+    int skew_num;                // helpers on when max * n_experts > skew_num * sum over the group's experts
+    int ge_base;                 // this rank's first expert inside the weight arrays (member * EPR with group weights)
+    int w_experts;               // experts in the weight arrays w1 / w2 (EPR, or group_ranks * EPR)
     unsigned long long local_wait_ns, remote_wait_ns;
     uint8_t* rwk;
     uint8_t* unk;
@@ -150,7 +155,7 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
         const int per_cta = min(nkb, kPrefetchBytesPerCta / (2 * kABytes));
         for (int tile = blockIdx.x; tile < a.EPR * nt1 && tile < (int)gridDim.x; tile += gridDim.x) {
             const int e = tile / nt1, nt = tile % nt1;
-            const int row0 = e * 2 * a.I + nt * 128;
+            const int row0 = (a.ge_base + e) * 2 * a.I + nt * 128;   // this rank's own experts inside the weight arrays
             for (int kb = (int)(threadIdx.x & 31); kb < per_cta; kb += 32) {
                 tma_prefetch_l2_2d(&tm_w1, kb * kBlockK, row0);
                 tma_prefetch_l2_2d(&tm_w1, kb * kBlockK, row0 + a.I);
@@ -486,6 +491,25 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     if (la->dispatch_mode == 2 && !k->L.push_eligible)
         return fail(MXK_ERR_BAD_ARG, "dispatch_mode = 2 (push) needs R <= 64, experts_per_rank <= 256 and R * max_tokens * topk <= 16384");
     k->push = la->dispatch_mode == 2 || (la->dispatch_mode == 0 && k->L.push_eligible);
+    // cross-rank helper scheduling: group-replicated weights, push-mode prologue only
+    k->group_ranks = 1; k->skew_num = 2; k->ge_base = 0; k->w_experts = g.experts_per_rank;
+    const uint8_t *w1 = la->w1, *w2 = la->w2, *w1_sf = la->w1_sf, *w2_sf = la->w2_sf;
+    if (la->group_ranks < 0) return fail(MXK_ERR_BAD_ARG, "group_ranks must be >= 0");
+    if (la->group_ranks > 1 && la->group_weights_ready) {
+        const int G = la->group_ranks;
+        if (G > kSchedMaxGroupRanks || g.R % G) return fail(MXK_ERR_BAD_ARG, "group_ranks must divide R and be at most 16");
+        if (!k->push) return fail(MXK_ERR_BAD_ARG, "helper groups need the push-mode prologue (dispatch_mode 2 or an eligible geometry)");
+        if ((int64_t)G * g.experts_per_rank * (g.R + 1) > kPushMaxCnt)
+            return fail(MXK_ERR_BAD_ARG, "group_ranks * experts_per_rank * (R + 1) exceeds the shared-memory tables of the prologue");
+        if (!la->w1_group || !la->w2_group) return fail(MXK_ERR_BAD_ARG, "w1_group / w2_group must be non-null with group_weights_ready");
+        if ((la->w1_sf_group == nullptr) != (la->w2_sf_group == nullptr) || (la->w1_sf_group == nullptr) != (la->w1_sf == nullptr))
+            return fail(MXK_ERR_BAD_ARG, "group scale planes must be given exactly when w1_sf / w2_sf are");
+        k->group_ranks = G;
+        k->skew_num = la->group_skew_num == 0 ? 2 : (la->group_skew_num < 0 ? 0 : la->group_skew_num);
+        k->ge_base = (g.rank / (g.R / G)) * g.experts_per_rank;
+        k->w_experts = G * g.experts_per_rank;
+        w1 = la->w1_group; w2 = la->w2_group; w1_sf = la->w1_sf_group; w2_sf = la->w2_sf_group;
+    }
     k->R = g.R; k->rank = g.rank; k->EPR = g.experts_per_rank; k->E = g.R * g.experts_per_rank;
     k->topk = g.topk; k->H = g.hidden; k->I = g.intermediate; k->cap = g.max_tokens;
     k->slot_cap = g.slot_capacity ? g.slot_capacity : g.max_tokens;
@@ -497,7 +521,7 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     k->rwk = static_cast<uint8_t*>(la->rwk); k->unk = static_cast<uint8_t*>(la->unk);
     k->unk_peers = la->unk_peers; k->self = la->self; k->peer_bases = la->peer_bases;
     k->topk_idx = la->topk_idx ? la->topk_idx : reinterpret_cast<const int64_t*>(la->self + la->topk_idx_off);
-    k->w1 = la->w1; k->w2 = la->w2; k->w1_sf = la->w1_sf; k->w2_sf = la->w2_sf;
+    k->w1 = w1; k->w2 = w2; k->w1_sf = w1_sf; k->w2_sf = w2_sf;
     k->x_off = la->x_off; k->x_sf_off = la->x_sf_off; k->weights_off = la->weights_off;
     k->y = la->y; k->y_bf16 = la->y_bf16;
     DeviceInfo di;
@@ -541,7 +565,7 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
         const MapSet* hit = nullptr;
         for (int i = 0; i < cache_n; ++i) {
             const MapSet& c = cache[i];
-            if (c.rwk == k.rwk && c.w1 == k.w1 && c.w2 == k.w2 && c.rows == k.L.pool_rows && c.H == k.H && c.I == k.I && c.EPR == k.EPR) {
+            if (c.rwk == k.rwk && c.w1 == k.w1 && c.w2 == k.w2 && c.rows == k.L.pool_rows && c.H == k.H && c.I == k.I && c.EPR == k.w_experts) {
                 hit = &c;
                 break;
             }
@@ -549,11 +573,11 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
         if (!hit) {
             MapSet n;
             std::memset(&n, 0, sizeof(n));
-            n.rwk = k.rwk; n.w1 = k.w1; n.w2 = k.w2; n.rows = k.L.pool_rows; n.H = k.H; n.I = k.I; n.EPR = k.EPR;
+            n.rwk = k.rwk; n.w1 = k.w1; n.w2 = k.w2; n.rows = k.L.pool_rows; n.H = k.H; n.I = k.I; n.EPR = k.w_experts;
             if (int rc = make_map(&n.m[0], k.rwk + k.L.pool_off, k.L.pool_rows + 128, k.H)) return rc;
             if (int rc = make_map(&n.m[1], k.rwk + k.L.ffn_off, k.L.pool_rows + 128, k.I)) return rc;
-            if (int rc = make_map(&n.m[2], k.w1, (int64_t)k.EPR * 2 * k.I, k.H)) return rc;
-            if (int rc = make_map(&n.m[3], k.w2, (int64_t)k.EPR * k.H, k.I)) return rc;
+            if (int rc = make_map(&n.m[2], k.w1, (int64_t)k.w_experts * 2 * k.I, k.H)) return rc;
+            if (int rc = make_map(&n.m[3], k.w2, (int64_t)k.w_experts * k.H, k.I)) return rc;
             cache[cache_next] = n;
             hit = &cache[cache_next];
             cache_next = (cache_next + 1) % 4;
@@ -713,6 +737,7 @@ int mxk_launch_full_static(const MxkLaunchArgs* a, void* stream) {
         last_geom[dev] = g;
     } else {
         // a device-side failure of an earlier call must not be reported for this one
+        static_assert(offsetof(DevFlags, dbg) == offsetof(DevFlags, status) + sizeof(int), "status word, then the expiry counters");
         e = cudaMemsetAsync(rwk + offsetof(DevFlags, status), 0, sizeof(int) * 9, st);
         if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status words)");
     }
@@ -798,6 +823,7 @@ int mxk_read_status(const void* rwk, MxkStatus* out) {
     out->launches = f.current_time;
     out->status = f.status;
     out->n_tasks = f.n_tasks; out->n_l1_tasks = f.n_l1_tasks; out->n_windows = f.n_windows; out->total_rows = f.total_rows;
+    out->helper_on = f.helper_on;
     for (int i = 0; i < 8; ++i) out->dbg[i] = f.dbg[i];
     for (int i = 0; i < 16; ++i) out->ticks[i] = f.ticks[i];
     for (int i = 0; i < 64; ++i) out->trace[i] = f.trace[i];

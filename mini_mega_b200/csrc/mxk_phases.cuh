@@ -341,8 +341,11 @@ __device__ __forceinline__ bool tables_overflow(const KArgs& a, int n_windows, i
 // CTA 0 writes the tables of this launch to global memory (row bases, windows, the task list — L1
 // tasks then L2 tasks, each (expert, n-tile, window) with windows fastest so that concurrent CTAs
 // share a weight tile in L2), clears the gate counters, and publishes the set-up flag.
+struct PushTabs;
+__device__ void publish_helper_lists(const KArgs& a, const PushTabs* T);
+__device__ void helper_counts(const PushTabs* T, int* n_windows, int* n_l1, int* rows);
 __device__ void publish_tables(const KArgs& a, DevFlags* f, long long epoch, const int* s_tot, const int* s_order,
-                               const int* s_first, const int* s_base) {
+                               const int* s_first, const int* s_base, const PushTabs* helper = nullptr) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int EPR = a.EPR;
     const int par = (int)(epoch & 1);
@@ -373,8 +376,11 @@ __device__ void publish_tables(const KArgs& a, DevFlags* f, long long epoch, con
     __syncthreads();   // n_windows of the previous launch was read by every thread above
     l1_done += (size_t)par * a.L.max_windows;
     pool_ready += (size_t)par * a.L.max_windows;
-    const int n_l1 = n_windows * nt1;
-    if (!overflow) {
+    int n_l1 = n_windows * nt1;
+    if (helper) {
+        // cross-rank helper scheduling: the lists are this member's windows, not the owner layout
+        publish_helper_lists(a, helper);
+    } else if (!overflow) {
         // one warp per expert (sorted position p), lanes over its windows and tasks
         const int lane = tid & 31, wid = tid >> 5, nwarps = nthr >> 5;
         for (int p = wid; p < EPR; p += nwarps) {
@@ -399,10 +405,13 @@ __device__ void publish_tables(const KArgs& a, DevFlags* f, long long epoch, con
     if (ts) f->dbg_ts[4] = gtimer_ns();
     if (tid == 0) {
         if (overflow) raise_status(f, MXK_DEV_BAD_TABLE, 3);
+        int rows_out = overflow ? 0 : total_rows;
+        if (helper) helper_counts(helper, &n_windows, &n_l1, &rows_out);
+        f->helper_on = helper ? 1 : 0;
         f->n_windows = n_windows;
         f->n_l1_tasks = n_l1;
         f->n_tasks = n_windows * (nt1 + nt2);
-        f->total_rows = overflow ? 0 : total_rows;
+        f->total_rows = rows_out;
         f->task_ctr[par ^ 1] = 0;   // the next launch's claim counter
     }
     __threadfence();
@@ -583,24 +592,43 @@ constexpr int kPushMaxR = 64;
 constexpr int kPushMaxPairs = 16384;   // routing words of the whole world kept in shared memory per CTA
 constexpr int kPushMaxCnt = 4096;      // EPR * (R + 1)
 
+constexpr int kHelperMaxWin = 512;     // windows one member may be handed (reference: kGsMemberCap, src/group_sched.cuh:150-154)
+
 struct PushTabs {   // tables of this launch, in the control block of shared memory for the whole kernel
     int n_tasks, n_l1, n_windows, total_rows;
     int parts;                    // warps that share the copy of one pool row (each counts into pool_ready)
-    int tot[kPushMaxEPR];         // rows of local expert le
-    int order[kPushMaxEPR];       // expert at sorted position p (descending rows)
-    int first[kPushMaxEPR + 1];   // first window of sorted position p
-    int base[kPushMaxEPR + 1];    // first pool row of local expert le
+    int helper;                   // 1: cross-rank helper scheduling is on, the tables are this member's window list
+    union {
+        struct {                          // owner layout: this rank computes exactly its own experts
+            int tot[kPushMaxEPR];         // rows of local expert le
+            int order[kPushMaxEPR];       // expert at sorted position p (descending rows)
+            int first[kPushMaxEPR + 1];   // first window of sorted position p
+            int base[kPushMaxEPR + 1];    // first pool row of local expert le
+        };
+        struct {                          // helper layout: window i of this member's list
+            int gw[kHelperMaxWin];        // (group expert ge << 16) | window w of that expert
+            int rr[kHelperMaxWin];        // (first pool row << 10) | rows
+        };
+    };
 };
 
 struct PushScratch {   // carved from the operand-tile region, which is idle until the GEMM phase
     int* wid;      // [kPushMaxPairs] routing word of world pair i (expert id or -1), sources in rank order
-    int* cnt;      // [EPR][R]
-    int* prefix;   // [EPR][R+1]
+    int* cnt;      // [GE][R] pairs per (group expert, source); GE = EPR without helper groups
+    int* prefix;   // [GE][R+1]
     int* fw_e;     // [EPR] first window of local expert le
     int* tok;      // [R] tokens of source r in this launch
     int* sb;       // [R+1] first world pair of source r
     int* flag;     // [1] every source arrived in time
+    int* tot;      // [EPR] owner-layout tables of this rank's own experts (published by CTA 0; the
+    int* order;    // [EPR]  copy in PushTabs is what the GEMM phase uses unless helpers are on)
+    int* first;    // [EPR+1]
+    int* base;     // [EPR+1]
+    int* totg;     // [GE] rows per group expert
+    int* gws;      // [GE+1] first entry of group expert ge in widx
+    int* widx;     // [group windows] index of (ge, w) in this member's list, -1 = another member's
 };
+constexpr int kPushMaxGroupWin = 4096;   // windows of a whole helper group (lookup table entries)
 __device__ __forceinline__ PushScratch push_scratch(uint8_t* tiles) {
     PushScratch sc;
     sc.wid = reinterpret_cast<int*>(tiles);
@@ -610,8 +638,17 @@ __device__ __forceinline__ PushScratch push_scratch(uint8_t* tiles) {
     sc.tok = sc.fw_e + kPushMaxEPR;
     sc.sb = sc.tok + kPushMaxR;
     sc.flag = sc.sb + kPushMaxR + 1;
+    sc.tot = sc.flag + 1;
+    sc.order = sc.tot + kPushMaxEPR;
+    sc.first = sc.order + kPushMaxEPR;
+    sc.base = sc.first + kPushMaxEPR + 1;
+    sc.totg = sc.base + kPushMaxEPR + 1;
+    sc.gws = sc.totg + kPushMaxCnt;
+    sc.widx = sc.gws + kPushMaxCnt + 1;
     return sc;
 }
+static_assert((kPushMaxPairs + 4 * kPushMaxCnt + 8 * kPushMaxEPR + 2 * kPushMaxR + kPushMaxGroupWin + 16) * 4 <= 192 * 1024,
+              "push-mode scratch fits the operand-tile region (4 stages of 48 KB)");
 __device__ __forceinline__ int xin_sf_words(int H) { return (((H / 128) + 3) / 4 + 1) & ~1; }   // even: rows stay 16-byte aligned
 __device__ __forceinline__ uint64_t* xin_block(const KArgs& a, void* unk_base, int par, int src) {
     return reinterpret_cast<uint64_t*>(static_cast<uint8_t*>(unk_base) + a.L.xin_off) +
@@ -692,18 +729,89 @@ __device__ void push_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_
     }
 }
 
+__device__ void helper_counts(const PushTabs* T, int* n_windows, int* n_l1, int* rows) {
+    *n_windows = T->n_windows; *n_l1 = T->n_l1; *rows = T->total_rows;
+}
+// Helper layout: window i = (ge, first pool row, rows, w), tasks window-major (kind, i, n-tile, rows).
+__device__ void publish_helper_lists(const KArgs& a, const PushTabs* T) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
+    int4* windows = reinterpret_cast<int4*>(a.rwk + a.L.windows_off);
+    int4* tasks = reinterpret_cast<int4*>(a.rwk + a.L.tasks_off);
+    for (int i = tid; i < T->n_windows; i += nthr)
+        windows[i] = make_int4(T->gw[i] >> 16, T->rr[i] >> 10, T->rr[i] & 1023, T->gw[i] & 0xFFFF);
+    for (int t = tid; t < T->n_tasks; t += nthr) {
+        const int kind = t >= T->n_l1 ? 1 : 0, nt = kind ? nt2 : nt1, tt = kind ? t - T->n_l1 : t;
+        tasks[t] = make_int4(kind, tt / nt, tt % nt, T->rr[tt / nt] & 1023);
+    }
+}
+
+// The member's window list of the helper group, by ONE WARP: the assignment of
+// sched_member_windows (descending cost, (ge, w) ascending, least-loaded member, ties to the owner
+// then the lowest member) with the members' loads held one per lane, so that a window costs a few
+// shuffles instead of a loop over the members.  Every lane returns the same counts.
+__device__ void helper_member_list(const int* totg, int GE, int EPR, int G, int win_cap, int member, PushTabs* T) {
+    const int lane = threadIdx.x & 31;
+    int load = 0, n = 0, rowcur = 0;
+    const int full_cost = sched_window_cost(win_cap);
+    for (int level = full_cost; level >= 1; --level) {
+        for (int ge0 = 0; ge0 < GE; ge0 += 32) {
+            const int ge = ge0 + lane;
+            const int c = ge < GE ? max(totg[ge], 0) : 0;
+            const int n_full = c / win_cap, tail = c % win_cap;
+            int w_lo = 0, w_hi = 0;
+            if (level == full_cost) w_hi = n_full;
+            if (tail != 0 && sched_window_cost(tail) == level) {
+                if (w_hi == 0) w_lo = n_full;
+                w_hi = n_full + 1;
+            }
+            unsigned mask = __ballot_sync(0xFFFFFFFFu, w_hi > w_lo);
+            while (mask) {
+                const int l = __ffs(mask) - 1;
+                mask &= mask - 1;
+                const int g_e = ge0 + l, owner = g_e / EPR;
+                const int lo = __shfl_sync(0xFFFFFFFFu, w_lo, l), hi = __shfl_sync(0xFFFFFFFFu, w_hi, l);
+                const int ctot = __shfl_sync(0xFFFFFFFFu, c, l);
+                for (int w = lo; w < hi; ++w) {
+                    const int mine = lane < G ? load : 0x7FFFFFFF;
+                    int mn = mine;
+#pragma unroll
+                    for (int d = 16; d > 0; d >>= 1) mn = min(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, d));
+                    const unsigned tie = __ballot_sync(0xFFFFFFFFu, mine == mn);
+                    const int best = ((tie >> owner) & 1u) ? owner : __ffs(tie) - 1;
+                    if (lane == best) load += level;
+                    if (best == member) {
+                        const int rows = min(win_cap, ctot - w * win_cap);
+                        if (lane == 0 && n < kHelperMaxWin) {
+                            T->gw[n] = (g_e << 16) | w;
+                            T->rr[n] = (rowcur << 10) | rows;
+                        }
+                        ++n;
+                        rowcur += rows;
+                    }
+                }
+            }
+        }
+    }
+    if (lane == 0) { T->n_windows = n; T->total_rows = rowcur; }
+}
+
 // Owner side, EVERY CTA: wait for all sources' routing words of this launch (this is the
-// cross-rank barrier), count the pairs per (local expert, source) and build the tables in shared
-// memory.  Returns false when a source did not arrive in time or the tables overflow the buffers.
+// cross-rank barrier), count the pairs per (group expert, source) and build the tables in shared
+// memory: the owner-layout tables of this rank's own experts always (scratch; CTA 0 publishes
+// them), and what the GEMM phase runs on — the same tables, or, when helper groups are configured
+// and the group's load is skewed, this member's window list.  Without helper groups the "group" is
+// the rank itself.  Returns false when a source did not arrive in time or the tables overflow.
 __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const PushScratch& sc, PushTabs* T) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int par = (int)(epoch & 1), R = a.R, topk = a.topk, EPR = a.EPR;
+    const int G = a.group_ranks, GE = G * EPR, n_groups = R / G, my_group = a.rank % n_groups, mm = a.rank / n_groups;
     const uint32_t ep = (uint32_t)epoch;
     const uint64_t* mine = xin_block(a, a.unk, par, 0);
     const size_t src_words = (size_t)a.L.xin_src_words;
     const int row_words = a.L.xin_row_words;
     if (tid == 0) *sc.flag = 1;
-    for (int i = tid; i < EPR * R; i += nthr) sc.cnt[i] = 0;
+    for (int i = tid; i < GE * R; i += nthr) sc.cnt[i] = 0;
     for (int r = tid; r < R; r += nthr) {
         const uint64_t* hp = mine + r * src_words;
         uint64_t w = 0;
@@ -750,31 +858,84 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
             }
             const int e = (int)(uint32_t)t;
             sc.wid[i] = e;
-            if (e >= 0 && e / EPR == a.rank) atomicAdd(&sc.cnt[(e % EPR) * R + src[j]], 1);
+            if (e >= 0) {
+                const int owner = e / EPR;
+                if (owner < R && owner % n_groups == my_group)
+                    atomicAdd(&sc.cnt[((owner / n_groups) * EPR + e % EPR) * R + src[j]], 1);
+            }
         }
     }
     __syncthreads();
     const bool ts = a.ticks != 0 && tid == 0 && blockIdx.x == 0;
     if (ts) f->dbg_ts[0] = gtimer_ns();
     // pairs beyond the slot capacity of a (source, expert) row are dropped (src/prologue.cuh:171-174)
-    for (int i = tid; i < EPR * R; i += nthr) sc.cnt[i] = min(sc.cnt[i], a.slot_cap);
+    for (int i = tid; i < GE * R; i += nthr) sc.cnt[i] = min(sc.cnt[i], a.slot_cap);
     __syncthreads();
-    build_tables(a, sc.cnt, sc.prefix, T->tot, T->order, T->first, T->base);
+    for (int ge = tid; ge < GE && G > 1; ge += nthr) {   // prefix rows and totals of the whole group
+        int c = 0;
+        for (int r = 0; r < R; ++r) {
+            sc.prefix[ge * (R + 1) + r] = c;
+            c += sc.cnt[ge * R + r];
+        }
+        sc.prefix[ge * (R + 1) + R] = c;
+        sc.totg[ge] = c;
+    }
+    build_tables(a, sc.cnt + mm * EPR * R, sc.prefix + mm * EPR * (R + 1), sc.tot, sc.order, sc.first, sc.base);
     if (ts) f->dbg_ts[3] = gtimer_ns();
-    const int n_windows = T->first[EPR], total_rows = T->base[EPR];
-    const bool overflow = tables_overflow(a, n_windows, total_rows);
+    const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
+    // helpers on? (the same answer on every member of the group: it depends on the group's totals only)
     if (tid == 0) {
-        const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
-        T->n_windows = overflow ? 0 : n_windows;
-        T->n_l1 = overflow ? 0 : n_windows * nt1;
-        T->n_tasks = overflow ? 0 : n_windows * (nt1 + nt2);
-        T->total_rows = overflow ? 0 : total_rows;
+        int helper = 0;
+        if (G > 1) {
+            long long mx = 0, sum = 0, nwin = 0;
+            for (int ge = 0; ge < GE; ++ge) {
+                const long long c = sc.totg[ge];
+                mx = c > mx ? c : mx;
+                sum += c;
+                nwin += sched_window_count((int)c, a.win_cap);
+            }
+            helper = mx * GE > (long long)a.skew_num * sum && nwin <= kHelperMaxWin && nwin <= kPushMaxGroupWin;
+        }
+        T->helper = helper;
+    }
+    __syncthreads();
+    bool overflow;
+    if (T->helper) {
+        if (tid < 32) helper_member_list(sc.totg, GE, EPR, G, a.win_cap, mm, T);
+        if (tid == 32) {   // first lookup entry of every group expert
+            int c = 0;
+            for (int ge = 0; ge < GE; ++ge) { sc.gws[ge] = c; c += sched_window_count(sc.totg[ge], a.win_cap); }
+            sc.gws[GE] = c;
+        }
+        __syncthreads();
+        for (int i = tid; i < sc.gws[GE]; i += nthr) sc.widx[i] = -1;
+        __syncthreads();
+        for (int i = tid; i < T->n_windows; i += nthr) sc.widx[sc.gws[T->gw[i] >> 16] + (T->gw[i] & 0xFFFF)] = i;
+        overflow = tables_overflow(a, T->n_windows, T->total_rows);
+        if (tid == 0) {
+            if (overflow) { T->n_windows = 0; T->total_rows = 0; }
+            T->n_l1 = T->n_windows * nt1;
+            T->n_tasks = T->n_windows * (nt1 + nt2);
+        }
+    } else {
+        for (int i = tid; i < EPR; i += nthr) { T->tot[i] = sc.tot[i]; T->order[i] = sc.order[i]; }
+        for (int i = tid; i <= EPR; i += nthr) { T->first[i] = sc.first[i]; T->base[i] = sc.base[i]; }
+        const int n_windows = sc.first[EPR], total_rows = sc.base[EPR];
+        overflow = tables_overflow(a, n_windows, total_rows);
+        if (tid == 0) {
+            T->n_windows = overflow ? 0 : n_windows;
+            T->n_l1 = overflow ? 0 : n_windows * nt1;
+            T->n_tasks = overflow ? 0 : n_windows * (nt1 + nt2);
+            T->total_rows = overflow ? 0 : total_rows;
+        }
+        for (int p = tid; p < EPR; p += nthr) sc.fw_e[sc.order[p]] = sc.first[p];
+    }
+    if (tid == 0) {
         // a pool row is copied by `parts` warps when there are warps to spare, so that the copy of a
         // row costs one round trip to the staging area instead of several
         const int nwarps = (int)gridDim.x * (nthr >> 5);
         T->parts = W <= nwarps ? 4 : (W <= 2 * nwarps ? 2 : 1);
     }
-    for (int p = tid; p < EPR; p += nthr) sc.fw_e[T->order[p]] = T->first[p];
     __syncthreads();
     return *sc.flag != 0 && !overflow;
 }
@@ -785,27 +946,32 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
 __device__ void push_publish(const KArgs& a, DevFlags* f, long long epoch, const PushScratch& sc, const PushTabs* T) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int par = (int)(epoch & 1), R = a.R, EPR = a.EPR;
+    const int mm = a.rank / (R / a.group_ranks);
+    const int* cnt = sc.cnt + mm * EPR * R;                 // this rank's own experts inside the group tables
+    const int* prefix = sc.prefix + mm * EPR * (R + 1);
     int* g_prefix = reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off);
-    for (int i = tid; i < EPR * (R + 1); i += nthr) g_prefix[i] = sc.prefix[i];
+    for (int i = tid; i < EPR * (R + 1); i += nthr) g_prefix[i] = prefix[i];
     uint64_t* recv = reinterpret_cast<uint64_t*>(a.unk + a.L.expert_recv_counts_off) + (size_t)par * R * a.L.recv_stride;
     for (int i = tid; i < EPR * R; i += nthr) {
         const int le = i / R, r = i % R;
-        recv[(size_t)r * a.L.recv_stride + le] = tagged((uint32_t)sc.cnt[i], epoch);
+        recv[(size_t)r * a.L.recv_stride + le] = tagged((uint32_t)cnt[i], epoch);
     }
     for (int r = tid; r < R; r += nthr) {   // the reference's checksum word of a count row (src/prologue.cuh:248-255)
         uint32_t csum = 0;
-        for (int le = 0; le < EPR; ++le) csum += (uint32_t)sc.cnt[le * R + r];
+        for (int le = 0; le < EPR; ++le) csum += (uint32_t)cnt[le * R + r];
         recv[(size_t)r * a.L.recv_stride + EPR] = tagged(~(csum + 1u), epoch);
     }
-    publish_tables(a, f, epoch, T->tot, T->order, T->first, T->base);
+    publish_tables(a, f, epoch, sc.tot, sc.order, sc.first, sc.base, T->helper ? T : nullptr);
 }
 
-// Owner side: one WARP per (world pair whose expert lives here, part of its row).  The pair's slot
-// inside the (expert, source) row is the number of earlier pairs of the same source with the same
-// expert — the ascending-pair-index order of the pull-mode route — which fixes the pool row; the
-// warp then copies its part of the row's words from the staging area into the pool (tags
-// stripped); part 0 also stores the scale bytes and the staged (source, token, k, weight).  Every
-// part counts itself into the window's pool_ready.
+// Owner / helper side: one WARP per (world pair whose row this rank computes, part of its row).
+// The pair's slot inside the (expert, source) row is the number of earlier pairs of the same
+// source with the same expert — the ascending-pair-index order of the pull-mode route — which
+// fixes its place among the expert's rows; the warp then copies its part of the row into the
+// pool: from the staging area when the expert is this rank's own (tags stripped), from the
+// source rank's input block when it computes the window for another member of its helper group
+// (that member received the pushed row, not this one).  Part 0 also stores the scale bytes and
+// the staged (source, token, k, weight).  Every part counts itself into the window's pool_ready.
 // `do_tables`: also write the pair index into src_index_table (same words a pull-mode source writes).
 __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, const PushScratch& sc, const PushTabs* T,
                               const bool do_tables, const bool do_rows) {
@@ -815,81 +981,126 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
     // CTA 0 publishes the tables afterwards: it takes the last items, the last CTA the first ones
     const int gwarp = ((int)gridDim.x - 1 - (int)blockIdx.x) * nwarps_cta + (threadIdx.x >> 5);
     const int par = (int)(epoch & 1), R = a.R, topk = a.topk, EPR = a.EPR, H = a.H;
+    const int n_groups = R / a.group_ranks, my_group = a.rank % n_groups;
     const uint32_t ep = (uint32_t)epoch;
     const int W = sc.sb[R], P = T->parts;
+    const bool helper = T->helper != 0;
     const uint64_t* mine = xin_block(a, a.unk, par, 0);
     const size_t src_words = (size_t)a.L.xin_src_words;
-    const int row_words = a.L.xin_row_words, sfw = xin_sf_words(H), sfw_real = (H / 128 + 3) / 4;
+    const int row_words = a.L.xin_row_words, sfw = xin_sf_words(H), kb = H / 128, sfw_real = (kb + 3) / 4;
     uint64_t* tbl = reinterpret_cast<uint64_t*>(a.unk + a.L.src_index_table_off) + (size_t)par * EPR * R * a.slot_cap;
     uint8_t* pool = a.rwk + a.L.pool_off;
     uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
     int4* meta = reinterpret_cast<int4*>(a.rwk + a.L.row_meta_off);
     uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off) + (size_t)par * a.L.max_windows;
-    const int n16 = H / 8, per_part = n16 / P;   // H % 256 == 0: per_part is a multiple of 8
+    const int n16 = H / 8, per_part = n16 / P;   // 8-byte row units; H % 256 == 0: per_part is a multiple of 8
     for (int it = gwarp; it < W * P; it += nwarps) {
         const int i = it / P, part = it % P;
         const int e = sc.wid[i];
-        if (e < 0 || e / EPR != a.rank) continue;   // uniform over the warp
+        if (e < 0) continue;                         // (every `continue` here is uniform over the warp)
+        const int owner = e / EPR;
+        if (owner >= R || owner % n_groups != my_group) continue;
+        const bool own = owner == a.rank;
+        if (!own && !helper) continue;
+        const int ge = (owner / n_groups) * EPR + e % EPR, le = e % EPR;
         const int src = push_src_of(sc.sb, R, i);
-        const int p = i - sc.sb[src], le = e % EPR;
+        const int p = i - sc.sb[src];
         const int token = p / topk, k = p % topk;
         const uint64_t* row = mine + src * src_words + 16 + (size_t)token * row_words;
-        // this part's row words first (two per 16-byte load, up to eight loads in flight per lane):
-        // they do not depend on the slot, which is counted while they travel
         const uint64_t* xs = row + 2 * topk + sfw;
+        const uint8_t* peer = a.peer_bases[src];     // the source's input block, for rows of other members' experts
+        const uint2* px = reinterpret_cast<const uint2*>(peer + a.x_off + (size_t)token * H);
         const int u_lo = part * per_part, u_hi = u_lo + per_part;
-        ulonglong2 v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (do_rows && u_lo + lane + 32 * j < u_hi) v[j] = ld_relaxed_sys_v2_u64(xs + 2 * (u_lo + lane + 32 * j));
-        uint64_t wword = 0, sfword = 0;
         const bool lead = do_rows && part == 0;
-        if (lead && lane == 0) wword = ld_relaxed_sys_u64(row + topk + k);
-        if (lead && a.scaled && lane < sfw_real) sfword = ld_relaxed_sys_u64(row + 2 * topk + lane);
+        // this part's row words first (up to eight loads in flight per lane): they do not depend on
+        // the slot, which is counted while they travel
+        ulonglong2 v[8];
+        uint64_t wword = 0, sfword = 0;
+        if (own) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (do_rows && u_lo + lane + 32 * j < u_hi) v[j] = ld_relaxed_sys_v2_u64(xs + 2 * (u_lo + lane + 32 * j));
+            if (lead && lane == 0) wword = ld_relaxed_sys_u64(row + topk + k);
+            if (lead && a.scaled && lane < sfw_real) sfword = ld_relaxed_sys_u64(row + 2 * topk + lane);
+        }
         int c = 0;
         for (int j = lane; j < p; j += 32) c += sc.wid[sc.sb[src] + j] == e ? 1 : 0;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, d);
         const int slot = c;
         if (slot >= a.slot_cap) continue;           // over capacity: dropped
-        const int gl = sc.prefix[le * (R + 1) + src] + slot;
-        const int g = T->base[le] + gl;
-        if (do_tables && part == 0 && lane == 0) tbl[((size_t)le * R + src) * a.slot_cap + slot] = tagged((uint32_t)p, epoch);
+        const int gl = sc.prefix[ge * (R + 1) + src] + slot;
+        if (own && do_tables && part == 0 && lane == 0) tbl[((size_t)le * R + src) * a.slot_cap + slot] = tagged((uint32_t)p, epoch);
+        int g, ready_idx;
+        if (helper) {
+            const int li = sc.widx[sc.gws[ge] + gl / a.win_cap];
+            if (li < 0) continue;                   // another member computes this window
+            g = (T->rr[li] >> 10) + gl % a.win_cap;
+            ready_idx = li;
+        } else {
+            g = T->base[le] + gl;
+            ready_idx = sc.fw_e[le] + gl / a.win_cap;
+        }
         if (!do_rows) continue;
         bool ok = true;
-        auto settle = [&](const uint64_t* wp, uint64_t w) -> uint32_t {   // the word, polled until it is this launch's
-            if ((uint32_t)(w >> 32) != ep &&
-                !spin_until([&] { w = ld_relaxed_sys_u64(wp); return (uint32_t)(w >> 32) == ep; }, a.remote_wait_ns, nullptr))
-                ok = false;
-            return (uint32_t)w;
-        };
         uint2* drow = reinterpret_cast<uint2*>(pool + (size_t)g * H);
-        for (int u0 = u_lo + lane; u0 < u_hi; u0 += 32 * 8) {
-            if (u0 != u_lo + lane) {   // rows wider than 8 x 32 units per part: further batches
+        if (own) {
+            auto settle = [&](const uint64_t* wp, uint64_t w) -> uint32_t {   // the word, polled until it is this launch's
+                if ((uint32_t)(w >> 32) != ep &&
+                    !spin_until([&] { w = ld_relaxed_sys_u64(wp); return (uint32_t)(w >> 32) == ep; }, a.remote_wait_ns, nullptr))
+                    ok = false;
+                return (uint32_t)w;
+            };
+            for (int u0 = u_lo + lane; u0 < u_hi; u0 += 32 * 8) {
+                if (u0 != u_lo + lane) {   // rows wider than 8 x 32 units per part: further batches
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (u0 + 32 * j < u_hi) v[j] = ld_relaxed_sys_v2_u64(xs + 2 * (u0 + 32 * j));
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int u = u0 + 32 * j;
+                    if (u >= u_hi) continue;
+                    ulonglong2 t = v[j];
+                    if (((uint32_t)(t.x >> 32) != ep || (uint32_t)(t.y >> 32) != ep) &&
+                        !spin_until([&] { t = ld_relaxed_sys_v2_u64(xs + 2 * u);
+                                          return (uint32_t)(t.x >> 32) == ep && (uint32_t)(t.y >> 32) == ep; },
+                                    a.remote_wait_ns, nullptr))
+                        ok = false;
+                    drow[u] = make_uint2((uint32_t)t.x, (uint32_t)t.y);
+                }
+            }
+            if (lead) {
+                if (a.scaled) {
+                    uint32_t* dsf = reinterpret_cast<uint32_t*>(pool_sf + (size_t)g * a.L.sf_stride_h);
+                    if (lane < a.L.sf_stride_h / 4)   // sf_stride_h <= 64 bytes: one word per lane
+                        dsf[lane] = lane < sfw_real ? settle(row + 2 * topk + lane, sfword) : 0x7F7F7F7Fu;
+                }
+                if (lane == 0) meta[g] = make_int4(src, token, k, (int)settle(row + topk + k, wword));
+            }
+        } else {
+            // a window of another member's expert: the row comes from the source rank's input block
+            // (the inputs of a launch stay put until the source's own reduce is done, and that waits
+            // for this row's result)
+            for (int u0 = u_lo + lane; u0 < u_hi; u0 += 32 * 8) {
+                uint2 q[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
-                    if (u0 + 32 * j < u_hi) v[j] = ld_relaxed_sys_v2_u64(xs + 2 * (u0 + 32 * j));
-            }
+                    if (u0 + 32 * j < u_hi) q[j] = ld_relaxed_sys_v2_u32(px + u0 + 32 * j);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int u = u0 + 32 * j;
-                if (u >= u_hi) continue;
-                ulonglong2 t = v[j];
-                if (((uint32_t)(t.x >> 32) != ep || (uint32_t)(t.y >> 32) != ep) &&
-                    !spin_until([&] { t = ld_relaxed_sys_v2_u64(xs + 2 * u);
-                                      return (uint32_t)(t.x >> 32) == ep && (uint32_t)(t.y >> 32) == ep; },
-                                a.remote_wait_ns, nullptr))
-                    ok = false;
-                drow[u] = make_uint2((uint32_t)t.x, (uint32_t)t.y);
+                for (int j = 0; j < 8; ++j)
+                    if (u0 + 32 * j < u_hi) drow[u0 + 32 * j] = q[j];
             }
-        }
-        if (lead) {
-            if (a.scaled) {
-                uint32_t* dsf = reinterpret_cast<uint32_t*>(pool_sf + (size_t)g * a.L.sf_stride_h);
-                if (lane < a.L.sf_stride_h / 4)   // sf_stride_h <= 64 bytes: one word per lane
-                    dsf[lane] = lane < sfw_real ? settle(row + 2 * topk + lane, sfword) : 0x7F7F7F7Fu;
+            if (lead) {
+                if (a.scaled) {
+                    const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
+                    for (int b = lane; b < a.L.sf_stride_h; b += 32)
+                        pool_sf[(size_t)g * a.L.sf_stride_h + b] = b < kb ? ld_relaxed_sys_u8(ssf + b) : (uint8_t)127;
+                }
+                if (lane == 0)
+                    meta[g] = make_int4(src, token, k, (int)ld_relaxed_sys(reinterpret_cast<const uint32_t*>(peer + a.weights_off) +
+                                                                           (size_t)token * topk + k));
             }
-            if (lane == 0) meta[g] = make_int4(src, token, k, (int)settle(row + topk + k, wword));
         }
         if (!__all_sync(0xFFFFFFFFu, ok ? 1 : 0) && lane == 0) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 2);
         // this part of the row is complete: every lane makes its stores visible at GPU scope and to
@@ -897,7 +1108,7 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
         __threadfence();
         fence_proxy_async_global();
         __syncwarp();
-        if (lane == 0) red_release_gpu_add(pool_ready + sc.fw_e[le] + gl / a.win_cap, 1u);
+        if (lane == 0) red_release_gpu_add(pool_ready + ready_idx, 1u);
     }
 }
 

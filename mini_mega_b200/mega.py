@@ -81,6 +81,7 @@ class SymmBuffer:
                  intermediate_hidden: int, num_shared_experts: int = 0, mma_type: str = "fp8xfp8",
                  activation: str = "swiglu", grid_num_tokens: Optional[int] = None,
                  expert_window: Optional[int] = None, slot_capacity: int = 0, dispatch_mode: int = 0,
+                 group_ranks: int = 0, group_skew_num: int = 0,
                  _local_world: Optional[Tuple[int, int]] = None):
         if activation != "swiglu":
             raise ValueError(f"Only `swiglu` activation is supported, got `{activation}`")
@@ -112,6 +113,12 @@ class SymmBuffer:
         self.expert_window = int(expert_window)
         self.slot_capacity = int(slot_capacity)
         self.dispatch_mode = int(dispatch_mode)
+        # cross-rank helper scheduling for skewed routing (reference: MX_GROUP_SCHED): ranks per helper
+        # group and the skew threshold; the group's weights are handed to the layer call
+        self.group_ranks = int(group_ranks)
+        self.group_skew_num = int(group_skew_num)
+        if self.group_ranks > 1 and world_size % self.group_ranks:
+            raise ValueError("group_ranks must divide the group size")
         self.launch_count = 0
         self.device = torch.cuda.current_device()
         self.layout = compute_layout(world_size, rank, self.num_experts_per_rank, self.num_topk, self.hidden,
@@ -238,7 +245,7 @@ class SymmBuffer:
                     y_f32: Optional[torch.Tensor] = None, expert_window: Optional[int] = None,
                     max_spins: int = 0, grid: int = 0, skip_combine: int = 0,
                     cta_pair: Optional[int] = None, dispatch_mode: Optional[int] = None,
-                    packed: bool = False) -> MxkLaunchArgs:
+                    packed: bool = False, group_weights=None) -> MxkLaunchArgs:
         L = self.layout
         a = MxkLaunchArgs()
         a.R, a.rank, a.tokens = self.world_size, self.rank, int(num_tokens)
@@ -267,7 +274,21 @@ class SymmBuffer:
         # prologue protocol (0 automatic, 1 pull, 2 push): a property of the buffer because every
         # rank of a launch must use the same one
         a.dispatch_mode = int(self.dispatch_mode if dispatch_mode is None else dispatch_mode)
+        if group_weights is not None and self.group_ranks > 1:
+            for name, w in (("w1", group_weights[0]), ("w2", group_weights[1])):
+                data, sf = w if isinstance(w, tuple) else (w, None)
+                setattr(a, name + "_group", data.data_ptr())
+                setattr(a, name + "_sf_group", None if sf is None else sf.data_ptr())
+            a.group_ranks, a.group_skew_num, a.group_weights_ready = self.group_ranks, self.group_skew_num, 1
         return a
+
+    def group_members(self):
+        """Ranks of this rank's helper group in member order (interleaved groups: group =
+        rank % n_groups, member = rank // n_groups; reference src/group_sched.cuh:61-80)."""
+        if self.group_ranks <= 1:
+            return [self.rank]
+        n_groups = self.world_size // self.group_ranks
+        return [self.rank % n_groups + m * n_groups for m in range(self.group_ranks)]
 
     def destroy(self):
         lib = _lib.lib()
@@ -288,12 +309,13 @@ def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_ran
                                  use_fp8_dispatch: Optional[bool] = None, mma_type: str = "fp8xfp8",
                                  activation: str = "swiglu", num_tokens: Optional[int] = None,
                                  expert_window: Optional[int] = None, slot_capacity: int = 0,
-                                 dispatch_mode: int = 0) -> SymmBuffer:
+                                 dispatch_mode: int = 0, group_ranks: int = 0, group_skew_num: int = 0) -> SymmBuffer:
     if use_fp8_dispatch is not None:
         assert use_fp8_dispatch == (mma_type.split("x")[0] == "fp8")
     return SymmBuffer(group, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
                       num_shared_experts, mma_type=mma_type, activation=activation, grid_num_tokens=num_tokens,
-                      expert_window=expert_window, slot_capacity=slot_capacity, dispatch_mode=dispatch_mode)
+                      expert_window=expert_window, slot_capacity=slot_capacity, dispatch_mode=dispatch_mode,
+                      group_ranks=group_ranks, group_skew_num=group_skew_num)
 
 
 WeightArg = Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]
@@ -333,6 +355,33 @@ def transform_weights_for_mega_moe(l1_weights: WeightArg, l2_weights: WeightArg,
     return l1, l2
 
 
+def gather_group_weights(sym_buffer: SymmBuffer, l1_weights, l2_weights):
+    """The weights of every expert of this rank's helper group, in group order (member m's
+    experts at [m * EPR, (m + 1) * EPR)), collected from the members with broadcasts over the
+    buffer's process group (reference: the chunked all_gather into rwk->ld.w1g / w2g,
+    torch/mxmegakernel/mega/__init__.py:370-385).  Every rank of the group must call it; the
+    result is what ``fp8_mega_moe(..., group_weights=...)`` takes.  Memory: group_ranks times this
+    rank's own weights."""
+    G, R = sym_buffer.group_ranks, sym_buffer.world_size
+    if G <= 1:
+        return None
+    members = sym_buffer.group_members()
+    scaled = isinstance(l1_weights, tuple)
+    own = [t for w in (l1_weights, l2_weights) for t in (w if scaled else (w,))]
+    parts = [[None] * G for _ in own]
+    scratch = [torch.empty_like(t) for t in own]
+    for r in range(R):
+        mine = r in members
+        for i, t in enumerate(own):
+            buf = t if r == sym_buffer.rank else (torch.empty_like(t) if mine else scratch[i])
+            dist.broadcast(buf, src=dist.get_global_rank(sym_buffer.group, r) if sym_buffer.group is not None else r,
+                           group=sym_buffer.group)
+            if mine:
+                parts[i][members.index(r)] = buf
+    cat = [torch.cat(p, dim=0).contiguous() for p in parts]
+    return ((cat[0], cat[1]), (cat[2], cat[3])) if scaled else (cat[0], cat[1])
+
+
 def _quantize_input(sym_buffer: "SymmBuffer", num_tokens: int, scaled: bool) -> None:
     """bf16xfp8 buffers: quantise `x` (bf16) into the region peers pull from, on the launch stream."""
     if sym_buffer.mma_type != "bf16xfp8" or num_tokens == 0:
@@ -366,10 +415,13 @@ def _check_weights(sym_buffer: SymmBuffer, l1, l2):
 def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
                  cumulative_local_expert_recv_stats=None, activation: str = "swiglu", activation_clamp=None,
                  expert_window: Optional[int] = None, max_spins: int = 0, cta_pair: Optional[int] = None,
-                 packed_inputs: bool = False) -> None:
+                 packed_inputs: bool = False, group_weights=None) -> None:
     """One MoE layer: ``y[t] = sum_k w_k * W2_e SwiGLU(W1_e x_t)`` for this rank's
     ``y.shape[0]`` tokens, inputs taken from ``sym_buffer.x / x_sf / topk_idx / topk_weights``
     (or, with ``packed_inputs``, from the packed image described by ``SymmBuffer.packed_layout``).
+    ``group_weights`` (from ``gather_group_weights``) on a buffer created with ``group_ranks`` > 1
+    switches the cross-rank helper scheduling on: launches whose group load is skewed spread the
+    group's (expert, window) units over its members.
     Every rank of the group must call it the same number of times (a rank with zero
     tokens still launches so that it joins the barrier and serves its experts)."""
     _check_buffer(sym_buffer, "fp8_mega_moe")
@@ -384,7 +436,7 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
     lib = _lib.lib()
     _quantize_input(sym_buffer, num_tokens, isinstance(l1_weights, tuple) and l1_weights[1] is not None)
     a = sym_buffer.launch_args(num_tokens, l1_weights, l2_weights, y_bf16=y, expert_window=expert_window,
-                               max_spins=max_spins, cta_pair=cta_pair, packed=packed_inputs)
+                               max_spins=max_spins, cta_pair=cta_pair, packed=packed_inputs, group_weights=group_weights)
     if num_tokens == 0:  # nothing to reduce, but the rank still serves its experts
         check(lib.mxk_launch_compute(C.byref(a), _stream_ptr()), "mxk_launch_compute")
     else:

@@ -565,6 +565,47 @@ def layer_world(case: Case, slot_cap: Optional[int] = None, threads: int = 8,
     return st
 
 
+def helper_world(case: Case, states: List[RankState], group_ranks: int, win_cap: int, skew_num: int = 2,
+                 max_windows: int = 512):
+    """Cross-rank helper scheduling of the reference (src/compute.cuh:700-835, src/group_sched.cuh):
+    ranks form interleaved groups (group = rank % n_groups, member = rank // n_groups); when a
+    group's load is skewed (max * n_experts > skew_num * sum; skew_num 0 = always) its (expert,
+    window) units are spread over the members by gs_schedule_member, and a member computes the
+    windows it was given — its own and other members' — in the order of its list, the rows of a
+    window keeping the owner's pool order.  Returns per rank a dict: on (bool), windows
+    [(ge, w, rows)], meta [rows][3] (src, token, k) in the rank's pool order; ranks of groups that
+    are not skewed keep the owner layout (on = False, meta = the owner's)."""
+    R, EPR = case.R, case.EPR
+    n_groups = R // group_ranks
+    out = [None] * R
+    for g in range(n_groups):
+        members = [g + m * n_groups for m in range(group_ranks)]
+        tot = np.zeros(group_ranks * EPR, np.int32)
+        for m, r in enumerate(members):
+            tot[m * EPR:(m + 1) * EPR] = states[r].prefix_tbl[:, R]
+        skewed = int(tot.max()) * tot.size > skew_num * int(tot.sum())
+        for m, r in enumerate(members):
+            if not skewed:
+                out[r] = {"on": False, "windows": [], "meta": states[r].meta.copy()}
+                continue
+            ge = np.zeros(max_windows, np.int32)
+            w = np.zeros(max_windows, np.int32)
+            n = lib().orc_gs_schedule_member(tot, EPR, group_ranks, win_cap, m, ge, w, max_windows)
+            if n > max_windows:
+                raise ValueError("member window list exceeds its capacity")
+            wins, meta = [], []
+            for i in range(n):
+                owner = members[int(ge[i]) // EPR]
+                le = int(ge[i]) % EPR
+                rows = min(win_cap, int(tot[ge[i]]) - int(w[i]) * win_cap)
+                a0 = int(states[owner].row_base[le]) + int(w[i]) * win_cap
+                wins.append((int(ge[i]), int(w[i]), rows))
+                meta.append(states[owner].meta[a0:a0 + rows])
+            out[r] = {"on": True, "windows": wins,
+                      "meta": np.concatenate(meta) if meta else np.zeros((0, 3), np.int32)}
+    return out
+
+
 def rel_l2(got: np.ndarray, want: np.ndarray) -> float:
     """max over rows of ||got-want||_2 / ||want||_2 (rows with zero norm compare absolutely)."""
     got = np.asarray(got, np.float64)

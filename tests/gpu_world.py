@@ -38,12 +38,23 @@ def load_inputs(case, bufs):
 
 
 class World:
-    def __init__(self, case, slot_capacity=0, expert_window=128, dispatch_mode=0):
+    def __init__(self, case, slot_capacity=0, expert_window=128, dispatch_mode=0, group_ranks=0, group_skew_num=0):
         self.case = case
         self.bufs = mm.SymmBuffer.local_world(case.R, case.E, case.cap, case.topk, case.H, case.I,
                                               slot_capacity=slot_capacity, expert_window=expert_window,
-                                              dispatch_mode=dispatch_mode)
+                                              dispatch_mode=dispatch_mode, group_ranks=group_ranks,
+                                              group_skew_num=group_skew_num)
         self.weights = [dev_weights(case, r) for r in range(case.R)]
+        # helper groups: every member holds the weights of all its group's experts, in member order
+        self.group_weights = [None] * case.R
+        if group_ranks > 1:
+            for r, b in enumerate(self.bufs):
+                ws = [self.weights[m] for m in b.group_members()]
+                if case.scaled:
+                    self.group_weights[r] = tuple((torch.cat([w[i][0] for w in ws]).contiguous(),
+                                                   torch.cat([w[i][1] for w in ws]).contiguous()) for i in range(2))
+                else:
+                    self.group_weights[r] = tuple(torch.cat([w[i] for w in ws]).contiguous() for i in range(2))
         self.y = [torch.zeros((max(case.tokens[r], 1), case.H), dtype=torch.bfloat16, device="cuda")
                   for r in range(case.R)]
         self.y32 = [torch.zeros((max(case.tokens[r], 1), case.H), dtype=torch.float32, device="cuda")
@@ -52,7 +63,8 @@ class World:
 
     def args(self, r, **kw):
         l1, l2 = self.weights[r]
-        return self.bufs[r].launch_args(self.case.tokens[r], l1, l2, y_bf16=self.y[r], y_f32=self.y32[r], **kw)
+        return self.bufs[r].launch_args(self.case.tokens[r], l1, l2, y_bf16=self.y[r], y_f32=self.y32[r],
+                                        group_weights=self.group_weights[r], **kw)
 
     def run(self, phases=PHASES, **kw):
         lib = _lib.lib()

@@ -109,6 +109,49 @@ def run_gpu():
         dist.barrier()
         del g
         buf.destroy()
+    # cross-rank helper scheduling over real peer memory: one helper group spanning the world, helpers
+    # forced on; a member computes windows of the other rank's experts from its weight replica, pulling
+    # the rows from the source rank's input block; tables of the owner stay exact, pool rows follow the
+    # member's window list, y within tolerance; two launches on the same buffers
+    if world <= 16:
+        buf = None
+        for ci in (0, 1):
+            case = all_cases[ci]
+            if buf is None:
+                buf = mm.get_symm_buffer_for_mega_moe(group, case.E, case.cap, case.topk, case.H, case.I, dispatch_mode=2,
+                                                      expert_window=32, group_ranks=world, group_skew_num=-1)
+            T = case.tokens[rank]
+            buf.x.view(torch.uint8).copy_(torch.from_numpy(case.x[rank]))
+            buf.x_sf.copy_(torch.from_numpy(case.x_sf[rank]))
+            buf.topk_idx.copy_(torch.from_numpy(case.topk_idx[rank]))
+            buf.topk_weights.copy_(torch.from_numpy(case.topk_w[rank]))
+            sl = slice(rank * case.EPR, (rank + 1) * case.EPR)
+            l1, l2 = mm.transform_weights_for_mega_moe(
+                (torch.from_numpy(case.w1[sl]).cuda(), torch.from_numpy(case.w1_sf[sl]).cuda()),
+                (torch.from_numpy(case.w2[sl]).cuda(), torch.from_numpy(case.w2_sf[sl]).cuda()))
+            gw = mm.gather_group_weights(buf, l1, l2)
+            assert torch.equal(gw[0][0].cpu(), torch.from_numpy(case.w1)) and torch.equal(gw[1][1].cpu(), torch.from_numpy(case.w2_sf))
+            y = torch.zeros((T, case.H), dtype=torch.bfloat16, device="cuda")
+            torch.cuda.synchronize()
+            dist.barrier()
+            mm.fp8_mega_moe(y, l1, l2, buf, group_weights=gw)
+            torch.cuda.synchronize()
+            st = buf.status()
+            assert st.status == 0, f"rank {rank} helpers case {ci}: device status {st.status} dbg {list(st.dbg)}"
+            ref = refs[ci]
+            want = orc.helper_world(case, ref, world, 32, 0)[rank]
+            assert bool(st.helper_on) == want["on"]
+            rows = want["meta"].shape[0]
+            assert st.total_rows == rows
+            assert np.array_equal(buf.table("prefix_tbl").cpu().numpy(), ref[rank].prefix_tbl)
+            assert np.array_equal(buf.table("row_meta")[:rows, :3].cpu().numpy(), want["meta"])
+            assert np.array_equal(buf.table("pool")[:rows].cpu().numpy(), case.x[want["meta"][:, 0], want["meta"][:, 1]])
+            if T:
+                err = orc.rel_l2(y.float().cpu().numpy(), ref[rank].y)
+                worst = max(worst, err)
+                assert err <= 1e-2, f"rank {rank} helpers case {ci}: relative L2 {err}"
+            dist.barrier()
+        buf.destroy()
     print(f"MP_OK rank={rank} worst_rel_l2={worst:.3e}", flush=True)
     dist.destroy_process_group()
 

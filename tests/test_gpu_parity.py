@@ -198,3 +198,48 @@ def test_decode_world_full_width(mode):
     stage checks, y within 1e-2."""
     case = orc.gen_case_bytes(8, 4, 8, 6144, 2048, 16, seed=42)
     _run_case(case, dispatch_mode=mode, ref=orc.layer_world(case, threads=16))
+
+
+@pytest.mark.parametrize("group_ranks,skew_num", [(4, -1), (2, -1), (4, 0)])
+def test_helper_groups_world(group_ranks, skew_num):
+    """Cross-rank helper scheduling (reference: MX_GROUP_SCHED, src/compute.cuh:700-835): a world of 4
+    ranks with Zipf-skewed routing and 32-row windows, helper groups of 4 (one group) and of 2 (two
+    interleaved groups), helpers forced on (-1) or decided by the reference's skew test (0 -> 2).
+    Owner-side tables stay exact; every rank's window list equals the deterministic LPT of
+    gs_schedule_member; every pool row holds the (source, token, k) and the bytes the oracle's model
+    puts there, whether the rank owns the expert or helps with it; y within 1e-2."""
+    from gpu_world import World, assert_status_ok, check_tables
+    case = orc.gen_case(4, 4, 4, 1024, 512, [60, 50, 40, 64], seed=61, routing="zipf", scaled=True)
+    ref = orc.layer_world(case)
+    want = orc.helper_world(case, ref, group_ranks, 32, 0 if skew_num < 0 else 2)
+    assert any(h["on"] for h in want)
+    w = World(case, expert_window=32, dispatch_mode=2, group_ranks=group_ranks, group_skew_num=skew_num)
+    try:
+        w.run()
+        assert_status_ok(w)
+        check_tables(w, ref)
+        moved = 0
+        for r in range(case.R):
+            st = w.bufs[r].status()
+            h = want[r]
+            assert bool(st.helper_on) == h["on"], f"rank {r}: helper_on {st.helper_on}, expected {h['on']}"
+            meta = w.table(r, "row_meta")
+            rows = h["meta"].shape[0]
+            assert st.total_rows == rows
+            assert np.array_equal(meta[:rows, :3], h["meta"]), f"rank {r}: pool rows differ from the member's window list"
+            pool = w.table(r, "pool")[:rows]
+            assert np.array_equal(pool, case.x[h["meta"][:, 0], h["meta"][:, 1]])
+            assert np.array_equal(w.table(r, "pool_sf")[:rows, : case.H // 128], case.x_sf[h["meta"][:, 0], h["meta"][:, 1]])
+            if h["on"]:
+                win = w.table(r, "windows")[: len(h["windows"])]
+                assert st.n_windows == len(h["windows"])
+                assert np.array_equal(win[:, [0, 3, 2]], np.array(h["windows"], np.int32).reshape(-1, 3))
+                mm_ = w.bufs[r].group_members().index(r)
+                moved += sum(1 for ge, _, _ in h["windows"] if ge // case.EPR != mm_)
+            _reduce_check(w, r)
+            T = case.tokens[r]
+            err = orc.rel_l2(w.y32[r][:T].cpu().numpy(), ref[r].y)
+            assert err <= 1e-2, f"rank {r}: end-to-end relative L2 {err}"
+        assert moved > 0, "no window was computed by a helper: the case does not exercise the path"
+    finally:
+        w.destroy()
