@@ -305,14 +305,18 @@ class Job:
     """One geometry on this rank: symmetric buffers, this rank's expert weights, helpers that load
     inputs and time layers.  `hidden` 6144 = the decode layer, 7168 = the prefill-sized layer."""
 
-    def __init__(self, torch, dist, mm, lib, n, rank, dev, group, hidden, cap, cta_pair, dispatch_mode):
+    def __init__(self, torch, dist, mm, lib, n, rank, dev, group, hidden, cap, cta_pair, dispatch_mode, group_ranks=0):
         self.torch, self.dist, self.mm, self.lib = torch, dist, mm, lib
         self.n, self.rank, self.dev, self.hidden, self.cap = n, rank, dev, hidden, cap
         self.epr = E_TOTAL // n
-        self.buf = mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, hidden, I, dispatch_mode=dispatch_mode)
+        self.group_ranks = group_ranks
+        self.buf = mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, hidden, I, dispatch_mode=dispatch_mode,
+                                                   group_ranks=group_ranks)
         self.buf.cta_pair = cta_pair
         self.weights = make_weights(torch, self.epr, rank, dev, hidden)
         self.l1, self.l2 = mm.transform_weights_for_mega_moe(*self.weights)
+        # helper groups (skewed routing): every member holds a replica of its group's expert weights
+        self.group_weights = mm.gather_group_weights(self.buf, self.l1, self.l2) if group_ranks > 1 else None
         self.stream = torch.cuda.current_stream()
         self.inputs = None
         self.push = bool(self.buf.layout.push_eligible) if dispatch_mode == 0 else dispatch_mode == 2
@@ -351,7 +355,7 @@ class Job:
         return self.gather(idx)
 
     def layer(self, y=None):
-        self.mm.fp8_mega_moe(self.y if y is None else y, self.l1, self.l2, self.buf)
+        self.mm.fp8_mega_moe(self.y if y is None else y, self.l1, self.l2, self.buf, group_weights=self.group_weights)
 
     def check_status(self, what):
         st = self.buf.status()
@@ -484,7 +488,7 @@ class Job:
 
     def destroy(self):
         self.buf.destroy()
-        self.weights = self.l1 = self.l2 = None
+        self.weights = self.l1 = self.l2 = self.group_weights = None
 
 
 def parity_leg(job, routing_all, np):
@@ -505,13 +509,21 @@ def parity_leg(job, routing_all, np):
     idx_all = routing_all.numpy().reshape(n, tokens, TOPK)
     case = orc.Case(n, epr, TOPK, Hh, I, tokens, [tokens] * n, True, x_all, sf_all, idx_all,
                     np.zeros((n, tokens, TOPK), np.float32), None, None, None, None, "bench")
-    ref = orc.route_world(case, slot_cap=job.cap)[rank]
+    ref_all = orc.route_world(case, slot_cap=job.cap)
+    ref = ref_all[rank]
+    helper_on = None
+    if job.group_ranks > 1:   # the member's window list of the helper group decides which rows this rank holds
+        hw = orc.helper_world(case, ref_all, job.group_ranks, 128, 2)[rank]
+        helper_on = bool(hw["on"])
+        ref.meta = hw["meta"]
     rows = ref.meta.shape[0]
     ok = np.array_equal(buf.table("route_slot_counts").cpu().numpy(), ref.route_slot_counts)
     ok &= np.array_equal(buf.table("prefix_tbl").cpu().numpy(), ref.prefix_tbl)
     ok &= np.array_equal(buf.table("expert_row_base").cpu().numpy(), ref.row_base)
     ok &= np.array_equal(buf.table("row_meta")[:rows, :3].cpu().numpy(), ref.meta)
     ok &= int(st.total_rows) == rows
+    if helper_on is not None:
+        ok &= bool(st.helper_on) == helper_on
     pool = buf.table("pool")[:rows].cpu().numpy()
     psf = buf.table("pool_sf")[:rows, : Hh // 128].cpu().numpy()
     ok &= np.array_equal(pool, x_all[ref.meta[:, 0], ref.meta[:, 1]])
@@ -560,6 +572,7 @@ def parity_leg(job, routing_all, np):
         ok_all, worst_all, checked_all = bool(ok), worst, checked
     return {"tables_exact": ok_all, "max_rel_l2": worst_all, "tokens_checked": checked_all, "tolerance": 1e-2,
             "ranks": n, "tables": "route_slot_counts, prefix_tbl, expert_row_base, row_meta, pool bytes + scales",
+            "helper_groups": job.group_ranks if job.group_ranks > 1 else None,
             "passed": bool(ok_all and worst_all <= 1e-2)}
 
 
@@ -651,15 +664,41 @@ def gpu_arm(args):
             "rank_gemm_end_us_max": float(gemm_end.max()) / 1e3, "rank_gemm_end_us_mean": float(gemm_end.mean()) / 1e3,
             "rank_time_max_over_mean": float(gemm_end.max() / max(gemm_end.mean(), 1.0))}))
 
+    job_push = job.push
     # ---- parity of the headline configuration (outside every timed region) ----
     parity = None
     if not args.no_parity:
         routing = job.load(args.tpr, seed=1, routing=args.routing)
         parity = parity_leg(job, routing, np)
 
-    # ---- prefill-sized layer: H=7168, 4096 tokens per rank ----
-    if not args.no_points and args.hidden == 6144:
+    # ---- the skew configuration again with cross-rank helper scheduling: one helper group over all ranks,
+    #      every GPU holds a replica of all experts' weights (9.4 GB of 180 GB) ----
+    parity_helpers = None
+    if not args.no_points and n >= 2 and args.hidden == 6144 and E_TOTAL // n * n * (n + 1) <= 4096:
         job.destroy()
+        torch.cuda.empty_cache()
+        job_h = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, cap, args.cta_pair, args.dispatch_mode, group_ranks=n)
+        rt = job_h.load(256, seed=3, routing="zipf")
+        ms = job_h.time_eager(max(3, min(args.steps, 20)), 3)
+        mg = run_graph(job_h)
+        wk = algorithmic_work(rt, n, rank, 256, args.hidden)
+        sk, st_h = job_h.phase_stamps()
+        gemm_end = sk[:, 3]
+        points.append(point("skew_zipf1.2_tpr256_helpers", job_h, 256, ms, mg, wk, {
+            "helper_group_ranks": n, "helper_on_rank0": int(st_h.helper_on),
+            "rank_gemm_end_us_max": float(gemm_end.max()) / 1e3, "rank_gemm_end_us_mean": float(gemm_end.mean()) / 1e3,
+            "rank_time_max_over_mean": float(gemm_end.max() / max(gemm_end.mean(), 1.0)),
+            "note": "roofline figures count this rank's own experts; helpers stream replicas of other ranks' experts on top"}))
+        if not args.no_parity:
+            parity_helpers = parity_leg(job_h, rt, np)
+        job_h.destroy()
+        job = None
+
+    # ---- prefill-sized layer: H=7168, 4096 tokens per rank ----
+    push_headline = job_push
+    if not args.no_points and args.hidden == 6144:
+        if job is not None:
+            job.destroy()
         torch.cuda.empty_cache()
         pj = Job(torch, dist, mm, lib, n, rank, dev, group, 7168, 4096, args.cta_pair, args.dispatch_mode)
         rt = pj.load(4096, seed=4)
@@ -671,7 +710,7 @@ def gpu_arm(args):
             "frac_of_nominal_fp8_4500": wk["flops"] / (ms * 1e-3) / 1e12 / FP8_NOMINAL_TFLOPS,
             "phase_end_us_rank0": [float(v) / 1e3 for v in pst[0].tolist()]}))
         pj.destroy()
-    else:
+    elif job is not None:
         job.destroy()
 
     cpu = None
@@ -716,7 +755,7 @@ def gpu_arm(args):
             "us_per_layer_graph": None if ms_graph is None else ms_graph * 1e3,
             "e2e": {"value": n * args.tpr / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "copies_per_step": "1 H2D (packed image) + 1 D2H" if job.push else "4 H2D + 1 D2H"},
+                    "copies_per_step": "1 H2D (packed image) + 1 D2H" if push_headline else "4 H2D + 1 D2H"},
             "gpu_launches": int(lib.mxk_kernels_per_layer()) * args.steps,
             "roofline": roof,
             "nvlink": {"algorithmic_bytes_in": work["nvlink_in"], "algorithmic_bytes_out": work["nvlink_out"],
@@ -726,18 +765,20 @@ def gpu_arm(args):
                        "peak_gbs_per_direction": NVLINK_GBS, "note": "bytes per GPU and layer on rank 0's routing; "
                        "dispatch time = set-up end to dispatch end from the kernel's phase stamps"},
             "phase_end_us_by_rank": [[float(v) / 1e3 for v in row] for row in stamps.tolist()],
-            "prologue": "push" if job.push else "pull",
+            "prologue": "push" if push_headline else "pull",
             "points": points,
             "clocks": clocks,
         }
         if parity is not None:
             line["parity"] = parity
+        if parity_helpers is not None:
+            line["parity_helpers"] = parity_helpers
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
     if n > 1:
         dist.destroy_process_group()
-    if parity is not None and not parity["passed"]:
+    if (parity is not None and not parity["passed"]) or (parity_helpers is not None and not parity_helpers["passed"]):
         sys.exit(3)
 
 
@@ -801,7 +842,7 @@ def ticks_run(args):
     job = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, args.tpr, args.cta_pair, args.dispatch_mode)
     job.load(args.tpr, seed=1, routing=args.routing)
     ms_plain = job.time_eager(args.steps, args.warmup)
-    lib.mxk_set_ticks(1)
+    lib.mxk_set_ticks(2 if os.environ.get("MXK_TICKS") == "2" else 1)
     ms = job.time_eager(args.steps, args.warmup)
     st = job.buf.status()
     lib.mxk_set_ticks(-1)
@@ -822,11 +863,11 @@ def ticks_run(args):
               f"dispatch={tk[11] / 1e3:.1f} gemm={tk[12] / 1e3:.1f} reduce={tk[13] / 1e3:.1f}", file=sys.stderr, flush=True)
         tr = list(st.trace)
         lab = ["entry", "init", "pushed", "route_end", "barrier", "tables", "setup_end", "dispatch_end", "gate0", "tma0",
-               "tile0", "gemm_end", "reduce_end"]
+               "tile0", "gemm_end", "reduce_end", "tables_again"]
         for base, who in ((0, "first CTA"), (32, "last CTA")):
             t0 = tr[base]
             print(f"[rank {rank}] {who} time line (us): " +
-                  " ".join(f"{lab[i]}={(tr[base + i] - t0) / 1e3:.1f}" for i in range(1, 13) if tr[base + i] >= t0 and tr[base + i] != 0),
+                  " ".join(f"{lab[i]}={(tr[base + i] - t0) / 1e3:.1f}" for i in range(1, 14) if tr[base + i] >= t0 and tr[base + i] != 0),
                   file=sys.stderr, flush=True)
     if rank == 0:
         print(json.dumps({"ticks_run": True, "us_per_layer_plain": ms_plain * 1e3, "us_per_layer_with_accounting": ms * 1e3,

@@ -27,6 +27,27 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
 
+// ---- division by a launch constant ----------------------------------------------
+// The geometry (ranks, experts per rank, top-k, window rows) is known only at launch, and a
+// 32-bit division by a run-time value costs some twenty instructions; the host precomputes a
+// multiplier and a shift so that the kernels divide with one multiply-high (dividends < 2^31).
+struct FastDiv {
+    uint32_t d, mul, shr;
+    __host__ static FastDiv make(uint32_t d) {
+        FastDiv f{d, 0u, 0u};
+        if (d > 1) {
+            uint32_t lg = 0;
+            while ((1ull << lg) < d) ++lg;
+            const uint32_t p = 31 + lg;
+            f.mul = (uint32_t)(((1ull << p) + d - 1) / d);
+            f.shr = p - 32;
+        }
+        return f;
+    }
+    __device__ __forceinline__ int div(int n) const { return d == 1 ? n : (int)(__umulhi((uint32_t)n, mul) >> shr); }
+    __device__ __forceinline__ int mod(int n) const { return n - div(n) * (int)d; }
+};
+
 // ---- scoped flag accesses -------------------------------------------------
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;

@@ -64,6 +64,7 @@ struct KArgs {
     int skew_num;                // helpers on when max * n_experts > skew_num * sum over the group's experts
     int ge_base;                 // this rank's first expert inside the weight arrays (member * EPR with group weights)
     int w_experts;               // experts in the weight arrays w1 / w2 (EPR, or group_ranks * EPR)
+    FastDiv fR, fEPR, ftopk, fng, fwin;   // division by R, EPR, topk, R / group_ranks, win_cap
     unsigned long long local_wait_ns, remote_wait_ns;
     uint8_t* rwk;
     uint8_t* unk;
@@ -191,6 +192,10 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
             tables_ok = push_tables(a, f, epoch, sc, &S->tabs);
             tabs = &S->tabs;
             if (trace && threadIdx.x == 0) trace[5] = gtimer_ns();
+            if (a.ticks == 2) {   // diagnostic (MXK_TICKS=2): the same tables once more, to tell cold-start cost from work
+                tables_ok = push_tables(a, f, epoch, sc, &S->tabs);
+                if (trace && threadIdx.x == 0) trace[13] = gtimer_ns();
+            }
             if (stamp && blockIdx.x == 0) f->ticks[10] = gtimer_ns() - t0;
             if (tables_ok && (setup || disp)) push_dispatch(a, f, epoch, sc, tabs, setup, disp);
             if (trace && threadIdx.x == 0) trace[6] = gtimer_ns();
@@ -435,7 +440,7 @@ int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t k) {
 // Wait-time accounting and phase stamps: MXK_TICKS=1 in the environment, or mxk_set_ticks().
 int g_ticks_override = -1;
 int ticks_enabled() {
-    static const int ticks_env = [] { const char* e = std::getenv("MXK_TICKS"); return e && e[0] == '1' ? 1 : 0; }();
+    static const int ticks_env = [] { const char* e = std::getenv("MXK_TICKS"); return e && e[0] >= '1' && e[0] <= '2' ? e[0] - '0' : 0; }();
     return g_ticks_override >= 0 ? g_ticks_override : ticks_env;
 }
 
@@ -542,6 +547,8 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
         k->win_cap = 256;   // rows per window of a CTA pair
     }
     k->gemm_grid = grid;
+    k->fR = FastDiv::make((uint32_t)k->R); k->fEPR = FastDiv::make((uint32_t)k->EPR); k->ftopk = FastDiv::make((uint32_t)k->topk);
+    k->fng = FastDiv::make((uint32_t)(k->R / k->group_ranks)); k->fwin = FastDiv::make((uint32_t)k->win_cap);
     return 0;
 }
 
@@ -883,7 +890,7 @@ int mxk_gs_schedule_on_device(const int32_t* rows_of_ge, int EPR, int group_rank
 
 int mxk_set_ticks(int on) {
     const int before = ticks_enabled();
-    g_ticks_override = on < 0 ? -1 : (on ? 1 : 0);
+    g_ticks_override = on < 0 ? -1 : (on > 2 ? 1 : on);
     return before;
 }
 int64_t mxk_rwk_ticks_off(void) { return (int64_t)offsetof(DevFlags, ticks); }   // flags_off is 0 in every layout

@@ -67,6 +67,7 @@ __device__ void ensure_counts_clean(const KArgs& a, DevFlags* f, long long epoch
     if (clean_epoch == (uint32_t)(epoch - 1)) return;   // uniform over the grid
     const int tid = threadIdx.x, nthr = blockDim.x;
     unsigned* cnt = reinterpret_cast<unsigned*>(a.unk + a.L.combine_cnt_off);
+#pragma unroll 1
     for (int i = blockIdx.x * nthr + tid; i < a.topk * a.cap; i += gridDim.x * nthr) cnt[i] = 0;
     __threadfence();
     __syncthreads();
@@ -102,22 +103,27 @@ __device__ bool route_onepass(const KArgs& a, DevFlags* f, long long epoch, int*
     uint8_t* pair_state = a.rwk + a.L.pair_state_off;
     int* rsc = reinterpret_cast<int*>(a.rwk + a.L.route_slot_counts_off);
     int* g_cnt = reinterpret_cast<int*>(a.rwk + a.L.route_scratch_off);   // [G][E]
+#pragma unroll 1
     for (int e = tid; e < E; e += nthr) s_hist[e] = 0;
+#pragma unroll 1
     for (int i = tid; i < n; i += nthr) {
         const int64_t v = ti[p0 + i];
         s_id[i] = (uint64_t)v < (uint64_t)E ? (int)v : -1;   // invalid ids take no slot (src/prologue.cuh:166-167)
     }
     __syncthreads();
+#pragma unroll 1
     for (int i = tid; i < n; i += nthr) {
         const int id = s_id[i];
         int r = 0;
         if (id >= 0) {
+#pragma unroll 1
             for (int j = 0; j < i; ++j) r += s_id[j] == id ? 1 : 0;
             atomicAdd(&s_hist[id], 1);
         }
         s_rank[i] = r;
     }
     __syncthreads();
+#pragma unroll 1
     for (int e = tid; e < E; e += nthr) g_cnt[(size_t)c * E + e] = s_hist[e];
     __threadfence();
     __syncthreads();
@@ -130,8 +136,10 @@ __device__ bool route_onepass(const KArgs& a, DevFlags* f, long long epoch, int*
     __syncthreads();
     // pairs of the earlier slices per expert (coalesced over the experts); the experts this CTA
     // owns (e = c, c + G, ...) also get their totals, their count is published from here
+#pragma unroll 1
     for (int e = tid; e < E; e += nthr) {
         int before = 0, total = 0;
+#pragma unroll 1
         for (int cc = 0; cc < G; ++cc) {
             const int v = ld_relaxed_gpu(g_cnt + (size_t)cc * E + e);
             before += cc < c ? v : 0;
@@ -142,14 +150,15 @@ __device__ bool route_onepass(const KArgs& a, DevFlags* f, long long epoch, int*
             const int cnt = total < a.slot_cap ? total : a.slot_cap;
             rsc[e] = cnt;
             if (!local_only) {
-                uint64_t* recv = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[e / a.EPR]) +
+                uint64_t* recv = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[a.fEPR.div(e)]) +
                                                              a.L.expert_recv_counts_off) +
                                  ((size_t)par * a.R + a.rank) * a.L.recv_stride;
-                st_relaxed_sys_u64(recv + e % a.EPR, tagged((uint32_t)cnt, epoch));
+                st_relaxed_sys_u64(recv + a.fEPR.mod(e), tagged((uint32_t)cnt, epoch));
             }
         }
     }
     __syncthreads();
+#pragma unroll 1
     for (int i = tid; i < n; i += nthr) {
         const int id = s_id[i], p = p0 + i;
         bool ok = false;
@@ -157,9 +166,9 @@ __device__ bool route_onepass(const KArgs& a, DevFlags* f, long long epoch, int*
             const int slot = s_base[id] + s_rank[i];
             ok = slot < a.slot_cap;   // over capacity: dropped (src/prologue.cuh:171-174)
             if (ok && !local_only) {
-                uint64_t* tbl = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[id / a.EPR]) +
+                uint64_t* tbl = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[a.fEPR.div(id)]) +
                                                             a.L.src_index_table_off) +
-                                (((size_t)par * a.EPR + id % a.EPR) * a.R + a.rank) * (size_t)a.slot_cap;
+                                (((size_t)par * a.EPR + a.fEPR.mod(id)) * a.R + a.rank) * (size_t)a.slot_cap;
                 st_relaxed_sys_u64(tbl + slot, tagged((uint32_t)p, epoch));
             }
         }
@@ -184,14 +193,16 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
 
     // many pairs: one pass over this rank's pairs instead of one scan per expert
     const bool onepass = team.bar == 0 && np > kRoutePer * nthr && route_onepass(a, f, epoch, s_big, s_big_ints, local_only);
+#pragma unroll 1
     for (int e = blockIdx.x; e < a.E && !onepass; e += gridDim.x) {
-        const int dst = e / a.EPR, le = e % a.EPR;
+        const int dst = a.fEPR.div(e), le = a.fEPR.mod(e);
         uint8_t* peer_unk = reinterpret_cast<uint8_t*>(a.unk_peers[dst]);
         uint64_t* tbl = reinterpret_cast<uint64_t*>(peer_unk + a.L.src_index_table_off) +
                         (((size_t)par * a.EPR + le) * a.R + a.rank) * (size_t)a.slot_cap;
         int base = 0;
         // kRoutePer sub-chunks of blockDim pairs per iteration: the index loads of all sub-chunks
         // are in flight together, then slots are handed out sub-chunk by sub-chunk (ascending idx)
+#pragma unroll 1
         for (int p0 = 0; p0 < np; p0 += nthr * kRoutePer) {
             bool hit[kRoutePer];
             unsigned bal[kRoutePer];
@@ -211,6 +222,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
 #pragma unroll
             for (int j = 0; j < kRoutePer; ++j) {
                 int wpre = 0, tot = 0;
+#pragma unroll 1
                 for (int w = 0; w < nwarps; ++w) {
                     const int c = s_wtot[j * nwarps + w];
                     wpre += (w < warp) ? c : 0;
@@ -241,6 +253,7 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     // counts and build the tables, which is the critical path of the prologue.
     const bool closer = blockIdx.x == gridDim.x - 1;
     if (closer && !onepass)  // invalid expert ids (negative / >= E) take no slot (src/prologue.cuh:166-167)
+#pragma unroll 1
         for (int p = tid; p < np; p += nthr)
             if ((uint64_t)ti[p] >= (uint64_t)a.E) pair_state[p] = 0;
 
@@ -259,8 +272,10 @@ __device__ void route_phase(const KArgs& a, DevFlags* f, long long epoch, int* s
     team.sync();
     // Row checksum word ~(sum + 1) at index EPR of each row sent (src/prologue.cuh:248-255), kept
     // for layout parity with the reference; nothing here waits on it.
+#pragma unroll 1
     for (int d = tid; d < a.R && !local_only; d += nthr) {
         uint32_t csum = 0;
+#pragma unroll 1
         for (int le = 0; le < a.EPR; ++le) csum += (uint32_t)ld_relaxed_gpu(rsc + d * a.EPR + le);
         uint64_t* recv = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(a.unk_peers[d]) +
                                                      a.L.expert_recv_counts_off) +
@@ -289,8 +304,10 @@ __device__ void build_tables(const KArgs& a, const int* s_cnt, int* prefix, int*
                              int* s_order /*[EPR]*/, int* s_first /*[EPR+1]*/, int* s_base /*[EPR+1]*/) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int EPR = a.EPR, R = a.R;
+#pragma unroll 1
     for (int le = tid; le < EPR; le += nthr) {
         int c = 0;
+#pragma unroll 1
         for (int r = 0; r < R; ++r) {
             prefix[le * (R + 1) + r] = c;
             c += s_cnt[le * R + r];
@@ -299,9 +316,11 @@ __device__ void build_tables(const KArgs& a, const int* s_cnt, int* prefix, int*
         s_tot[le] = c;
     }
     __syncthreads();
+#pragma unroll 1
     for (int le = tid; le < EPR; le += nthr) {
         const int c = s_tot[le];
         int rk = 0;
+#pragma unroll 1
         for (int j = 0; j < EPR; ++j) {
             const int cj = s_tot[j];
             rk += (cj > c || (cj == c && j < le)) ? 1 : 0;
@@ -313,6 +332,7 @@ __device__ void build_tables(const KArgs& a, const int* s_cnt, int* prefix, int*
         // exclusive scans by warp 0: pool rows in expert-index order, windows in sorted order
         const int lane = tid;
         int carry_rows = 0, carry_win = 0;
+#pragma unroll 1
         for (int b = 0; b < EPR; b += 32) {
             const int i = b + lane;
             const int c = i < EPR ? s_tot[i] : 0;
@@ -352,7 +372,9 @@ __device__ void publish_tables(const KArgs& a, DevFlags* f, long long epoch, con
     const bool ts = a.ticks != 0 && tid == 0;
     int* row_base = reinterpret_cast<int*>(a.rwk + a.L.expert_row_base_off);
     int* first_win = reinterpret_cast<int*>(a.rwk + a.L.expert_first_win_off);
+#pragma unroll 1
     for (int le = tid; le <= EPR; le += nthr) row_base[le] = s_base[le];
+#pragma unroll 1
     for (int p = tid; p < EPR; p += nthr) first_win[s_order[p]] = s_first[p];
 
     int n_windows = s_first[EPR];
@@ -371,6 +393,7 @@ __device__ void publish_tables(const KArgs& a, DevFlags* f, long long epoch, con
         const int prev_windows = min(max(ld_relaxed_gpu(&f->n_windows), 0), a.L.max_windows);
         uint32_t* l1_o = l1_done + (size_t)(par ^ 1) * a.L.max_windows;
         uint32_t* pr_o = pool_ready + (size_t)(par ^ 1) * a.L.max_windows;
+#pragma unroll 1
         for (int i = tid; i < prev_windows; i += nthr) { l1_o[i] = 0; pr_o[i] = 0; }
     }
     __syncthreads();   // n_windows of the previous launch was read by every thread above
@@ -383,19 +406,23 @@ __device__ void publish_tables(const KArgs& a, DevFlags* f, long long epoch, con
     } else if (!overflow) {
         // one warp per expert (sorted position p), lanes over its windows and tasks
         const int lane = tid & 31, wid = tid >> 5, nwarps = nthr >> 5;
+#pragma unroll 1
         for (int p = wid; p < EPR; p += nwarps) {
             const int e = s_order[p], c = s_tot[e];
             const int fw = s_first[p], nw = s_first[p + 1] - fw;
             if (nw == 0) break;  // sorted: every later expert is empty too
+#pragma unroll 1
             for (int w = lane; w < nw; w += 32) {
                 const int rows = min(a.win_cap, c - w * a.win_cap);
                 windows[fw + w] = make_int4(e, s_base[e] + w * a.win_cap, rows, 0);
                 if (!a.push) { l1_done[fw + w] = 0; pool_ready[fw + w] = 0; }
             }
+#pragma unroll 1
             for (int i = lane; i < nt1 * nw; i += 32) {
                 const int nt = i / nw, w = i % nw;
                 tasks[fw * nt1 + i] = make_int4(0, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
             }
+#pragma unroll 1
             for (int i = lane; i < nt2 * nw; i += 32) {
                 const int nt = i / nw, w = i % nw;
                 tasks[n_l1 + fw * nt2 + i] = make_int4(1, fw + w, nt, min(a.win_cap, c - w * a.win_cap));
@@ -436,6 +463,7 @@ __device__ void setup_phase_leader(const KArgs& a, DevFlags* f, long long epoch,
     int* s_cnt = s_base + EPR + 1;     // [EPR][R]
     const uint64_t* recv = reinterpret_cast<const uint64_t*>(a.unk + a.L.expert_recv_counts_off) +
                            (size_t)par * R * a.L.recv_stride;
+#pragma unroll 1
     for (int i = tid; i < EPR * R; i += nthr) {
         const int le = i / R, r = i % R;
         const uint64_t* wp = recv + (size_t)r * a.L.recv_stride + le;
@@ -499,14 +527,19 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
         const int* g_base = reinterpret_cast<const int*>(a.rwk + a.L.expert_row_base_off);
         const int* g_fw = reinterpret_cast<const int*>(a.rwk + a.L.expert_first_win_off);
         const int* g_pf = reinterpret_cast<const int*>(a.rwk + a.L.prefix_tbl_off);
+#pragma unroll 1
         for (int i = threadIdx.x; i <= EPR; i += blockDim.x) row_base[i] = ld_relaxed_gpu(g_base + i);
+#pragma unroll 1
         for (int i = threadIdx.x; i < EPR; i += blockDim.x) first_win[i] = ld_relaxed_gpu(g_fw + i);
+#pragma unroll 1
         for (int i = threadIdx.x; i < EPR * (R + 1); i += blockDim.x) prefix[i] = ld_relaxed_gpu(g_pf + i);
         __syncthreads();
     }
 
+#pragma unroll 1
     for (int g = gwarp; g < total; g += nwarps) {
         int lo = 0, hi = EPR;  // largest le with row_base[le] <= g
+#pragma unroll 1
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
             if (row_base[mid] <= g) lo = mid; else hi = mid;
@@ -515,6 +548,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
         const int gl = g - row_base[le];
         const int* pf = prefix + le * (R + 1);
         int slo = 0, shi = R;  // largest src with pf[src] <= gl (src/compute_big.cuh:1760-1769)
+#pragma unroll 1
         while (shi - slo > 1) {
             const int mid = (slo + shi) >> 1;
             if (pf[mid] <= gl) slo = mid; else shi = mid;
@@ -535,7 +569,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
             if (lane == 0) raise_status(f, MXK_DEV_BAD_TABLE, 3);
             idx = 0;
         }
-        const int token = (int)(idx / (uint32_t)a.topk), k = (int)(idx % (uint32_t)a.topk);
+        const int token = a.ftopk.div((int)idx), k = (int)idx - token * a.topk;
         const uint8_t* peer = a.peer_bases[src];
         const uint4* srow = reinterpret_cast<const uint4*>(peer + a.x_off + (size_t)token * H);
         uint4* drow = reinterpret_cast<uint4*>(pool + (size_t)g * H);
@@ -553,6 +587,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
         }
         // up to 16 loads in flight per lane before the first store (the strong loads are not
         // reordered by the compiler, so issue order is what hides the NVLink round trip)
+#pragma unroll 1
         for (int i0 = lane; i0 < n16; i0 += 32 * 16) {
             uint4 v[16];
 #pragma unroll
@@ -564,6 +599,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
         }
         if (a.scaled) {
             const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
+#pragma unroll 1
             for (int i = lane; i < a.L.sf_stride_h; i += 32)
                 pool_sf[(size_t)g * a.L.sf_stride_h + i] =
                     i < 64 ? sfb[i >> 5] : (i < kb ? ld_relaxed_sys_u8(ssf + i) : (uint8_t)127);
@@ -574,7 +610,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
         __threadfence();
         fence_proxy_async_global();
         __syncwarp();
-        if (lane == 0) red_release_gpu_add(pool_ready + first_win[le] + gl / a.win_cap, 1u);
+        if (lane == 0) red_release_gpu_add(pool_ready + first_win[le] + a.fwin.div(gl), 1u);
     }
 }
 
@@ -657,6 +693,7 @@ __device__ __forceinline__ uint64_t* xin_block(const KArgs& a, void* unk_base, i
 // largest r with sb[r] <= i (sources without tokens share their successor's start)
 __device__ __forceinline__ int push_src_of(const int* sb, int R, int i) {
     int lo = 0, hi = R;
+#pragma unroll 1
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
         if (sb[mid] <= i) lo = mid; else hi = mid;
@@ -671,7 +708,7 @@ __device__ __forceinline__ int push_src_of(const int* sb, int R, int i) {
 // whole phase costs one memory round trip plus the stores.
 __device__ void push_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_ids) {
     const int tid = threadIdx.x, nthr = blockDim.x;
-    const int par = (int)(epoch & 1), R = a.R, topk = a.topk, H = a.H, EPR = a.EPR;
+    const int par = (int)(epoch & 1), R = a.R, topk = a.topk, H = a.H;
     const int np = a.tokens * topk;
     const int sfw = xin_sf_words(H), kb = H / 128, row_words = a.L.xin_row_words, n16 = H / 8;
     const uint32_t* wts = reinterpret_cast<const uint32_t*>(a.self + a.weights_off);
@@ -679,7 +716,7 @@ __device__ void push_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_
     constexpr int kMaxPer = 3;   // 16-byte units of a row per thread: H <= 8192 -> 1024 units over 384 threads
     struct Unit { uint2 x[kMaxPer]; uint32_t w, sf; void* peer; };
     auto load_unit = [&](int u, Unit& un) {
-        const int t = u / R, d = (u + t) % R;
+        const int t = a.fR.div(u);
         const uint2* xs = reinterpret_cast<const uint2*>(a.self + a.x_off + (size_t)t * H);
 #pragma unroll
         for (int j = 0; j < kMaxPer; ++j)
@@ -688,17 +725,19 @@ __device__ void push_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_
         un.sf = 0;
         if (a.scaled && tid >= 128 && tid < 128 + sfw) {   // four scale bytes per word, 127 (x1.0) beyond H/128
             const int i = tid - 128;
+#pragma unroll 1
             for (int j = 0; j < 4; ++j) {
                 const int b = 4 * i + j;
                 un.sf |= (uint32_t)(b < kb ? xsf[(size_t)t * kb + b] : (uint8_t)127) << (8 * j);
             }
         }
-        un.peer = a.unk_peers[d];
+        un.peer = a.unk_peers[a.fR.mod(u + t)];
     };
     const int n_units = a.tokens * R;
     Unit un;
     if ((int)blockIdx.x < n_units) load_unit(blockIdx.x, un);
     void* hdr_peer = (blockIdx.x == gridDim.x - 1 && tid < R) ? a.unk_peers[tid] : nullptr;
+#pragma unroll 1
     for (int p = tid; p < np; p += nthr) {   // invalid ids (negative / >= E) travel as -1 (src/prologue.cuh:166-167)
         const int64_t v = a.topk_idx[p];
         s_ids[p] = (uint64_t)v < (uint64_t)a.E ? (int)v : -1;
@@ -706,12 +745,14 @@ __device__ void push_phase(const KArgs& a, DevFlags* f, long long epoch, int* s_
     if (hdr_peer)   // header: how many rows the destination has to expect from this rank
         st_relaxed_sys_u64(xin_block(a, hdr_peer, par, a.rank), tagged((uint32_t)a.tokens, epoch));
     __syncthreads();
+#pragma unroll 1
     for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
-        const int t = u / R, d = (u + t) % R;
+        const int t = a.fR.div(u), d = a.fR.mod(u + t);
         bool routed = false;
+#pragma unroll 1
         for (int k = 0; k < topk; ++k) {
             const int e = s_ids[t * topk + k];
-            routed |= e >= 0 && e / EPR == d;
+            routed |= e >= 0 && a.fEPR.div(e) == d;
         }
         uint64_t* row = xin_block(a, un.peer, par, a.rank) + 16 + (size_t)t * row_words;
         if (tid < topk) st_relaxed_sys_u64(row + tid, tagged((uint32_t)s_ids[t * topk + tid], epoch));
@@ -738,8 +779,10 @@ __device__ void publish_helper_lists(const KArgs& a, const PushTabs* T) {
     const int nt1 = a.I / 128, nt2 = a.H / kBlockN;
     int4* windows = reinterpret_cast<int4*>(a.rwk + a.L.windows_off);
     int4* tasks = reinterpret_cast<int4*>(a.rwk + a.L.tasks_off);
+#pragma unroll 1
     for (int i = tid; i < T->n_windows; i += nthr)
         windows[i] = make_int4(T->gw[i] >> 16, T->rr[i] >> 10, T->rr[i] & 1023, T->gw[i] & 0xFFFF);
+#pragma unroll 1
     for (int t = tid; t < T->n_tasks; t += nthr) {
         const int kind = t >= T->n_l1 ? 1 : 0, nt = kind ? nt2 : nt1, tt = kind ? t - T->n_l1 : t;
         tasks[t] = make_int4(kind, tt / nt, tt % nt, T->rr[tt / nt] & 1023);
@@ -750,11 +793,13 @@ __device__ void publish_helper_lists(const KArgs& a, const PushTabs* T) {
 // sched_member_windows (descending cost, (ge, w) ascending, least-loaded member, ties to the owner
 // then the lowest member) with the members' loads held one per lane, so that a window costs a few
 // shuffles instead of a loop over the members.  Every lane returns the same counts.
-__device__ void helper_member_list(const int* totg, int GE, int EPR, int G, int win_cap, int member, PushTabs* T) {
+__device__ void helper_member_list(const int* totg, int GE, const FastDiv fEPR, int G, int win_cap, int member, PushTabs* T) {
     const int lane = threadIdx.x & 31;
     int load = 0, n = 0, rowcur = 0;
     const int full_cost = sched_window_cost(win_cap);
+#pragma unroll 1
     for (int level = full_cost; level >= 1; --level) {
+#pragma unroll 1
         for (int ge0 = 0; ge0 < GE; ge0 += 32) {
             const int ge = ge0 + lane;
             const int c = ge < GE ? max(totg[ge], 0) : 0;
@@ -766,12 +811,14 @@ __device__ void helper_member_list(const int* totg, int GE, int EPR, int G, int 
                 w_hi = n_full + 1;
             }
             unsigned mask = __ballot_sync(0xFFFFFFFFu, w_hi > w_lo);
+#pragma unroll 1
             while (mask) {
                 const int l = __ffs(mask) - 1;
                 mask &= mask - 1;
-                const int g_e = ge0 + l, owner = g_e / EPR;
+                const int g_e = ge0 + l, owner = fEPR.div(g_e);
                 const int lo = __shfl_sync(0xFFFFFFFFu, w_lo, l), hi = __shfl_sync(0xFFFFFFFFu, w_hi, l);
                 const int ctot = __shfl_sync(0xFFFFFFFFu, c, l);
+#pragma unroll 1
                 for (int w = lo; w < hi; ++w) {
                     const int mine = lane < G ? load : 0x7FFFFFFF;
                     int mn = mine;
@@ -811,7 +858,9 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
     const size_t src_words = (size_t)a.L.xin_src_words;
     const int row_words = a.L.xin_row_words;
     if (tid == 0) *sc.flag = 1;
+#pragma unroll 1
     for (int i = tid; i < GE * R; i += nthr) sc.cnt[i] = 0;
+#pragma unroll 1
     for (int r = tid; r < R; r += nthr) {
         const uint64_t* hp = mine + r * src_words;
         uint64_t w = 0;
@@ -823,13 +872,16 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
         sc.tok[r] = min((int)(uint32_t)w, a.cap);
     }
     __syncthreads();
+#pragma unroll 1
     for (int r = tid; r <= R; r += nthr) {   // first world pair of source r
         int c = 0;
+#pragma unroll 1
         for (int q = 0; q < r; ++q) c += sc.tok[q];
         sc.sb[r] = c * topk;
     }
     __syncthreads();
     const int W = sc.sb[R];   // <= R * cap * topk <= kPushMaxPairs
+#pragma unroll 1
     for (int i0 = tid; i0 < W; i0 += nthr * 4) {   // four polls in flight per thread
         const uint64_t* ptr[4];
         uint64_t w[4];
@@ -840,7 +892,8 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
             if (i < W) {
                 src[j] = push_src_of(sc.sb, R, i);
                 const int q = i - sc.sb[src[j]];
-                ptr[j] = mine + src[j] * src_words + 16 + (size_t)(q / topk) * row_words + q % topk;
+                const int qt = a.ftopk.div(q);
+                ptr[j] = mine + src[j] * src_words + 16 + (size_t)qt * row_words + (q - qt * topk);
                 w[j] = ld_relaxed_sys_u64(ptr[j]);
             }
         }
@@ -859,9 +912,9 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
             const int e = (int)(uint32_t)t;
             sc.wid[i] = e;
             if (e >= 0) {
-                const int owner = e / EPR;
-                if (owner < R && owner % n_groups == my_group)
-                    atomicAdd(&sc.cnt[((owner / n_groups) * EPR + e % EPR) * R + src[j]], 1);
+                const int owner = a.fEPR.div(e);
+                if (owner < R && a.fng.mod(owner) == my_group)
+                    atomicAdd(&sc.cnt[(a.fng.div(owner) * EPR + (e - owner * EPR)) * R + src[j]], 1);
             }
         }
     }
@@ -869,10 +922,13 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
     const bool ts = a.ticks != 0 && tid == 0 && blockIdx.x == 0;
     if (ts) f->dbg_ts[0] = gtimer_ns();
     // pairs beyond the slot capacity of a (source, expert) row are dropped (src/prologue.cuh:171-174)
+#pragma unroll 1
     for (int i = tid; i < GE * R; i += nthr) sc.cnt[i] = min(sc.cnt[i], a.slot_cap);
     __syncthreads();
+#pragma unroll 1
     for (int ge = tid; ge < GE && G > 1; ge += nthr) {   // prefix rows and totals of the whole group
         int c = 0;
+#pragma unroll 1
         for (int r = 0; r < R; ++r) {
             sc.prefix[ge * (R + 1) + r] = c;
             c += sc.cnt[ge * R + r];
@@ -888,6 +944,7 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
         int helper = 0;
         if (G > 1) {
             long long mx = 0, sum = 0, nwin = 0;
+#pragma unroll 1
             for (int ge = 0; ge < GE; ++ge) {
                 const long long c = sc.totg[ge];
                 mx = c > mx ? c : mx;
@@ -901,15 +958,18 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
     __syncthreads();
     bool overflow;
     if (T->helper) {
-        if (tid < 32) helper_member_list(sc.totg, GE, EPR, G, a.win_cap, mm, T);
+        if (tid < 32) helper_member_list(sc.totg, GE, a.fEPR, G, a.win_cap, mm, T);
         if (tid == 32) {   // first lookup entry of every group expert
             int c = 0;
+#pragma unroll 1
             for (int ge = 0; ge < GE; ++ge) { sc.gws[ge] = c; c += sched_window_count(sc.totg[ge], a.win_cap); }
             sc.gws[GE] = c;
         }
         __syncthreads();
+#pragma unroll 1
         for (int i = tid; i < sc.gws[GE]; i += nthr) sc.widx[i] = -1;
         __syncthreads();
+#pragma unroll 1
         for (int i = tid; i < T->n_windows; i += nthr) sc.widx[sc.gws[T->gw[i] >> 16] + (T->gw[i] & 0xFFFF)] = i;
         overflow = tables_overflow(a, T->n_windows, T->total_rows);
         if (tid == 0) {
@@ -918,7 +978,9 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
             T->n_tasks = T->n_windows * (nt1 + nt2);
         }
     } else {
+#pragma unroll 1
         for (int i = tid; i < EPR; i += nthr) { T->tot[i] = sc.tot[i]; T->order[i] = sc.order[i]; }
+#pragma unroll 1
         for (int i = tid; i <= EPR; i += nthr) { T->first[i] = sc.first[i]; T->base[i] = sc.base[i]; }
         const int n_windows = sc.first[EPR], total_rows = sc.base[EPR];
         overflow = tables_overflow(a, n_windows, total_rows);
@@ -928,6 +990,7 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
             T->n_tasks = overflow ? 0 : n_windows * (nt1 + nt2);
             T->total_rows = overflow ? 0 : total_rows;
         }
+#pragma unroll 1
         for (int p = tid; p < EPR; p += nthr) sc.fw_e[sc.order[p]] = sc.first[p];
     }
     if (tid == 0) {
@@ -950,14 +1013,18 @@ __device__ void push_publish(const KArgs& a, DevFlags* f, long long epoch, const
     const int* cnt = sc.cnt + mm * EPR * R;                 // this rank's own experts inside the group tables
     const int* prefix = sc.prefix + mm * EPR * (R + 1);
     int* g_prefix = reinterpret_cast<int*>(a.rwk + a.L.prefix_tbl_off);
+#pragma unroll 1
     for (int i = tid; i < EPR * (R + 1); i += nthr) g_prefix[i] = prefix[i];
     uint64_t* recv = reinterpret_cast<uint64_t*>(a.unk + a.L.expert_recv_counts_off) + (size_t)par * R * a.L.recv_stride;
+#pragma unroll 1
     for (int i = tid; i < EPR * R; i += nthr) {
         const int le = i / R, r = i % R;
         recv[(size_t)r * a.L.recv_stride + le] = tagged((uint32_t)cnt[i], epoch);
     }
+#pragma unroll 1
     for (int r = tid; r < R; r += nthr) {   // the reference's checksum word of a count row (src/prologue.cuh:248-255)
         uint32_t csum = 0;
+#pragma unroll 1
         for (int le = 0; le < EPR; ++le) csum += (uint32_t)cnt[le * R + r];
         recv[(size_t)r * a.L.recv_stride + EPR] = tagged(~(csum + 1u), epoch);
     }
@@ -993,19 +1060,21 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
     uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
     int4* meta = reinterpret_cast<int4*>(a.rwk + a.L.row_meta_off);
     uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off) + (size_t)par * a.L.max_windows;
-    const int n16 = H / 8, per_part = n16 / P;   // 8-byte row units; H % 256 == 0: per_part is a multiple of 8
+    const int pshift = P == 4 ? 2 : (P == 2 ? 1 : 0);
+    const int n16 = H / 8, per_part = n16 >> pshift;   // 8-byte row units; H % 256 == 0: per_part is a multiple of 8
+#pragma unroll 1
     for (int it = gwarp; it < W * P; it += nwarps) {
-        const int i = it / P, part = it % P;
+        const int i = it >> pshift, part = it & (P - 1);   // parts are a power of two
         const int e = sc.wid[i];
         if (e < 0) continue;                         // (every `continue` here is uniform over the warp)
-        const int owner = e / EPR;
-        if (owner >= R || owner % n_groups != my_group) continue;
+        const int owner = a.fEPR.div(e);
+        if (owner >= R || a.fng.mod(owner) != my_group) continue;
         const bool own = owner == a.rank;
         if (!own && !helper) continue;
-        const int ge = (owner / n_groups) * EPR + e % EPR, le = e % EPR;
+        const int le = e - owner * EPR, ge = a.fng.div(owner) * EPR + le;
         const int src = push_src_of(sc.sb, R, i);
         const int p = i - sc.sb[src];
-        const int token = p / topk, k = p % topk;
+        const int token = a.ftopk.div(p), k = p - token * topk;
         const uint64_t* row = mine + src * src_words + 16 + (size_t)token * row_words;
         const uint64_t* xs = row + 2 * topk + sfw;
         const uint8_t* peer = a.peer_bases[src];     // the source's input block, for rows of other members' experts
@@ -1024,6 +1093,7 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
             if (lead && a.scaled && lane < sfw_real) sfword = ld_relaxed_sys_u64(row + 2 * topk + lane);
         }
         int c = 0;
+#pragma unroll 1
         for (int j = lane; j < p; j += 32) c += sc.wid[sc.sb[src] + j] == e ? 1 : 0;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, d);
@@ -1033,13 +1103,14 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
         if (own && do_tables && part == 0 && lane == 0) tbl[((size_t)le * R + src) * a.slot_cap + slot] = tagged((uint32_t)p, epoch);
         int g, ready_idx;
         if (helper) {
-            const int li = sc.widx[sc.gws[ge] + gl / a.win_cap];
+            const int gw_ = a.fwin.div(gl);
+            const int li = sc.widx[sc.gws[ge] + gw_];
             if (li < 0) continue;                   // another member computes this window
-            g = (T->rr[li] >> 10) + gl % a.win_cap;
+            g = (T->rr[li] >> 10) + (gl - gw_ * a.win_cap);
             ready_idx = li;
         } else {
             g = T->base[le] + gl;
-            ready_idx = sc.fw_e[le] + gl / a.win_cap;
+            ready_idx = sc.fw_e[le] + a.fwin.div(gl);
         }
         if (!do_rows) continue;
         bool ok = true;
@@ -1051,6 +1122,7 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
                     ok = false;
                 return (uint32_t)w;
             };
+#pragma unroll 1
             for (int u0 = u_lo + lane; u0 < u_hi; u0 += 32 * 8) {
                 if (u0 != u_lo + lane) {   // rows wider than 8 x 32 units per part: further batches
 #pragma unroll
@@ -1082,6 +1154,7 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
             // a window of another member's expert: the row comes from the source rank's input block
             // (the inputs of a launch stay put until the source's own reduce is done, and that waits
             // for this row's result)
+#pragma unroll 1
             for (int u0 = u_lo + lane; u0 < u_hi; u0 += 32 * 8) {
                 uint2 q[8];
 #pragma unroll
@@ -1094,6 +1167,7 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
             if (lead) {
                 if (a.scaled) {
                     const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
+#pragma unroll 1
                     for (int b = lane; b < a.L.sf_stride_h; b += 32)
                         pool_sf[(size_t)g * a.L.sf_stride_h + b] = b < kb ? ld_relaxed_sys_u8(ssf + b) : (uint8_t)127;
                 }
@@ -1151,6 +1225,7 @@ __device__ void reduce_tokens(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, f
         // latency of its loads overlap across the warps of the CTA (a CTA-wide token would put
         // a poll, a fence and two barriers between any two tokens).  Same arithmetic order.
         const int lane = tid & 31, warp = tid >> 5, nw = nthr >> 5;
+#pragma unroll 1
         for (int t = blockIdx.x * nw + warp; t < a.tokens; t += (int)gridDim.x * nw) {
             int ok = 0;
             float w_mine = 0.0f;
@@ -1174,11 +1249,13 @@ __device__ void reduce_tokens(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, f
             const unsigned okmask = __ballot_sync(0xFFFFFFFFu, ok != 0);
             // two column groups per pass: up to 16 row segments of 16 B in flight per lane
             // (H/8 is a multiple of 32, so the second group's validity is uniform over the warp)
+#pragma unroll 1
             for (int c0 = lane; c0 < H / 8; c0 += 64) {
                 const bool two = c0 + 32 < H / 8;
                 float acc[2][8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[0][j] = acc[1][j] = 0.0f;
+#pragma unroll 1
                 for (int k0 = 0; k0 < topk; k0 += 8) {
                     uint4 v[2][8];
                     float wk[8];
@@ -1227,6 +1304,7 @@ __device__ void reduce_tokens(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, f
         }
         return;
     }
+#pragma unroll 1
     for (int t = blockIdx.x; t < a.tokens; t += gridDim.x) {
         if (tid < topk) {
             int ok = ld_relaxed_gpu_u8(pair_state + t * topk + tid);
@@ -1244,10 +1322,12 @@ __device__ void reduce_tokens(const KArgs& a, DevFlags* f, int* s_ok /*[64]*/, f
             s_w[tid] = tw[(size_t)t * topk + tid];
         }
         __syncthreads();
+#pragma unroll 1
         for (int c8 = tid; c8 < H / 8; c8 += nthr) {
             float acc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll 1
             for (int k0 = 0; k0 < topk; k0 += 8) {
                 uint4 v[8];  // up to 8 rows in flight, then summed in k order
 #pragma unroll

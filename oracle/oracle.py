@@ -584,6 +584,9 @@ def helper_world(case: Case, states: List[RankState], group_ranks: int, win_cap:
         for m, r in enumerate(members):
             tot[m * EPR:(m + 1) * EPR] = states[r].prefix_tbl[:, R]
         skewed = int(tot.max()) * tot.size > skew_num * int(tot.sum())
+        # a member's list holds at most max_windows entries (reference kGsMemberCap); the CUDA path keeps
+        # the owner layout when the whole group has more windows than that
+        skewed = skewed and int(sum((int(c) + win_cap - 1) // win_cap for c in tot)) <= max_windows
         for m, r in enumerate(members):
             if not skewed:
                 out[r] = {"on": False, "windows": [], "meta": states[r].meta.copy()}
