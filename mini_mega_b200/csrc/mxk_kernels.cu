@@ -64,6 +64,7 @@ struct KArgs {
     int skew_num;                // helpers on when max * n_experts > skew_num * sum over the group's experts
     int ge_base;                 // this rank's first expert inside the weight arrays (member * EPR with group weights)
     int w_experts;               // experts in the weight arrays w1 / w2 (EPR, or group_ranks * EPR)
+    int prefetch_bytes;          // bytes of W1 every CTA asks into L2 while the prologue runs
     FastDiv fR, fEPR, ftopk, fng, fwin;   // division by R, EPR, topk, R / group_ranks, win_cap
     unsigned long long local_wait_ns, remote_wait_ns;
     uint8_t* rwk;
@@ -153,7 +154,7 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
         // issued by all lanes of one warp (a lane per K block), so that the warp reaches the
         // route phase's first barrier without delay
         const int nt1 = a.I / 128, nkb = a.H / kBlockK;
-        const int per_cta = min(nkb, kPrefetchBytesPerCta / (2 * kABytes));
+        const int per_cta = min(nkb, a.prefetch_bytes / (2 * kABytes));
         for (int tile = blockIdx.x; tile < a.EPR * nt1 && tile < (int)gridDim.x; tile += gridDim.x) {
             const int e = tile / nt1, nt = tile % nt1;
             const int row0 = (a.ge_base + e) * 2 * a.I + nt * 128;   // this rank's own experts inside the weight arrays
@@ -547,6 +548,11 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
         k->win_cap = 256;   // rows per window of a CTA pair
     }
     k->gemm_grid = grid;
+    {
+        // MXK_PREFETCH_KB overrides the L2 prefetch per CTA (tuning knob; 0 switches it off)
+        static const int pf_env = [] { const char* e = std::getenv("MXK_PREFETCH_KB"); return e ? std::atoi(e) * 1024 : -1; }();
+        k->prefetch_bytes = pf_env >= 0 ? pf_env : kPrefetchBytesPerCta;
+    }
     k->fR = FastDiv::make((uint32_t)k->R); k->fEPR = FastDiv::make((uint32_t)k->EPR); k->ftopk = FastDiv::make((uint32_t)k->topk);
     k->fng = FastDiv::make((uint32_t)(k->R / k->group_ranks)); k->fwin = FastDiv::make((uint32_t)k->win_cap);
     return 0;

@@ -116,7 +116,7 @@ __device__ bool route_onepass(const KArgs& a, DevFlags* f, long long epoch, int*
         const int id = s_id[i];
         int r = 0;
         if (id >= 0) {
-#pragma unroll 1
+#pragma unroll 8
             for (int j = 0; j < i; ++j) r += s_id[j] == id ? 1 : 0;
             atomicAdd(&s_hist[id], 1);
         }
@@ -140,10 +140,15 @@ __device__ bool route_onepass(const KArgs& a, DevFlags* f, long long epoch, int*
     for (int e = tid; e < E; e += nthr) {
         int before = 0, total = 0;
 #pragma unroll 1
-        for (int cc = 0; cc < G; ++cc) {
-            const int v = ld_relaxed_gpu(g_cnt + (size_t)cc * E + e);
-            before += cc < c ? v : 0;
-            total += v;
+        for (int c0 = 0; c0 < G; c0 += 16) {   // sixteen loads in flight, then the sums
+            int v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = c0 + j < G ? ld_relaxed_gpu(g_cnt + (size_t)(c0 + j) * E + e) : 0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                before += c0 + j < c ? v[j] : 0;
+                total += v[j];
+            }
         }
         s_base[e] = before;
         if (e % G == c) {
@@ -1093,7 +1098,7 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
             if (lead && a.scaled && lane < sfw_real) sfword = ld_relaxed_sys_u64(row + 2 * topk + lane);
         }
         int c = 0;
-#pragma unroll 1
+#pragma unroll 4
         for (int j = lane; j < p; j += 32) c += sc.wid[sc.sb[src] + j] == e ? 1 : 0;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, d);
