@@ -319,6 +319,16 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                  : "memory");
 }
+// The same commit delivered to the barrier at this offset in BOTH CTAs of the pair with one
+// instruction (a commit costs the issuing thread on the order of a hundred cycles, and the MMA
+// issue loop of a CTA pair needs every stage release and every scale-slot release in both CTAs).
+// This is a signal between the two CTAs of one cluster on one GPU; no memory of another GPU and
+// no TMA load is involved.
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar_smem_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar_smem_addr), "h"((uint16_t)3)
+                 : "memory");
+}
 __device__ __forceinline__ void umma_mxf8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                                uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
     asm volatile(

@@ -238,18 +238,42 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                 if (lookahead) pending = claim_publish(it + 1);
                 const int e = win.x, row0 = win.y + 128 * (int)crank;
                 const bool is_l2 = task.x == 1;
-                // L2: every L1 tile of this window must have landed in ffn; L1: every row of this
-                // window must have been pulled into the pool
-                if (!gate_ok && !MXK_TIMED(w_gate, spin_until([&] { return gate_passed(task, win); }, wait_ns, abort_flag))) {
-                    raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
-                }
-                if (trace && it == 0) trace[8] = gtimer_ns();
-                fence_proxy_async_global();  // pool / ffn rows were written with ordinary stores
                 const CUtensorMap* ma = is_l2 ? &tm_ffn : &tm_pool;
                 const CUtensorMap* mb = is_l2 ? &tm_w2 : &tm_w1;
                 const int nkb = is_l2 ? kb2 : kb1;
                 const int brow0 = is_l2 ? e * a.H + task.z * kBlockN : e * 2 * a.I + task.z * 128;
                 const int brow1 = is_l2 ? brow0 + 128 : brow0 + a.I;
+                // weight tiles of K block kb into ring stage st (the stage's byte count is announced with them)
+                auto load_b = [&](int kb, uint32_t st) {
+                    uint8_t* sa = tiles + st * kStageB;
+                    if constexpr (kPair) {
+                        // both CTAs' bytes complete on the leader's barrier: 2 x (A 16 KB + weight half 16 KB)
+                        if (leader) mbar_expect_tx(&S->full[st], 2 * kPairStageBytes);
+                        tma_load_2d_pair_hint(sa + kABytes, mb, kb * kBlockK, leader ? brow0 : brow1, mapa_u32(smem_u32(&S->full[st]), 0), stream_policy);
+                    } else {
+                        mbar_expect_tx(&S->full[st], kStageBytes);
+                        tma_load_2d_hint(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[st], stream_policy);
+                        tma_load_2d_hint(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[st], stream_policy);
+                    }
+                };
+                // L2: every L1 tile of this window must have landed in ffn; L1: every row of this
+                // window must have been pulled into the pool.  The weight tiles do not depend on that:
+                // while the gate is still closed they are requested into whatever stages are free, so
+                // that HBM streams during the wait (the first task of a layer waits for the dispatch).
+                int pre = 0;
+                if (!gate_ok) {
+                    uint32_t st2 = stage, ph2 = phase;
+                    while (pre < nkb && pre < kNStages && mbar_try_wait(&S->empty[st2], ph2 ^ 1)) {
+                        load_b(pre, st2);
+                        ++pre;
+                        if (++st2 == (uint32_t)kNStages) { st2 = 0; ph2 ^= 1; }
+                    }
+                    if (!MXK_TIMED(w_gate, spin_until([&] { return gate_passed(task, win); }, wait_ns, abort_flag))) {
+                        raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
+                    }
+                }
+                if (trace && it == 0) trace[8] = gtimer_ns();
+                fence_proxy_async_global();  // pool / ffn rows were written with ordinary stores
                 bool dead = false;
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (lookahead && pending.x >= 0) {
@@ -259,20 +283,13 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                         if (kb == 0) { pending_win = get_window(pending.y); pending_win_valid = true; pending_gate = false; }
                         else if (kb == 2) pending_gate = gate_passed(pending, pending_win);
                     }
-                    if (!MXK_TIMED(w_empty, mbar_wait(&S->empty[stage], phase ^ 1, wait_ns, abort_flag))) { dead = true; break; }
-                    uint8_t* sa = tiles + stage * kStageB;
-                    if constexpr (kPair) {
-                        // both CTAs' bytes complete on the leader's barrier: 2 x (A 16 KB + weight half 16 KB)
-                        if (leader) mbar_expect_tx(&S->full[stage], 2 * kPairStageBytes);
-                        const uint32_t bar = mapa_u32(smem_u32(&S->full[stage]), 0);
-                        tma_load_2d_pair(sa, ma, kb * kBlockK, row0, bar);
-                        tma_load_2d_pair_hint(sa + kABytes, mb, kb * kBlockK, leader ? brow0 : brow1, bar, stream_policy);
-                    } else {
-                        mbar_expect_tx(&S->full[stage], kStageBytes);
-                        tma_load_2d(sa, ma, kb * kBlockK, row0, &S->full[stage]);
-                        tma_load_2d_hint(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[stage], stream_policy);
-                        tma_load_2d_hint(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[stage], stream_policy);
+                    if (kb >= pre) {
+                        if (!MXK_TIMED(w_empty, mbar_wait(&S->empty[stage], phase ^ 1, wait_ns, abort_flag))) { dead = true; break; }
+                        load_b(kb, stage);
                     }
+                    uint8_t* sa = tiles + stage * kStageB;
+                    if constexpr (kPair) tma_load_2d_pair(sa, ma, kb * kBlockK, row0, mapa_u32(smem_u32(&S->full[stage]), 0));
+                    else tma_load_2d(sa, ma, kb * kBlockK, row0, &S->full[stage]);
                     if (trace && it == 0 && kb == 0) trace[9] = gtimer_ns();
                     if (++stage == kNStages) { stage = 0; phase ^= 1; }
                 }
@@ -292,13 +309,6 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
             bool sf_ready = false;      // likewise sf_full of the next group
             const uint64_t tile_desc0 = umma_smem_desc_sw128(smem_u32(tiles));
             const uint32_t idesc0 = umma_idesc_mx_e4m3(kPair ? 2 * kBlockM : kBlockM, kBlockN, 0, 0);
-            // the partner's copies of the barriers the MMAs release
-            uint32_t peer_empty0 = 0, peer_sf_empty0 = 0, peer_tmem_full = 0;
-            if constexpr (kPair) {
-                peer_empty0 = mapa_u32(smem_u32(&S->empty[0]), 1);
-                peer_sf_empty0 = mapa_u32(smem_u32(&S->sf_empty[0]), 1);
-                peer_tmem_full = mapa_u32(smem_u32(&S->tmem_full), 1);
-            }
             for (uint32_t it = 0;; ++it) {
                 const uint32_t slot = it % kTaskRing;
                 if (!mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag)) {
@@ -342,9 +352,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                             if (i == 2) sf_ready = mbar_try_wait_cluster(&S->sf_full[nsf_slot], nsf_parity);
                             umma_mxf8_pair(tmem_base, adesc + 4, bdesc + 4, idesc, tsf, tsf + 4, 1u);
                             umma_mxf8_pair(tmem_base, adesc + 6, bdesc + 6, idesc, tsf, tsf + 4, 1u);
-                            // one commit per barrier and CTA: both producers / builders move on
-                            umma_commit_pair(smem_u32(&S->empty[stage]));
-                            umma_commit_pair(peer_empty0 + stage * 8);
+                            // one commit releases the stage in both CTAs: both producers move on
+                            umma_commit_pair_both(smem_u32(&S->empty[stage]));
                         } else {
                             umma_mxf8(tmem_base, adesc, bdesc, idesc, tsf, tsf + 4, acc);
                             umma_mxf8(tmem_base, adesc + 2, bdesc + 2, idesc, tsf, tsf + 4, 1u);
@@ -359,8 +368,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                     }
                     if (dead) break;
                     if constexpr (kPair) {
-                        umma_commit_pair(smem_u32(&S->sf_empty[sf_slot]));
-                        umma_commit_pair(peer_sf_empty0 + sf_slot * 8);
+                        umma_commit_pair_both(smem_u32(&S->sf_empty[sf_slot]));
                     } else {
                         umma_commit(&S->sf_empty[sf_slot]);
                     }
@@ -368,8 +376,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                 }
                 if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 6); *abort_flag = 1; break; }
                 if constexpr (kPair) {
-                    umma_commit_pair(smem_u32(&S->tmem_full));
-                    umma_commit_pair(peer_tmem_full);
+                    umma_commit_pair_both(smem_u32(&S->tmem_full));
                 } else {
                     umma_commit(&S->tmem_full);  // accumulators complete
                 }
