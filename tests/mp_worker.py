@@ -109,6 +109,38 @@ def run_gpu():
         dist.barrier()
         del g
         buf.destroy()
+    # many rows per rank with the pull-mode prologue: the dispatch is streamed behind the GEMM phase
+    # (rows pulled over NVLink by the builder warps while L1 tasks of earlier windows already run)
+    big = orc.gen_case(world, 4, 4, 1024, 512, [1100] * world, seed=24, routing="uniform", scaled=True, cap=1100)
+    big_ref = orc.layer_world(big)
+    buf = mm.get_symm_buffer_for_mega_moe(group, big.E, big.cap, big.topk, big.H, big.I, dispatch_mode=1)
+    buf.x.view(torch.uint8).copy_(torch.from_numpy(big.x[rank]))
+    buf.x_sf.copy_(torch.from_numpy(big.x_sf[rank]))
+    buf.topk_idx.copy_(torch.from_numpy(big.topk_idx[rank]))
+    buf.topk_weights.copy_(torch.from_numpy(big.topk_w[rank]))
+    sl = slice(rank * big.EPR, (rank + 1) * big.EPR)
+    l1, l2 = mm.transform_weights_for_mega_moe(
+        (torch.from_numpy(big.w1[sl]).cuda(), torch.from_numpy(big.w1_sf[sl]).cuda()),
+        (torch.from_numpy(big.w2[sl]).cuda(), torch.from_numpy(big.w2_sf[sl]).cuda()))
+    y = torch.zeros((1100, big.H), dtype=torch.bfloat16, device="cuda")
+    for rep in range(2):
+        y.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        mm.fp8_mega_moe(y, l1, l2, buf)
+        torch.cuda.synchronize()
+        st = buf.status()
+        assert st.status == 0, f"rank {rank} streamed dispatch: device status {st.status} dbg {list(st.dbg)}"
+        s_ = big_ref[rank]
+        rows = s_.meta.shape[0]
+        assert rows >= 4096 and st.total_rows == rows
+        assert np.array_equal(buf.table("row_meta")[:rows, :3].cpu().numpy(), s_.meta)
+        assert np.array_equal(buf.table("pool")[:rows].cpu().numpy(), s_.pool)
+        err = orc.rel_l2(y.float().cpu().numpy(), s_.y)
+        worst = max(worst, err)
+        assert err <= 1e-2, f"rank {rank} streamed dispatch: relative L2 {err}"
+        dist.barrier()
+    buf.destroy()
     # cross-rank helper scheduling over real peer memory: one helper group spanning the world, helpers
     # forced on; a member computes windows of the other rank's experts from its weight replica, pulling
     # the rows from the source rank's input block; tables of the owner stay exact, pool rows follow the

@@ -178,6 +178,19 @@ def test_cta_pair_mode():
     _run_case(orc.gen_case(1, 4, 2, 1024, 512, 400, seed=15, routing="uniform", scaled=False), cta_pair=2, dispatch_mode=2)
 
 
+def test_streamed_dispatch_fused():
+    """Pull-mode prologue with more than 4096 pool rows in ONE launch of the whole layer: the dispatch
+    is then streamed — only the first wave's windows are pulled before the GEMM phase starts, the
+    rest row by row (in task order, from a global counter) by the scale-tile builder warps while
+    they wait; every L1 task is gated on its window's row count.  Phase-split reference run, then the
+    fused launch three times on the same buffers, single CTAs and CTA pairs."""
+    case = orc.gen_case(1, 8, 4, 512, 256, 1100, seed=43, routing="zipf", scaled=True)
+    ref = orc.layer_world(case)
+    assert ref[0].meta.shape[0] >= 4096
+    _run_case(case, dispatch_mode=1, cta_pair=1, ref=ref)
+    _run_case(case, dispatch_mode=1, cta_pair=2, ref=ref, full_stage_checks=False)
+
+
 def test_prefill_geometry_h7168():
     """BASELINE config 4's geometry (H=7168, I=2048: 56 K blocks = 14 scale groups per L1 task, scale
     rows of 56 live bytes in a stride of 64) on a small world: 8 experts, top-4, 600 tokens, so that the
