@@ -432,6 +432,10 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
             int asf_stride = 0;
             const uint8_t* wsf0 = nullptr;
             const uint8_t* wsf1 = nullptr;
+            if (!a.scaled && !is_l2) {   // streamed dispatch without scale planes: same duty, no scales to wait for
+                while (more_rows && !__all_sync(0xFFFFFFFFu, ld_acquire_gpu(pool_ready + task.y) >= (uint32_t)win.z * row_parts ? 1 : 0))
+                    more_rows = dispatch_claim_row(a, f, epoch, disp_windows, nullptr);
+            }
             if (a.scaled) {
                 if (is_l2) {
                     // ffn scales are written by L1 epilogues of this same kernel
@@ -448,6 +452,10 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                     // pool scales are written by the dispatch phase of this same kernel
                     bool ready = true;
                     const uint32_t need_rows = (uint32_t)win.z * row_parts;
+                    // streamed dispatch: the rows this task waits for may not even be claimed yet, and the
+                    // builder warps are the ones that pull them — never sit on the gate while rows are left
+                    while (more_rows && !__all_sync(0xFFFFFFFFu, ld_acquire_gpu(pool_ready + task.y) >= need_rows ? 1 : 0))
+                        more_rows = dispatch_claim_row(a, f, epoch, disp_windows, nullptr);
                     ready = spin_until([&] { return ld_acquire_gpu(pool_ready + task.y) >= need_rows; }, wait_ns, abort_flag);
                     ready = __all_sync(0xFFFFFFFFu, ready ? 1 : 0) != 0;
                     if (!ready) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; } break; }

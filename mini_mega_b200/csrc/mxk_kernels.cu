@@ -527,8 +527,13 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     k->tokens = la->tokens; k->win_cap = win;
     k->skip_combine = la->skip_combine; k->scaled = la->w1_sf != nullptr;
     k->ticks = ticks_enabled();  // the kernel accounts its wait cycles and stamps its phases (MxkStatus.ticks / trace)
-    k->local_wait_ns = la->max_spins > 0 ? (unsigned long long)la->max_spins * 250ull : kDefaultLocalWaitNs;
-    k->remote_wait_ns = la->max_spins > 0 ? (unsigned long long)la->max_spins * 250ull : kDefaultRemoteWaitNs;
+    {
+        // MXK_MAX_SPINS: bound of every device wait (units of 250 ns) for launches that leave max_spins at 0
+        static const int spins_env = [] { const char* e = std::getenv("MXK_MAX_SPINS"); return e ? std::atoi(e) : 0; }();
+        const int spins = la->max_spins > 0 ? la->max_spins : spins_env;
+        k->local_wait_ns = spins > 0 ? (unsigned long long)spins * 250ull : kDefaultLocalWaitNs;
+        k->remote_wait_ns = spins > 0 ? (unsigned long long)spins * 250ull : kDefaultRemoteWaitNs;
+    }
     k->rwk = static_cast<uint8_t*>(la->rwk); k->unk = static_cast<uint8_t*>(la->unk);
     k->unk_peers = la->unk_peers; k->self = la->self; k->peer_bases = la->peer_bases;
     k->topk_idx = la->topk_idx ? la->topk_idx : reinterpret_cast<const int64_t*>(la->self + la->topk_idx_off);
