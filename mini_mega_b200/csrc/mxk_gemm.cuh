@@ -131,8 +131,7 @@ __device__ void gemm_init_barriers(GemmSmem* S, const bool pair) {
 // set-up tables of this launch are visible.  Returns when every role has left its loop.
 template <bool kPair>
 __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, const PushTabs* tabs,
-                           unsigned long long* trace, int* deferred_route_smem, const bool stream_dispatch, uint8_t* tiles,
-                           uint8_t* sf_tiles, GemmSmem* S,
+                           unsigned long long* trace, int* deferred_route_smem, uint8_t* tiles, uint8_t* sf_tiles, GemmSmem* S,
                            const uint32_t tmem_base, const CUtensorMap* tm_pool_p, const CUtensorMap* tm_ffn_p,
                            const CUtensorMap* tm_w1_p, const CUtensorMap* tm_w2_p) {
     const CUtensorMap& tm_pool = *tm_pool_p;
@@ -400,17 +399,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
         const uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
         const uint8_t* ffn_sf = a.rwk + a.L.ffn_sf_off;
         uint32_t sfg = 0;
-        bool more_rows = stream_dispatch;   // pool rows left to claim (streamed dispatch)
-        const int disp_windows = stream_dispatch ? ld_relaxed_gpu(&f->n_windows) : 0;
         for (uint32_t it = 0;; ++it) {
             const uint32_t slot = it % kTaskRing;
-            // streamed dispatch: while the next ring entry is not there, this warp pulls pool rows
-            while (more_rows) {
-                bool there = false;
-                if (lane == 0) there = mbar_try_wait(&S->task_full[slot], (it / kTaskRing) & 1);
-                if (__shfl_sync(0xFFFFFFFFu, there ? 1 : 0, 0)) break;
-                more_rows = dispatch_claim_row(a, f, epoch, disp_windows, nullptr);
-            }
             bool ok = true;
             if (lane == 0) ok = wait_bar(&S->task_full[slot], (it / kTaskRing) & 1);
             ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
@@ -422,20 +412,13 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
             const bool is_l2 = task.x == 1;
             const int nkb = is_l2 ? kb2 : kb1;
             const int ngroups = (nkb + 3) >> 2;
-            if ((it & 1u) != my_parity) {   // the other warp's task: time for a few pool rows
-                sfg += (uint32_t)ngroups;
-                continue;
-            }
+            if ((it & 1u) != my_parity) { sfg += (uint32_t)ngroups; continue; }   // the other warp's task
             const int4 win = get_window(task.y);
             const int e = win.x, row0 = win.y + 128 * (int)crank, rows = task.w - 128 * (int)crank;
             const uint8_t* asf = nullptr;   // activation scale rows of this window
             int asf_stride = 0;
             const uint8_t* wsf0 = nullptr;
             const uint8_t* wsf1 = nullptr;
-            if (!a.scaled && !is_l2) {   // streamed dispatch without scale planes: same duty, no scales to wait for
-                while (more_rows && !__all_sync(0xFFFFFFFFu, ld_acquire_gpu(pool_ready + task.y) >= (uint32_t)win.z * row_parts ? 1 : 0))
-                    more_rows = dispatch_claim_row(a, f, epoch, disp_windows, nullptr);
-            }
             if (a.scaled) {
                 if (is_l2) {
                     // ffn scales are written by L1 epilogues of this same kernel
@@ -452,10 +435,6 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                     // pool scales are written by the dispatch phase of this same kernel
                     bool ready = true;
                     const uint32_t need_rows = (uint32_t)win.z * row_parts;
-                    // streamed dispatch: the rows this task waits for may not even be claimed yet, and the
-                    // builder warps are the ones that pull them — never sit on the gate while rows are left
-                    while (more_rows && !__all_sync(0xFFFFFFFFu, ld_acquire_gpu(pool_ready + task.y) >= need_rows ? 1 : 0))
-                        more_rows = dispatch_claim_row(a, f, epoch, disp_windows, nullptr);
                     ready = spin_until([&] { return ld_acquire_gpu(pool_ready + task.y) >= need_rows; }, wait_ns, abort_flag);
                     ready = __all_sync(0xFFFFFFFFu, ready ? 1 : 0) != 0;
                     if (!ready) { if (lane == 0) { raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; } break; }
@@ -502,12 +481,6 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                 load_group(g + 1, na, n0, n1);
                 const uint32_t sslot = sfg % kSfRing;
                 bool free_ = true;
-                while (more_rows) {   // streamed dispatch while the slot is still in use
-                    bool there = false;
-                    if (lane == 0) there = mbar_try_wait(&S->sf_empty[sslot], ((sfg / kSfRing) & 1) ^ 1);
-                    if (__shfl_sync(0xFFFFFFFFu, there ? 1 : 0, 0)) break;
-                    more_rows = dispatch_claim_row(a, f, epoch, disp_windows, nullptr);
-                }
                 if (lane == 0) free_ = mbar_wait(&S->sf_empty[sslot], ((sfg / kSfRing) & 1) ^ 1, wait_ns, abort_flag);
                 free_ = __shfl_sync(0xFFFFFFFFu, free_ ? 1 : 0, 0) != 0;
                 if (!free_) { dead = true; break; }

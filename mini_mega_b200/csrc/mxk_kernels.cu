@@ -41,7 +41,6 @@ struct DevFlags {  // head of rwk (flags_off)
     unsigned pad0_;
     unsigned task_ctr[2];        // claimed tasks beyond the first per CTA, by launch parity (the
                                  // copy of the other parity is reset for the next launch)
-    unsigned dispatch_ctr[2];    // claimed pool rows of the streamed dispatch, likewise
     int n_tasks, n_l1_tasks, n_windows, total_rows;
     int helper_on;               // the last launch ran the member's window list of the helper group
     int status;
@@ -186,7 +185,7 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
     if (stamp && blockIdx.x == 0) f->ticks[9] = gtimer_ns() - t0;
     if (trace && threadIdx.x == 0) trace[3] = gtimer_ns();
 
-    bool tables_ok = true, stream_dispatch = false;
+    bool tables_ok = true;
     const PushTabs* tabs = nullptr;
     if (a.push) {
         if (phase_mask & (MXK_PHASE_SETUP | MXK_PHASE_DISPATCH | MXK_PHASE_GEMM)) {
@@ -215,11 +214,7 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
         if (stamp && blockIdx.x == 0) f->ticks[10] = gtimer_ns() - t0;
         if (trace && threadIdx.x == 0) trace[6] = gtimer_ns();
         if ((phase_mask & MXK_PHASE_DISPATCH) && tables_ok) {
-            // many rows and a GEMM phase behind: only the first wave's rows now, the rest is claimed by
-            // the epilogue warps while they wait (dispatch_claim_row)
-            stream_dispatch = do_gemm && ld_relaxed_gpu(&f->total_rows) >= kStreamDispatchMinRows;
-            if (stream_dispatch) dispatch_first_wave(a, f, epoch, kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x);
-            else dispatch_phase(a, f, epoch, reinterpret_cast<int*>(tiles));  // tile region still idle: scratch
+            dispatch_phase(a, f, epoch, reinterpret_cast<int*>(tiles));  // tile region still idle: scratch
             fence_proxy_async_smem();
             __syncthreads();
         }
@@ -229,8 +224,8 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
 
     if (do_gemm) {
         if (tables_ok)
-            gemm_phase<kPair>(a, f, epoch, tabs, trace, defer_route ? s_small : nullptr, stream_dispatch, tiles, sf_tiles, S,
-                              tmem_base, &tm_pool, &tm_ffn, &tm_w1, &tm_w2);
+            gemm_phase<kPair>(a, f, epoch, tabs, trace, defer_route ? s_small : nullptr, tiles, sf_tiles, S, tmem_base, &tm_pool,
+                              &tm_ffn, &tm_w1, &tm_w2);
         else if (defer_route)   // no GEMM phase after all (tables failed): the launch bookkeeping still has to happen
             route_phase(a, f, epoch, s_small, nullptr, 0, true, cta_team);
         if (S->abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain

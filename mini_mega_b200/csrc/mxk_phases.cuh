@@ -419,7 +419,7 @@ __device__ void publish_tables(const KArgs& a, DevFlags* f, long long epoch, con
 #pragma unroll 1
             for (int w = lane; w < nw; w += 32) {
                 const int rows = min(a.win_cap, c - w * a.win_cap);
-                windows[fw + w] = make_int4(e, s_base[e] + w * a.win_cap, rows, 0);   // (expert, first pool row, rows, -)
+                windows[fw + w] = make_int4(e, s_base[e] + w * a.win_cap, rows, 0);
                 if (!a.push) { l1_done[fw + w] = 0; pool_ready[fw + w] = 0; }
             }
 #pragma unroll 1
@@ -444,8 +444,7 @@ __device__ void publish_tables(const KArgs& a, DevFlags* f, long long epoch, con
         f->n_l1_tasks = n_l1;
         f->n_tasks = n_windows * (nt1 + nt2);
         f->total_rows = rows_out;
-        f->task_ctr[par ^ 1] = 0;   // the next launch's claim counters
-        f->dispatch_ctr[par ^ 1] = 0;
+        f->task_ctr[par ^ 1] = 0;   // the next launch's claim counter
     }
     __threadfence();
     __syncthreads();
@@ -617,111 +616,6 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
         fence_proxy_async_global();
         __syncwarp();
         if (lane == 0) red_release_gpu_add(pool_ready + first_win[le] + a.fwin.div(gl), 1u);
-    }
-}
-
-// Streamed dispatch (pull mode, many rows): instead of a whole-grid phase in front of the GEMM
-// phase, pool rows are claimed one by one IN TASK ORDER (window by window) from a global counter:
-// by every warp until the windows of the first wave of tasks are covered, then by the epilogue warps
-// of the GEMM phase whenever they would otherwise wait — an L1 task is gated on its window's
-// pool_ready count anyway, so the GEMMs start after a few microseconds and the rest of the dispatch
-// (NVLink-bound on several GPUs) hides behind them.  Claim u = window * win_cap + row.
-// Returns false when every unit has been claimed.  Called by all lanes of a warp.
-__device__ __noinline__ bool dispatch_claim_row(const KArgs& a, DevFlags* f, long long epoch, int n_windows, int* claimed) {
-    const int lane = threadIdx.x & 31;
-    const int par = (int)(epoch & 1);
-    int u = 0;
-    if (lane == 0) u = (int)atomicAdd(&f->dispatch_ctr[par], 1u);
-    u = __shfl_sync(0xFFFFFFFFu, u, 0);
-    if (claimed) *claimed = u;
-    const int w_idx = a.fwin.div(u), r = u - w_idx * a.win_cap;
-    if (w_idx >= n_windows) return false;
-    const int R = a.R, EPR = a.EPR, H = a.H, kb = H / 128;
-    const int4 win = ld_relaxed_gpu_v4(reinterpret_cast<const int4*>(a.rwk + a.L.windows_off) + w_idx);
-    if (r >= win.z) return true;   // the window's tail: nothing behind this claim
-    const int le = win.x, g = win.y + r;
-    const int gl = g - ld_relaxed_gpu(reinterpret_cast<const int*>(a.rwk + a.L.expert_row_base_off) + le);
-    // source rank = largest src with prefix[le][src] <= gl; the expert's prefix row is read by the lanes
-    const int* pf = reinterpret_cast<const int*>(a.rwk + a.L.prefix_tbl_off) + le * (R + 1);
-    int src = 0, pf_src = 0;
-#pragma unroll 1
-    for (int c0 = 0; c0 < R; c0 += 32) {
-        const int v = c0 + lane < R ? ld_relaxed_gpu(pf + c0 + lane) : 0x7FFFFFFF;
-        const unsigned m = __ballot_sync(0xFFFFFFFFu, v <= gl);
-        if (m) {
-            const int hi = 31 - __clz(m);
-            src = c0 + hi;
-            pf_src = __shfl_sync(0xFFFFFFFFu, v, hi);
-        }
-    }
-    const int slot = gl - pf_src;
-    const uint64_t* tbl = reinterpret_cast<const uint64_t*>(a.unk + a.L.src_index_table_off) + (size_t)par * EPR * R * a.slot_cap;
-    uint64_t tw = 0;
-    {
-        const uint64_t* tp = tbl + ((size_t)le * R + src) * a.slot_cap + slot;
-        if (!spin_until([&] { tw = ld_relaxed_sys_u64(tp); return (uint32_t)(tw >> 32) == (uint32_t)epoch; },
-                        a.remote_wait_ns, nullptr)) {
-            if (lane == 0) raise_status(f, MXK_DEV_TIMEOUT_BARRIER, 2);
-            tw = 0;
-        }
-    }
-    uint32_t idx = (uint32_t)tw;
-    if (idx >= (uint32_t)(a.cap * a.topk)) {
-        if (lane == 0) raise_status(f, MXK_DEV_BAD_TABLE, 3);
-        idx = 0;
-    }
-    const int token = a.ftopk.div((int)idx), k = (int)idx - token * a.topk;
-    const uint8_t* peer = a.peer_bases[src];
-    const uint4* srow = reinterpret_cast<const uint4*>(peer + a.x_off + (size_t)token * H);
-    uint4* drow = reinterpret_cast<uint4*>(a.rwk + a.L.pool_off + (size_t)g * H);
-    const int n16 = H / 16;
-    uint32_t wbits = 0;
-    if (lane == 0)
-        wbits = ld_relaxed_sys(reinterpret_cast<const uint32_t*>(peer + a.weights_off) + (size_t)token * a.topk + k);
-    uint8_t sfb[2] = {127, 127};
-    if (a.scaled) {
-        const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
-        if (lane < kb) sfb[0] = ld_relaxed_sys_u8(ssf + lane);
-        if (lane + 32 < kb) sfb[1] = ld_relaxed_sys_u8(ssf + lane + 32);
-    }
-#pragma unroll 1
-    for (int i0 = lane; i0 < n16; i0 += 32 * 8) {
-        uint4 v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (i0 + 32 * j < n16) v[j] = ld_relaxed_sys_v4(srow + i0 + 32 * j);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (i0 + 32 * j < n16) drow[i0 + 32 * j] = v[j];
-    }
-    if (a.scaled) {
-        uint8_t* pool_sf = a.rwk + a.L.pool_sf_off;
-        const uint8_t* ssf = peer + a.x_sf_off + (size_t)token * kb;
-#pragma unroll 1
-        for (int i = lane; i < a.L.sf_stride_h; i += 32)
-            pool_sf[(size_t)g * a.L.sf_stride_h + i] = i < 64 ? sfb[i >> 5] : (i < kb ? ld_relaxed_sys_u8(ssf + i) : (uint8_t)127);
-    }
-    if (lane == 0) reinterpret_cast<int4*>(a.rwk + a.L.row_meta_off)[g] = make_int4(src, token, k, (int)wbits);
-    __threadfence();
-    fence_proxy_async_global();
-    __syncwarp();
-    if (lane == 0)
-        red_release_gpu_add(reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off) + (size_t)par * a.L.max_windows + w_idx, 1u);
-    return true;
-}
-
-constexpr int kStreamDispatchMinRows = 4096;   // below this the whole-grid dispatch phase is short anyway
-
-// First stage of the streamed dispatch, all warps of the grid: rows of the windows the first wave
-// of tasks works on.
-__device__ void dispatch_first_wave(const KArgs& a, DevFlags* f, long long epoch, int n_units) {
-    const int n_windows = ld_relaxed_gpu(&f->n_windows);
-    const int nt1 = a.I / 128;
-    const int first = min(n_windows, n_units / nt1 + 2) * a.win_cap;   // claims below this cover the first wave's windows
-#pragma unroll 1
-    for (;;) {
-        int u = 0;
-        if (!dispatch_claim_row(a, f, epoch, n_windows, &u) || u >= first) break;
     }
 }
 

@@ -109,8 +109,8 @@ def run_gpu():
         dist.barrier()
         del g
         buf.destroy()
-    # many rows per rank with the pull-mode prologue: the dispatch is streamed behind the GEMM phase
-    # (rows pulled over NVLink by the builder warps while L1 tasks of earlier windows already run)
+    # many rows per rank with the pull-mode prologue (one-pass route build, thousands of rows pulled
+    # over NVLink, CTA pairs chosen by load)
     big = orc.gen_case(world, 4, 4, 1024, 512, [1100] * world, seed=24, routing="uniform", scaled=True, cap=1100)
     big_ref = orc.layer_world(big)
     buf = mm.get_symm_buffer_for_mega_moe(group, big.E, big.cap, big.topk, big.H, big.I, dispatch_mode=1)
@@ -130,7 +130,7 @@ def run_gpu():
         mm.fp8_mega_moe(y, l1, l2, buf)
         torch.cuda.synchronize()
         st = buf.status()
-        assert st.status == 0, f"rank {rank} streamed dispatch: device status {st.status} dbg {list(st.dbg)}"
+        assert st.status == 0, f"rank {rank} large pull-mode layer: device status {st.status} dbg {list(st.dbg)}"
         s_ = big_ref[rank]
         rows = s_.meta.shape[0]
         assert rows >= 4096 and st.total_rows == rows
@@ -138,7 +138,7 @@ def run_gpu():
         assert np.array_equal(buf.table("pool")[:rows].cpu().numpy(), s_.pool)
         err = orc.rel_l2(y.float().cpu().numpy(), s_.y)
         worst = max(worst, err)
-        assert err <= 1e-2, f"rank {rank} streamed dispatch: relative L2 {err}"
+        assert err <= 1e-2, f"rank {rank} large pull-mode layer: relative L2 {err}"
         dist.barrier()
     buf.destroy()
     # cross-rank helper scheduling over real peer memory: one helper group spanning the world, helpers

@@ -178,12 +178,10 @@ def test_cta_pair_mode():
     _run_case(orc.gen_case(1, 4, 2, 1024, 512, 400, seed=15, routing="uniform", scaled=False), cta_pair=2, dispatch_mode=2)
 
 
-def test_streamed_dispatch_fused():
-    """Pull-mode prologue with more than 4096 pool rows in ONE launch of the whole layer: the dispatch
-    is then streamed — only the first wave's windows are pulled before the GEMM phase starts, the
-    rest row by row (in task order, from a global counter) by the scale-tile builder warps while
-    they wait; every L1 task is gated on its window's row count.  Phase-split reference run, then the
-    fused launch three times on the same buffers, single CTAs and CTA pairs."""
+def test_pull_mode_many_rows_fused():
+    """Pull-mode prologue with more than 4096 pool rows (one-pass route build, several windows per
+    expert), phase-split against the oracle and then as ONE launch of the whole layer three times on
+    the same buffers; single CTAs and CTA pairs."""
     case = orc.gen_case(1, 8, 4, 512, 256, 1100, seed=43, routing="zipf", scaled=True)
     ref = orc.layer_world(case)
     assert ref[0].meta.shape[0] >= 4096
