@@ -247,7 +247,7 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
-k_mega(const __grid_constant__ KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap tm_pool,
+k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap tm_pool,
        const __grid_constant__ CUtensorMap tm_ffn, const __grid_constant__ CUtensorMap tm_w1,
        const __grid_constant__ CUtensorMap tm_w2) {
     mega_body<false>(a, phase_mask, tm_pool, tm_ffn, tm_w1, tm_w2);
@@ -256,7 +256,7 @@ k_mega(const __grid_constant__ KArgs a, const int phase_mask, const __grid_const
 // The same layer with the GEMM phase on CTA pairs (clusters of two, 2-CTA tcgen05 MMA with
 // M = 256): for windows of up to 256 rows, i.e. the compute-bound regime.
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
-k_mega_pair(const __grid_constant__ KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap tm_pool,
+k_mega_pair(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap tm_pool,
             const __grid_constant__ CUtensorMap tm_ffn, const __grid_constant__ CUtensorMap tm_w1,
             const __grid_constant__ CUtensorMap tm_w2) {
     mega_body<true>(a, phase_mask, tm_pool, tm_ffn, tm_w1, tm_w2);

@@ -668,8 +668,6 @@ struct PushScratch {   // carved from the operand-tile region, which is idle unt
     int* totg;     // [GE] rows per group expert
     int* gws;      // [GE+1] first entry of group expert ge in widx
     int* widx;     // [group windows] index of (ge, w) in this member's list, -1 = another member's
-    unsigned short* mine;   // [kPushMaxPairs] world pairs whose expert belongs to this rank (its helper group), any order
-    int* n_mine;   // [1]
 };
 constexpr int kPushMaxGroupWin = 4096;   // windows of a whole helper group (lookup table entries)
 __device__ __forceinline__ PushScratch push_scratch(uint8_t* tiles) {
@@ -688,12 +686,9 @@ __device__ __forceinline__ PushScratch push_scratch(uint8_t* tiles) {
     sc.totg = sc.base + kPushMaxEPR + 1;
     sc.gws = sc.totg + kPushMaxCnt;
     sc.widx = sc.gws + kPushMaxCnt + 1;
-    sc.n_mine = sc.widx + kPushMaxGroupWin;
-    sc.mine = reinterpret_cast<unsigned short*>(sc.n_mine + 1);
-    static_assert(kPushMaxPairs <= 65536, "pair indices fit 16 bits");
     return sc;
 }
-static_assert((kPushMaxPairs + kPushMaxPairs / 2 + 4 * kPushMaxCnt + 8 * kPushMaxEPR + 2 * kPushMaxR + kPushMaxGroupWin + 32) * 4 <= 192 * 1024,
+static_assert((kPushMaxPairs + 4 * kPushMaxCnt + 8 * kPushMaxEPR + 2 * kPushMaxR + kPushMaxGroupWin + 16) * 4 <= 192 * 1024,
               "push-mode scratch fits the operand-tile region (4 stages of 48 KB)");
 __device__ __forceinline__ int xin_sf_words(int H) { return (((H / 128) + 3) / 4 + 1) & ~1; }   // even: rows stay 16-byte aligned
 __device__ __forceinline__ uint64_t* xin_block(const KArgs& a, void* unk_base, int par, int src) {
@@ -867,7 +862,7 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
     const uint64_t* mine = xin_block(a, a.unk, par, 0);
     const size_t src_words = (size_t)a.L.xin_src_words;
     const int row_words = a.L.xin_row_words;
-    if (tid == 0) { *sc.flag = 1; *sc.n_mine = 0; }
+    if (tid == 0) *sc.flag = 1;
 #pragma unroll 1
     for (int i = tid; i < GE * R; i += nthr) sc.cnt[i] = 0;
 #pragma unroll 1
@@ -923,10 +918,8 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
             sc.wid[i] = e;
             if (e >= 0) {
                 const int owner = a.fEPR.div(e);
-                if (owner < R && a.fng.mod(owner) == my_group) {
+                if (owner < R && a.fng.mod(owner) == my_group)
                     atomicAdd(&sc.cnt[(a.fng.div(owner) * EPR + (e - owner * EPR)) * R + src[j]], 1);
-                    sc.mine[atomicAdd(sc.n_mine, 1)] = (unsigned short)i;   // the dispatch walks this list instead of the whole world
-                }
             }
         }
     }
@@ -1075,10 +1068,8 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
     const int pshift = P == 4 ? 2 : (P == 2 ? 1 : 0);
     const int n16 = H / 8, per_part = n16 >> pshift;   // 8-byte row units; H % 256 == 0: per_part is a multiple of 8
 #pragma unroll 1
-    const int n_mine = *sc.n_mine;
-    (void)W;
-    for (int it = gwarp; it < n_mine * P; it += nwarps) {
-        const int i = sc.mine[it >> pshift], part = it & (P - 1);   // parts are a power of two
+    for (int it = gwarp; it < W * P; it += nwarps) {
+        const int i = it >> pshift, part = it & (P - 1);   // parts are a power of two
         const int e = sc.wid[i];
         if (e < 0) continue;                         // (every `continue` here is uniform over the warp)
         const int owner = a.fEPR.div(e);
