@@ -146,7 +146,9 @@ def make_inputs(torch, tokens, rank, seed, hidden, routing):
     ex = torch.randint(3, 11, (tokens, hidden), generator=g, dtype=torch.uint8)
     x = ((r & 0x87) | (ex << 3)).pin_memory()
     x_sf = (torch.randint(0, 3, (tokens, hidden // 128), generator=g, dtype=torch.uint8) + (127 - 3)).pin_memory()
-    if routing == "zipf":
+    if isinstance(routing, tuple):   # ("corpus", per-expert pair counts of one recorded launch, number of ranks)
+        idx = corpus_routes(torch, routing[1], routing[2], tokens)[rank].contiguous().pin_memory()
+    elif routing == "zipf":
         gp = torch.Generator()
         gp.manual_seed(4242)                       # the same expert popularity on every rank and step
         perm = torch.randperm(E_TOTAL, generator=gp)
@@ -157,6 +159,20 @@ def make_inputs(torch, tokens, rank, seed, hidden, routing):
         idx = torch.rand((tokens, E_TOTAL), generator=g).topk(TOPK, dim=1).indices.to(torch.int64).pin_memory()
     w = torch.softmax(torch.randn((tokens, TOPK), generator=g), dim=1).float().pin_memory()
     return x, x_sf, idx, w
+
+
+def corpus_routes(torch, per_expert, n_ranks, tokens):
+    """Routes [ranks][tokens][topk] that reproduce recorded per-expert received-pair counts, built
+    the way the reference replays its real-serving corpus (test/mega_common.cuh:460-482): walking
+    the experts in order, the j-th pair overall belongs to source rank j % R, q = j / R, token
+    q % tokens, top-k position q / tokens."""
+    ge = torch.repeat_interleave(torch.arange(len(per_expert), dtype=torch.int64), torch.as_tensor(per_expert, dtype=torch.int64))
+    assert ge.numel() == n_ranks * tokens * TOPK, "the recorded launch does not fill this world"
+    j = torch.arange(ge.numel())
+    src, q = j % n_ranks, j // n_ranks
+    out = torch.zeros((n_ranks, tokens, TOPK), dtype=torch.int64)
+    out[src, q % tokens, q // tokens] = ge
+    return out
 
 
 def algorithmic_work(idx_all, n_ranks, rank, tokens, hidden):
@@ -305,13 +321,14 @@ class Job:
     """One geometry on this rank: symmetric buffers, this rank's expert weights, helpers that load
     inputs and time layers.  `hidden` 6144 = the decode layer, 7168 = the prefill-sized layer."""
 
-    def __init__(self, torch, dist, mm, lib, n, rank, dev, group, hidden, cap, cta_pair, dispatch_mode, group_ranks=0):
+    def __init__(self, torch, dist, mm, lib, n, rank, dev, group, hidden, cap, cta_pair, dispatch_mode, group_ranks=0,
+                 expert_window=0):
         self.torch, self.dist, self.mm, self.lib = torch, dist, mm, lib
         self.n, self.rank, self.dev, self.hidden, self.cap = n, rank, dev, hidden, cap
         self.epr = E_TOTAL // n
         self.group_ranks = group_ranks
         self.buf = mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, hidden, I, dispatch_mode=dispatch_mode,
-                                                   group_ranks=group_ranks)
+                                                   group_ranks=group_ranks, expert_window=expert_window or None)
         self.buf.cta_pair = cta_pair
         self.weights = make_weights(torch, self.epr, rank, dev, hidden)
         self.l1, self.l2 = mm.transform_weights_for_mega_moe(*self.weights)
@@ -665,6 +682,20 @@ def gpu_arm(args):
             "rank_time_max_over_mean": float(gemm_end.max() / max(gemm_end.mean(), 1.0))}))
 
     job_push = job.push
+    # ---- recorded real-decode launches (per-expert pair counts of the reference's corpus sample), owner only ----
+    corpus = None
+    gold = os.path.join(ROOT, "tests", "golden", "tk_info.npz")
+    if not args.no_points and os.path.exists(gold) and E_TOTAL == 256 and args.hidden == 6144:
+        g_ = np.load(gold)
+        corpus = [(int(g_["launch"][i]), g_["counts"][i].astype(np.int64)) for i in range(g_["counts"].shape[0])]
+        corpus = [(lid, c) for lid, c in corpus if int(c.sum()) % (n * TOPK) == 0 and 0 < int(c.sum()) // (n * TOPK) <= cap]
+        for lid, c in corpus:
+            tk = int(c.sum()) // (n * TOPK)
+            rt = job.load(tk, seed=5, routing=("corpus", c, n))
+            ms = job.time_eager(10, 3)
+            wk = algorithmic_work(rt, n, rank, tk, args.hidden)
+            points.append(point(f"corpus_launch{lid}", job, tk, ms, None, wk, {"hottest_over_mean": float(c.max() / c.mean())}))
+
     # ---- parity of the headline configuration (outside every timed region) ----
     parity = None
     if not args.no_parity:
@@ -691,6 +722,14 @@ def gpu_arm(args):
             "note": "roofline figures count this rank's own experts; helpers stream replicas of other ranks' experts on top"}))
         if not args.no_parity:
             parity_helpers = parity_leg(job_h, rt, np)
+        for lid, c in (corpus or []):   # the recorded launches again, with helpers
+            tk = int(c.sum()) // (n * TOPK)
+            rt = job_h.load(tk, seed=5, routing=("corpus", c, n))
+            ms = job_h.time_eager(10, 3)
+            wk = algorithmic_work(rt, n, rank, tk, args.hidden)
+            stc = job_h.buf.status()
+            points.append(point(f"corpus_launch{lid}_helpers", job_h, tk, ms, None, wk,
+                                {"hottest_over_mean": float(c.max() / c.mean()), "helper_on_rank0": int(stc.helper_on)}))
         job_h.destroy()
         job = None
 
@@ -798,6 +837,7 @@ def main():
                     help="GEMM tiling: 1 single CTAs, 2 CTA pairs with 256-row windows, 0 chosen by load")
     ap.add_argument("--dispatch-mode", type=int, default=0, choices=[0, 1, 2],
                     help="prologue protocol: 1 pull, 2 push, 0 chosen by geometry")
+    ap.add_argument("--expert-window", type=int, default=0, help="rows per window (multiple of 8 in [8,128]); 0 = 128")
     ap.add_argument("--ticks", action="store_true", help="print the kernel's wait-time breakdown and time line to stderr")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-points", action="store_true", help="skip the sweep points (16/64/256 tokens per rank, skew, prefill)")
@@ -839,7 +879,8 @@ def ticks_run(args):
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     lib = _lib.lib()
-    job = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, args.tpr, args.cta_pair, args.dispatch_mode)
+    job = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, args.tpr, args.cta_pair, args.dispatch_mode,
+              expert_window=args.expert_window)
     job.load(args.tpr, seed=1, routing=args.routing)
     ms_plain = job.time_eager(args.steps, args.warmup)
     lib.mxk_set_ticks(2 if os.environ.get("MXK_TICKS") == "2" else 1)
