@@ -106,12 +106,21 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- workload
-def make_weights(torch, epr, rank, device, hidden):
+def make_weights(torch, epr, rank, device, hidden, e2m1=False):
     """Seeded synthetic expert weights of this rank, directly as E4M3 bytes + UE8M0 exponents
     (random sign / mantissa, exponent field 3..10, block scale 2^-9): same shapes and value range
-    as N(0, 0.02) weights quantised per 128x128 block, without materialising FP32 tensors."""
+    as N(0, 0.02) weights quantised per 128x128 block, without materialising FP32 tensors.
+    e2m1: packed 4-bit codes instead (uniform over the 16 codes, two per byte, block scale 2^-3)."""
     g = torch.Generator(device=device)
     g.manual_seed(1000 + rank + 7 * hidden)
+    if e2m1:
+        w1 = torch.randint(0, 256, (epr, 2 * I, hidden // 2), generator=g, device=device, dtype=torch.uint8)
+        w2 = torch.randint(0, 256, (epr, hidden, I // 2), generator=g, device=device, dtype=torch.uint8)
+        s1 = torch.full((epr, 2 * I // 128, hidden // 128), 127 - 3, dtype=torch.uint8, device=device)
+        s2 = torch.full((epr, hidden // 128, I // 128), 127 - 3, dtype=torch.uint8, device=device)
+        s1 += torch.randint(0, 3, s1.shape, generator=g, device=device, dtype=torch.uint8)
+        s2 += torch.randint(0, 3, s2.shape, generator=g, device=device, dtype=torch.uint8)
+        return (w1, s1), (w2, s2)
 
     def fp8_bytes(shape):
         n = 1
@@ -175,7 +184,7 @@ def corpus_routes(torch, per_expert, n_ranks, tokens):
     return out
 
 
-def algorithmic_work(idx_all, n_ranks, rank, tokens, hidden):
+def algorithmic_work(idx_all, n_ranks, rank, tokens, hidden, weight_bits=8):
     """Per-GPU algorithmic bytes / flops of one layer for the routing actually drawn.
     idx_all: [n_ranks*tokens, topk] global expert ids of every rank's tokens."""
     epr = E_TOTAL // n_ranks
@@ -187,7 +196,7 @@ def algorithmic_work(idx_all, n_ranks, rank, tokens, hidden):
     P_remote_in = int((mine & (src_rank != rank)).sum())              # pairs pulled / pushed in from peers
     P_remote_out = int(((src_rank == rank) & (owner != rank)).sum())  # this rank's pairs served elsewhere
     kb = hidden // 128
-    w_bytes = active * (2 * I * hidden + hidden * I + (2 * I // 128) * kb + kb * (I // 128))
+    w_bytes = active * ((2 * I * hidden + hidden * I) * weight_bits // 8 + (2 * I // 128) * kb + kb * (I // 128))
     gemm_bytes = w_bytes + P * (hidden + kb) + 2 * P * (I + I // 128) + P * 2 * hidden
     layer_bytes = gemm_bytes + P * (hidden + kb) + tokens * TOPK * 2 * hidden + tokens * 2 * hidden
     flops = P * 6 * hidden * I
@@ -322,7 +331,7 @@ class Job:
     inputs and time layers.  `hidden` 6144 = the decode layer, 7168 = the prefill-sized layer."""
 
     def __init__(self, torch, dist, mm, lib, n, rank, dev, group, hidden, cap, cta_pair, dispatch_mode, group_ranks=0,
-                 expert_window=0):
+                 expert_window=0, e2m1=False):
         self.torch, self.dist, self.mm, self.lib = torch, dist, mm, lib
         self.n, self.rank, self.dev, self.hidden, self.cap = n, rank, dev, hidden, cap
         self.epr = E_TOTAL // n
@@ -330,13 +339,14 @@ class Job:
         self.buf = mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, hidden, I, dispatch_mode=dispatch_mode,
                                                    group_ranks=group_ranks, expert_window=expert_window or None)
         self.buf.cta_pair = cta_pair
-        self.weights = make_weights(torch, self.epr, rank, dev, hidden)
-        self.l1, self.l2 = mm.transform_weights_for_mega_moe(*self.weights)
+        self.e2m1 = e2m1            # 4-bit weights (packed e2m1 codes) instead of E4M3 bytes
+        self.weights = make_weights(torch, self.epr, rank, dev, hidden, e2m1)
+        self.l1, self.l2 = mm.transform_weights_for_mega_moe(*self.weights, weight_format="e2m1" if e2m1 else "e4m3")
         # helper groups (skewed routing): every member holds a replica of its group's expert weights
         self.group_weights = mm.gather_group_weights(self.buf, self.l1, self.l2) if group_ranks > 1 else None
         self.stream = torch.cuda.current_stream()
         self.inputs = None
-        self.push = bool(self.buf.layout.push_eligible) if dispatch_mode == 0 else dispatch_mode == 2
+        self.push = bool(self.buf.layout.push_auto or (group_ranks > 1 and self.buf.layout.push_eligible)) if dispatch_mode == 0 else dispatch_mode == 2
 
     def barrier(self):
         self.torch.cuda.synchronize()
@@ -372,7 +382,8 @@ class Job:
         return self.gather(idx)
 
     def layer(self, y=None):
-        self.mm.fp8_mega_moe(self.y if y is None else y, self.l1, self.l2, self.buf, group_weights=self.group_weights)
+        self.mm.fp8_mega_moe(self.y if y is None else y, self.l1, self.l2, self.buf, group_weights=self.group_weights,
+                             weight_format=int(self.e2m1))
 
     def check_status(self, what):
         st = self.buf.status()
@@ -424,7 +435,7 @@ class Job:
         """Average duration of the GEMM phase launched alone (events bracket it on the launching stream)."""
         torch, lib = self.torch, self.lib
         from mini_mega_b200 import _lib
-        a = self.buf.launch_args(self.inputs[0], self.l1, self.l2, y_bf16=self.y)
+        a = self.buf.launch_args(self.inputs[0], self.l1, self.l2, y_bf16=self.y, weight_format=int(self.e2m1))
         evs = []
         for i in range(warmup + steps):
             _lib.check(lib.mxk_launch_phases(C.byref(a), 1 | 2 | 4, self.stream.cuda_stream), "prologue+dispatch")
@@ -458,7 +469,7 @@ class Job:
 
             def step():
                 dst.copy_(img, non_blocking=True)
-                self.mm.fp8_mega_moe(self.y, self.l1, self.l2, buf, packed_inputs=True)
+                self.mm.fp8_mega_moe(self.y, self.l1, self.l2, buf, packed_inputs=True, weight_format=int(self.e2m1))
                 y_host.copy_(self.y, non_blocking=True)
         else:
             h2d = x.numel() + x_sf.numel() + idx.numel() * 8 + w.numel() * 4
@@ -468,7 +479,7 @@ class Job:
                 buf.x_sf[:tokens].copy_(x_sf, non_blocking=True)
                 buf.topk_idx[:tokens].copy_(idx, non_blocking=True)
                 buf.topk_weights[:tokens].copy_(w, non_blocking=True)
-                self.mm.fp8_mega_moe(self.y, self.l1, self.l2, buf)
+                self.mm.fp8_mega_moe(self.y, self.l1, self.l2, buf, weight_format=int(self.e2m1))
                 y_host.copy_(self.y, non_blocking=True)
 
         for _ in range(warmup):
@@ -569,6 +580,8 @@ def parity_leg(job, routing_all, np):
                 if rank != r:
                     continue
                 a1, b1, a2, b2 = (p_.cpu().numpy() for p_ in parts)
+                if job.e2m1:    # the codes' E4M3 values: the 8-bit arithmetic is the oracle of the 4-bit layer
+                    a1, a2 = orc.expand_e2m1(a1), orc.expand_e2m1(a2)
                 h = orc.l1(x_all[r, t:t + 1], sf_all[r, t:t + 1], a1, b1)
                 q, sf = orc.requant(h, True)
                 o = orc.bf16_to_f32(orc.f32_to_bf16(orc.l2(q, sf, a2, b2)))[0]
@@ -590,6 +603,7 @@ def parity_leg(job, routing_all, np):
     return {"tables_exact": ok_all, "max_rel_l2": worst_all, "tokens_checked": checked_all, "tolerance": 1e-2,
             "ranks": n, "tables": "route_slot_counts, prefix_tbl, expert_row_base, row_meta, pool bytes + scales",
             "helper_groups": job.group_ranks if job.group_ranks > 1 else None,
+            "weights": "e2m1" if job.e2m1 else "e4m3",
             "passed": bool(ok_all and worst_all <= 1e-2)}
 
 
@@ -615,7 +629,9 @@ def gpu_arm(args):
     hbm_gbs, bf16_tf, peak_kind = load_peaks()
     fp8_peak = 2.0 * bf16_tf * 1e12
     cap = max(256, args.tpr) if not args.no_points else args.tpr
-    job = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, cap, args.cta_pair, args.dispatch_mode)
+    e2m1 = args.weights == "e2m1"
+    wbits = 4 if e2m1 else 8
+    job = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, cap, args.cta_pair, args.dispatch_mode, e2m1=e2m1)
 
     def binding(work):
         t_h = work["layer_bytes"] / (hbm_gbs * 1e9)
@@ -652,7 +668,7 @@ def gpu_arm(args):
         sampler.start()
     ms_step = job.time_eager(args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
-    work = algorithmic_work(routing, n, rank, args.tpr, args.hidden)
+    work = algorithmic_work(routing, n, rank, args.tpr, args.hidden, wbits)
     ms_graph = run_graph(job)
     gemm_ms = job.time_gemm_phase(max(3, min(args.steps, 20)), 3)
     e2e_ms, h2d, d2h, _ = job.time_e2e(args.steps, args.warmup)
@@ -667,7 +683,7 @@ def gpu_arm(args):
             rt = job.load(tpr, seed=2)
             ms = job.time_eager(max(3, min(args.steps, 20)), 3)
             mg = run_graph(job)
-            wk = algorithmic_work(rt, n, rank, tpr, args.hidden)
+            wk = algorithmic_work(rt, n, rank, tpr, args.hidden, wbits)
         points.append(point(f"balanced_tpr{tpr}", job, tpr, ms, mg, wk))
     if not args.no_points:
         # BASELINE skew configuration: Zipf(1.2) routing, 256 tokens per rank
@@ -682,6 +698,20 @@ def gpu_arm(args):
             "rank_time_max_over_mean": float(gemm_end.max() / max(gemm_end.mean(), 1.0))}))
 
     job_push = job.push
+    # ---- the decode layer with 4-bit (e2m1) weights: half the weight bytes (reference: its MX_FP4_W build) ----
+    parity_e2m1 = None
+    if not args.no_points and not e2m1 and args.hidden == 6144:
+        j4 = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, cap, args.cta_pair, args.dispatch_mode, e2m1=True)
+        rt = j4.load(args.tpr, seed=1)
+        ms = j4.time_eager(max(3, min(args.steps, 20)), 3)
+        mg = run_graph(j4)
+        wk = algorithmic_work(rt, n, rank, args.tpr, args.hidden, 4)
+        points.append(point(f"balanced_tpr{args.tpr}_e2m1_weights", j4, args.tpr, ms, mg, wk, {"weights": "e2m1 (4-bit codes, 128x128 UE8M0 scales)"}))
+        if not args.no_parity:
+            parity_e2m1 = parity_leg(j4, rt, np)
+        j4.destroy()
+        del j4
+        torch.cuda.empty_cache()
     # ---- recorded real-decode launches (per-expert pair counts of the reference's corpus sample), owner only ----
     corpus = None
     gold = os.path.join(ROOT, "tests", "golden", "tk_info.npz")
@@ -812,12 +842,16 @@ def gpu_arm(args):
             line["parity"] = parity
         if parity_helpers is not None:
             line["parity_helpers"] = parity_helpers
+        if parity_e2m1 is not None:
+            line["parity_e2m1_weights"] = parity_e2m1
+        if e2m1:
+            line["dtype"] = "fp8_e4m3 x e2m1 weights"
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
     if n > 1:
         dist.destroy_process_group()
-    if (parity is not None and not parity["passed"]) or (parity_helpers is not None and not parity_helpers["passed"]):
+    if any(p_ is not None and not p_["passed"] for p_ in (parity, parity_helpers, parity_e2m1)):
         sys.exit(3)
 
 
@@ -833,6 +867,8 @@ def main():
     ap.add_argument("--hidden", type=int, default=6144, help="H (7168 for the prefill-sized configuration)")
     ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"],
                     help="expert choice per token: uniform (the baseline's balanced layer) or Zipf(1.2) skew")
+    ap.add_argument("--weights", default="e4m3", choices=["e4m3", "e2m1"],
+                    help="weight format of the headline job: E4M3 bytes (the baseline's) or packed 4-bit e2m1 codes")
     ap.add_argument("--cta-pair", type=int, default=0, choices=[0, 1, 2],
                     help="GEMM tiling: 1 single CTAs, 2 CTA pairs with 256-row windows, 0 chosen by load")
     ap.add_argument("--dispatch-mode", type=int, default=0, choices=[0, 1, 2],
@@ -880,7 +916,7 @@ def ticks_run(args):
         group = dist.group.WORLD
     lib = _lib.lib()
     job = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, args.tpr, args.cta_pair, args.dispatch_mode,
-              expert_window=args.expert_window)
+              expert_window=args.expert_window, e2m1=args.weights == "e2m1")
     job.load(args.tpr, seed=1, routing=args.routing)
     ms_plain = job.time_eager(args.steps, args.warmup)
     lib.mxk_set_ticks(2 if os.environ.get("MXK_TICKS") == "2" else 1)

@@ -80,6 +80,9 @@ struct MegaLaunchArgs {
     const uint8_t* w2_group = nullptr;
     const uint8_t* w1_sf_group = nullptr;
     const uint8_t* w2_sf_group = nullptr;
+    // 4-bit weights (reference: the MX_FP4_W build, src/common.cuh:99-134): MXK_WEIGHTS_E2M1 = every weight
+    // tensor holds e2m1 codes, two per byte, row-major [experts][rows][k / 2]
+    int weight_format = 0;
 };
 
 inline int& last_status() {
@@ -103,6 +106,7 @@ inline MxkLaunchArgs to_c(const MegaLaunchArgs& a) {
     c.x_sf_off = a.x_sf_off; c.w1_sf = a.w1_sf; c.w2_sf = a.w2_sf; c.y_bf16 = a.y_bf16; c.cta_pair = a.cta_pair; c.dispatch_mode = a.dispatch_mode;
     c.group_ranks = a.group_ranks; c.group_skew_num = a.group_skew_num;
     c.w1_group = a.w1_group; c.w2_group = a.w2_group; c.w1_sf_group = a.w1_sf_group; c.w2_sf_group = a.w2_sf_group;
+    c.weight_format = a.weight_format;
     return c;
 }
 
@@ -133,6 +137,10 @@ inline void launch_empty(int grid, int threads, int64_t smem, mcStream_t stream)
 // Device-side deterministic weights (reference: fill_weights_lane, :66-105; row-major here).
 inline void fill_weights_lane(uint8_t* w, int n_rows, int k_cols, uint32_t seed, mcStream_t stream) {
     last_status() = mxk_fill_weights(w, n_rows, k_cols, seed, stream);
+}
+// The same for 4-bit weights: packed e2m1 codes WPROBE_FP4_CODE (reference: src/common.cuh:127-131), row-major.
+inline void fill_weights_e2m1(uint8_t* w, int n_rows, int k_cols, uint32_t seed, mcStream_t stream) {
+    last_status() = mxk_fill_weights_e2m1(w, n_rows, k_cols, seed, stream);
 }
 // Registers / local / shared memory of the kernels (reference: dump_kernel_resources, :270-282).
 inline void dump_kernel_resources() { last_status() = mxk_dump_kernel_resources(); }

@@ -101,13 +101,20 @@ typedef struct MxkLayout {
     int64_t route_scratch_off;  /* rwk: int32 [route_scratch_ctas][E] pairs per (CTA slice, expert),
                                    scratch of the one-pass route build for large batches */
     int32_t route_scratch_ctas;
-    int32_t reserved0_;
+    int32_t push_auto;          /* 1: dispatch_mode 0 runs the push-mode prologue here: eligible and
+                                   max_tokens * topk <= 2048 per rank.  A pushed row travels as
+                                   tagged words (twice its bytes) once per routed pair and is copied
+                                   again into the pool; beyond that size the pull protocol's three
+                                   round trips cost less than the extra bytes                      */
 } MxkLayout;
 
 /* One launch.  Field names follow fp8mega::MegaLaunchArgs (reference
  * src/megakernel.h:54-114); the fields after max_spins/skip_prologue are new:
  * geometry and the UE8M0 scale planes (all-null planes == the reference's
  * scale-free mode). */
+#define MXK_WEIGHTS_E4M3 0
+#define MXK_WEIGHTS_E2M1 1
+
 typedef struct MxkLaunchArgs {
     int32_t R, rank;
     int32_t tokens;            /* valid tokens of this rank in this launch        */
@@ -147,7 +154,8 @@ typedef struct MxkLaunchArgs {
                                   rows; reference r19_pull_flags), 2 = push (source ranks
                                   store ids + rows into the owners' staging area, every CTA
                                   derives the tables itself; needs layout.push_eligible),
-                                  0 = push when the geometry is eligible, else pull       */
+                                  0 = push for small batches (layout.push_auto, or any eligible
+                                  geometry when helper groups are on), else pull          */
     /* ---- cross-rank helper scheduling for skewed routing (reference: MX_GROUP_SCHED,
      * src/compute.cuh:700-835; group-replicated weights rwk->ld.w1g / w2g,
      * src/flags_defs.cuh:160-169, gated by group_weights_ready above) ----
@@ -166,6 +174,14 @@ typedef struct MxkLaunchArgs {
     const uint8_t* w2_group;   /* [group_ranks * EPR][H][I]                                 */
     const uint8_t* w1_sf_group;/* [group_ranks * EPR][2I/128][H/128] or NULL                */
     const uint8_t* w2_sf_group;/* [group_ranks * EPR][H/128][I/128]  or NULL                */
+    /* ---- 4-bit weights (reference: the MX_FP4_W build, src/common.cuh:99-134) ----
+     * MXK_WEIGHTS_E2M1: every weight tensor above (w1, w2 and the group replicas) holds e2m1
+     * codes, two per byte, row-major [experts][rows][k / 2] with the element of even k in the
+     * low nibble; a code stands for the E4M3 value of mxk_e2m1_to_e4m3 (0, 0.5, 1, 1.5, 2, 3,
+     * 4, 6 and their negatives) and the 128x128 scale planes apply as for 8-bit weights.  The
+     * layer reads half the weight bytes from HBM; its results are those of the 8-bit layer on
+     * the expanded weights.  The tensors must be 32-byte aligned. */
+    int32_t weight_format;     /* MXK_WEIGHTS_E4M3 (0) or MXK_WEIGHTS_E2M1 (1)              */
 } MxkLaunchArgs;
 
 /* Host-readable copy of the device status header. */
@@ -278,6 +294,15 @@ int64_t mxk_static_scratch_bytes(void);
  * (row, k), row-major (reference: fill_weights_lane writes the same values in
  * MetaX lane order, src/megakernel.cu:66-105, src/megakernel.h:46-47). */
 int mxk_fill_weights(uint8_t* w, int64_t n_rows, int32_t k_cols, uint32_t seed, void* stream);
+
+/* 4-bit test weights: e2m1 code ((seed + 131*row + 7*k) >> 1) & 0xf at logical (row, k)
+ * (reference: WPROBE_FP4_CODE, src/common.cuh:127-131), packed two per byte (even k in the
+ * low nibble), row-major [n_rows][k_cols / 2]; k_cols must be even. */
+int mxk_fill_weights_e2m1(uint8_t* w, int64_t n_rows, int32_t k_cols, uint32_t seed, void* stream);
+
+/* The E4M3 byte an e2m1 code (low 4 bits) stands for (reference: fp4_code_to_fp8,
+ * src/common.cuh:116-126): magnitudes 0, 0.5, 1, 1.5, 2, 3, 4, 6; bit 3 is the sign. */
+uint8_t mxk_e2m1_to_e4m3(uint8_t code);
 
 /* bf16 activations -> E4M3 rows + one UE8M0 scale per 128 columns (x_sf [tokens][hidden/128]),
  * the reference's activation quantiser per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=128)

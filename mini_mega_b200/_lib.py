@@ -51,7 +51,7 @@ class MxkLayout(C.Structure):
         ("pool_ready_off", C.c_int64), ("expert_first_win_off", C.c_int64),
         ("xin_off", C.c_int64), ("xin_src_words", C.c_int64), ("xin_row_words", C.c_int32),
         ("push_eligible", C.c_int32),
-        ("route_scratch_off", C.c_int64), ("route_scratch_ctas", C.c_int32), ("reserved0_", C.c_int32),
+        ("route_scratch_off", C.c_int64), ("route_scratch_ctas", C.c_int32), ("push_auto", C.c_int32),
     ]
 
 
@@ -71,6 +71,7 @@ class MxkLaunchArgs(C.Structure):
         ("cta_pair", C.c_int32), ("dispatch_mode", C.c_int32),
         ("group_ranks", C.c_int32), ("group_skew_num", C.c_int32),
         ("w1_group", C.c_void_p), ("w2_group", C.c_void_p), ("w1_sf_group", C.c_void_p), ("w2_sf_group", C.c_void_p),
+        ("weight_format", C.c_int32),
     ]
 
 
@@ -85,7 +86,7 @@ EXPORTS = [
     "mxk_last_error", "mxk_version", "mxk_compute_layout", "mxk_sym_bytes", "mxk_rwk_bytes", "mxk_unk_bytes",
     "mxk_launch_prelude", "mxk_launch_compute", "mxk_launch_reduce", "mxk_launch_full", "mxk_launch_empty",
     "mxk_kernels_per_layer", "mxk_launch_phases", "mxk_launch_full_static",
-    "mxk_static_scratch_bytes", "mxk_fill_weights", "mxk_quantize_rows", "mxk_dump_kernel_resources", "mxk_read_status",
+    "mxk_static_scratch_bytes", "mxk_fill_weights", "mxk_fill_weights_e2m1", "mxk_e2m1_to_e4m3", "mxk_quantize_rows", "mxk_dump_kernel_resources", "mxk_read_status",
     "mxk_read_status_static", "mxk_rwk_ticks_off", "mxk_ticks_count", "mxk_set_ticks", "mxk_select_win",
     "mxk_group_ranks", "mxk_gs_schedule_member", "mxk_gs_group_skewed", "mxk_lpt_assign", "mxk_gs_schedule_on_device",
     "mxk_symm_alloc", "mxk_symm_free", "mxk_ipc_export", "mxk_ipc_import", "mxk_ipc_close",
@@ -119,6 +120,9 @@ def lib():
     L.mxk_launch_phases.argtypes = [C.POINTER(MxkLaunchArgs), C.c_int, C.c_void_p]
     L.mxk_launch_empty.argtypes = [C.c_int, C.c_int, C.c_int64, C.c_void_p]
     L.mxk_fill_weights.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_uint32, C.c_void_p]
+    L.mxk_fill_weights_e2m1.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_uint32, C.c_void_p]
+    L.mxk_e2m1_to_e4m3.argtypes = [C.c_uint8]
+    L.mxk_e2m1_to_e4m3.restype = C.c_uint8
     L.mxk_quantize_rows.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
     L.mxk_read_status.argtypes = [C.c_void_p, C.POINTER(MxkStatus)]
     L.mxk_read_status_static.argtypes = [C.POINTER(MxkStatus)]

@@ -463,6 +463,9 @@ __host__ __device__ constexpr uint32_t umma_idesc_e4m3(int m, int n) {
 __host__ __device__ constexpr uint32_t umma_idesc_mx_e4m3(int m, int n, uint32_t a_sf_id, uint32_t b_sf_id) {
     return (b_sf_id << 4) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(m >> 4) << 24) | (a_sf_id << 29);
 }
+// OR-ed into the descriptor above: the B operand is given as e2m1 codes, one per byte position in
+// the padded shared-memory form (operand format field, bits [10,13): 0 = E4M3, 5 = E2M1).
+constexpr uint32_t kUmmaBFormatE2M1 = 5u << 10;
 
 // 32-byte global store (256-bit vector): one full sector per thread.
 __device__ __forceinline__ void st_global_v8(void* p, uint4 a, uint4 b) {

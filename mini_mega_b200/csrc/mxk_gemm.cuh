@@ -244,14 +244,17 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                 const int brow0 = is_l2 ? e * a.H + task.z * kBlockN : e * 2 * a.I + task.z * 128;
                 const int brow1 = is_l2 ? brow0 + 128 : brow0 + a.I;
                 // weight tiles of K block kb into ring stage st (the stage's byte count is announced with them)
+                // a 128-row weight tile counts on the barrier with the bytes read from memory: half of its
+                // 16 KB in shared memory when the weights are packed 4-bit codes
+                const uint32_t b_half_tx = a.w_fp4 ? kABytes / 2 : kABytes;
                 auto load_b = [&](int kb, uint32_t st) {
                     uint8_t* sa = tiles + st * kStageB;
                     if constexpr (kPair) {
                         // both CTAs' bytes complete on the leader's barrier: 2 x (A 16 KB + weight half 16 KB)
-                        if (leader) mbar_expect_tx(&S->full[st], 2 * kPairStageBytes);
+                        if (leader) mbar_expect_tx(&S->full[st], 2 * (kABytes + b_half_tx));
                         tma_load_2d_pair_hint(sa + kABytes, mb, kb * kBlockK, leader ? brow0 : brow1, mapa_u32(smem_u32(&S->full[st]), 0), stream_policy);
                     } else {
-                        mbar_expect_tx(&S->full[st], kStageBytes);
+                        mbar_expect_tx(&S->full[st], kABytes + 2 * b_half_tx);
                         tma_load_2d_hint(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[st], stream_policy);
                         tma_load_2d_hint(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[st], stream_policy);
                     }
@@ -308,7 +311,8 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
             bool stage_ready = false;   // full[stage] already seen complete by the early poll
             bool sf_ready = false;      // likewise sf_full of the next group
             const uint64_t tile_desc0 = umma_smem_desc_sw128(smem_u32(tiles));
-            const uint32_t idesc0 = umma_idesc_mx_e4m3(kPair ? 2 * kBlockM : kBlockM, kBlockN, 0, 0);
+            const uint32_t idesc0 = umma_idesc_mx_e4m3(kPair ? 2 * kBlockM : kBlockM, kBlockN, 0, 0) |
+                                    (a.w_fp4 ? kUmmaBFormatE2M1 : 0u);
             for (uint32_t it = 0;; ++it) {
                 const uint32_t slot = it % kTaskRing;
                 if (!mbar_wait(&S->task_full[slot], (it / kTaskRing) & 1, wait_ns, abort_flag)) {

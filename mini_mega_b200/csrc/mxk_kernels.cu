@@ -65,6 +65,7 @@ struct KArgs {
     int ge_base;                 // this rank's first expert inside the weight arrays (member * EPR with group weights)
     int w_experts;               // experts in the weight arrays w1 / w2 (EPR, or group_ranks * EPR)
     int prefetch_bytes;          // bytes of W1 every CTA asks into L2 while the prologue runs
+    int w_fp4;                   // weights are e2m1 codes, two per byte; TMA unpacks them to one code per byte
     FastDiv fR, fEPR, ftopk, fng, fwin;   // division by R, EPR, topk, R / group_ranks, win_cap
     unsigned long long local_wait_ns, remote_wait_ns;
     uint8_t* rwk;
@@ -317,6 +318,18 @@ __global__ void k_fill_weights(uint8_t* w, long long n_rows, int k_cols, uint32_
     }
 }
 
+// Packed e2m1 test weights: code ((seed + 131*row + 7*k) >> 1) & 0xf at logical (row, k), two codes
+// per byte (even k in the low nibble), row-major.
+__global__ void k_fill_weights_e2m1(uint8_t* w, long long n_rows, int k_cols, uint32_t seed) {
+    const int kb = k_cols / 2;
+    const long long n = n_rows * kb;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const uint32_t row = (uint32_t)(i / kb), k = 2u * (uint32_t)(i % kb);
+        const uint32_t lo = ((seed + row * 131u + k * 7u) >> 1) & 0xfu, hi = ((seed + row * 131u + (k + 1) * 7u) >> 1) & 0xfu;
+        w[i] = (uint8_t)(lo | (hi << 4));
+    }
+}
+
 // =============================================================== host side ====
 thread_local std::string g_err;
 int fail(int code, const std::string& msg) {
@@ -366,6 +379,7 @@ int compute_layout(const MxkGeom* g, MxkLayout* L) {
     // push-mode staging area, only for geometries whose world routing fits a CTA's shared memory
     L->push_eligible = (R <= kPushMaxR && EPR <= kPushMaxEPR && R * cap * topk <= kPushMaxPairs &&
                         EPR * (R + 1) <= kPushMaxCnt) ? 1 : 0;
+    L->push_auto = (L->push_eligible && (int64_t)cap * topk <= kPushAutoPairsPerRank) ? 1 : 0;
     {
         const int64_t sfw = (((H / 128) + 3) / 4 + 1) & ~(int64_t)1;
         L->xin_row_words = (int32_t)(2 * topk + sfw + H / 4);
@@ -438,6 +452,27 @@ int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t k) {
     return 0;
 }
 
+// e2m1 codes [rows][k], two per byte in memory (row pitch k / 2 bytes); a tile of 128 rows x 128 codes
+// arrives in shared memory as 128 x 128 BYTES, one code per byte position in the padded form the
+// block-scaled MMA reads (every 16 codes: 8 bytes of data, 8 bytes of gap), 128-byte swizzle.
+// The driver asks for: base 32-byte aligned, k a multiple of 128, pitch a multiple of 32 bytes,
+// an inner box of exactly 128 codes.
+int make_map_e2m1(CUtensorMap* m, const void* base, int64_t rows, int64_t k) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return fail(MXK_ERR_NO_DRIVER, "cuTensorMapEncodeTiled not available from the CUDA driver");
+    if ((reinterpret_cast<uintptr_t>(base) & 31) || k % 128)
+        return fail(MXK_ERR_BAD_ARG, "e2m1 weights must be 32-byte aligned with k a multiple of 128");
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)(k / 2)};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MXK_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled (e2m1) failed, CUresult " + std::to_string((int)r));
+    return 0;
+}
+
 // Wait-time accounting and phase stamps: MXK_TICKS=1 in the environment, or mxk_set_ticks().
 int g_ticks_override = -1;
 int ticks_enabled() {
@@ -496,7 +531,8 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     if (la->dispatch_mode < 0 || la->dispatch_mode > 2) return fail(MXK_ERR_BAD_ARG, "dispatch_mode must be 0, 1 or 2");
     if (la->dispatch_mode == 2 && !k->L.push_eligible)
         return fail(MXK_ERR_BAD_ARG, "dispatch_mode = 2 (push) needs R <= 64, experts_per_rank <= 256 and R * max_tokens * topk <= 16384");
-    k->push = la->dispatch_mode == 2 || (la->dispatch_mode == 0 && k->L.push_eligible);
+    const bool want_helpers = la->group_ranks > 1 && la->group_weights_ready;
+    k->push = la->dispatch_mode == 2 || (la->dispatch_mode == 0 && (k->L.push_auto || (want_helpers && k->L.push_eligible)));
     // cross-rank helper scheduling: group-replicated weights, push-mode prologue only
     k->group_ranks = 1; k->skew_num = 2; k->ge_base = 0; k->w_experts = g.experts_per_rank;
     const uint8_t *w1 = la->w1, *w2 = la->w2, *w1_sf = la->w1_sf, *w2_sf = la->w2_sf;
@@ -516,6 +552,9 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
         k->w_experts = G * g.experts_per_rank;
         w1 = la->w1_group; w2 = la->w2_group; w1_sf = la->w1_sf_group; w2_sf = la->w2_sf_group;
     }
+    if (la->weight_format != MXK_WEIGHTS_E4M3 && la->weight_format != MXK_WEIGHTS_E2M1)
+        return fail(MXK_ERR_BAD_ARG, "weight_format must be MXK_WEIGHTS_E4M3 or MXK_WEIGHTS_E2M1");
+    k->w_fp4 = la->weight_format == MXK_WEIGHTS_E2M1;
     k->R = g.R; k->rank = g.rank; k->EPR = g.experts_per_rank; k->E = g.R * g.experts_per_rank;
     k->topk = g.topk; k->H = g.hidden; k->I = g.intermediate; k->cap = g.max_tokens;
     k->slot_cap = g.slot_capacity ? g.slot_capacity : g.max_tokens;
@@ -577,7 +616,7 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
     if (mask == 0) return 0;
     // The four tensor maps depend only on (workspace, weights, geometry): a serving loop launches the
     // same ones every layer, so the last few sets are kept per thread instead of being re-encoded.
-    struct MapSet { const void* rwk; const void* w1; const void* w2; int64_t rows; int H, I, EPR; CUtensorMap m[4]; };
+    struct MapSet { const void* rwk; const void* w1; const void* w2; int64_t rows; int H, I, EPR, fp4; CUtensorMap m[4]; };
     static thread_local MapSet cache[4];
     static thread_local int cache_n = 0, cache_next = 0;
     CUtensorMap zero_maps[4];
@@ -587,7 +626,7 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
         const MapSet* hit = nullptr;
         for (int i = 0; i < cache_n; ++i) {
             const MapSet& c = cache[i];
-            if (c.rwk == k.rwk && c.w1 == k.w1 && c.w2 == k.w2 && c.rows == k.L.pool_rows && c.H == k.H && c.I == k.I && c.EPR == k.w_experts) {
+            if (c.rwk == k.rwk && c.w1 == k.w1 && c.w2 == k.w2 && c.rows == k.L.pool_rows && c.H == k.H && c.I == k.I && c.EPR == k.w_experts && c.fp4 == k.w_fp4) {
                 hit = &c;
                 break;
             }
@@ -595,11 +634,11 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
         if (!hit) {
             MapSet n;
             std::memset(&n, 0, sizeof(n));
-            n.rwk = k.rwk; n.w1 = k.w1; n.w2 = k.w2; n.rows = k.L.pool_rows; n.H = k.H; n.I = k.I; n.EPR = k.w_experts;
+            n.rwk = k.rwk; n.w1 = k.w1; n.w2 = k.w2; n.rows = k.L.pool_rows; n.H = k.H; n.I = k.I; n.EPR = k.w_experts; n.fp4 = k.w_fp4;
             if (int rc = make_map(&n.m[0], k.rwk + k.L.pool_off, k.L.pool_rows + 128, k.H)) return rc;
             if (int rc = make_map(&n.m[1], k.rwk + k.L.ffn_off, k.L.pool_rows + 128, k.I)) return rc;
-            if (int rc = make_map(&n.m[2], k.w1, (int64_t)k.w_experts * 2 * k.I, k.H)) return rc;
-            if (int rc = make_map(&n.m[3], k.w2, (int64_t)k.w_experts * k.H, k.I)) return rc;
+            if (int rc = (k.w_fp4 ? make_map_e2m1 : make_map)(&n.m[2], k.w1, (int64_t)k.w_experts * 2 * k.I, k.H)) return rc;
+            if (int rc = (k.w_fp4 ? make_map_e2m1 : make_map)(&n.m[3], k.w2, (int64_t)k.w_experts * k.H, k.I)) return rc;
             cache[cache_next] = n;
             hit = &cache[cache_next];
             cache_next = (cache_next + 1) % 4;
@@ -806,6 +845,21 @@ int mxk_fill_weights(uint8_t* w, int64_t n_rows, int32_t k_cols, uint32_t seed, 
     k_fill_weights<<<1024, 256, 0, static_cast<cudaStream_t>(stream)>>>(w, n_rows, k_cols, seed);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : cuda_fail(e, "launch fill_weights");
+}
+
+int mxk_fill_weights_e2m1(uint8_t* w, int64_t n_rows, int32_t k_cols, uint32_t seed, void* stream) {
+    if (!w || n_rows < 0 || k_cols < 2 || k_cols % 2) return fail(MXK_ERR_BAD_ARG, "bad fill_weights_e2m1 arguments");
+    if (n_rows == 0) return 0;
+    k_fill_weights_e2m1<<<1024, 256, 0, static_cast<cudaStream_t>(stream)>>>(w, n_rows, k_cols, seed);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail(e, "launch fill_weights_e2m1");
+}
+
+uint8_t mxk_e2m1_to_e4m3(uint8_t code) {
+    // e2m1: sign, 2 exponent bits (bias 1), 1 mantissa bit; exponent 0 is the subnormal pair {0, 0.5}
+    const uint8_t sign = (code & 8u) ? 0x80u : 0u, e = (code >> 1) & 3u, m = code & 1u;
+    const uint8_t mag = e == 0 ? (m ? 0x30u : 0u) : (uint8_t)(((e + 6u) << 3) | (m << 2));
+    return sign | mag;
 }
 
 int mxk_quantize_rows(const void* x_bf16, int32_t tokens, int32_t hidden, void* x_fp8, void* x_sf, void* stream) {

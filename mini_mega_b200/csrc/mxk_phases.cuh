@@ -631,6 +631,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
 constexpr int kPushMaxEPR = 256;       // local experts whose tables fit the control block
 constexpr int kPushMaxR = 64;
 constexpr int kPushMaxPairs = 16384;   // routing words of the whole world kept in shared memory per CTA
+constexpr int kPushAutoPairsPerRank = 2048;  // dispatch_mode 0 pushes up to this many routed pairs per rank (max_tokens * topk)
 constexpr int kPushMaxCnt = 4096;      // EPR * (R + 1)
 
 constexpr int kHelperMaxWin = 512;     // windows one member may be handed (reference: kGsMemberCap, src/group_sched.cuh:150-154)

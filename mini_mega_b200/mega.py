@@ -31,7 +31,7 @@ from ._lib import MxkLaunchArgs, MxkStatus, check, compute_layout
 EXPERT_WINDOW_MIN = 8
 EXPERT_WINDOW_MAX = 128
 EXPERT_WINDOW_MULTIPLE = 8
-_SUPPORTED_MMA_TYPES = ("fp8xfp8", "bf16xfp8")
+_SUPPORTED_MMA_TYPES = ("fp8xfp8", "bf16xfp8", "fp8xfp4")   # fp8xfp4: the buffer of fp8xfp8, 4-bit weights at launch
 
 
 class _DevMem:
@@ -245,7 +245,7 @@ class SymmBuffer:
                     y_f32: Optional[torch.Tensor] = None, expert_window: Optional[int] = None,
                     max_spins: int = 0, grid: int = 0, skip_combine: int = 0,
                     cta_pair: Optional[int] = None, dispatch_mode: Optional[int] = None,
-                    packed: bool = False, group_weights=None) -> MxkLaunchArgs:
+                    packed: bool = False, group_weights=None, weight_format: int = 0) -> MxkLaunchArgs:
         L = self.layout
         a = MxkLaunchArgs()
         a.R, a.rank, a.tokens = self.world_size, self.rank, int(num_tokens)
@@ -280,6 +280,7 @@ class SymmBuffer:
                 setattr(a, name + "_group", data.data_ptr())
                 setattr(a, name + "_sf_group", None if sf is None else sf.data_ptr())
             a.group_ranks, a.group_skew_num, a.group_weights_ready = self.group_ranks, self.group_skew_num, 1
+        a.weight_format = int(weight_format)   # 0 = E4M3 bytes, 1 = packed e2m1 codes (every weight tensor of the launch)
         return a
 
     def group_members(self):
@@ -321,13 +322,16 @@ def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_ran
 WeightArg = Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]
 
 
-def _norm_weight(name: str, w: WeightArg):
+def _norm_weight(name: str, w: WeightArg, fp4: bool = False):
     data, sf = w if isinstance(w, tuple) else (w, None)
-    if not isinstance(data, torch.Tensor) or data.dtype not in (torch.float8_e4m3fn, torch.uint8):
-        raise TypeError(f"{name} must be a float8_e4m3fn (or raw uint8) tensor")
+    ok = (torch.uint8, torch.int8) if fp4 else (torch.float8_e4m3fn, torch.uint8)
+    if not isinstance(data, torch.Tensor) or data.dtype not in ok:
+        raise TypeError(f"{name} must be a " + ("packed e2m1 (uint8 / int8) tensor" if fp4 else "float8_e4m3fn (or raw uint8) tensor"))
     if data.dim() != 3:
-        raise ValueError(f"{name} must be [experts, rows, k]")
+        raise ValueError(f"{name} must be [experts, rows, k]" + (" with k / 2 bytes per row" if fp4 else ""))
     data = data.contiguous().view(torch.uint8)
+    if fp4 and data.data_ptr() % 32:
+        data = data.clone()      # the 4-bit tensor map wants a 32-byte aligned base; fresh allocations are 256-byte aligned
     if sf is None:
         return data
     if sf.dtype == torch.float32:  # power-of-two floats as the reference quantisers return them
@@ -338,18 +342,25 @@ def _norm_weight(name: str, w: WeightArg):
     elif sf.dtype != torch.uint8:
         raise TypeError(f"{name} scales must be float32 powers of two or uint8 exponents")
     e, rows, k = data.shape
+    k = 2 * k if fp4 else k
     if tuple(sf.shape) != (e, rows // 128, k // 128):
         raise ValueError(f"{name} scales must be [experts, rows/128, k/128], got {tuple(sf.shape)}")
     return data, sf.contiguous()
 
 
-def transform_weights_for_mega_moe(l1_weights: WeightArg, l2_weights: WeightArg, activation: str = "swiglu"):
+def transform_weights_for_mega_moe(l1_weights: WeightArg, l2_weights: WeightArg, activation: str = "swiglu",
+                                   weight_format: str = "e4m3"):
     """Offline weight preparation.  ``l1`` is ``[EPR, 2I, H]`` with gate rows first, ``l2`` is
     ``[EPR, H, I]``; each may come with 128x128 UE8M0 block scales.  The B200 kernels read
     plain row-major bytes through TMA, so this only validates, makes contiguous and turns
-    scale planes into exponent bytes (the reference re-tiles into MetaX lane order here)."""
+    scale planes into exponent bytes (the reference re-tiles into MetaX lane order here).
+    ``weight_format="e2m1"``: the tensors hold packed 4-bit codes, ``[EPR, rows, k / 2]`` bytes with the
+    element of even k in the low nibble (``quant.per_block_cast_to_fp4``), for ``fp8_fp4_mega_moe``."""
     assert activation == "swiglu", f"Only `swiglu` supported, got `{activation}`"
-    l1, l2 = _norm_weight("l1_weights", l1_weights), _norm_weight("l2_weights", l2_weights)
+    if weight_format not in ("e4m3", "e2m1"):
+        raise ValueError(f"weight_format must be 'e4m3' or 'e2m1', got {weight_format!r}")
+    fp4 = weight_format == "e2m1"
+    l1, l2 = _norm_weight("l1_weights", l1_weights, fp4), _norm_weight("l2_weights", l2_weights, fp4)
     if isinstance(l1, tuple) != isinstance(l2, tuple):
         raise ValueError("l1 and l2 must both carry scales or both be raw")
     return l1, l2
@@ -395,27 +406,32 @@ def _quantize_input(sym_buffer: "SymmBuffer", num_tokens: int, scaled: bool) -> 
 def _check_buffer(sym_buffer: SymmBuffer, fn: str):
     # like the reference (torch/mxmegakernel/mega/__init__.py:615-618) the fp8 entry points take
     # both buffer kinds; a bf16xfp8 buffer gets its input quantised first
-    if sym_buffer.mma_type not in ("fp8xfp8", "bf16xfp8"):
-        raise ValueError(f"{fn} requires an fp8xfp8 / bf16xfp8 SymmBuffer, got {sym_buffer.mma_type!r}")
+    if sym_buffer.mma_type not in _SUPPORTED_MMA_TYPES:
+        raise ValueError(f"{fn} requires an fp8xfp8 / bf16xfp8 / fp8xfp4 SymmBuffer, got {sym_buffer.mma_type!r}")
 
 
 def _stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check_weights(sym_buffer: SymmBuffer, l1, l2):
+def _check_weights(sym_buffer: SymmBuffer, l1, l2, weight_format: int = 0):
     d1 = l1[0] if isinstance(l1, tuple) else l1
     d2 = l2[0] if isinstance(l2, tuple) else l2
     EPR, H, I = sym_buffer.num_experts_per_rank, sym_buffer.hidden, sym_buffer.intermediate_hidden
-    if tuple(d1.shape) != (EPR, 2 * I, H) or tuple(d2.shape) != (EPR, H, I):
-        raise ValueError(f"weights must be [{EPR},{2 * I},{H}] and [{EPR},{H},{I}], got {tuple(d1.shape)} "
+    if weight_format not in (0, 1):
+        raise ValueError(f"weight_format must be 0 (E4M3) or 1 (packed e2m1), got {weight_format!r}")
+    div = 2 if weight_format == 1 else 1     # bytes per row: k, or k / 2 for packed 4-bit codes
+    if tuple(d1.shape) != (EPR, 2 * I, H // div) or tuple(d2.shape) != (EPR, H, I // div):
+        raise ValueError(f"weights must be [{EPR},{2 * I},{H // div}] and [{EPR},{H},{I // div}], got {tuple(d1.shape)} "
                          f"and {tuple(d2.shape)}")
+    if weight_format == 1 and (d1.data_ptr() % 32 or d2.data_ptr() % 32):
+        raise ValueError("packed e2m1 weights must be 32-byte aligned (see transform_weights_for_mega_moe)")
 
 
 def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
                  cumulative_local_expert_recv_stats=None, activation: str = "swiglu", activation_clamp=None,
                  expert_window: Optional[int] = None, max_spins: int = 0, cta_pair: Optional[int] = None,
-                 packed_inputs: bool = False, group_weights=None) -> None:
+                 packed_inputs: bool = False, group_weights=None, weight_format: int = 0) -> None:
     """One MoE layer: ``y[t] = sum_k w_k * W2_e SwiGLU(W1_e x_t)`` for this rank's
     ``y.shape[0]`` tokens, inputs taken from ``sym_buffer.x / x_sf / topk_idx / topk_weights``
     (or, with ``packed_inputs``, from the packed image described by ``SymmBuffer.packed_layout``).
@@ -432,11 +448,12 @@ def fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer
         raise ValueError(f"num_tokens={num_tokens} exceeds capacity {sym_buffer.num_max_tokens_per_rank}")
     if y.dtype != torch.bfloat16 or (num_tokens and (y.shape[1] != sym_buffer.hidden or not y.is_contiguous())):
         raise ValueError("y must be a contiguous bf16 [tokens, hidden] tensor")
-    _check_weights(sym_buffer, l1_weights, l2_weights)
+    _check_weights(sym_buffer, l1_weights, l2_weights, weight_format)
     lib = _lib.lib()
     _quantize_input(sym_buffer, num_tokens, isinstance(l1_weights, tuple) and l1_weights[1] is not None)
     a = sym_buffer.launch_args(num_tokens, l1_weights, l2_weights, y_bf16=y, expert_window=expert_window,
-                               max_spins=max_spins, cta_pair=cta_pair, packed=packed_inputs, group_weights=group_weights)
+                               max_spins=max_spins, cta_pair=cta_pair, packed=packed_inputs, group_weights=group_weights,
+                               weight_format=weight_format)
     if num_tokens == 0:  # nothing to reduce, but the rank still serves its experts
         check(lib.mxk_launch_compute(C.byref(a), _stream_ptr()), "mxk_launch_compute")
     else:
@@ -484,8 +501,14 @@ def bf16_fp8_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmB
     fp8_mega_moe(y, l1_weights, l2_weights, sym_buffer, **kwargs)
 
 
-def fp8_fp4_mega_moe(*args, **kwargs):
-    raise NotImplementedError("only fp8xfp8 and bf16xfp8 are implemented")
+def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer, **kwargs) -> None:
+    """FP8 activations x 4-bit (e2m1) weights (reference: the MX_FP4_W build of the kernel,
+    src/common.cuh:99-134; its Python layer leaves this entry point unimplemented).  The weights are
+    packed codes ``[EPR, 2I, H/2]`` / ``[EPR, H, I/2]`` (``quant.per_block_cast_to_fp4``,
+    ``transform_weights_for_mega_moe(..., weight_format="e2m1")``) with the usual 128x128 scale
+    planes; everything else is ``fp8_mega_moe``.  The result equals the 8-bit layer run on the
+    expanded weights (``quant.e2m1_to_e4m3``); the layer reads half the weight bytes."""
+    fp8_mega_moe(y, l1_weights, l2_weights, sym_buffer, weight_format=1, **kwargs)
 
 
 def read_dbg_report(sym_buffer: SymmBuffer, hidden: int = 0, intermediate_hidden: int = 0):

@@ -405,6 +405,37 @@ ORC_API void orc_fill_weights(uint8_t* w, long long n_rows, int k_cols, uint32_t
             w[(size_t)r * k_cols + k] = (uint8_t)((seed + (uint32_t)r * 131u + (uint32_t)k * 7u) & 0x3f);
 }
 
+// 4-bit weights (the reference's MX_FP4_W build).  A code is sign(1) exponent(2, bias 1)
+// mantissa(1); the kernel multiplies with the E4M3 byte of the same value
+// (fp4_code_to_fp8, src/common.cuh:116-126): exponent 0 -> 0 or 0.5, else
+// 2^(e-1) * (1 + m/2), i.e. E4M3 exponent field e - 1 + 7 and mantissa m << 2.
+ORC_API uint8_t orc_e2m1_to_e4m3(uint8_t c) {
+    const uint8_t sign = (c & 8u) ? 0x80u : 0u;
+    const unsigned e = (c >> 1) & 3u, m = c & 1u;
+    const uint8_t mag = e == 0 ? (m ? 0x30u : 0x00u) : (uint8_t)(((e - 1u + 7u) << 3) | (m ? 4u : 0u));
+    return (uint8_t)(sign | mag);
+}
+// Packed codes [n_rows][k_cols / 2] (element of even k in the low nibble) -> E4M3 bytes
+// [n_rows][k_cols]: what the CPU reference reads through w_lane_get in that build
+// (src/bench_check.cuh:405-421; row-major here instead of the MetaX lane order).
+ORC_API void orc_expand_e2m1(const uint8_t* packed, long long n_rows, int k_cols, uint8_t* out) {
+    for (long long r = 0; r < n_rows; ++r)
+        for (int k = 0; k < k_cols; ++k) {
+            const uint8_t b = packed[(size_t)r * (k_cols / 2) + k / 2];
+            out[(size_t)r * k_cols + k] = orc_e2m1_to_e4m3((uint8_t)((b >> (4 * (k & 1))) & 0xfu));
+        }
+}
+// Test-data generator WPROBE_FP4_CODE (src/common.cuh:127-131): code at logical (row, k) =
+// ((seed + 131*row + 7*k) >> 1) & 0xf, packed two per byte.
+ORC_API void orc_fill_weights_e2m1(uint8_t* w, long long n_rows, int k_cols, uint32_t seed) {
+    for (long long r = 0; r < n_rows; ++r)
+        for (int k = 0; k < k_cols; k += 2) {
+            const uint32_t lo = ((seed + (uint32_t)r * 131u + (uint32_t)k * 7u) >> 1) & 0xfu;
+            const uint32_t hi = ((seed + (uint32_t)r * 131u + (uint32_t)(k + 1) * 7u) >> 1) & 0xfu;
+            w[(size_t)r * (k_cols / 2) + k / 2] = (uint8_t)(lo | (hi << 4));
+        }
+}
+
 // ------------------------------------------------------------------ numerics --
 template <class F>
 static void parallel_rows(int rows, int threads, F fn) {  // test/check.cu:155-165
@@ -419,7 +450,9 @@ static void parallel_rows(int rows, int threads, F fn) {  // test/check.cu:155-1
 // One dot product, FP32.  Unscaled: strictly sequential over K as the reference
 // (src/bench_check.cuh:446-451).  Scaled: sequential inside each 128-wide K
 // block, the block sum multiplied by (sa*sb) (both exact powers of two) and
-// added to the running total — the DeepGEMM-style promotion the CUDA path uses.
+// added to the running total.  The CUDA path applies the same scales inside the
+// block-scaled tensor-core MMA, whose summation order inside a K block is not
+// specified: the comparison tolerance of the parity tests covers the difference.
 static inline float dot_fp8(const float* a, const uint8_t* a_sf, const uint8_t* w,
                             const uint8_t* w_sf, int K) {
     if (!a_sf && !w_sf) {

@@ -81,6 +81,10 @@ def lib():
     L.orc_select_win.restype = C.c_int
     L.orc_select_win.argtypes = [_u32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
     L.orc_fill_weights.argtypes = [_u8p, C.c_longlong, C.c_int, C.c_uint32]
+    L.orc_fill_weights_e2m1.argtypes = [_u8p, C.c_longlong, C.c_int, C.c_uint32]
+    L.orc_expand_e2m1.argtypes = [_u8p, C.c_longlong, C.c_int, _u8p]
+    L.orc_e2m1_to_e4m3.argtypes = [C.c_uint8]
+    L.orc_e2m1_to_e4m3.restype = C.c_uint8
     L.orc_l1.argtypes = [_u8p, C.c_void_p, _u8p, C.c_void_p, C.c_int, C.c_int, C.c_int, _f32p, C.c_int]
     L.orc_requant.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, _u8p, C.c_void_p]
     L.orc_l2.argtypes = [_u8p, C.c_void_p, _u8p, C.c_void_p, C.c_int, C.c_int, C.c_int, _f32p, C.c_int]
@@ -241,6 +245,24 @@ def fill_weights(n_rows: int, k_cols: int, seed: int) -> np.ndarray:
     w = np.empty((n_rows, k_cols), np.uint8)
     lib().orc_fill_weights(w, n_rows, k_cols, seed)
     return w
+
+
+def fill_weights_e2m1(n_rows: int, k_cols: int, seed: int) -> np.ndarray:
+    """Packed e2m1 test weights [n_rows, k_cols / 2] (reference: WPROBE_FP4_CODE, src/common.cuh:127-131)."""
+    w = np.empty((n_rows, k_cols // 2), np.uint8)
+    lib().orc_fill_weights_e2m1(w, n_rows, k_cols, seed)
+    return w
+
+
+def expand_e2m1(packed: np.ndarray) -> np.ndarray:
+    """Packed e2m1 codes [..., k / 2] -> the E4M3 bytes [..., k] they stand for (reference:
+    fp4_code_to_fp8, src/common.cuh:116-126; w_lane_get of the 4-bit build, src/bench_check.cuh:405-421).
+    The oracle of the 4-bit layer is the 8-bit oracle on these bytes."""
+    p = np.ascontiguousarray(packed, np.uint8)
+    rows = int(np.prod(p.shape[:-1])) if p.ndim > 1 else 1
+    out = np.empty(p.shape[:-1] + (p.shape[-1] * 2,), np.uint8)
+    lib().orc_expand_e2m1(p.reshape(rows, -1), rows, p.shape[-1] * 2, out.reshape(rows, -1))
+    return out
 
 
 def schedule(expert_rows, row_base, win_cap, nt1, nt2):

@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout (its path is the first argument):
 
-    python tests/golden/make_golden.py [/path/to/reference] [--only-tk-info]
+    python tests/golden/make_golden.py [/path/to/reference] [--only-tk-info | --only-e2m1]
 
 Three sources are used, none copied into this repository:
   * the reference's host-side C++ functions, compiled from its sources into
@@ -10,7 +10,8 @@ Three sources are used, none copied into this repository:
     ref_l2, ref_reduce, make_routes, gs_schedule_member, select_win, lpt_assign);
   * the reference's Python quantisers, imported by file path from
     torch/mxmegakernel/utils/math.py (ceil_to_ue8m0, per_token_cast_to_fp8,
-    per_block_cast_to_fp8, cast_back_from_fp8).
+    per_block_cast_to_fp8, cast_back_from_fp8; for e2m1.npz _quantize_to_fp4_e2m1,
+    per_token_cast_to_fp4, cast_back_from_fp4, _dequantize_from_fp4_e2m1).
   * the reference's recorded route corpus test/76.real_decode/dataset.tk_info, of
     which four launches' per-expert counts are kept (tk_info.npz).
 The fixtures are small .npz files; tests/test_oracle_golden.py checks the
@@ -55,8 +56,42 @@ def make_tk_info(ref_root):
           "max/mean", [round(float(skew(full[k])), 1) for k in pick])
 
 
+def _ref_math(ref_root):
+    spec = importlib.util.spec_from_file_location(
+        "ref_math", os.path.join(ref_root, "torch", "mxmegakernel", "utils", "math.py"))
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    return m
+
+
+def make_e2m1(m):
+    """4-bit (e2m1) codes: the reference's Python quantiser, packing and value table
+    (torch/mxmegakernel/utils/math.py:84-164)."""
+    import torch
+    g4 = torch.Generator().manual_seed(5)
+    x4 = torch.randn((6, 384), generator=g4).bfloat16()
+    x4[1, 128:256] = 0            # all-zero group -> amax clamp
+    x4[2, :128] *= 300.0
+    p4, sf4 = m.per_token_cast_to_fp4(x4, use_ue8m0=True, gran_k=128)
+    back4 = m.cast_back_from_fp4(p4, sf4, 128)
+    q_in = torch.tensor([0.0, 0.25, 0.2500001, -0.25, 0.75, 0.76, 1.25, 1.3, 1.75, 1.8, 2.5, 2.6, 3.5, 3.6, 5.0, 5.1,
+                         6.0, 100.0, -0.1, -0.3, -6.0, -7.0], dtype=torch.float32)
+    q_codes = m._quantize_to_fp4_e2m1(q_in).view(torch.uint8)
+    codes = torch.arange(16, dtype=torch.int8)
+    code_e4m3 = m._dequantize_from_fp4_e2m1(codes).to(torch.float8_e4m3fn).view(torch.uint8)
+    code_e4m3[8] = 0x80           # the value table folds -0 into +0; the kernel keeps the sign bit of the code
+    np.savez_compressed(
+        os.path.join(HERE, "e2m1.npz"),
+        x=x4.float().numpy(), x_packed=p4.view(torch.uint8).numpy(),
+        x_sf=(sf4.contiguous().view(torch.int32) >> 23).to(torch.uint8).numpy(), x_back=back4.numpy(),
+        q_in=q_in.numpy(), q_codes=q_codes.numpy(), code_e4m3=code_e4m3.numpy())
+
+
 def main():
     ref_root = next((a for a in sys.argv[1:] if not a.startswith("--")), "/root/reference")
+    if "--only-e2m1" in sys.argv:
+        make_e2m1(_ref_math(ref_root))
+        return
     if "--only-tk-info" in sys.argv:
         make_tk_info(ref_root)
         return
@@ -160,10 +195,7 @@ def main():
 
     # ---- Python quantisers (torch) ----
     import torch
-    spec = importlib.util.spec_from_file_location(
-        "ref_math", os.path.join(ref_root, "torch", "mxmegakernel", "utils", "math.py"))
-    m = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(m)
+    m = _ref_math(ref_root)
     g = torch.Generator().manual_seed(11)
     xt = torch.randn((5, 384), generator=g).bfloat16()
     xt[2, 128:256] = 0          # all-zero group -> amax clamp 1e-4
@@ -181,6 +213,7 @@ def main():
         w=wt.numpy(), wq=wq.view(torch.uint8).numpy(),
         wsf=(wsf.contiguous().view(torch.int32) >> 23).to(torch.uint8).numpy(),
         back=back.numpy(), ceil_in=cin.numpy(), ceil_out=cout.numpy())
+    make_e2m1(m)
     print("golden fixtures written to", HERE)
 
 
