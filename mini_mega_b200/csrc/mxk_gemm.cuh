@@ -146,17 +146,18 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
 
     const int par = (int)(epoch & 1);
     // pull mode: written by the set-up phase of this same kernel (CTA 0); push mode: own tables
-    const int n_tasks = tabs ? tabs->n_tasks : ld_relaxed_gpu(&f->n_tasks);
+    (void)tabs;   // = &S->tabs in push mode; addressed through S below, so that no extra pointer stays live in the hot loops
+    const int n_tasks = a.push ? S->tabs.n_tasks : ld_relaxed_gpu(&f->n_tasks);
     const int4* tasks = reinterpret_cast<const int4*>(a.rwk + a.L.tasks_off);
     const int4* windows = reinterpret_cast<const int4*>(a.rwk + a.L.windows_off);
-    auto get_task = [&](int t) -> int4 { return tabs ? tabs_task(tabs, a, t) : ld_relaxed_gpu_v4(tasks + t); };
-    auto get_window = [&](int w) -> int4 { return tabs ? tabs_window(tabs, a, w) : ld_relaxed_gpu_v4(windows + w); };
+    auto get_task = [&](int t) -> int4 { return a.push ? tabs_task(&S->tabs, a, t) : ld_relaxed_gpu_v4(tasks + t); };
+    auto get_window = [&](int w) -> int4 { return a.push ? tabs_window(&S->tabs, a, w) : ld_relaxed_gpu_v4(windows + w); };
     uint32_t* l1_done = reinterpret_cast<uint32_t*>(a.rwk + a.L.l1_done_off) + (size_t)par * a.L.max_windows;
     const uint32_t* pool_ready = reinterpret_cast<const uint32_t*>(a.rwk + a.L.pool_ready_off) + (size_t)par * a.L.max_windows;
     const int kb1 = a.H / kBlockK, kb2 = a.I / kBlockK;
     const int nt1 = a.I / 128;
     const uint32_t l1_need = (uint32_t)nt1 * kEpiWarps * (kPair ? 2u : 1u);   // arrivals that complete a window's ffn rows
-    const uint32_t row_parts = tabs ? (uint32_t)tabs->parts : 1u;             // pool_ready arrivals per dispatched row
+    const uint32_t row_parts = a.push ? (uint32_t)S->tabs.parts : 1u;             // pool_ready arrivals per dispatched row
     // Pair mode: CTA `crank` of the cluster owns rows [128*crank, 128*crank+128) of a 256-row
     // window and weight half `crank`; rank 0 (the leader) claims tasks and issues the MMAs.
     const uint32_t crank = kPair ? cluster_ctarank() : 0u;
@@ -277,6 +278,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                 }
                 if (trace && it == 0) trace[8] = gtimer_ns();
                 fence_proxy_async_global();  // pool / ffn rows were written with ordinary stores
+                if (trace && it == 0) trace[9] = gtimer_ns();   // first activation tile requested next
                 bool dead = false;
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (lookahead && pending.x >= 0) {
@@ -293,7 +295,6 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                     uint8_t* sa = tiles + stage * kStageB;
                     if constexpr (kPair) tma_load_2d_pair(sa, ma, kb * kBlockK, row0, mapa_u32(smem_u32(&S->full[stage]), 0));
                     else tma_load_2d(sa, ma, kb * kBlockK, row0, &S->full[stage]);
-                    if (trace && it == 0 && kb == 0) trace[9] = gtimer_ns();
                     if (++stage == kNStages) { stage = 0; phase ^= 1; }
                 }
                 if (dead) { raise_status(f, MXK_DEV_TIMEOUT_PIPE, 5); *abort_flag = 1; break; }
@@ -330,6 +331,12 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                 // next stage and the next scale group polled under the MMAs already queued, and the
                 // scale-tile copies issued by the builder warps instead of here.
                 uint32_t acc = 0;
+                if (trace && it == 0 && !dead) {
+                    // time line: when the first operand tile of the layer has landed (kept out of the issue
+                    // loop below, where even a never-taken test per K block cost 3 % of a prefill-sized layer)
+                    if (MXK_TIMED(w_full, mbar_wait(&S->full[stage], phase, wait_ns, abort_flag))) { stage_ready = true; trace[10] = gtimer_ns(); }
+                    else dead = true;
+                }
                 for (int kb0 = 0; kb0 < nkb && !dead; kb0 += 4) {
                     // a new group of four K blocks: its scale tiles were copied into TMEM slot
                     // sf_slot by a builder warp
@@ -342,7 +349,6 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                     for (int i = 0; i < 4; ++i) {
                         if (kb0 + i >= nkb) break;
                         if (!stage_ready && !MXK_TIMED(w_full, mbar_wait(&S->full[stage], phase, wait_ns, abort_flag))) { dead = true; break; }
-                        if (trace && it == 0 && kb0 + i == 0) trace[10] = gtimer_ns();
                         tc_fence_after();
                         const uint64_t adesc = tile_desc0 + (uint64_t)(stage * (kStageB >> 4));
                         const uint64_t bdesc = adesc + (uint64_t)(kABytes >> 4);

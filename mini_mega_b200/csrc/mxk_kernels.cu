@@ -597,9 +597,12 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
         static const int pf_env = [] { const char* e = std::getenv("MXK_PREFETCH_KB"); return e ? std::atoi(e) * 1024 : -1; }();
         // The push-mode prologue is short and made of dependent memory round trips; a bulk prefetch
         // issued beside it lengthens every one of them (measured: first operand tile at 24.4 us with
-        // 704 KB per CTA against 20.9 us without, GEMM phase unchanged), so only the pull-mode
-        // prologue, which leaves the memory system idle for longer, prefetches.
-        k->prefetch_bytes = pf_env >= 0 ? pf_env : (k->push ? 0 : kPrefetchBytesPerCta);
+        // 704 KB per CTA against 20.9 us without, GEMM phase unchanged).  With large batches the pull-mode
+        // prologue is itself memory traffic (route build, row copies) and loses more to the prefetch than
+        // the GEMM phase gains (prefill-sized quarter: layer 392 us with it, 389 us without).  Only the
+        // pull-mode prologue of a small batch, three round trips with the memory system idle, prefetches.
+        const bool small_batch = (int64_t)k->cap * k->topk <= kPushAutoPairsPerRank;
+        k->prefetch_bytes = pf_env >= 0 ? pf_env : ((k->push || !small_batch) ? 0 : kPrefetchBytesPerCta);
     }
     k->fR = FastDiv::make((uint32_t)k->R); k->fEPR = FastDiv::make((uint32_t)k->EPR); k->ftopk = FastDiv::make((uint32_t)k->topk);
     k->fng = FastDiv::make((uint32_t)(k->R / k->group_ranks)); k->fwin = FastDiv::make((uint32_t)k->win_cap);
