@@ -43,7 +43,7 @@ NVLINK_GBS = 770.0               # peer copy per direction (nominal 900)
 # DRAM bytes of k_mega per launch over its algorithmic bytes, from the ncu capture of the
 # 32-expert decode shard; the benchmark's own launches stream more experts through the same
 # code, so traffic is scaled from that capture in proportion to the algorithmic bytes.
-NCU_TRAFFIC_RATIO = 1.1862 / 1.1757
+NCU_TRAFFIC_RATIO = 1.1790 / 1.1757   # dram__bytes_read.sum + dram__bytes_write.sum = 1.17208 GB + 6.9 MB
 GRAPH_NODES, GRAPH_WARM, GRAPH_TIMED = 20, 2, 3
 
 

@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout (its path is the first argument):
 
-    python tests/golden/make_golden.py [/path/to/reference] [--only-tk-info | --only-e2m1]
+    python tests/golden/make_golden.py /path/to/reference [--only-tk-info | --only-e2m1]
 
 Three sources are used, none copied into this repository:
   * the reference's host-side C++ functions, compiled from its sources into
@@ -88,7 +88,9 @@ def make_e2m1(m):
 
 
 def main():
-    ref_root = next((a for a in sys.argv[1:] if not a.startswith("--")), "/root/reference")
+    ref_root = next((a for a in sys.argv[1:] if not a.startswith("--")), os.environ.get("REF", ""))
+    if not os.path.isdir(os.path.join(ref_root, "src")):
+        sys.exit("usage: make_golden.py /path/to/reference [--only-tk-info | --only-e2m1]  (or REF=/path/to/reference)")
     if "--only-e2m1" in sys.argv:
         make_e2m1(_ref_math(ref_root))
         return
