@@ -35,7 +35,9 @@ constexpr int kStageBytes = kABytes + kBBytes;       // 48 KB
 // Per 128-row block of M each SM then moves 32 KB instead of 48 KB through shared memory.
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = 2 * kABytes;         // 32 KB
+constexpr int kSlimStages = 5;                       // single CTAs, windows of at most kSlimRows rows: 5 x (4 KB + 32 KB)
 constexpr int kMaxStages = kPairStages;
+static_assert(kSlimStages * (kSlimRows * kBlockK + kBBytes) <= kStages * kStageBytes && kSlimStages <= kMaxStages, "slim ring fits the tile region");
 static_assert(kPairStages * kPairStageBytes == kStages * kStageBytes, "both modes use the same tile region");
 constexpr int kTaskRing = 4;
 constexpr int kGemmThreads = 384;
@@ -133,7 +135,8 @@ template <bool kPair>
 __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, const PushTabs* tabs,
                            unsigned long long* trace, int* deferred_route_smem, uint8_t* tiles, uint8_t* sf_tiles, GemmSmem* S,
                            const uint32_t tmem_base, const CUtensorMap* tm_pool_p, const CUtensorMap* tm_ffn_p,
-                           const CUtensorMap* tm_w1_p, const CUtensorMap* tm_w2_p) {
+                           const CUtensorMap* tm_w1_p, const CUtensorMap* tm_w2_p, const CUtensorMap* tm_pool_slim_p,
+                           const CUtensorMap* tm_ffn_slim_p) {
     const CUtensorMap& tm_pool = *tm_pool_p;
     const CUtensorMap& tm_ffn = *tm_ffn_p;
     const CUtensorMap& tm_w1 = *tm_w1_p;
@@ -164,8 +167,17 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
     const bool leader = crank == 0;
     const int n_units = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;   // CTAs or CTA pairs pulling tasks
     const int unit_id = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
-    constexpr int kNStages = kPair ? kPairStages : kStages;
-    constexpr int kStageB = kPair ? kPairStageBytes : kStageBytes;
+    // Ring geometry.  Pairs: 6 stages of 32 KB.  Single CTAs: 4 stages of 48 KB (128 activation rows +
+    // 256 weight rows) — or, when no window of the launch has more than kSlimRows rows (decode: a few
+    // rows per expert), 5 stages of 36 KB with only kSlimRows activation rows staged per slot.  The MMA
+    // still reads 128 rows from the slot's start; rows kSlimRows.. are then the first bytes of the same
+    // slot's weight tile, they produce accumulator rows nobody reads.  The gain is the fifth stage: a
+    // quarter more weight bytes in flight per CTA, which is what a latency-bound stream (packed 4-bit
+    // weights: 16 KB of traffic per 32 KB tile) is short of.
+    const bool slim = !kPair && a.push && a.slim_ok && S->tabs.slim != 0;
+    const uint32_t a_bytes = kPair ? (uint32_t)kABytes : (slim ? (uint32_t)(kSlimRows * kBlockK) : (uint32_t)kABytes);
+    const uint32_t kNStages = kPair ? (uint32_t)kPairStages : (slim ? (uint32_t)kSlimStages : (uint32_t)kStages);
+    const uint32_t kStageB = kPair ? (uint32_t)kPairStageBytes : a_bytes + (uint32_t)kBBytes;
     // barrier helpers: in pair mode consumers release ring slots / scale tiles / accumulators on
     // the leader's barriers (cluster address of rank 0; for the leader that is its own barrier)
     auto wait_bar = [&](uint64_t* bar, uint32_t parity) -> bool {
@@ -239,7 +251,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                 if (lookahead) pending = claim_publish(it + 1);
                 const int e = win.x, row0 = win.y + 128 * (int)crank;
                 const bool is_l2 = task.x == 1;
-                const CUtensorMap* ma = is_l2 ? &tm_ffn : &tm_pool;
+                const CUtensorMap* ma = slim ? (is_l2 ? tm_ffn_slim_p : tm_pool_slim_p) : (is_l2 ? &tm_ffn : &tm_pool);
                 const CUtensorMap* mb = is_l2 ? &tm_w2 : &tm_w1;
                 const int nkb = is_l2 ? kb2 : kb1;
                 const int brow0 = is_l2 ? e * a.H + task.z * kBlockN : e * 2 * a.I + task.z * 128;
@@ -255,9 +267,9 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                         if (leader) mbar_expect_tx(&S->full[st], 2 * (kABytes + b_half_tx));
                         tma_load_2d_pair_hint(sa + kABytes, mb, kb * kBlockK, leader ? brow0 : brow1, mapa_u32(smem_u32(&S->full[st]), 0), stream_policy);
                     } else {
-                        mbar_expect_tx(&S->full[st], kABytes + 2 * b_half_tx);
-                        tma_load_2d_hint(sa + kABytes, mb, kb * kBlockK, brow0, &S->full[st], stream_policy);
-                        tma_load_2d_hint(sa + kABytes + kABytes, mb, kb * kBlockK, brow1, &S->full[st], stream_policy);
+                        mbar_expect_tx(&S->full[st], a_bytes + 2 * b_half_tx);
+                        tma_load_2d_hint(sa + a_bytes, mb, kb * kBlockK, brow0, &S->full[st], stream_policy);
+                        tma_load_2d_hint(sa + a_bytes + kABytes, mb, kb * kBlockK, brow1, &S->full[st], stream_policy);
                     }
                 };
                 // L2: every L1 tile of this window must have landed in ffn; L1: every row of this
@@ -267,10 +279,10 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                 int pre = 0;
                 if (!gate_ok) {
                     uint32_t st2 = stage, ph2 = phase;
-                    while (pre < nkb && pre < kNStages && mbar_try_wait(&S->empty[st2], ph2 ^ 1)) {
+                    while (pre < nkb && pre < (int)kNStages && mbar_try_wait(&S->empty[st2], ph2 ^ 1)) {
                         load_b(pre, st2);
                         ++pre;
-                        if (++st2 == (uint32_t)kNStages) { st2 = 0; ph2 ^= 1; }
+                        if (++st2 == kNStages) { st2 = 0; ph2 ^= 1; }
                     }
                     if (!MXK_TIMED(w_gate, spin_until([&] { return gate_passed(task, win); }, wait_ns, abort_flag))) {
                         raise_status(f, MXK_DEV_TIMEOUT_GATE, 4); *abort_flag = 1; break;
@@ -351,7 +363,7 @@ __device__ void gemm_phase(const KArgs& a, DevFlags* f, const long long epoch, c
                         if (!stage_ready && !MXK_TIMED(w_full, mbar_wait(&S->full[stage], phase, wait_ns, abort_flag))) { dead = true; break; }
                         tc_fence_after();
                         const uint64_t adesc = tile_desc0 + (uint64_t)(stage * (kStageB >> 4));
-                        const uint64_t bdesc = adesc + (uint64_t)(kABytes >> 4);
+                        const uint64_t bdesc = adesc + (uint64_t)(a_bytes >> 4);
                         const uint32_t idesc = idesc0 | ((uint32_t)i << 4) | ((uint32_t)i << 29);   // scale byte i of the group
                         uint32_t nstage = stage + 1, nphase = phase;
                         if (nstage == kNStages) { nstage = 0; nphase ^= 1; }

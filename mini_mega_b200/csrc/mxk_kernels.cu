@@ -66,6 +66,7 @@ struct KArgs {
     int w_experts;               // experts in the weight arrays w1 / w2 (EPR, or group_ranks * EPR)
     int prefetch_bytes;          // bytes of W1 every CTA asks into L2 while the prologue runs
     int w_fp4;                   // weights are e2m1 codes, two per byte; TMA unpacks them to one code per byte
+    int slim_ok;                 // launches whose windows are all small may use the five-stage ring (MXK_SLIM=0: never)
     FastDiv fR, fEPR, ftopk, fng, fwin;   // division by R, EPR, topk, R / group_ranks, win_cap
     unsigned long long local_wait_ns, remote_wait_ns;
     uint8_t* rwk;
@@ -101,7 +102,8 @@ __device__ __forceinline__ void raise_status(DevFlags* f, int code, int dbg_slot
 // pool counters), so the grid never exceeds the SM count and every CTA is resident.
 template <bool kPair>
 __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, const CUtensorMap& tm_pool,
-                                          const CUtensorMap& tm_ffn, const CUtensorMap& tm_w1,
+                                          const CUtensorMap& tm_ffn, const CUtensorMap& tm_pool_slim,
+                                          const CUtensorMap& tm_ffn_slim, const CUtensorMap& tm_w1,
                                           const CUtensorMap& tm_w2) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -226,7 +228,7 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
     if (do_gemm) {
         if (tables_ok)
             gemm_phase<kPair>(a, f, epoch, tabs, trace, defer_route ? s_small : nullptr, tiles, sf_tiles, S, tmem_base, &tm_pool,
-                              &tm_ffn, &tm_w1, &tm_w2);
+                              &tm_ffn, &tm_w1, &tm_w2, &tm_pool_slim, &tm_ffn_slim);
         else if (defer_route)   // no GEMM phase after all (tables failed): the launch bookkeeping still has to happen
             route_phase(a, f, epoch, s_small, nullptr, 0, true, cta_team);
         if (S->abort_flag) __nanosleep(200000);  // let copies / MMAs in flight drain
@@ -250,8 +252,9 @@ __device__ __forceinline__ void mega_body(const KArgs& a, const int phase_mask, 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 k_mega(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap tm_pool,
        const __grid_constant__ CUtensorMap tm_ffn, const __grid_constant__ CUtensorMap tm_w1,
-       const __grid_constant__ CUtensorMap tm_w2) {
-    mega_body<false>(a, phase_mask, tm_pool, tm_ffn, tm_w1, tm_w2);
+       const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_pool_slim,
+       const __grid_constant__ CUtensorMap tm_ffn_slim) {
+    mega_body<false>(a, phase_mask, tm_pool, tm_ffn, tm_pool_slim, tm_ffn_slim, tm_w1, tm_w2);
 }
 
 // The same layer with the GEMM phase on CTA pairs (clusters of two, 2-CTA tcgen05 MMA with
@@ -260,7 +263,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 k_mega_pair(const KArgs a, const int phase_mask, const __grid_constant__ CUtensorMap tm_pool,
             const __grid_constant__ CUtensorMap tm_ffn, const __grid_constant__ CUtensorMap tm_w1,
             const __grid_constant__ CUtensorMap tm_w2) {
-    mega_body<true>(a, phase_mask, tm_pool, tm_ffn, tm_w1, tm_w2);
+    mega_body<true>(a, phase_mask, tm_pool, tm_ffn, tm_pool, tm_ffn, tm_w1, tm_w2);   // pairs never stage slim slots
 }
 
 __global__ void k_empty() {}
@@ -437,13 +440,13 @@ EncodeTiledFn get_encode() {
     return fn;
 }
 
-// uint8 [rows][k] row-major, tile 128 rows x 128 bytes, 128-byte swizzle.
-int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t k) {
+// uint8 [rows][k] row-major, tile `box_rows` rows x 128 bytes, 128-byte swizzle.
+int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t k, int box_rows = 128) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return fail(MXK_ERR_NO_DRIVER, "cuTensorMapEncodeTiled not available from the CUDA driver");
     const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)k};
-    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t box[2] = {128, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -555,6 +558,10 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     if (la->weight_format != MXK_WEIGHTS_E4M3 && la->weight_format != MXK_WEIGHTS_E2M1)
         return fail(MXK_ERR_BAD_ARG, "weight_format must be MXK_WEIGHTS_E4M3 or MXK_WEIGHTS_E2M1");
     k->w_fp4 = la->weight_format == MXK_WEIGHTS_E2M1;
+    {
+        static const int slim_env = [] { const char* e = std::getenv("MXK_SLIM"); return e ? std::atoi(e) : 1; }();
+        k->slim_ok = slim_env != 0;
+    }
     k->R = g.R; k->rank = g.rank; k->EPR = g.experts_per_rank; k->E = g.R * g.experts_per_rank;
     k->topk = g.topk; k->H = g.hidden; k->I = g.intermediate; k->cap = g.max_tokens;
     k->slot_cap = g.slot_capacity ? g.slot_capacity : g.max_tokens;
@@ -619,10 +626,10 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
     if (mask == 0) return 0;
     // The four tensor maps depend only on (workspace, weights, geometry): a serving loop launches the
     // same ones every layer, so the last few sets are kept per thread instead of being re-encoded.
-    struct MapSet { const void* rwk; const void* w1; const void* w2; int64_t rows; int H, I, EPR, fp4; CUtensorMap m[4]; };
+    struct MapSet { const void* rwk; const void* w1; const void* w2; int64_t rows; int H, I, EPR, fp4; CUtensorMap m[6]; };
     static thread_local MapSet cache[4];
     static thread_local int cache_n = 0, cache_next = 0;
-    CUtensorMap zero_maps[4];
+    CUtensorMap zero_maps[6];
     const CUtensorMap* maps = zero_maps;
     if (mask & MXK_PHASE_GEMM) {
         if (!k.w1 || !k.w2) return fail(MXK_ERR_BAD_ARG, "w1 / w2 must be non-null");
@@ -640,8 +647,16 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
             n.rwk = k.rwk; n.w1 = k.w1; n.w2 = k.w2; n.rows = k.L.pool_rows; n.H = k.H; n.I = k.I; n.EPR = k.w_experts; n.fp4 = k.w_fp4;
             if (int rc = make_map(&n.m[0], k.rwk + k.L.pool_off, k.L.pool_rows + 128, k.H)) return rc;
             if (int rc = make_map(&n.m[1], k.rwk + k.L.ffn_off, k.L.pool_rows + 128, k.I)) return rc;
-            if (int rc = (k.w_fp4 ? make_map_e2m1 : make_map)(&n.m[2], k.w1, (int64_t)k.w_experts * 2 * k.I, k.H)) return rc;
-            if (int rc = (k.w_fp4 ? make_map_e2m1 : make_map)(&n.m[3], k.w2, (int64_t)k.w_experts * k.H, k.I)) return rc;
+            if (k.w_fp4) {
+                if (int rc = make_map_e2m1(&n.m[2], k.w1, (int64_t)k.w_experts * 2 * k.I, k.H)) return rc;
+                if (int rc = make_map_e2m1(&n.m[3], k.w2, (int64_t)k.w_experts * k.H, k.I)) return rc;
+            } else {
+                if (int rc = make_map(&n.m[2], k.w1, (int64_t)k.w_experts * 2 * k.I, k.H)) return rc;
+                if (int rc = make_map(&n.m[3], k.w2, (int64_t)k.w_experts * k.H, k.I)) return rc;
+            }
+            // the same activation tensors with kSlimRows-row boxes (launches whose windows are all that small)
+            if (int rc = make_map(&n.m[4], k.rwk + k.L.pool_off, k.L.pool_rows + 128, k.H, kSlimRows)) return rc;
+            if (int rc = make_map(&n.m[5], k.rwk + k.L.ffn_off, k.L.pool_rows + 128, k.I, kSlimRows)) return rc;
             cache[cache_next] = n;
             hit = &cache[cache_next];
             cache_next = (cache_next + 1) % 4;
@@ -651,7 +666,7 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
     } else {
         std::memset(zero_maps, 0, sizeof(zero_maps));
     }
-    const CUtensorMap &tm_pool = maps[0], &tm_ffn = maps[1], &tm_w1 = maps[2], &tm_w2 = maps[3];
+    const CUtensorMap &tm_pool = maps[0], &tm_ffn = maps[1], &tm_w1 = maps[2], &tm_w2 = maps[3], &tm_pool_slim = maps[4], &tm_ffn_slim = maps[5];
     static thread_local int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -685,7 +700,7 @@ int launch_mega(const KArgs& k, int mask, cudaStream_t st) {
         k_mega_pair<<<kk.gemm_grid, kGemmThreads, kGemmSmem, st>>>(kk, mask, tm_pool, tm_ffn, tm_w1, tm_w2);
     }
     else
-        k_mega<<<k.gemm_grid, kGemmThreads, kGemmSmem, st>>>(k, mask, tm_pool, tm_ffn, tm_w1, tm_w2);
+        k_mega<<<k.gemm_grid, kGemmThreads, kGemmSmem, st>>>(k, mask, tm_pool, tm_ffn, tm_w1, tm_w2, tm_pool_slim, tm_ffn_slim);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : cuda_fail(e, k.pair ? "launch k_mega_pair" : "launch k_mega");
 }

@@ -630,6 +630,7 @@ __device__ void dispatch_phase(const KArgs& a, DevFlags* f, long long epoch, int
 // pull-mode tables: no rank can finish launch N+1 before every rank has pushed for N+1.
 constexpr int kPushMaxEPR = 256;       // local experts whose tables fit the control block
 constexpr int kPushMaxR = 64;
+constexpr int kSlimRows = 32;         // activation rows staged per ring slot when every window is that small
 constexpr int kPushMaxPairs = 16384;   // routing words of the whole world kept in shared memory per CTA
 constexpr int kPushAutoPairsPerRank = 2048;  // dispatch_mode 0 pushes up to this many routed pairs per rank (max_tokens * topk)
 constexpr int kPushMaxCnt = 4096;      // EPR * (R + 1)
@@ -640,6 +641,7 @@ struct PushTabs {   // tables of this launch, in the control block of shared mem
     int n_tasks, n_l1, n_windows, total_rows;
     int parts;                    // warps that share the copy of one pool row (each counts into pool_ready)
     int helper;                   // 1: cross-rank helper scheduling is on, the tables are this member's window list
+    int slim;                     // 1: no window of this launch has more than kSlimRows rows (see gemm_phase)
     union {
         struct {                          // owner layout: this rank computes exactly its own experts
             int tot[kPushMaxEPR];         // rows of local expert le
@@ -1004,6 +1006,15 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
         // row costs one round trip to the staging area instead of several
         const int nwarps = (int)gridDim.x * (nthr >> 5);
         T->parts = W <= nwarps ? 4 : (W <= 2 * nwarps ? 2 : 1);
+        // the largest window of the launch: the hottest expert's rows, capped by the window size
+        int mx = 0;
+        if (T->helper) {
+#pragma unroll 1
+            for (int ge = 0; ge < GE; ++ge) mx = max(mx, sc.totg[ge]);
+        } else {
+            mx = sc.tot[sc.order[0]];
+        }
+        T->slim = min(mx, a.win_cap) <= kSlimRows ? 1 : 0;
     }
     __syncthreads();
     return *sc.flag != 0 && !overflow;
