@@ -102,7 +102,7 @@ typedef struct MxkLayout {
                                    scratch of the one-pass route build for large batches */
     int32_t route_scratch_ctas;
     int32_t push_auto;          /* 1: dispatch_mode 0 runs the push-mode prologue here: eligible and
-                                   max_tokens * topk <= 1024 per rank.  A pushed row travels as
+                                   max_tokens * topk <= 2048 per rank.  A pushed row travels as
                                    tagged words (twice its bytes) once per routed pair and is copied
                                    again into the pool; beyond that size the pull protocol's three
                                    round trips cost less than the extra bytes                      */

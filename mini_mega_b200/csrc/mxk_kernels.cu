@@ -608,7 +608,7 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
         // prologue is itself memory traffic (route build, row copies) and loses more to the prefetch than
         // the GEMM phase gains (prefill-sized quarter: layer 392 us with it, 389 us without).  Only the
         // pull-mode prologue of a small batch, three round trips with the memory system idle, prefetches.
-        const bool small_batch = (int64_t)k->cap * k->topk <= 2048;   // up to 256 tokens per rank at top-8
+        const bool small_batch = (int64_t)k->cap * k->topk <= kPushAutoPairsPerRank;
         k->prefetch_bytes = pf_env >= 0 ? pf_env : ((k->push || !small_batch) ? 0 : kPrefetchBytesPerCta);
     }
     k->fR = FastDiv::make((uint32_t)k->R); k->fEPR = FastDiv::make((uint32_t)k->EPR); k->ftopk = FastDiv::make((uint32_t)k->topk);

@@ -632,7 +632,7 @@ constexpr int kPushMaxEPR = 256;       // local experts whose tables fit the con
 constexpr int kPushMaxR = 64;
 constexpr int kSlimRows = 32;         // activation rows staged per ring slot when every window is that small
 constexpr int kPushMaxPairs = 16384;   // routing words of the whole world kept in shared memory per CTA
-constexpr int kPushAutoPairsPerRank = 1024;  // dispatch_mode 0 pushes up to this many routed pairs per rank (max_tokens * topk)
+constexpr int kPushAutoPairsPerRank = 2048;  // dispatch_mode 0 pushes up to this many routed pairs per rank (max_tokens * topk)
 constexpr int kPushMaxCnt = 4096;      // EPR * (R + 1)
 
 constexpr int kHelperMaxWin = 512;     // windows one member may be handed (reference: kGsMemberCap, src/group_sched.cuh:150-154)
