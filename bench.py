@@ -417,6 +417,9 @@ class Job:
             with torch.cuda.graph(g, stream=side):
                 for _ in range(GRAPH_NODES):
                     self.layer()
+        # capture and instantiation take a different time on every rank: without this barrier the first
+        # replay of one rank waits inside the kernel for a rank that is still on the host
+        self.barrier()
         for _ in range(GRAPH_WARM):
             g.replay()
         self.barrier()
