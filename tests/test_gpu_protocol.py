@@ -198,3 +198,38 @@ def test_compute_without_reduce_then_full_layer():
             assert int(buf.table("combine_cnt").sum()) == 0   # consumed counts are zeroed by the reduce
         finally:
             buf.destroy()
+
+
+def test_ring_geometry_switches_between_launches():
+    """Launches whose windows all have at most 32 rows stage 32 activation rows per ring slot and run
+    five stages; any larger window brings the four-stage ring back.  The same buffers take small and
+    large batches in turn, 8-bit and 4-bit weights, and every launch is checked against the oracle
+    (the ring, its barriers and the tensor maps are per launch: nothing may carry over)."""
+    import mini_mega_b200 as mm
+    from gpu_world import dev_weights, load_inputs, to_e2m1_case
+    small = orc.gen_case(1, 8, 2, 512, 256, 6, seed=31, routing="logits", scaled=True, cap=96)
+    large = orc.gen_case(1, 8, 2, 512, 256, 96, seed=32, routing="zipf", scaled=True, cap=96)
+    assert max(np.bincount(large.topk_idx[0][:96].ravel(), minlength=8)) > 32      # some window beyond the slim ring
+    assert max(np.bincount(small.topk_idx[0][:6].ravel(), minlength=8)) <= 32
+    for fmt in (0, 1):
+        cases = [small, large]
+        if fmt == 1:
+            cases = [to_e2m1_case(orc.gen_case(1, 8, 2, 512, 256, 6, seed=31, routing="logits", scaled=True, cap=96), seed=33),
+                     to_e2m1_case(orc.gen_case(1, 8, 2, 512, 256, 96, seed=32, routing="zipf", scaled=True, cap=96), seed=34)]
+        wants = [orc.bf16_to_f32(orc.f32_to_bf16(orc.layer_world(c)[0].y)) for c in cases]
+        buf = mm.get_symm_buffer_for_mega_moe(None, 8, 96, 2, 512, 256)
+        try:
+            for rep in range(3):
+                for c, want in zip(cases, wants):
+                    load_inputs(c, [buf])
+                    l1, l2 = dev_weights(c, 0, weight_format=fmt)
+                    T = c.tokens[0]
+                    y = torch.zeros((T, 512), dtype=torch.bfloat16, device="cuda")
+                    mm.fp8_mega_moe(y, l1, l2, buf, weight_format=fmt)
+                    torch.cuda.synchronize()
+                    st = buf.status()
+                    assert st.status == 0, f"format {fmt} rep {rep} tokens {T}: device status {st.status} dbg {list(st.dbg)}"
+                    err = orc.rel_l2(y.float().cpu().numpy(), want[:T])
+                    assert err <= 1e-2, f"format {fmt} rep {rep} tokens {T}: relative L2 {err}"
+        finally:
+            buf.destroy()
