@@ -321,7 +321,9 @@ def workload_config(n, tokens, hidden, routing):
                         f"({E_TOTAL // n} experts/GPU), {how}",
             "tokens_per_rank": tokens, "global_tokens": n * tokens, "ep": n, "experts_per_gpu": E_TOTAL // n,
             "l2_policy": "inputs larger than L2 (expert weights streamed per layer >> 126 MB)",
-            "timing": "eager launches, CUDA events on the launching stream, max over ranks; us_per_layer_graph: "
+            "timing": "the K timed steps are one replay of a CUDA graph of K layer nodes after W eager warm-up "
+                      "steps (eager launches with --no-graph; us_per_layer_eager times K eager launches), CUDA "
+                      "events on the launching stream, max over ranks; us_per_layer_graph: "
                       f"one CUDA graph of {GRAPH_NODES} layer nodes, {GRAPH_WARM} warm replays, {GRAPH_TIMED} timed"}
 
 
@@ -403,6 +405,33 @@ class Job:
         self.barrier()
         ms = self.max_over_ranks(e0.elapsed_time(e1)) / steps
         self.check_status("eager layers")
+        return ms
+
+    def time_graph_steps(self, steps, warmup):
+        """The timed region of the headline: `warmup` eager layers, then EXACTLY `steps` layers replayed
+        from one CUDA graph of `steps` layer nodes (how a serving loop launches a decode step, and how the
+        reference times itself, test/mybench.cu:230-257), bracketed by barrier + synchronize, CUDA events
+        on the launching stream, max over ranks.  Eager launches of a 0.2 ms kernel from eight Python
+        processes measure the hosts' launch jitter as much as the kernel."""
+        torch = self.torch
+        for _ in range(warmup):
+            self.layer()
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(self.stream)
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(steps):
+                    self.layer()
+        self.barrier()    # capture takes a different time on every rank
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(self.stream)
+        g.replay()
+        e1.record(self.stream)
+        self.barrier()
+        ms = self.max_over_ranks(e0.elapsed_time(e1)) / steps
+        self.check_status("graph of the timed steps")
+        del g
         return ms
 
     def time_graph(self):
@@ -669,7 +698,8 @@ def gpu_arm(args):
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    ms_step = job.time_eager(args.steps, args.warmup)
+    ms_eager = job.time_eager(args.steps, args.warmup)
+    ms_step = ms_eager if args.no_graph else job.time_graph_steps(args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
     work = algorithmic_work(routing, n, rank, args.tpr, args.hidden, wbits)
     ms_graph = run_graph(job)
@@ -824,6 +854,7 @@ def gpu_arm(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
             "config": workload_config(n, args.tpr, args.hidden, args.routing),
             "us_per_layer": ms_step * 1e3,
+            "us_per_layer_eager": ms_eager * 1e3,
             "us_per_layer_graph": None if ms_graph is None else ms_graph * 1e3,
             "e2e": {"value": n * args.tpr / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
