@@ -722,7 +722,7 @@ def gpu_arm(args):
             wk = algorithmic_work(rt, n, rank, tpr, args.hidden, wbits)
         points.append(point(f"balanced_tpr{tpr}", job, tpr, ms, mg, wk))
     if not args.no_points:
-        # BASELINE skew configuration: Zipf(1.2) routing, 256 tokens per rank
+        # the skew configuration of the reference's benchmark set: Zipf(1.2) routing, 256 tokens per rank
         rt = job.load(256, seed=3, routing="zipf")
         ms = job.time_eager(max(3, min(args.steps, 20)), 3)
         mg = run_graph(job)

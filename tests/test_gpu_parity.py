@@ -129,7 +129,7 @@ def _run_fused(case, want_y, expert_window, e2e_tol, cta_pair=None, dispatch_mod
 
 @pytest.mark.parametrize("mode", MODES)
 def test_toy_scaled(mode):
-    """BASELINE config 0: E=8, topk=2, H=512, I=256, T=32, world=1, UE8M0 block scales,
+    """The CPU-runnable toy configuration: E=8, topk=2, H=512, I=256, T=32, world=1, UE8M0 block scales,
     top-k of router logits."""
     _run_case(orc.gen_case(1, 8, 2, 512, 256, 32, seed=1, routing="logits", scaled=True), dispatch_mode=mode)
 
@@ -190,7 +190,7 @@ def test_pull_mode_many_rows_fused():
 
 
 def test_prefill_geometry_h7168():
-    """BASELINE config 4's geometry (H=7168, I=2048: 56 K blocks = 14 scale groups per L1 task, scale
+    """The prefill-sized configuration's geometry (H=7168, I=2048: 56 K blocks = 14 scale groups per L1 task, scale
     rows of 56 live bytes in a stride of 64) on a small world: 8 experts, top-4, 600 tokens, so that the
     hottest expert fills more than two 128-row windows (and more than one 256-row window of a CTA
     pair).  Full stage checks with single CTAs and with CTA pairs, pull and push prologue."""
