@@ -95,3 +95,27 @@ def test_select_win_matches_reference_golden(lib):
         got = [lib.mxk_select_win(counts.ctypes.data_as(C.POINTER(C.c_uint32)), 256, cap, wmin)
                for cap in (64, 96, 128) for wmin in (8, 32)]
         assert got == g[f"win_{ci}_out"].tolist()
+
+
+def test_ctypes_mirrors_match_the_c_header(tmp_path):
+    """Sizes and the offsets of the last fields of the three structs, as a C compiler lays out
+    include/mxk_b200.h, against the ctypes mirrors in mini_mega_b200/_lib.py."""
+    import subprocess
+    src = tmp_path / "sizes.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "mxk_b200.h"\n'
+        'int main(void) {\n'
+        '  printf("%zu %zu %zu %zu\\n", sizeof(MxkLaunchArgs), offsetof(MxkLaunchArgs, weight_format),\n'
+        '         offsetof(MxkLaunchArgs, w1_group), offsetof(MxkLaunchArgs, dispatch_mode));\n'
+        '  printf("%zu %zu %zu\\n", sizeof(MxkLayout), offsetof(MxkLayout, push_auto), offsetof(MxkLayout, xin_off));\n'
+        '  printf("%zu %zu %zu\\n", sizeof(MxkStatus), offsetof(MxkStatus, ticks), offsetof(MxkStatus, trace));\n'
+        '  printf("%zu\\n", sizeof(MxkGeom));\n'
+        '  return 0;\n}\n')
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    la, lay, st = _lib.MxkLaunchArgs, _lib.MxkLayout, _lib.MxkStatus
+    assert [int(v) for v in out[0].split()] == [C.sizeof(la), la.weight_format.offset, la.w1_group.offset, la.dispatch_mode.offset]
+    assert [int(v) for v in out[1].split()] == [C.sizeof(lay), lay.push_auto.offset, lay.xin_off.offset]
+    assert [int(v) for v in out[2].split()] == [C.sizeof(st), st.ticks.offset, st.trace.offset]
+    assert int(out[3]) == C.sizeof(_lib.MxkGeom)
