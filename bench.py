@@ -322,7 +322,7 @@ def workload_config(n, tokens, hidden, routing):
             "tokens_per_rank": tokens, "global_tokens": n * tokens, "ep": n, "experts_per_gpu": E_TOTAL // n,
             "l2_policy": "inputs larger than L2 (expert weights streamed per layer >> 126 MB)",
             "timing": "the K timed steps are one replay of a CUDA graph of K layer nodes after W eager warm-up "
-                      "steps (eager launches with --no-graph; us_per_layer_eager times K eager launches), CUDA "
+                      "steps and one untimed replay (eager launches with --no-graph; us_per_layer_eager times K eager launches), CUDA "
                       "events on the launching stream, max over ranks; us_per_layer_graph: "
                       f"one CUDA graph of {GRAPH_NODES} layer nodes, {GRAPH_WARM} warm replays, {GRAPH_TIMED} timed"}
 
@@ -408,8 +408,8 @@ class Job:
         return ms
 
     def time_graph_steps(self, steps, warmup):
-        """The timed region of the headline: `warmup` eager layers, then EXACTLY `steps` layers replayed
-        from one CUDA graph of `steps` layer nodes (how a serving loop launches a decode step, and how the
+        """The timed region of the headline: `warmup` eager layers and one untimed replay, then EXACTLY
+        `steps` layers replayed from one CUDA graph of `steps` layer nodes (how a serving loop launches a decode step, and how the
         reference times itself, test/mybench.cu:230-257), bracketed by barrier + synchronize, CUDA events
         on the launching stream, max over ranks.  Eager launches of a 0.2 ms kernel from eight Python
         processes measure the hosts' launch jitter as much as the kernel."""
@@ -424,6 +424,8 @@ class Job:
                 for _ in range(steps):
                     self.layer()
         self.barrier()    # capture takes a different time on every rank
+        g.replay()        # untimed: the GPU was idle during the capture, the timed replay starts from a busy one
+        self.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(self.stream)
         g.replay()
