@@ -322,7 +322,7 @@ def workload_config(n, tokens, hidden, routing):
             "tokens_per_rank": tokens, "global_tokens": n * tokens, "ep": n, "experts_per_gpu": E_TOTAL // n,
             "l2_policy": "inputs larger than L2 (expert weights streamed per layer >> 126 MB)",
             "timing": "the K timed steps are one replay of a CUDA graph of K layer nodes after W eager warm-up "
-                      "steps and one untimed replay (eager launches with --no-graph; us_per_layer_eager times K eager launches), CUDA "
+                      "steps (eager launches with --no-graph; us_per_layer_eager times K eager launches), CUDA "
                       "events on the launching stream, max over ranks; us_per_layer_graph: "
                       f"one CUDA graph of {GRAPH_NODES} layer nodes, {GRAPH_WARM} warm replays, {GRAPH_TIMED} timed"}
 
@@ -338,6 +338,7 @@ class Job:
         self.n, self.rank, self.dev, self.hidden, self.cap = n, rank, dev, hidden, cap
         self.epr = E_TOTAL // n
         self.group_ranks = group_ranks
+        self._buf_args = (group, dispatch_mode, expert_window, cta_pair)
         self.buf = mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, hidden, I, dispatch_mode=dispatch_mode,
                                                    group_ranks=group_ranks, expert_window=expert_window or None)
         self.buf.cta_pair = cta_pair
@@ -349,6 +350,18 @@ class Job:
         self.stream = torch.cuda.current_stream()
         self.inputs = None
         self.push = bool(self.buf.layout.push_auto or (group_ranks > 1 and self.buf.layout.push_eligible)) if dispatch_mode == 0 else dispatch_mode == 2
+
+    def rebuffer(self, cap):
+        """The same weights behind symmetric buffers of another capacity (the prologue protocol that
+        `dispatch_mode` 0 runs depends on the capacity: decode-sized buffers push, larger ones pull)."""
+        group, dispatch_mode, expert_window, cta_pair = self._buf_args
+        self.buf.destroy()
+        self.cap = cap
+        self.buf = self.mm.get_symm_buffer_for_mega_moe(group, E_TOTAL, cap, TOPK, self.hidden, I, dispatch_mode=dispatch_mode,
+                                                        group_ranks=self.group_ranks, expert_window=expert_window or None)
+        self.buf.cta_pair = cta_pair
+        self.inputs = None
+        self.push = bool(self.buf.layout.push_auto or (self.group_ranks > 1 and self.buf.layout.push_eligible)) if dispatch_mode == 0 else dispatch_mode == 2
 
     def barrier(self):
         self.torch.cuda.synchronize()
@@ -408,8 +421,8 @@ class Job:
         return ms
 
     def time_graph_steps(self, steps, warmup):
-        """The timed region of the headline: `warmup` eager layers and one untimed replay, then EXACTLY
-        `steps` layers replayed from one CUDA graph of `steps` layer nodes (how a serving loop launches a decode step, and how the
+        """The timed region of the headline: `warmup` eager layers, then EXACTLY `steps` layers replayed
+        from one CUDA graph of `steps` layer nodes (how a serving loop launches a decode step, and how the
         reference times itself, test/mybench.cu:230-257), bracketed by barrier + synchronize, CUDA events
         on the launching stream, max over ranks.  Eager launches of a 0.2 ms kernel from eight Python
         processes measure the hosts' launch jitter as much as the kernel."""
@@ -424,8 +437,6 @@ class Job:
                 for _ in range(steps):
                     self.layer()
         self.barrier()    # capture takes a different time on every rank
-        g.replay()        # untimed: the GPU was idle during the capture, the timed replay starts from a busy one
-        self.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(self.stream)
         g.replay()
@@ -575,7 +586,7 @@ def parity_leg(job, routing_all, np):
     ref = ref_all[rank]
     helper_on = None
     if job.group_ranks > 1:   # the member's window list of the helper group decides which rows this rank holds
-        hw = orc.helper_world(case, ref_all, job.group_ranks, 128, 2)[rank]
+        hw = orc.helper_world(case, ref_all, job.group_ranks, 128, 2, hot_windows=3)[rank]
         helper_on = bool(hw["on"])
         ref.meta = hw["meta"]
     rows = ref.meta.shape[0]
@@ -662,10 +673,12 @@ def gpu_arm(args):
     lib = _lib.lib()
     hbm_gbs, bf16_tf, peak_kind = load_peaks()
     fp8_peak = 2.0 * bf16_tf * 1e12
+    # the headline and the small points run on a decode-sized buffer, the larger points on one of 256 tokens
+    cap_small = args.tpr if args.no_points else max(64, args.tpr)
     cap = max(256, args.tpr) if not args.no_points else args.tpr
     e2m1 = args.weights == "e2m1"
     wbits = 4 if e2m1 else 8
-    job = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, cap, args.cta_pair, args.dispatch_mode, e2m1=e2m1)
+    job = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, cap_small, args.cta_pair, args.dispatch_mode, e2m1=e2m1)
 
     def binding(work):
         t_h = work["layer_bytes"] / (hbm_gbs * 1e9)
@@ -714,7 +727,18 @@ def gpu_arm(args):
     disp_ns = float(st_ticks.ticks[11]) - float(st_ticks.ticks[10])   # rank 0: set-up end -> dispatch end
 
     points = []
+    parity = None
+    push_headline = job.push
+
+    def headline_parity():   # parity of the headline configuration, outside every timed region, on the headline's buffer
+        rt_ = job.load(args.tpr, seed=1, routing=args.routing)
+        return parity_leg(job, rt_, np)
+
     for tpr in (() if args.no_points else (16, 64, 256)):
+        if tpr > job.cap:
+            if parity is None and not args.no_parity:
+                parity = headline_parity()
+            job.rebuffer(cap)
         if tpr == args.tpr and args.routing == "uniform":
             ms, mg, wk = ms_step, ms_graph, work
         else:
@@ -723,8 +747,12 @@ def gpu_arm(args):
             mg = run_graph(job)
             wk = algorithmic_work(rt, n, rank, tpr, args.hidden, wbits)
         points.append(point(f"balanced_tpr{tpr}", job, tpr, ms, mg, wk))
+    if parity is None and not args.no_parity:
+        parity = headline_parity()
     if not args.no_points:
         # the skew configuration of the reference's benchmark set: Zipf(1.2) routing, 256 tokens per rank
+        if job.cap < cap:
+            job.rebuffer(cap)
         rt = job.load(256, seed=3, routing="zipf")
         ms = job.time_eager(max(3, min(args.steps, 20)), 3)
         mg = run_graph(job)
@@ -735,11 +763,10 @@ def gpu_arm(args):
             "rank_gemm_end_us_max": float(gemm_end.max()) / 1e3, "rank_gemm_end_us_mean": float(gemm_end.mean()) / 1e3,
             "rank_time_max_over_mean": float(gemm_end.max() / max(gemm_end.mean(), 1.0))}))
 
-    job_push = job.push
     # ---- the decode layer with 4-bit (e2m1) weights: half the weight bytes (reference: its MX_FP4_W build) ----
     parity_e2m1 = None
     if not args.no_points and not e2m1 and args.hidden == 6144:
-        j4 = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, cap, args.cta_pair, args.dispatch_mode, e2m1=True)
+        j4 = Job(torch, dist, mm, lib, n, rank, dev, group, args.hidden, cap_small, args.cta_pair, args.dispatch_mode, e2m1=True)
         rt = j4.load(args.tpr, seed=1)
         ms = j4.time_eager(max(3, min(args.steps, 20)), 3)
         mg = run_graph(j4)
@@ -763,12 +790,6 @@ def gpu_arm(args):
             ms = job.time_eager(10, 3)
             wk = algorithmic_work(rt, n, rank, tk, args.hidden)
             points.append(point(f"corpus_launch{lid}", job, tk, ms, None, wk, {"hottest_over_mean": float(c.max() / c.mean())}))
-
-    # ---- parity of the headline configuration (outside every timed region) ----
-    parity = None
-    if not args.no_parity:
-        routing = job.load(args.tpr, seed=1, routing=args.routing)
-        parity = parity_leg(job, routing, np)
 
     # ---- the skew configuration again with cross-rank helper scheduling: one helper group over all ranks,
     #      every GPU holds a replica of all experts' weights (9.4 GB of 180 GB) ----
@@ -802,7 +823,6 @@ def gpu_arm(args):
         job = None
 
     # ---- prefill-sized layer: H=7168, 4096 tokens per rank ----
-    push_headline = job_push
     if not args.no_points and args.hidden == 6144:
         if job is not None:
             job.destroy()

@@ -83,6 +83,9 @@ struct MegaLaunchArgs {
     // 4-bit weights (reference: the MX_FP4_W build, src/common.cuh:99-134): MXK_WEIGHTS_E2M1 = every weight
     // tensor holds e2m1 codes, two per byte, row-major [experts][rows][k / 2]
     int weight_format = 0;
+    // helper groups: experts with fewer windows than this stay with their owners (0 = 3, negative = the reference's
+    // schedule, every window may move)
+    int group_hot_windows = 0;
 };
 
 inline int& last_status() {
@@ -106,7 +109,7 @@ inline MxkLaunchArgs to_c(const MegaLaunchArgs& a) {
     c.x_sf_off = a.x_sf_off; c.w1_sf = a.w1_sf; c.w2_sf = a.w2_sf; c.y_bf16 = a.y_bf16; c.cta_pair = a.cta_pair; c.dispatch_mode = a.dispatch_mode;
     c.group_ranks = a.group_ranks; c.group_skew_num = a.group_skew_num;
     c.w1_group = a.w1_group; c.w2_group = a.w2_group; c.w1_sf_group = a.w1_sf_group; c.w2_sf_group = a.w2_sf_group;
-    c.weight_format = a.weight_format;
+    c.weight_format = a.weight_format; c.group_hot_windows = a.group_hot_windows;
     return c;
 }
 

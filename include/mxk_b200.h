@@ -102,7 +102,8 @@ typedef struct MxkLayout {
                                    scratch of the one-pass route build for large batches */
     int32_t route_scratch_ctas;
     int32_t push_auto;          /* 1: dispatch_mode 0 runs the push-mode prologue here: eligible and
-                                   max_tokens * topk <= 2048 per rank.  A pushed row travels as
+                                   max_tokens * topk <= 2048 per rank (1024 in a world of
+                                   several ranks, where the doubled bytes cross NVLink).  A pushed row travels as
                                    tagged words (twice its bytes) once per routed pair and is copied
                                    again into the pool; beyond that size the pull protocol's three
                                    round trips cost less than the extra bytes                      */
@@ -182,6 +183,10 @@ typedef struct MxkLaunchArgs {
      * layer reads half the weight bytes from HBM; its results are those of the 8-bit layer on
      * the expanded weights.  The tensors must be 32-byte aligned. */
     int32_t weight_format;     /* MXK_WEIGHTS_E4M3 (0) or MXK_WEIGHTS_E2M1 (1)              */
+    int32_t group_hot_windows; /* helper groups spread the windows of experts with at least this many
+                                  windows and leave the others with their owners (see
+                                  mxk_gs_schedule_member_hot): 0 = 3, negative = every window may
+                                  move (the reference's schedule); the same on every rank   */
 } MxkLaunchArgs;
 
 /* Host-readable copy of the device status header. */
@@ -342,6 +347,12 @@ int mxk_select_win(const uint32_t* counts, int E, int cap_hint, int win_min);
  *                           lowest member (reference: gs_schedule_member, src/group_sched.cuh:164-205).
  *                           rows_of_ge [group_ranks * EPR], ge = member * EPR + local expert.
  *                           Returns the member's window count (at most cap entries are written).
+ *   mxk_gs_schedule_member_hot  the same with the spreading limited to HOT experts, those with at least
+ *                           hot_windows windows (not in the reference: a window computed away from its
+ *                           expert's owner costs the helper a pass over the expert's weights, worth several
+ *                           windows of arithmetic on a memory-bound layer).  Every other expert stays with its
+ *                           owner; its cost is in the owner's load before the first hot window is placed.
+ *                           hot_windows 0 = mxk_gs_schedule_member.  What the kernels run (group_hot_windows).
  *   mxk_gs_group_skewed     1 when max * n_experts > skew_num * sum (reference: MX_GS_SKEW_NUM = 2,
  *                           src/group_sched.cuh:26-28)
  *   mxk_lpt_assign          LPT over (expert, window, slice) tasks with cost = rows (reference:
@@ -353,11 +364,13 @@ int mxk_select_win(const uint32_t* counts, int E, int cap_hint, int win_min);
 int mxk_group_ranks(void);
 int mxk_gs_schedule_member(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int member,
                            int32_t* out_ge, int32_t* out_w, int cap);
+int mxk_gs_schedule_member_hot(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int member, int hot_windows,
+                               int32_t* out_ge, int32_t* out_w, int cap);
 int mxk_gs_group_skewed(const int32_t* rows_of_ge, int n_experts, int skew_num);
 int mxk_lpt_assign(const int32_t* counts, const int32_t* experts, int n_experts, int win_cap, int n_slice, int n_members,
                    int32_t* tasks, int32_t* member_of, int64_t* load, int cap);
-int mxk_gs_schedule_on_device(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int32_t* out_ge,
-                              int32_t* out_w, int32_t* out_n, int cap);
+int mxk_gs_schedule_on_device(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int hot_windows,
+                              int32_t* out_ge, int32_t* out_w, int32_t* out_n, int cap);
 
 /* Symmetric-memory helpers (reference SymmBuffer C++ side,
  * torch/csrc/apis/mega.hpp:86-195): device allocation that can be exported to

@@ -71,7 +71,7 @@ class MxkLaunchArgs(C.Structure):
         ("cta_pair", C.c_int32), ("dispatch_mode", C.c_int32),
         ("group_ranks", C.c_int32), ("group_skew_num", C.c_int32),
         ("w1_group", C.c_void_p), ("w2_group", C.c_void_p), ("w1_sf_group", C.c_void_p), ("w2_sf_group", C.c_void_p),
-        ("weight_format", C.c_int32),
+        ("weight_format", C.c_int32), ("group_hot_windows", C.c_int32),
     ]
 
 
@@ -88,7 +88,7 @@ EXPORTS = [
     "mxk_kernels_per_layer", "mxk_launch_phases", "mxk_launch_full_static",
     "mxk_static_scratch_bytes", "mxk_fill_weights", "mxk_fill_weights_e2m1", "mxk_e2m1_to_e4m3", "mxk_quantize_rows", "mxk_dump_kernel_resources", "mxk_read_status",
     "mxk_read_status_static", "mxk_rwk_ticks_off", "mxk_ticks_count", "mxk_set_ticks", "mxk_select_win",
-    "mxk_group_ranks", "mxk_gs_schedule_member", "mxk_gs_group_skewed", "mxk_lpt_assign", "mxk_gs_schedule_on_device",
+    "mxk_group_ranks", "mxk_gs_schedule_member", "mxk_gs_schedule_member_hot", "mxk_gs_group_skewed", "mxk_lpt_assign", "mxk_gs_schedule_on_device",
     "mxk_symm_alloc", "mxk_symm_free", "mxk_ipc_export", "mxk_ipc_import", "mxk_ipc_close",
 ]
 
@@ -133,7 +133,8 @@ def lib():
     L.mxk_gs_schedule_member.argtypes = [i32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p, i32p, C.c_int]
     L.mxk_gs_group_skewed.argtypes = [i32p, C.c_int, C.c_int]
     L.mxk_lpt_assign.argtypes = [i32p, i32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p, i32p, C.POINTER(C.c_int64), C.c_int]
-    L.mxk_gs_schedule_on_device.argtypes = [i32p, C.c_int, C.c_int, C.c_int, i32p, i32p, i32p, C.c_int]
+    L.mxk_gs_schedule_member_hot.argtypes = [i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, i32p, i32p, C.c_int]
+    L.mxk_gs_schedule_on_device.argtypes = [i32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p, i32p, i32p, C.c_int]
     L.mxk_select_win.argtypes = [C.POINTER(C.c_uint32), C.c_int, C.c_int, C.c_int]
     L.mxk_symm_alloc.argtypes = [C.POINTER(C.c_void_p), C.c_int64]
     L.mxk_symm_free.argtypes = [C.c_void_p]

@@ -62,6 +62,7 @@ struct KArgs {
     int push;                    // push-mode prologue (see push_phase)
     int group_ranks;             // members of a helper group (1 = none); helper scheduling needs push mode
     int skew_num;                // helpers on when max * n_experts > skew_num * sum over the group's experts
+    int hot_windows;             // helpers take windows only of experts with at least this many windows (0 = of all)
     int ge_base;                 // this rank's first expert inside the weight arrays (member * EPR with group weights)
     int w_experts;               // experts in the weight arrays w1 / w2 (EPR, or group_ranks * EPR)
     int prefetch_bytes;          // bytes of W1 every CTA asks into L2 while the prologue runs
@@ -271,11 +272,12 @@ __global__ void k_empty() {}
 // The cross-rank window scheduler on the device: thread m computes member m's list (the same pure
 // function the host entry point calls; reference check.cu:287-315 re-runs it on the host to find
 // which windows a rank computes, which doubles as a host/device determinism test).
-__global__ void k_sched_members(const int* rows_of_ge, int EPR, int group_ranks, int win_cap, int* out_ge, int* out_w,
-                                int* out_n, int cap) {
+__global__ void k_sched_members(const int* rows_of_ge, int EPR, int group_ranks, int win_cap, int hot_windows, int* out_ge,
+                                int* out_w, int* out_n, int cap) {
     const int m = blockIdx.x * blockDim.x + threadIdx.x;
     if (m >= group_ranks) return;
-    out_n[m] = sched_member_windows(rows_of_ge, EPR, group_ranks, win_cap, m, out_ge + (size_t)m * cap, out_w + (size_t)m * cap, cap);
+    out_n[m] = sched_member_windows(rows_of_ge, EPR, group_ranks, win_cap, m, out_ge + (size_t)m * cap, out_w + (size_t)m * cap, cap,
+                                    hot_windows);
 }
 
 // bf16 rows -> E4M3 + one UE8M0 scale per 128 columns, the reference's activation quantiser
@@ -382,7 +384,7 @@ int compute_layout(const MxkGeom* g, MxkLayout* L) {
     // push-mode staging area, only for geometries whose world routing fits a CTA's shared memory
     L->push_eligible = (R <= kPushMaxR && EPR <= kPushMaxEPR && R * cap * topk <= kPushMaxPairs &&
                         EPR * (R + 1) <= kPushMaxCnt) ? 1 : 0;
-    L->push_auto = (L->push_eligible && (int64_t)cap * topk <= kPushAutoPairsPerRank) ? 1 : 0;
+    L->push_auto = (L->push_eligible && (int64_t)cap * topk <= (R > 1 ? kPushAutoPairsPerRankWorld : kPushAutoPairsPerRank)) ? 1 : 0;
     {
         const int64_t sfw = (((H / 128) + 3) / 4 + 1) & ~(int64_t)1;
         L->xin_row_words = (int32_t)(2 * topk + sfw + H / 4);
@@ -537,7 +539,7 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
     const bool want_helpers = la->group_ranks > 1 && la->group_weights_ready;
     k->push = la->dispatch_mode == 2 || (la->dispatch_mode == 0 && (k->L.push_auto || (want_helpers && k->L.push_eligible)));
     // cross-rank helper scheduling: group-replicated weights, push-mode prologue only
-    k->group_ranks = 1; k->skew_num = 2; k->ge_base = 0; k->w_experts = g.experts_per_rank;
+    k->group_ranks = 1; k->skew_num = 2; k->hot_windows = 0; k->ge_base = 0; k->w_experts = g.experts_per_rank;
     const uint8_t *w1 = la->w1, *w2 = la->w2, *w1_sf = la->w1_sf, *w2_sf = la->w2_sf;
     if (la->group_ranks < 0) return fail(MXK_ERR_BAD_ARG, "group_ranks must be >= 0");
     if (la->group_ranks > 1 && la->group_weights_ready) {
@@ -551,6 +553,7 @@ int build_kargs(const MxkLaunchArgs* la, KArgs* k) {
             return fail(MXK_ERR_BAD_ARG, "group scale planes must be given exactly when w1_sf / w2_sf are");
         k->group_ranks = G;
         k->skew_num = la->group_skew_num == 0 ? 2 : (la->group_skew_num < 0 ? 0 : la->group_skew_num);
+        k->hot_windows = la->group_hot_windows == 0 ? kHelperHotWindows : (la->group_hot_windows < 0 ? 0 : la->group_hot_windows);
         k->ge_base = (g.rank / (g.R / G)) * g.experts_per_rank;
         k->w_experts = G * g.experts_per_rank;
         w1 = la->w1_group; w2 = la->w2_group; w1_sf = la->w1_sf_group; w2_sf = la->w2_sf_group;
@@ -941,6 +944,13 @@ int mxk_gs_schedule_member(const int32_t* rows_of_ge, int EPR, int group_ranks, 
         return fail(MXK_ERR_BAD_ARG, "scheduler: member outside the group or null output");
     return sched_member_windows(rows_of_ge, EPR, group_ranks, win_cap, member, out_ge, out_w, cap);
 }
+int mxk_gs_schedule_member_hot(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int member, int hot_windows,
+                               int32_t* out_ge, int32_t* out_w, int cap) {
+    if (sched_args_ok(rows_of_ge, EPR, group_ranks, win_cap)) return MXK_ERR_BAD_ARG;
+    if (member < 0 || member >= group_ranks || cap < 0 || hot_windows < 0 || (cap > 0 && (!out_ge || !out_w)))
+        return fail(MXK_ERR_BAD_ARG, "scheduler: member outside the group, negative hot_windows or null output");
+    return sched_member_windows(rows_of_ge, EPR, group_ranks, win_cap, member, out_ge, out_w, cap, hot_windows);
+}
 int mxk_gs_group_skewed(const int32_t* rows_of_ge, int n_experts, int skew_num) {
     if (!rows_of_ge || n_experts < 1) return fail(MXK_ERR_BAD_ARG, "scheduler: null counts");
     return sched_group_skewed(rows_of_ge, n_experts, skew_num) ? 1 : 0;
@@ -953,10 +963,10 @@ int mxk_lpt_assign(const int32_t* counts, const int32_t* experts, int n_experts,
     return sched_lpt_assign(counts, experts, n_experts, win_cap, n_slice, n_members, tasks, member_of,
                             reinterpret_cast<long long*>(load), cap);
 }
-int mxk_gs_schedule_on_device(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int32_t* out_ge,
-                              int32_t* out_w, int32_t* out_n, int cap) {
+int mxk_gs_schedule_on_device(const int32_t* rows_of_ge, int EPR, int group_ranks, int win_cap, int hot_windows,
+                              int32_t* out_ge, int32_t* out_w, int32_t* out_n, int cap) {
     if (sched_args_ok(rows_of_ge, EPR, group_ranks, win_cap)) return MXK_ERR_BAD_ARG;
-    if (!out_ge || !out_w || !out_n || cap < 1) return fail(MXK_ERR_BAD_ARG, "scheduler: null output");
+    if (!out_ge || !out_w || !out_n || cap < 1 || hot_windows < 0) return fail(MXK_ERR_BAD_ARG, "scheduler: null output");
     const size_t n_in = (size_t)EPR * group_ranks * 4, n_out = (size_t)group_ranks * cap * 4;
     int *d_in = nullptr, *d_ge = nullptr, *d_w = nullptr, *d_n = nullptr;
     cudaError_t e = cudaMalloc(&d_in, n_in);
@@ -965,7 +975,7 @@ int mxk_gs_schedule_on_device(const int32_t* rows_of_ge, int EPR, int group_rank
     if (e == cudaSuccess) e = cudaMalloc(&d_n, (size_t)group_ranks * 4);
     if (e == cudaSuccess) e = cudaMemcpy(d_in, rows_of_ge, n_in, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) {
-        k_sched_members<<<1, 32>>>(d_in, EPR, group_ranks, win_cap, d_ge, d_w, d_n, cap);
+        k_sched_members<<<1, 32>>>(d_in, EPR, group_ranks, win_cap, hot_windows, d_ge, d_w, d_n, cap);
         e = cudaGetLastError();
     }
     if (e == cudaSuccess) e = cudaMemcpy(out_ge, d_ge, n_out, cudaMemcpyDeviceToHost);

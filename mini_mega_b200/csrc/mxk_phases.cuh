@@ -633,6 +633,8 @@ constexpr int kPushMaxR = 64;
 constexpr int kSlimRows = 32;         // activation rows staged per ring slot when every window is that small
 constexpr int kPushMaxPairs = 16384;   // routing words of the whole world kept in shared memory per CTA
 constexpr int kPushAutoPairsPerRank = 2048;  // dispatch_mode 0 pushes up to this many routed pairs per rank (max_tokens * topk)
+constexpr int kPushAutoPairsPerRankWorld = 1024;  // ... in a world of several ranks, where the tagged rows cross NVLink
+constexpr int kHelperHotWindows = 3;         // helper groups spread the windows of experts with at least this many windows
 constexpr int kPushMaxCnt = 4096;      // EPR * (R + 1)
 
 constexpr int kHelperMaxWin = 512;     // windows one member may be handed (reference: kGsMemberCap, src/group_sched.cuh:150-154)
@@ -801,10 +803,20 @@ __device__ void publish_helper_lists(const KArgs& a, const PushTabs* T) {
 // sched_member_windows (descending cost, (ge, w) ascending, least-loaded member, ties to the owner
 // then the lowest member) with the members' loads held one per lane, so that a window costs a few
 // shuffles instead of a loop over the members.  Every lane returns the same counts.
-__device__ void helper_member_list(const int* totg, int GE, const FastDiv fEPR, int G, int win_cap, int member, PushTabs* T) {
+__device__ void helper_member_list(const int* totg, int GE, const FastDiv fEPR, int G, int win_cap, int member, int hot_windows,
+                                   PushTabs* T) {
     const int lane = threadIdx.x & 31;
     int load = 0, n = 0, rowcur = 0;
     const int full_cost = sched_window_cost(win_cap);
+    if (hot_windows > 0 && lane < G) {   // lane m: the work of member m's own experts that stays with it
+        const int EPR = GE / G;
+#pragma unroll 1
+        for (int le = 0; le < EPR; ++le) {
+            const int c = max(totg[lane * EPR + le], 0);
+            if (c == 0 || sched_expert_hot(c, win_cap, hot_windows)) continue;
+            load += (c / win_cap) * full_cost + (c % win_cap ? sched_window_cost(c % win_cap) : 0);
+        }
+    }
 #pragma unroll 1
     for (int level = full_cost; level >= 1; --level) {
 #pragma unroll 1
@@ -826,15 +838,19 @@ __device__ void helper_member_list(const int* totg, int GE, const FastDiv fEPR, 
                 const int g_e = ge0 + l, owner = fEPR.div(g_e);
                 const int lo = __shfl_sync(0xFFFFFFFFu, w_lo, l), hi = __shfl_sync(0xFFFFFFFFu, w_hi, l);
                 const int ctot = __shfl_sync(0xFFFFFFFFu, c, l);
+                const bool hot = sched_expert_hot(ctot, win_cap, hot_windows);
 #pragma unroll 1
                 for (int w = lo; w < hi; ++w) {
-                    const int mine = lane < G ? load : 0x7FFFFFFF;
-                    int mn = mine;
+                    int best = owner;
+                    if (hot) {
+                        const int mine = lane < G ? load : 0x7FFFFFFF;
+                        int mn = mine;
 #pragma unroll
-                    for (int d = 16; d > 0; d >>= 1) mn = min(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, d));
-                    const unsigned tie = __ballot_sync(0xFFFFFFFFu, mine == mn);
-                    const int best = ((tie >> owner) & 1u) ? owner : __ffs(tie) - 1;
-                    if (lane == best) load += level;
+                        for (int d = 16; d > 0; d >>= 1) mn = min(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, d));
+                        const unsigned tie = __ballot_sync(0xFFFFFFFFu, mine == mn);
+                        best = ((tie >> owner) & 1u) ? owner : __ffs(tie) - 1;
+                        if (lane == best) load += level;
+                    }
                     if (best == member) {
                         const int rows = min(win_cap, ctot - w * win_cap);
                         if (lane == 0 && n < kHelperMaxWin) {
@@ -959,14 +975,16 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
                 sum += c;
                 nwin += sched_window_count((int)c, a.win_cap);
             }
-            helper = mx * GE > (long long)a.skew_num * sum && nwin <= kHelperMaxWin && nwin <= kPushMaxGroupWin;
+            // with hot-only spreading there must be a hot expert, or nothing would move
+            helper = mx * GE > (long long)a.skew_num * sum && nwin <= kHelperMaxWin && nwin <= kPushMaxGroupWin &&
+                     sched_expert_hot((int)mx, a.win_cap, a.hot_windows);
         }
         T->helper = helper;
     }
     __syncthreads();
     bool overflow;
     if (T->helper) {
-        if (tid < 32) helper_member_list(sc.totg, GE, a.fEPR, G, a.win_cap, mm, T);
+        if (tid < 32) helper_member_list(sc.totg, GE, a.fEPR, G, a.win_cap, mm, a.hot_windows, T);
         if (tid == 32) {   // first lookup entry of every group expert
             int c = 0;
 #pragma unroll 1

@@ -14,7 +14,8 @@
 //   sched_member_windows the (group expert, window) units one member computes:
 //                       deterministic longest-processing-time assignment with
 //                       cost = ceil(rows / 16) (reference: gs_schedule_member,
-//                        src/group_sched.cuh:164-205)
+//                        src/group_sched.cuh:164-205); optionally only the windows
+//                       of HOT experts move (see there)
 //   sched_lpt_assign    LPT over (expert, window, slice) tasks with cost = rows
 //                       (reference: enumerate_group_tasks / bp_sort_lpt /
 //                        lpt_assign, src/balance_partition.cuh:62-115)
@@ -74,13 +75,29 @@ MXK_HD bool sched_group_skewed(const int* rows_of_ge, int n_experts, int skew_nu
 // visited by descending cost and, inside one cost, by ascending (ge, w); each goes to the member
 // with the smallest accumulated cost, a tie going to the expert's owner (ge / EPR) first and to
 // the lowest member otherwise.  Writes at most `cap` entries and returns how many `member` got.
+//
+// hot_windows > 0 (not in the reference): only experts with at least that many windows are spread.
+// A window computed away from the expert's owner costs the helper a pass over the expert's weights,
+// which on a memory-bound layer is worth several windows of arithmetic, so an expert with one or
+// two windows is cheaper left where its weights are already streamed.  Every other expert stays with
+// its owner: its cost is in the owner's load before the first hot window is placed, and its windows
+// appear in the owner's list at their usual position.  0 = every window may move (the reference).
+MXK_HD bool sched_expert_hot(int rows, int win_cap, int hot_windows) {
+    return hot_windows <= 0 || sched_window_count(rows, win_cap) >= hot_windows;
+}
 MXK_HD int sched_member_windows(const int* rows_of_ge, int EPR, int group_ranks, int win_cap, int member,
-                                int* out_ge, int* out_w, int cap) {
+                                int* out_ge, int* out_w, int cap, int hot_windows = 0) {
     long long load[kSchedMaxGroupRanks];
     for (int m = 0; m < group_ranks; ++m) load[m] = 0;
     const int n_experts = EPR * group_ranks;
     const int full_cost = sched_window_cost(win_cap);
     int n_out = 0;
+    if (hot_windows > 0)
+        for (int ge = 0; ge < n_experts; ++ge) {
+            const int c = rows_of_ge[ge];
+            if (c <= 0 || sched_expert_hot(c, win_cap, hot_windows)) continue;
+            load[ge / EPR] += (long long)(c / win_cap) * full_cost + (c % win_cap ? sched_window_cost(c % win_cap) : 0);
+        }
     for (int level = full_cost; level >= 1; --level) {
         for (int ge = 0; ge < n_experts; ++ge) {
             const int c = rows_of_ge[ge];
@@ -94,12 +111,16 @@ MXK_HD int sched_member_windows(const int* rows_of_ge, int EPR, int group_ranks,
                 w_hi = n_full + 1;
             }
             const int owner = ge / EPR;
+            const bool hot = sched_expert_hot(c, win_cap, hot_windows);
             for (int w = w_lo; w < w_hi; ++w) {
-                int best = 0;
-                for (int m = 1; m < group_ranks; ++m)
-                    if (load[m] < load[best]) best = m;
-                if (load[owner] == load[best]) best = owner;
-                load[best] += level;
+                int best = owner;
+                if (hot) {
+                    best = 0;
+                    for (int m = 1; m < group_ranks; ++m)
+                        if (load[m] < load[best]) best = m;
+                    if (load[owner] == load[best]) best = owner;
+                    load[best] += level;
+                }
                 if (best == member) {
                     if (n_out < cap) { out_ge[n_out] = ge; out_w[n_out] = w; }
                     ++n_out;

@@ -81,7 +81,7 @@ class SymmBuffer:
                  intermediate_hidden: int, num_shared_experts: int = 0, mma_type: str = "fp8xfp8",
                  activation: str = "swiglu", grid_num_tokens: Optional[int] = None,
                  expert_window: Optional[int] = None, slot_capacity: int = 0, dispatch_mode: int = 0,
-                 group_ranks: int = 0, group_skew_num: int = 0,
+                 group_ranks: int = 0, group_skew_num: int = 0, group_hot_windows: int = 0,
                  _local_world: Optional[Tuple[int, int]] = None):
         if activation != "swiglu":
             raise ValueError(f"Only `swiglu` activation is supported, got `{activation}`")
@@ -117,6 +117,9 @@ class SymmBuffer:
         # group and the skew threshold; the group's weights are handed to the layer call
         self.group_ranks = int(group_ranks)
         self.group_skew_num = int(group_skew_num)
+        # helper groups spread the windows of experts with at least this many windows (0 = 3; negative =
+        # every window may move, the reference's schedule)
+        self.group_hot_windows = int(group_hot_windows)
         if self.group_ranks > 1 and world_size % self.group_ranks:
             raise ValueError("group_ranks must divide the group size")
         self.launch_count = 0
@@ -280,6 +283,7 @@ class SymmBuffer:
                 setattr(a, name + "_group", data.data_ptr())
                 setattr(a, name + "_sf_group", None if sf is None else sf.data_ptr())
             a.group_ranks, a.group_skew_num, a.group_weights_ready = self.group_ranks, self.group_skew_num, 1
+            a.group_hot_windows = self.group_hot_windows
         a.weight_format = int(weight_format)   # 0 = E4M3 bytes, 1 = packed e2m1 codes (every weight tensor of the launch)
         return a
 
@@ -310,13 +314,14 @@ def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_ran
                                  use_fp8_dispatch: Optional[bool] = None, mma_type: str = "fp8xfp8",
                                  activation: str = "swiglu", num_tokens: Optional[int] = None,
                                  expert_window: Optional[int] = None, slot_capacity: int = 0,
-                                 dispatch_mode: int = 0, group_ranks: int = 0, group_skew_num: int = 0) -> SymmBuffer:
+                                 dispatch_mode: int = 0, group_ranks: int = 0, group_skew_num: int = 0,
+                                 group_hot_windows: int = 0) -> SymmBuffer:
     if use_fp8_dispatch is not None:
         assert use_fp8_dispatch == (mma_type.split("x")[0] == "fp8")
     return SymmBuffer(group, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
                       num_shared_experts, mma_type=mma_type, activation=activation, grid_num_tokens=num_tokens,
                       expert_window=expert_window, slot_capacity=slot_capacity, dispatch_mode=dispatch_mode,
-                      group_ranks=group_ranks, group_skew_num=group_skew_num)
+                      group_ranks=group_ranks, group_skew_num=group_skew_num, group_hot_windows=group_hot_windows)
 
 
 WeightArg = Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]

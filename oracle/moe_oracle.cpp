@@ -326,6 +326,46 @@ ORC_API int orc_gs_schedule_member(const int* cg, int EPR, int group_ranks,
     return nout;
 }
 
+// The same schedule with the spreading limited to hot experts (not in the reference; what the
+// CUDA path runs by default): an expert with fewer than hot_windows windows stays with its
+// owner, its cost counted into the owner's load before the first window is placed.
+ORC_API int orc_gs_schedule_member_hot(const int* cg, int EPR, int group_ranks, int win_cap, int member,
+                                       int hot_windows, int* out_ge, int* out_w, int cap) {
+    std::vector<long long> load(group_ranks, 0);
+    const int GE = EPR * group_ranks;
+    const int maxcost = (win_cap + 15) / 16;
+    auto n_windows = [&](int c) { return c > 0 ? (c + win_cap - 1) / win_cap : 0; };
+    auto hot = [&](int c) { return hot_windows <= 0 || n_windows(c) >= hot_windows; };
+    for (int ge = 0; ge < GE; ++ge)
+        if (!hot(cg[ge]))
+            for (int w = 0; w < n_windows(cg[ge]); ++w)
+                load[ge / EPR] += (std::min(win_cap, cg[ge] - w * win_cap) + 15) / 16;
+    int nout = 0;
+    for (int cost = maxcost; cost >= 1; --cost)
+        for (int ge = 0; ge < GE; ++ge) {
+            const int c = cg[ge];
+            for (int w = 0; w < n_windows(c); ++w) {
+                const int rows = std::min(win_cap, c - w * win_cap);
+                if ((rows + 15) / 16 != cost) continue;
+                const int owner = ge / EPR;
+                int chosen = owner;
+                if (hot(c)) {
+                    long long minl = load[0];
+                    for (int m = 1; m < group_ranks; ++m) minl = std::min(minl, load[m]);
+                    if (load[owner] != minl)
+                        for (int m = 0; m < group_ranks; ++m)
+                            if (load[m] == minl) { chosen = m; break; }
+                    load[chosen] += cost;
+                }
+                if (chosen == member) {
+                    if (nout < cap) { out_ge[nout] = ge; out_w[nout] = w; }
+                    ++nout;
+                }
+            }
+        }
+    return nout;
+}
+
 // LPT over (expert, window, slice) tasks of src/balance_partition.cuh:62-115:
 // cost = rows of the window, stable descending sort, each task to the member
 // with the strictly smallest load (ties to the lowest member).  experts[] lists

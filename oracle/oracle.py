@@ -75,6 +75,8 @@ def lib():
                                C.POINTER(C.c_int), C.POINTER(C.c_int)]
     L.orc_gs_schedule_member.restype = C.c_int
     L.orc_gs_schedule_member.argtypes = [_i32p, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, _i32p, C.c_int]
+    L.orc_gs_schedule_member_hot.restype = C.c_int
+    L.orc_gs_schedule_member_hot.argtypes = [_i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, _i32p, C.c_int]
     L.orc_lpt_assign.restype = C.c_int
     L.orc_lpt_assign.argtypes = [_i32p, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, _i32p,
                                  np.ctypeslib.ndpointer(np.int64, flags="C")]
@@ -588,7 +590,7 @@ def layer_world(case: Case, slot_cap: Optional[int] = None, threads: int = 8,
 
 
 def helper_world(case: Case, states: List[RankState], group_ranks: int, win_cap: int, skew_num: int = 2,
-                 max_windows: int = 512):
+                 max_windows: int = 512, hot_windows: int = 0):
     """Cross-rank helper scheduling of the reference (src/compute.cuh:700-835, src/group_sched.cuh):
     ranks form interleaved groups (group = rank % n_groups, member = rank // n_groups); when a
     group's load is skewed (max * n_experts > skew_num * sum; skew_num 0 = always) its (expert,
@@ -596,7 +598,9 @@ def helper_world(case: Case, states: List[RankState], group_ranks: int, win_cap:
     windows it was given — its own and other members' — in the order of its list, the rows of a
     window keeping the owner's pool order.  Returns per rank a dict: on (bool), windows
     [(ge, w, rows)], meta [rows][3] (src, token, k) in the rank's pool order; ranks of groups that
-    are not skewed keep the owner layout (on = False, meta = the owner's)."""
+    are not skewed keep the owner layout (on = False, meta = the owner's).
+    hot_windows > 0 (the CUDA path's default is 3): only experts with at least that many windows are
+    spread, the others stay with their owners; a group without a hot expert is left alone."""
     R, EPR = case.R, case.EPR
     n_groups = R // group_ranks
     out = [None] * R
@@ -609,13 +613,14 @@ def helper_world(case: Case, states: List[RankState], group_ranks: int, win_cap:
         # a member's list holds at most max_windows entries (reference kGsMemberCap); the CUDA path keeps
         # the owner layout when the whole group has more windows than that
         skewed = skewed and int(sum((int(c) + win_cap - 1) // win_cap for c in tot)) <= max_windows
+        skewed = skewed and (hot_windows <= 0 or (int(tot.max()) + win_cap - 1) // win_cap >= hot_windows)
         for m, r in enumerate(members):
             if not skewed:
                 out[r] = {"on": False, "windows": [], "meta": states[r].meta.copy()}
                 continue
             ge = np.zeros(max_windows, np.int32)
             w = np.zeros(max_windows, np.int32)
-            n = lib().orc_gs_schedule_member(tot, EPR, group_ranks, win_cap, m, ge, w, max_windows)
+            n = lib().orc_gs_schedule_member_hot(tot, EPR, group_ranks, win_cap, m, max(hot_windows, 0), ge, w, max_windows)
             if n > max_windows:
                 raise ValueError("member window list exceeds its capacity")
             wins, meta = [], []

@@ -26,7 +26,7 @@ SAME_FIELD(y); SAME_FIELD(max_spins); SAME_FIELD(skip_prologue); SAME_FIELD(expe
 SAME_FIELD(topk); SAME_FIELD(hidden); SAME_FIELD(intermediate); SAME_FIELD(max_tokens);
 SAME_FIELD(x_sf_off); SAME_FIELD(w1_sf); SAME_FIELD(w2_sf); SAME_FIELD(y_bf16); SAME_FIELD(cta_pair);
 SAME_FIELD(dispatch_mode); SAME_FIELD(group_ranks); SAME_FIELD(group_skew_num); SAME_FIELD(w1_group);
-SAME_FIELD(w2_group); SAME_FIELD(w1_sf_group); SAME_FIELD(w2_sf_group); SAME_FIELD(weight_format);
+SAME_FIELD(w2_group); SAME_FIELD(w1_sf_group); SAME_FIELD(w2_sf_group); SAME_FIELD(weight_format); SAME_FIELD(group_hot_windows);
 static_assert(sizeof(MegaLaunchArgs) == sizeof(MxkLaunchArgs), "MegaLaunchArgs and MxkLaunchArgs differ in size");
 static_assert(std::is_standard_layout<MegaLaunchArgs>::value, "MegaLaunchArgs must stay a plain struct");
 

@@ -63,13 +63,13 @@ def load_inputs(case, bufs):
 
 class World:
     def __init__(self, case, slot_capacity=0, expert_window=128, dispatch_mode=0, group_ranks=0, group_skew_num=0,
-                 weight_format=0):
+                 weight_format=0, group_hot_windows=0):
         self.case = case
         self.weight_format = weight_format
         self.bufs = mm.SymmBuffer.local_world(case.R, case.E, case.cap, case.topk, case.H, case.I,
                                               slot_capacity=slot_capacity, expert_window=expert_window,
                                               dispatch_mode=dispatch_mode, group_ranks=group_ranks,
-                                              group_skew_num=group_skew_num)
+                                              group_skew_num=group_skew_num, group_hot_windows=group_hot_windows)
         self.weights = [dev_weights(case, r, weight_format=weight_format) for r in range(case.R)]
         # helper groups: every member holds the weights of all its group's experts, in member order
         self.group_weights = [None] * case.R

@@ -151,7 +151,8 @@ def run_gpu():
             case = all_cases[ci]
             if buf is None:
                 buf = mm.get_symm_buffer_for_mega_moe(group, case.E, case.cap, case.topk, case.H, case.I, dispatch_mode=2,
-                                                      expert_window=32, group_ranks=world, group_skew_num=-1)
+                                                      expert_window=32, group_ranks=world, group_skew_num=-1,
+                                                      group_hot_windows=2 if ci == 0 else 0)
             T = case.tokens[rank]
             buf.x.view(torch.uint8).copy_(torch.from_numpy(case.x[rank]))
             buf.x_sf.copy_(torch.from_numpy(case.x_sf[rank]))
@@ -171,7 +172,7 @@ def run_gpu():
             st = buf.status()
             assert st.status == 0, f"rank {rank} helpers case {ci}: device status {st.status} dbg {list(st.dbg)}"
             ref = refs[ci]
-            want = orc.helper_world(case, ref, world, 32, 0)[rank]
+            want = orc.helper_world(case, ref, world, 32, 0, hot_windows=buf.group_hot_windows or 3)[rank]
             assert bool(st.helper_on) == want["on"]
             rows = want["meta"].shape[0]
             assert st.total_rows == rows

@@ -48,12 +48,17 @@ def test_layout_is_consistent(lib):
 
 
 def test_push_protocol_choice_by_geometry(lib):
-    """push_eligible: the world's routing fits a CTA's shared memory; push_auto: in addition at most
-    2048 routed pairs per rank, the batch sizes where pushing tagged rows beats the pull round trips."""
+    """push_eligible: the world's routing fits a CTA's shared memory; push_auto: in addition at most 2048
+    routed pairs of capacity per rank on one GPU, 1024 in a world of several ranks (the tagged rows then
+    cross NVLink with twice their bytes): the batch sizes where pushing beats the pull round trips."""
     d = _lib.compute_layout(8, 0, 32, 8, 6144, 2048, 16)        # baseline decode: 128 pairs per rank
     assert d.push_eligible == 1 and d.push_auto == 1 and d.xin_off > 0
-    m = _lib.compute_layout(8, 0, 32, 8, 6144, 2048, 256)       # 2048 pairs per rank, 16384 in the world: the edge
+    m = _lib.compute_layout(8, 0, 32, 8, 6144, 2048, 128)       # 1024 pairs per rank: the edge in a world of 8
     assert m.push_eligible == 1 and m.push_auto == 1
+    m = _lib.compute_layout(8, 0, 32, 8, 6144, 2048, 256)       # 2048 pairs per rank, 16384 in the world: may push
+    assert m.push_eligible == 1 and m.push_auto == 0
+    s1 = _lib.compute_layout(1, 0, 32, 8, 6144, 2048, 256)      # one GPU: no NVLink to pay for
+    assert s1.push_eligible == 1 and s1.push_auto == 1
     q = _lib.compute_layout(1, 0, 8, 8, 7168, 2048, 1024)       # one rank, 8192 pairs: may push, does not by default
     assert q.push_eligible == 1 and q.push_auto == 0
     p = _lib.compute_layout(8, 0, 32, 8, 7168, 2048, 4096)      # prefill-sized: pull only

@@ -83,7 +83,7 @@ def test_helper_groups_with_e2m1_replicas():
     from gpu_world import World, assert_status_ok, check_tables, to_e2m1_case
     case = to_e2m1_case(orc.gen_case(4, 4, 4, 1024, 512, [60, 50, 40, 64], seed=61, routing="zipf", scaled=True), seed=29)
     ref = orc.layer_world(case)
-    w = World(case, expert_window=32, dispatch_mode=2, group_ranks=4, group_skew_num=-1, weight_format=1)
+    w = World(case, expert_window=32, dispatch_mode=2, group_ranks=4, group_skew_num=-1, weight_format=1, group_hot_windows=-1)
     try:
         w.run()
         assert_status_ok(w)

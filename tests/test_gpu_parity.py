@@ -211,20 +211,22 @@ def test_decode_world_full_width(mode):
     _run_case(case, dispatch_mode=mode, ref=orc.layer_world(case, threads=16))
 
 
-@pytest.mark.parametrize("group_ranks,skew_num", [(4, -1), (2, -1), (4, 0)])
-def test_helper_groups_world(group_ranks, skew_num):
+@pytest.mark.parametrize("group_ranks,skew_num,hot", [(4, -1, -1), (2, -1, -1), (4, 0, -1), (4, -1, 0), (2, 0, 2)])
+def test_helper_groups_world(group_ranks, skew_num, hot):
     """Cross-rank helper scheduling (reference: MX_GROUP_SCHED, src/compute.cuh:700-835): a world of 4
     ranks with Zipf-skewed routing and 32-row windows, helper groups of 4 (one group) and of 2 (two
     interleaved groups), helpers forced on (-1) or decided by the reference's skew test (0 -> 2).
     Owner-side tables stay exact; every rank's window list equals the deterministic LPT of
     gs_schedule_member; every pool row holds the (source, token, k) and the bytes the oracle's model
-    puts there, whether the rank owns the expert or helps with it; y within 1e-2."""
+    puts there, whether the rank owns the expert or helps with it; y within 1e-2.  `hot` -1 is the reference's
+    schedule (every window may move), 0 the library's default (only experts with at least 3 windows are spread,
+    the others stay with their owners), 2 a lower limit."""
     from gpu_world import World, assert_status_ok, check_tables
     case = orc.gen_case(4, 4, 4, 1024, 512, [60, 50, 40, 64], seed=61, routing="zipf", scaled=True)
     ref = orc.layer_world(case)
-    want = orc.helper_world(case, ref, group_ranks, 32, 0 if skew_num < 0 else 2)
+    want = orc.helper_world(case, ref, group_ranks, 32, 0 if skew_num < 0 else 2, hot_windows=0 if hot < 0 else (hot or 3))
     assert any(h["on"] for h in want)
-    w = World(case, expert_window=32, dispatch_mode=2, group_ranks=group_ranks, group_skew_num=skew_num)
+    w = World(case, expert_window=32, dispatch_mode=2, group_ranks=group_ranks, group_skew_num=skew_num, group_hot_windows=hot)
     try:
         w.run()
         assert_status_ok(w)
