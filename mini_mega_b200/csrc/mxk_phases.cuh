@@ -673,6 +673,8 @@ struct PushScratch {   // carved from the operand-tile region, which is idle unt
     int* totg;     // [GE] rows per group expert
     int* gws;      // [GE+1] first entry of group expert ge in widx
     int* widx;     // [group windows] index of (ge, w) in this member's list, -1 = another member's
+    int* scan;     // [17] warp totals of the compaction below, then the length of `mine`
+    unsigned short* mine;   // [kPushMaxPairs] the world pairs whose expert belongs to this rank's group, ascending
 };
 constexpr int kPushMaxGroupWin = 4096;   // windows of a whole helper group (lookup table entries)
 __device__ __forceinline__ PushScratch push_scratch(uint8_t* tiles) {
@@ -691,9 +693,12 @@ __device__ __forceinline__ PushScratch push_scratch(uint8_t* tiles) {
     sc.totg = sc.base + kPushMaxEPR + 1;
     sc.gws = sc.totg + kPushMaxCnt;
     sc.widx = sc.gws + kPushMaxCnt + 1;
+    sc.scan = sc.widx + kPushMaxGroupWin;
+    sc.mine = reinterpret_cast<unsigned short*>(sc.scan + 20);
     return sc;
 }
-static_assert((kPushMaxPairs + 4 * kPushMaxCnt + 8 * kPushMaxEPR + 2 * kPushMaxR + kPushMaxGroupWin + 16) * 4 <= 192 * 1024,
+static_assert(kPushMaxPairs <= 65536, "pair indices fit 16 bits");
+static_assert((kPushMaxPairs + kPushMaxPairs / 2 + 4 * kPushMaxCnt + 8 * kPushMaxEPR + 2 * kPushMaxR + kPushMaxGroupWin + 48) * 4 <= 192 * 1024,
               "push-mode scratch fits the operand-tile region (4 stages of 48 KB)");
 __device__ __forceinline__ int xin_sf_words(int H) { return (((H / 128) + 3) / 4 + 1) & ~1; }   // even: rows stay 16-byte aligned
 __device__ __forceinline__ uint64_t* xin_block(const KArgs& a, void* unk_base, int par, int src) {
@@ -943,6 +948,39 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
         }
     }
     __syncthreads();
+    {
+        // The dispatch gives one warp to every (pair of this rank's group, row part).  Walking the whole
+        // world's pairs for that leaves the warps with an uneven number of real items (on 8 ranks seven
+        // pairs in eight belong to other ranks, and a warp that draws two or three of the eighth kind
+        // runs them one after the other); a compact list gives every warp at most one more than any
+        // other.  Every CTA must build the SAME list: thread t compacts the contiguous slice
+        // [t*c, (t+1)*c) and a block-wide exclusive sum places it, so the list is the ascending order.
+        auto is_mine = [&](int e) -> bool {
+            if (e < 0) return false;
+            const int owner = a.fEPR.div(e);
+            return owner < R && a.fng.mod(owner) == my_group;
+        };
+        const int c = (W + nthr - 1) / nthr, lo = min(tid * c, W), hi = min(lo + c, W);
+        int n = 0;
+#pragma unroll 1
+        for (int i = lo; i < hi; ++i) n += is_mine(sc.wid[i]) ? 1 : 0;
+        int incl = n;   // inclusive sum inside the warp
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if ((tid & 31) >= d) incl += v;
+        }
+        if ((tid & 31) == 31) sc.scan[tid >> 5] = incl;
+        __syncthreads();
+        int base = incl - n;
+#pragma unroll 1
+        for (int w = 0; w < (tid >> 5); ++w) base += sc.scan[w];
+#pragma unroll 1
+        for (int i = lo; i < hi; ++i)
+            if (is_mine(sc.wid[i])) sc.mine[base++] = (unsigned short)i;
+        if (tid == nthr - 1) sc.scan[16] = base;   // the last thread ends at the total
+        __syncthreads();
+    }
     const bool ts = a.ticks != 0 && tid == 0 && blockIdx.x == 0;
     if (ts) f->dbg_ts[0] = gtimer_ns();
     // pairs beyond the slot capacity of a (source, expert) row are dropped (src/prologue.cuh:171-174)
@@ -1023,7 +1061,8 @@ __device__ bool push_tables(const KArgs& a, DevFlags* f, long long epoch, const 
         // a pool row is copied by `parts` warps when there are warps to spare, so that the copy of a
         // row costs one round trip to the staging area instead of several
         const int nwarps = (int)gridDim.x * (nthr >> 5);
-        T->parts = W <= nwarps ? 4 : (W <= 2 * nwarps ? 2 : 1);
+        const int n_items = sc.scan[16];
+        T->parts = n_items <= nwarps ? 4 : (n_items <= 2 * nwarps ? 2 : 1);
         // the largest window of the launch: the hottest expert's rows, capped by the window size
         int mx = 0;
         if (T->helper) {
@@ -1085,7 +1124,7 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
     const int par = (int)(epoch & 1), R = a.R, topk = a.topk, EPR = a.EPR, H = a.H;
     const int n_groups = R / a.group_ranks, my_group = a.rank % n_groups;
     const uint32_t ep = (uint32_t)epoch;
-    const int W = sc.sb[R], P = T->parts;
+    const int P = T->parts;
     const bool helper = T->helper != 0;
     const uint64_t* mine = xin_block(a, a.unk, par, 0);
     const size_t src_words = (size_t)a.L.xin_src_words;
@@ -1097,9 +1136,10 @@ __device__ void push_dispatch(const KArgs& a, DevFlags* f, long long epoch, cons
     uint32_t* pool_ready = reinterpret_cast<uint32_t*>(a.rwk + a.L.pool_ready_off) + (size_t)par * a.L.max_windows;
     const int pshift = P == 4 ? 2 : (P == 2 ? 1 : 0);
     const int n16 = H / 8, per_part = n16 >> pshift;   // 8-byte row units; H % 256 == 0: per_part is a multiple of 8
+    const int n_mine = sc.scan[16];
 #pragma unroll 1
-    for (int it = gwarp; it < W * P; it += nwarps) {
-        const int i = it >> pshift, part = it & (P - 1);   // parts are a power of two
+    for (int it = gwarp; it < n_mine * P; it += nwarps) {
+        const int i = sc.mine[it >> pshift], part = it & (P - 1);   // parts are a power of two
         const int e = sc.wid[i];
         if (e < 0) continue;                         // (every `continue` here is uniform over the warp)
         const int owner = a.fEPR.div(e);
