@@ -835,7 +835,10 @@ __device__ void helper_member_list(const int* totg, int GE, const FastDiv fEPR, 
                 if (w_hi == 0) w_lo = n_full;
                 w_hi = n_full + 1;
             }
-            unsigned mask = __ballot_sync(0xFFFFFFFFu, w_hi > w_lo);
+            // hot-expert schedule: a cold expert of ANOTHER member changes nothing here (its windows stay with
+            // that member, whose load already counts them), so only hot experts and this member's own are walked
+            const bool relevant = hot_windows <= 0 || sched_expert_hot(c, win_cap, hot_windows) || fEPR.div(ge) == member;
+            unsigned mask = __ballot_sync(0xFFFFFFFFu, w_hi > w_lo && relevant);
 #pragma unroll 1
             while (mask) {
                 const int l = __ffs(mask) - 1;
